@@ -1,0 +1,184 @@
+/*
+ * sapphire_b200.h -- C ABI of the B200 (sm_100a) back end for Sapphire's
+ * matrix-multiplication path.
+ *
+ * Everything below the raw-pointer leaf functions of Sapphire's compute
+ * interface is replaced by this library; the C++ shims under
+ * sapphire_b200/compat/ keep Sapphire's own signatures and forward here.
+ * Plain C types only; every function returns an int status (0 = success) and
+ * no exception crosses this boundary.  All pointers named "device" are device
+ * pointers of the context's GPU; the caller owns every input and output
+ * buffer unless stated otherwise.  Work is enqueued on the given stream and
+ * the call returns without synchronising, unless stated otherwise.
+ *
+ * Reference interface citations are paths inside the Sapphire project.
+ */
+#ifndef SAPPHIRE_B200_H
+#define SAPPHIRE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+enum {
+    SB200_OK = 0,
+    SB200_ERR_INVALID_ARG = 1,   /* NULL pointer, negative size, ld < cols, ...     */
+    SB200_ERR_CUDA = 2,          /* a CUDA runtime / driver call failed              */
+    SB200_ERR_UNSUPPORTED = 3,   /* valid request this build cannot run              */
+    SB200_ERR_DEVICE_TIMEOUT = 4,/* a bounded wait inside a kernel expired           */
+    SB200_ERR_ALLOC = 5,         /* device or host allocation failed                 */
+    SB200_ERR_TOO_LARGE = 6      /* size beyond a documented limit                   */
+};
+
+/* Arithmetic of the dense GEMM.
+ *   TF32     operands rounded to TF32 by the tensor core, fp32 accumulate: what
+ *            the reference's GPU path asks of cuBLAS
+ *            (CUBLAS_COMPUTE_32F_FAST_TF32, Sources/Sapphire/compute/dense/cuda/Gemm.cu:31,49).
+ *   TF32X3   each operand split into a TF32 high part and a TF32 low part,
+ *            three tensor-core products per k-block; agrees with the
+ *            reference's fp32 CPU loop (Sources/Sapphire/compute/dense/naive/NaiveGemm.cpp:20-37)
+ *            to about 1e-6 relative.
+ */
+enum { SB200_MODE_TF32 = 0, SB200_MODE_TF32X3 = 1 };
+
+/* Which kernel family ran; for tests and profiling. */
+enum { SB200_PATH_AUTO = 0, SB200_PATH_TCGEN05 = 1, SB200_PATH_SIMT = 2 };
+
+typedef struct sb200_ctx sb200_ctx;
+
+/* Opaque stream handle: a cudaStream_t passed as void* (NULL = the legacy
+ * default stream). */
+typedef void* sb200_stream;
+
+/*
+ * One context per (device, host thread); it owns the per-device workspace,
+ * the device status word and the tensor-map cache.  Replaces the per
+ * (device, thread) cuBLAS handle map of the reference
+ * (Sources/Sapphire/compute/dense/cuda/Gemm.cu:24-30,
+ *  Sources/Sapphire/util/ResourceManager.cpp:209-214).
+ */
+int sb200_ctx_create(int device, sb200_ctx** out);
+int sb200_ctx_destroy(sb200_ctx* ctx);
+
+const char* sb200_status_string(int status);
+
+/* Kernel family used by the last sb200_gemm_batched call on this context
+ * (SB200_PATH_TCGEN05 or SB200_PATH_SIMT), and a running count of kernels
+ * this context has launched. */
+int sb200_last_path(const sb200_ctx* ctx);
+int64_t sb200_launch_count(const sb200_ctx* ctx);
+
+/* Tuning knobs of a context (the counterpart of cublasSetMathMode at
+ * Sources/Sapphire/compute/dense/cuda/Gemm.cu:31).
+ *   SB200_OPT_SPLIT_EXPLICIT_HI  (TF32X3 mode) 0, the default: the high part of
+ *       an operand is the raw fp32 word, cut to TF32 by the tensor core; 1: the
+ *       high part is rounded to nearest TF32 and rewritten in shared memory. */
+enum { SB200_OPT_SPLIT_EXPLICIT_HI = 1 };
+int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value);
+
+/* Reads (and clears) the device status word after synchronising the stream.
+ * Non-zero means a bounded wait in a kernel gave up; the results of that
+ * launch are undefined but the context stays usable. */
+int sb200_check_device_status(sb200_ctx* ctx, sb200_stream stream);
+
+/*
+ * Batched dense GEMM, row-major fp32:
+ *
+ *     D[b] = (C[b] + bias) + op(A[b]) . op(B[b])          b = 0 .. batch-1
+ *
+ * op(A) is M x K, op(B) is K x N.  transA = 0: A is stored [M, K] with leading
+ * dimension lda >= K; transA = 1: A is stored [K, M], lda >= M.  Likewise
+ * transB = 0: B stored [K, N], ldb >= N; transB = 1: B stored [N, K],
+ * ldb >= K.  C and D are [M, N] with ldc, ldd >= N.  Batch strides are in
+ * elements; a stride of 0 re-reads one matrix for every batch.
+ *
+ * C may be NULL (zero) and may alias D exactly (same pointer, ld and stride):
+ * the reference's entry point is y <- y + a.b
+ * (Sources/Sapphire/compute/BasicOps.cpp:183-248; alpha = beta = 1 in
+ * Sources/Sapphire/compute/dense/cuda/Gemm.cu:33-34,44-50), so the aliased call
+ * is the drop-in for Dense::Cuda::Gemm (Includes/Sapphire/compute/dense/cuda/Gemm.cuh:15-18)
+ * and, with strideA or strideB = 0, for GemmMatrixWiseBroadcast (Gemm.cuh:20-25).
+ *
+ * transA / transB replace the explicit Transpose + Gemm pairs of the Linear
+ * backward pass (Sources/Sapphire/operations/Backward/LinearBackward.cpp:49-50, 70-72).
+ *
+ * bias (device, [N], may be NULL) is added to every row: it replaces the
+ * rank-1 Gemm y += ones[B,1].bias[1,N] of
+ * Sources/Sapphire/operations/Forward/Linear.cpp:134-135.
+ *
+ * colsum_out (device, [N], may be NULL): additionally writes
+ * colsum_out[n] = colsum_scale * sum_k op(B)[k, n] of batch 0; it replaces the
+ * bias-gradient Gemm dB = ones[1,B].dy followed by Scale(1/B)
+ * (LinearBackward.cpp:93-97) when this call is dW = x^T.dy.  Requires batch == 1.
+ *
+ * path: SB200_PATH_AUTO picks the tcgen05 kernel when the operands satisfy
+ * TMA's alignment rules (16-byte aligned base pointers, ld and batch strides
+ * multiples of 4 elements) and the SIMT kernel otherwise; the other two
+ * values force a family (SB200_ERR_UNSUPPORTED when it cannot run the request).
+ */
+int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA, int transB,
+                       int64_t M, int64_t N, int64_t K,
+                       const float* A, int64_t lda, int64_t strideA,
+                       const float* B, int64_t ldb, int64_t strideB,
+                       const float* C, int64_t ldc, int64_t strideC,
+                       float* D, int64_t ldd, int64_t strideD,
+                       const float* bias, float* colsum_out, float colsum_scale,
+                       int64_t batch, sb200_stream stream);
+
+/*
+ * CSR matrix, device arrays.  Same fields and order as the reference's
+ * SparseMatrix (Includes/Sapphire/compute/sparse/SparseMatrix.hpp:28-38):
+ * V values, COL column indices, ROW offsets of length M + 1, then NNZ, M, N
+ * and padding to 48 bytes, so an array of them can be cast either way.
+ */
+typedef struct sb200_csr {
+    float* V;
+    uint32_t* COL;
+    uint32_t* ROW;
+    uint32_t NNZ;
+    uint32_t M;
+    uint32_t N;
+    uint32_t Padding[3];
+} sb200_csr;
+
+/*
+ * C = A . B for CSR operands on the device; two passes (symbolic: row sizes,
+ * numeric: values), columns ascending inside every row, structural zeros
+ * kept.  The callee allocates C->V, C->COL, C->ROW (cudaMalloc) and fills
+ * NNZ, M, N; the caller frees them with sb200_csr_free.  The call
+ * synchronises the stream once between the passes (it needs nnz(C) on the
+ * host to size the output).
+ * Replaces Sparse::Cuda::Gemm (Includes/Sapphire/compute/sparse/cuda/SparseGemm.cuh:16-41:
+ * "Required memory is automatically allocated", caller frees), one matrix per call.
+ * Limit: B->N <= 1048576 columns (SB200_ERR_TOO_LARGE beyond).
+ */
+int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, sb200_csr* C,
+                     sb200_stream stream);
+
+/* The two passes separately, for callers that own the output arrays:
+ * symbolic writes rowC[0..M] (device) and returns nnz(C) through *nnzC after
+ * synchronising; numeric fills colC / valC (device, nnz(C) entries). */
+int sb200_spgemm_csr_symbolic(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B,
+                              uint32_t* rowC, int64_t* nnzC, sb200_stream stream);
+int sb200_spgemm_csr_numeric(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B,
+                             const uint32_t* rowC, uint32_t* colC, float* valC,
+                             sb200_stream stream);
+
+int sb200_csr_free(sb200_csr* C);
+
+/* Copies the three arrays of a device CSR matrix into caller-owned arrays
+ * (row: M + 1, col and val: NNZ entries) on the device (to_host = 0) or in
+ * host memory (to_host = 1), then synchronises the stream.  One matrix of
+ * DeepCopyDeviceToDevice / DeepCopyDeviceToHost
+ * (Includes/Sapphire/compute/sparse/Sparse.hpp:49-51, 65-67). */
+int sb200_csr_copy_out(const sb200_csr* src, uint32_t* row, uint32_t* col, float* val,
+                       int to_host, sb200_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAPPHIRE_B200_H */

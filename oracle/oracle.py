@@ -1,0 +1,301 @@
+"""TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+ctypes front end of the two CPU checkers:
+
+* ``port``  -- ``oracle/sapphire_oracle.c``, the restatement of Sapphire's CPU
+  arithmetic (built on demand with gcc into ``oracle/_build``);
+* ``ref``   -- ``oracle/_ref/libsapphire_ref.so``, the reference's own CPU leaf
+  files compiled by ``oracle/Makefile`` from the reference tree.  It exists
+  only where that tree was present at build time (or the prebuilt ``.so`` was
+  shipped along); ``have_ref()`` says which.
+
+Only tests, the smoke check and the CPU-baseline legs of the benchmark import
+this module.  The product package never does.
+
+Dense parity is pinned (port == ref bit-for-bit, plus fixtures made from ref
+under ``tests/golden``).  Sparse parity is UNPINNED: the reference ships no
+sparse GEMM implementation, see the header of ``sapphire_oracle.c``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PORT_SO = os.path.join(_HERE, "_build", "libsapphire_oracle.so")
+_REF_SO = os.path.join(_HERE, "_ref", "libsapphire_ref.so")
+
+_f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+_u32p = np.ctypeslib.ndpointer(dtype=np.uint32, flags="C_CONTIGUOUS")
+
+
+def build(with_ref: bool = True) -> None:
+    """Run oracle/Makefile (port always; ref when the reference tree is there)."""
+    target = "all" if with_ref else os.path.join(_HERE, "_build", "libsapphire_oracle.so")
+    subprocess.run(["make", "-s", "-C", _HERE, "-f", os.path.join(_HERE, "Makefile"), target],
+                   check=True)
+
+
+_port = None
+_ref = None
+
+
+def port():
+    global _port
+    if _port is None:
+        src = os.path.join(_HERE, "sapphire_oracle.c")
+        if (not os.path.exists(_PORT_SO)
+                or os.path.getmtime(_PORT_SO) < os.path.getmtime(src)):
+            build(with_ref=False)
+        lib = C.CDLL(_PORT_SO)
+        lib.orc_gemm.argtypes = [C.c_uint, _f32p, _f32p, _f32p, C.c_uint, C.c_uint, C.c_uint]
+        lib.orc_gemm.restype = None
+        lib.orc_gemm_ex.argtypes = [C.c_int, C.c_int, C.c_long, C.c_long, C.c_long,
+                                    C.c_void_p, C.c_long, C.c_long,
+                                    C.c_void_p, C.c_long, C.c_long,
+                                    C.c_void_p, C.c_long, C.c_long,
+                                    C.c_void_p, C.c_long, C.c_long,
+                                    C.c_void_p, C.c_long]
+        lib.orc_gemm_ex.restype = None
+        lib.orc_colsum.argtypes = [_f32p, C.c_void_p, C.c_long, C.c_long, C.c_long, C.c_float]
+        lib.orc_colsum.restype = None
+        lib.orc_transpose.argtypes = [_f32p, _f32p, C.c_uint, C.c_uint, C.c_uint, C.c_int]
+        lib.orc_scale.argtypes = [_f32p, _f32p, C.c_float, C.c_uint]
+        lib.orc_sub.argtypes = [_f32p, _f32p, _f32p, C.c_uint]
+        lib.orc_relu.argtypes = [_f32p, _f32p, C.c_uint]
+        lib.orc_relu_backward.argtypes = [_f32p, _f32p, _f32p, C.c_uint]
+        lib.orc_softmax.argtypes = [_f32p, _f32p, C.c_uint, C.c_uint]
+        lib.orc_softmax_backward.argtypes = [_f32p, _f32p, _f32p, C.c_uint, C.c_uint]
+        lib.orc_cross_entropy.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int]
+        lib.orc_cross_entropy_backward.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int]
+        for n in ("orc_transpose", "orc_scale", "orc_sub", "orc_relu", "orc_relu_backward",
+                  "orc_softmax", "orc_softmax_backward", "orc_cross_entropy",
+                  "orc_cross_entropy_backward"):
+            getattr(lib, n).restype = None
+        lib.orc_spgemm_symbolic.argtypes = [C.c_uint32, C.c_uint32, _u32p, _u32p, _u32p, _u32p,
+                                            _u32p, C.POINTER(C.c_long)]
+        lib.orc_spgemm_symbolic.restype = C.c_long
+        lib.orc_spgemm_numeric.argtypes = [C.c_uint32, C.c_uint32, _u32p, _u32p, _f32p,
+                                           _u32p, _u32p, _f32p, _u32p, _u32p, _f32p]
+        lib.orc_spgemm_numeric.restype = C.c_int
+        _port = lib
+    return _port
+
+
+def have_ref() -> bool:
+    return os.path.exists(_REF_SO)
+
+
+def ref():
+    global _ref
+    if _ref is None:
+        if not have_ref():
+            raise FileNotFoundError(
+                f"{_REF_SO} is missing: run `make -C oracle` where the reference tree is mounted")
+        lib = C.CDLL(_REF_SO)
+        lib.ref_gemm.argtypes = [C.c_uint, _f32p, _f32p, _f32p, C.c_uint, C.c_uint, C.c_uint]
+        lib.ref_transpose.argtypes = [_f32p, _f32p, C.c_uint, C.c_uint, C.c_uint, C.c_int]
+        lib.ref_scale.argtypes = [_f32p, _f32p, C.c_float, C.c_uint]
+        lib.ref_sub.argtypes = [C.c_uint, _f32p, _f32p, _f32p, C.c_uint, C.c_int, C.c_int]
+        lib.ref_relu.argtypes = [_f32p, _f32p, C.c_uint]
+        lib.ref_relu_backward.argtypes = [_f32p, _f32p, _f32p, C.c_uint]
+        lib.ref_softmax.argtypes = [_f32p, _f32p, C.c_uint, C.c_uint]
+        lib.ref_softmax_backward.argtypes = [_f32p, _f32p, _f32p, C.c_uint, C.c_uint]
+        lib.ref_cross_entropy.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int]
+        lib.ref_cross_entropy_backward.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int]
+        for n in ("ref_gemm", "ref_transpose", "ref_scale", "ref_sub", "ref_relu",
+                  "ref_relu_backward", "ref_softmax", "ref_softmax_backward",
+                  "ref_cross_entropy", "ref_cross_entropy_backward"):
+            getattr(lib, n).restype = None
+        _ref = lib
+    return _ref
+
+
+# ---------------------------------------------------------------- dense helpers
+
+def _c(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def gemm(c, a, b, impl: str = "port"):
+    """y = c + a.b over [batch, M, K] x [batch, K, N]; returns a new array.
+
+    The reference entry point accumulates into y (Compute::Gemm,
+    Sources/Sapphire/compute/BasicOps.cpp:183-248), so "c" is the initial y.
+    """
+    a, b = _c(a), _c(b)
+    y = _c(c).copy()
+    M, K = a.shape[-2], a.shape[-1]
+    N = b.shape[-1]
+    fn = port().orc_gemm if impl == "port" else ref().ref_gemm
+    fn(y.size, y.reshape(-1), a.reshape(-1), b.reshape(-1), M, N, K)
+    return y
+
+
+def gemm_ex(transA, transB, M, N, K, A, lda, strideA, B, ldb, strideB,
+            C_, ldc, strideC, ldd, strideD, bias, batch, d_size):
+    """General strided form on flat fp32 buffers; returns the flat D buffer.
+
+    C_ may be None.  D starts as a copy of C_ when the two have the same
+    geometry (the in-place case), else zeros.
+    """
+    A, B = _c(A).reshape(-1), _c(B).reshape(-1)
+    D = np.zeros(d_size, dtype=np.float32)
+    cptr = None
+    if C_ is not None:
+        C_ = _c(C_).reshape(-1)
+        cptr = C_.ctypes.data
+    bptr = None
+    if bias is not None:
+        bias = _c(bias).reshape(-1)
+        bptr = bias.ctypes.data
+    port().orc_gemm_ex(int(transA), int(transB), M, N, K,
+                       A.ctypes.data, lda, strideA, B.ctypes.data, ldb, strideB,
+                       cptr, ldc, strideC, D.ctypes.data, ldd, strideD, bptr, batch)
+    return D
+
+
+def colsum(dy, scale: float, ld=None):
+    dy = _c(dy)
+    rows, cols = dy.shape
+    out = np.zeros(cols, dtype=np.float32)
+    port().orc_colsum(out, dy.ctypes.data, rows, cols, ld or cols, scale)
+    return out
+
+
+def transpose(x, impl: str = "port"):
+    x = _c(x)
+    x3 = x.reshape((-1,) + x.shape[-2:])
+    out = np.empty((x3.shape[0], x3.shape[2], x3.shape[1]), dtype=np.float32)
+    fn = port().orc_transpose if impl == "port" else ref().ref_transpose
+    fn(out.reshape(-1), x3.reshape(-1), x3.shape[1], x3.shape[2], x3.shape[0], 0)
+    return out.reshape(x.shape[:-2] + (x.shape[-1], x.shape[-2]))
+
+
+# --------------------------------------------------------------- sparse helpers
+
+def spgemm(rowA, colA, valA, rowB, colB, valB, M, N):
+    """CSR x CSR (parity unpinned).  Returns (rowC, colC, valC, products)."""
+    rowA, colA, rowB, colB = (np.ascontiguousarray(x, dtype=np.uint32)
+                              for x in (rowA, colA, rowB, colB))
+    valA, valB = _c(valA), _c(valB)
+    # zero-length arrays still need a valid pointer for ndpointer
+    pad_u = lambda x: x if x.size else np.zeros(1, np.uint32)
+    pad_f = lambda x: x if x.size else np.zeros(1, np.float32)
+    rowC = np.zeros(M + 1, dtype=np.uint32)
+    prods = C.c_long(0)
+    nnz = port().orc_spgemm_symbolic(M, N, rowA, pad_u(colA), rowB, pad_u(colB), rowC,
+                                     C.byref(prods))
+    if nnz < 0:
+        raise MemoryError("oracle spgemm symbolic")
+    colC = np.zeros(max(nnz, 1), dtype=np.uint32)
+    valC = np.zeros(max(nnz, 1), dtype=np.float32)
+    rc = port().orc_spgemm_numeric(M, N, rowA, pad_u(colA), pad_f(valA), rowB, pad_u(colB),
+                                   pad_f(valB), rowC, colC, valC)
+    if rc != 0:
+        raise RuntimeError(f"oracle spgemm numeric failed: {rc}")
+    return rowC, colC[:nnz], valC[:nnz], prods.value
+
+
+# ------------------------------------------------------------------- MLP step
+
+class MlpOracle:
+    """One SGD step of Linear->ReLU->Linear->ReLU->Linear->SoftMax->CrossEntropy,
+    restated call by call from the reference's units:
+
+    forward   Sources/Sapphire/operations/Forward/Linear.cpp:134-136 (bias rank-1 Gemm,
+              then y += x.W with W stored [in, out]); NaiveBasic.cpp:159-165 (ReLU),
+              :235-255 (SoftMax); NaiveCrossEntropy.cpp:15-31
+    backward  NaiveCrossEntropy.cpp:33-51 (dx -= label/x), NaiveBasic.cpp:257-281,
+              :167-174; Sources/Sapphire/operations/Backward/LinearBackward.cpp:27-99
+              (dx with the pre-update W, dW unscaled, dB scaled by 1/batch,
+              optimizer inside backward)
+    SGD       Sources/Sapphire/operations/optimizers/SGD.cpp:22-28 (temp = lr*dz; z = z - temp)
+    """
+
+    def __init__(self, weights, biases, lr: float, impl: str = "port"):
+        self.W = [_c(w).copy() for w in weights]
+        self.b = [_c(b).copy() for b in biases]
+        self.lr = np.float32(lr)
+        self.impl = impl
+
+    # leaf dispatch: identical results either way; `ref` proves it
+    def _gemm_acc(self, y, a, b):
+        M, K = a.shape
+        N = b.shape[1]
+        fn = port().orc_gemm if self.impl == "port" else ref().ref_gemm
+        fn(y.size, y.reshape(-1), _c(a).reshape(-1), _c(b).reshape(-1), M, N, K)
+
+    def _leaves(self):
+        """Elementwise leaves by name; with impl="ref" they are the reference's own."""
+        if self.impl == "port":
+            p = port()
+            return dict(scale=p.orc_scale, sub=p.orc_sub, relu=p.orc_relu,
+                        relu_bwd=p.orc_relu_backward, softmax=p.orc_softmax,
+                        softmax_bwd=p.orc_softmax_backward, ce=p.orc_cross_entropy,
+                        ce_bwd=p.orc_cross_entropy_backward)
+        r = ref()
+        return dict(scale=r.ref_scale,
+                    sub=lambda out, a, b, n: r.ref_sub(n, out, a, b, 0, 0, 0),
+                    relu=r.ref_relu, relu_bwd=r.ref_relu_backward, softmax=r.ref_softmax,
+                    softmax_bwd=r.ref_softmax_backward, ce=r.ref_cross_entropy,
+                    ce_bwd=r.ref_cross_entropy_backward)
+
+    def _sgd(self, z, dz):
+        f = self._leaves()
+        tmp = np.empty_like(dz)
+        f["scale"](tmp.reshape(-1), dz.reshape(-1), self.lr, dz.size)
+        out = np.empty_like(z)
+        f["sub"](out.reshape(-1), z.reshape(-1), tmp.reshape(-1), z.size)
+        z[...] = out
+
+    def step(self, x, onehot):
+        f = self._leaves()
+        B = x.shape[0]
+        acts = [_c(x)]
+        pre = []
+        nl = len(self.W)
+        for l in range(nl):
+            y = np.zeros((B, self.W[l].shape[1]), dtype=np.float32)
+            self._gemm_acc(y, np.ones((B, 1), np.float32), self.b[l].reshape(1, -1))
+            self._gemm_acc(y, acts[-1], self.W[l])
+            pre.append(y)
+            if l < nl - 1:
+                h = np.empty_like(y)
+                f["relu"](h.reshape(-1), y.reshape(-1), y.size)
+                acts.append(h)
+        logits = pre[-1]
+        unit = logits.shape[1]
+        prob = np.empty_like(logits)
+        f["softmax"](prob.reshape(-1), logits.reshape(-1), logits.size, unit)
+        loss = np.zeros(B, dtype=np.float32)
+        onehot = _c(onehot)
+        f["ce"](loss, prob.reshape(-1), onehot.reshape(-1), B, unit)
+        # backward
+        dprob = np.zeros_like(prob)
+        f["ce_bwd"](dprob.reshape(-1), prob.reshape(-1), onehot.reshape(-1), B, unit)
+        dy = np.zeros_like(logits)
+        f["softmax_bwd"](dy.reshape(-1), dprob.reshape(-1), prob.reshape(-1), prob.size, unit)
+        for l in reversed(range(nl)):
+            xin = acts[l]
+            # dx with the pre-update weight
+            dx = np.zeros_like(xin)
+            self._gemm_acc(dx, dy, transpose(self.W[l], self.impl))
+            dw = np.zeros_like(self.W[l])
+            self._gemm_acc(dw, transpose(xin, self.impl), dy)
+            self._sgd(self.W[l], dw)
+            db = np.zeros((1, self.b[l].size), dtype=np.float32)
+            self._gemm_acc(db, np.ones((1, B), np.float32), dy)
+            dbs = np.empty_like(db)
+            f["scale"](dbs.reshape(-1), db.reshape(-1), np.float32(1.0 / B), db.size)
+            bl = self.b[l].reshape(1, -1)
+            self._sgd(bl, dbs)
+            self.b[l] = bl.reshape(-1)
+            if l > 0:
+                dpre = np.zeros_like(pre[l - 1])
+                f["relu_bwd"](dpre.reshape(-1), dx.reshape(-1), pre[l - 1].reshape(-1), dx.size)
+                dy = dpre
+        return loss

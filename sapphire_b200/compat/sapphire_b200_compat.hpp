@@ -1,0 +1,76 @@
+// Source-compatible shims: Sapphire's own leaf signatures, implemented on the
+// sapphire_b200 C ABI.  A Sapphire build drops its cuBLAS wrapper
+// (Sources/Sapphire/compute/dense/cuda/Gemm.cu) and links these definitions
+// instead; everything above the leaf (Compute::Gemm, the Linear unit) is
+// untouched.  Errors from the C ABI become std::runtime_error, like the
+// reference's CHECK_CUBLAS (Includes/Sapphire/compute/cudaUtil/CudaParams.cuh:51-58).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <vector>
+
+#include "../../include/sapphire_b200.h"
+
+// Sapphire's CSR struct (Includes/Sapphire/compute/sparse/SparseMatrix.hpp:28-38) has the
+// same members in the same order as sb200_csr; when Sapphire's header is not
+// in the include path the ABI struct stands in for it.
+#ifndef Sapphire_SPARSEMATRIX_HPP
+typedef sb200_csr SparseMatrix;
+#endif
+
+namespace Sapphire::Compute::Dense::Cuda
+{
+// Includes/Sapphire/compute/dense/cuda/Gemm.cuh:15-18 -- out += A.B for
+// totalSize / (M*N) batches, dense row-major, on device `deviceId`.
+void Gemm(unsigned int totalSize, float* out, const float* A, const float* B,
+          unsigned int M, unsigned int N, unsigned int K, int deviceId);
+
+// Includes/Sapphire/compute/dense/cuda/Gemm.cuh:20-25 -- the same with one
+// operand shared by every batch.
+void GemmMatrixWiseBroadcast(float* out, const float* A, const float* B,
+                             unsigned int M, unsigned int N, unsigned int K,
+                             unsigned int batchSize, bool broadcastA,
+                             bool broadcastB, int deviceId);
+}  // namespace Sapphire::Compute::Dense::Cuda
+
+namespace Sapphire::Compute::Sparse::Cuda
+{
+// Includes/Sapphire/compute/sparse/cuda/SparseGemm.cuh:38-41 -- cudaA / cudaB
+// are device arrays of numMatrices structs whose V/COL/ROW are device arrays;
+// the outputs (a device array of structs, and a host deep copy when
+// copyResultToHost) are allocated here and owned by the caller.
+void Gemm(SparseMatrix** hostOutput, SparseMatrix** cudaOutput,
+          SparseMatrix* cudaA, SparseMatrix* cudaB, uint32_t m, uint32_t n,
+          size_t numMatrices, int deviceId, bool copyResultToHost);
+}  // namespace Sapphire::Compute::Sparse::Cuda
+
+namespace sb200::compat
+{
+// Arithmetic mode used by the shims (process-wide; default SB200_MODE_TF32,
+// what the reference asks of cuBLAS).
+void SetMode(int mode);
+int GetMode();
+
+// Per (device, host thread) context, created on first use.
+sb200_ctx* ContextFor(int deviceId);
+
+// One strided-batched leaf call of a broadcast plan; offsets in elements.
+struct LeafCall {
+    long long offY, offA, offB;
+    long long batch, strideA, strideB;
+};
+
+// Host-side planner that reproduces the batch/broadcast rules of
+// Compute::Gemm (Sources/Sapphire/compute/BasicOps.cpp:183-248 with
+// Includes/Sapphire/compute/Broadcast.hpp:82-133): shapes are right-aligned
+// and left-padded with 1s, the last two dimensions are the matrix, and a
+// leading dimension of a or b is indexed modulo its own extent.  Instead of
+// one leaf call per broadcast index it emits one strided call per run of the
+// innermost batch dimension (stride 0 for a shared operand).
+std::vector<LeafCall> PlanGemm(const std::vector<int>& yShape, const std::vector<int>& aShape,
+                               const std::vector<int>& bShape);
+
+// y <- y + a.b over the planned calls (device pointers).
+void Gemm(const std::vector<int>& yShape, float* y, const std::vector<int>& aShape,
+          const float* a, const std::vector<int>& bShape, const float* b, int deviceId);
+}  // namespace sb200::compat

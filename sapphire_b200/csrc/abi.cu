@@ -1,0 +1,200 @@
+// C ABI of libsapphire_b200: context life cycle, argument validation and the
+// choice between the tensor-core kernel and the CUDA-core kernel.
+#include <new>
+
+#include "common.cuh"
+
+using namespace sb200;
+
+namespace sb200 {
+
+int ensure_workspace(sb200_ctx* ctx, size_t bytes)
+{
+    if (bytes <= ctx->workspace_bytes)
+        return SB200_OK;
+    // cudaFree waits for work that may still use the old buffer
+    if (ctx->d_workspace)
+        cudaFree(ctx->d_workspace);
+    ctx->d_workspace = nullptr;
+    ctx->workspace_bytes = 0;
+    size_t want = bytes < (1u << 20) ? (1u << 20) : bytes + bytes / 4;
+    void* p = nullptr;
+    if (cudaMalloc(&p, want) != cudaSuccess)
+        return SB200_ERR_ALLOC;
+    ctx->d_workspace = static_cast<float*>(p);
+    ctx->workspace_bytes = want;
+    return SB200_OK;
+}
+
+}  // namespace sb200
+
+extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
+{
+    if (!out)
+        return SB200_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count)
+        return SB200_ERR_CUDA;
+    if (cudaSetDevice(device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    if (prop.major != 10)
+        return SB200_ERR_UNSUPPORTED;      // the kernels are sm_100a only
+    sb200_ctx* ctx = new (std::nothrow) sb200_ctx();
+    if (!ctx)
+        return SB200_ERR_ALLOC;
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->last_path = 0;
+    ctx->launches = 0;
+    ctx->d_workspace = nullptr;
+    ctx->workspace_bytes = 0;
+    ctx->split_explicit_hi = 0;
+    ctx->encode_tiled = nullptr;
+    ctx->d_status = nullptr;
+    if (cudaMalloc(&ctx->d_status, sizeof(unsigned)) != cudaSuccess ||
+        cudaMemset(ctx->d_status, 0, sizeof(unsigned)) != cudaSuccess) {
+        delete ctx;
+        return SB200_ERR_ALLOC;
+    }
+    cudaDriverEntryPointQueryResult q;
+    void* fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) !=
+            cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+        cudaFree(ctx->d_status);
+        delete ctx;
+        return SB200_ERR_CUDA;
+    }
+    ctx->encode_tiled = fn;
+    *out = ctx;
+    return SB200_OK;
+}
+
+extern "C" int sb200_ctx_destroy(sb200_ctx* ctx)
+{
+    if (!ctx)
+        return SB200_ERR_INVALID_ARG;
+    cudaSetDevice(ctx->device);
+    if (ctx->d_workspace) cudaFree(ctx->d_workspace);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    delete ctx;
+    return SB200_OK;
+}
+
+extern "C" const char* sb200_status_string(int status)
+{
+    switch (status) {
+        case SB200_OK: return "ok";
+        case SB200_ERR_INVALID_ARG: return "invalid argument";
+        case SB200_ERR_CUDA: return "CUDA call failed";
+        case SB200_ERR_UNSUPPORTED: return "request not supported by this build or path";
+        case SB200_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
+        case SB200_ERR_ALLOC: return "allocation failed";
+        case SB200_ERR_TOO_LARGE: return "size beyond a documented limit";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int sb200_last_path(const sb200_ctx* ctx) { return ctx ? ctx->last_path : 0; }
+
+extern "C" int64_t sb200_launch_count(const sb200_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value)
+{
+    if (!ctx)
+        return SB200_ERR_INVALID_ARG;
+    switch (option) {
+        case SB200_OPT_SPLIT_EXPLICIT_HI:
+            ctx->split_explicit_hi = value != 0;
+            return SB200_OK;
+        default:
+            return SB200_ERR_INVALID_ARG;
+    }
+}
+
+extern "C" int sb200_check_device_status(sb200_ctx* ctx, sb200_stream stream_)
+{
+    if (!ctx)
+        return SB200_ERR_INVALID_ARG;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    unsigned word = 0;
+    if (cudaMemcpyAsync(&word, ctx->d_status, sizeof(word), cudaMemcpyDeviceToHost, stream) !=
+            cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    if (word == 0)
+        return SB200_OK;
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(unsigned), stream);
+    cudaStreamSynchronize(stream);
+    return SB200_ERR_DEVICE_TIMEOUT;
+}
+
+extern "C" int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA, int transB,
+                                  int64_t M, int64_t N, int64_t K,
+                                  const float* A, int64_t lda, int64_t strideA,
+                                  const float* B, int64_t ldb, int64_t strideB,
+                                  const float* C, int64_t ldc, int64_t strideC,
+                                  float* D, int64_t ldd, int64_t strideD,
+                                  const float* bias, float* colsum_out, float colsum_scale,
+                                  int64_t batch, sb200_stream stream_)
+{
+    if (!ctx)
+        return SB200_ERR_INVALID_ARG;
+    if (mode != SB200_MODE_TF32 && mode != SB200_MODE_TF32X3)
+        return SB200_ERR_INVALID_ARG;
+    if (path != SB200_PATH_AUTO && path != SB200_PATH_TCGEN05 && path != SB200_PATH_SIMT)
+        return SB200_ERR_INVALID_ARG;
+    if (M < 0 || N < 0 || K < 0 || batch < 0)
+        return SB200_ERR_INVALID_ARG;
+    if (M == 0 || N == 0 || batch == 0)
+        return SB200_OK;
+    if (!D || (K > 0 && (!A || !B)))
+        return SB200_ERR_INVALID_ARG;
+    if (K > 0) {
+        if (lda < (transA ? M : K) || ldb < (transB ? K : N))
+            return SB200_ERR_INVALID_ARG;
+        if (strideA < 0 || strideB < 0)
+            return SB200_ERR_INVALID_ARG;
+    }
+    if (ldd < N || (C && ldc < N) || strideD < 0 || strideC < 0)
+        return SB200_ERR_INVALID_ARG;
+    if (batch > 1 && strideD < (M - 1) * ldd + N)
+        return SB200_ERR_INVALID_ARG;      // output batches would overlap
+    if (C == D && C && (ldc != ldd || strideC != strideD))
+        return SB200_ERR_INVALID_ARG;      // aliasing is exact or not at all
+    if (colsum_out && batch != 1)
+        return SB200_ERR_INVALID_ARG;
+
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (cudaSetDevice(ctx->device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+
+    GemmArgs g;
+    g.mode = mode; g.transA = transA != 0; g.transB = transB != 0;
+    g.M = M; g.N = N; g.K = K; g.batch = batch;
+    g.A = A; g.lda = lda; g.strideA = strideA;
+    g.B = B; g.ldb = ldb; g.strideB = strideB;
+    g.C = C; g.ldc = ldc; g.strideC = strideC;
+    g.D = D; g.ldd = ldd; g.strideD = strideD;
+    g.bias = bias;
+
+    const bool tc_ok = tcgen05_eligible(g);
+    int rc;
+    if (path == SB200_PATH_TCGEN05 && !tc_ok)
+        return SB200_ERR_UNSUPPORTED;
+    if ((path == SB200_PATH_AUTO && tc_ok) || path == SB200_PATH_TCGEN05) {
+        rc = launch_gemm_tcgen05(ctx, g, stream);
+        ctx->last_path = SB200_PATH_TCGEN05;
+    } else {
+        rc = launch_gemm_simt(ctx, g, stream);
+        ctx->last_path = SB200_PATH_SIMT;
+    }
+    if (rc)
+        return rc;
+    if (colsum_out)
+        rc = launch_colsum(ctx, B, g.transB, K, N, ldb, colsum_out, colsum_scale, stream);
+    return rc;
+}

@@ -1,0 +1,57 @@
+// Internal declarations shared by the translation units of libsapphire_b200.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/sapphire_b200.h"
+
+namespace sb200 {
+
+// Codes written to the device status word by a bounded wait that gave up.
+enum DeviceFault : unsigned {
+    FAULT_NONE = 0,
+    FAULT_PRODUCER_WAIT = 0x101,   // TMA producer waiting for a free stage
+    FAULT_MMA_WAIT_FULL = 0x102,   // MMA issuer waiting for a filled stage
+    FAULT_MMA_WAIT_TMEM = 0x103,   // MMA issuer waiting for a drained accumulator
+    FAULT_EPI_WAIT = 0x104,        // epilogue waiting for a finished accumulator
+    FAULT_SPLIT_WAIT = 0x105       // hi/lo split warps waiting for a filled stage
+};
+
+struct GemmArgs {
+    int mode, transA, transB;
+    int64_t M, N, K, batch;
+    const float* A; int64_t lda, strideA;
+    const float* B; int64_t ldb, strideB;
+    const float* C; int64_t ldc, strideC;
+    float* D; int64_t ldd, strideD;
+    const float* bias;
+};
+
+}  // namespace sb200
+
+struct sb200_ctx {
+    int device;
+    int sm_count;
+    int last_path;
+    int64_t launches;
+    unsigned* d_status;        // device status word
+    float* d_workspace;        // scratch for partial column sums / sparse row work
+    size_t workspace_bytes;
+    int split_explicit_hi;     // 3xTF32: rewrite the high part in shared memory too
+    void* encode_tiled;        // cuTensorMapEncodeTiled, resolved at context creation
+};
+
+namespace sb200 {
+
+// gemm_tcgen05.cu
+bool tcgen05_eligible(const GemmArgs& g);
+int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream);
+// gemm_simt.cu
+int launch_gemm_simt(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream);
+int launch_colsum(sb200_ctx* ctx, const float* B, int transB, int64_t K, int64_t N, int64_t ldb,
+                  float* out, float scale, cudaStream_t stream);
+// workspace (abi.cu)
+int ensure_workspace(sb200_ctx* ctx, size_t bytes);
+
+}  // namespace sb200

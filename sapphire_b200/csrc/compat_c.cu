@@ -1,0 +1,310 @@
+// Definitions of the Sapphire-signature shims declared in
+// compat/sapphire_b200_compat.hpp, plus C hooks so the test harness can drive
+// them through ctypes.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "sapphire_b200_compat.hpp"
+
+namespace {
+
+int g_mode = SB200_MODE_TF32;
+
+[[noreturn]] void fail(const char* where, int status)
+{
+    throw std::runtime_error(std::string(where) + ": " + sb200_status_string(status));
+}
+
+void check(const char* where, int status)
+{
+    if (status != SB200_OK)
+        fail(where, status);
+}
+
+}  // namespace
+
+namespace sb200::compat {
+
+void SetMode(int mode) { g_mode = mode; }
+int GetMode() { return g_mode; }
+
+sb200_ctx* ContextFor(int deviceId)
+{
+    // one context per (device, host thread), as the reference keeps one
+    // cuBLAS handle per (device, thread) -- Sources/Sapphire/compute/dense/cuda/Gemm.cu:24-30
+    thread_local std::map<int, sb200_ctx*> table;
+    auto it = table.find(deviceId);
+    if (it != table.end())
+        return it->second;
+    sb200_ctx* ctx = nullptr;
+    check("sb200_ctx_create", sb200_ctx_create(deviceId, &ctx));
+    table[deviceId] = ctx;
+    return ctx;
+}
+
+std::vector<LeafCall> PlanGemm(const std::vector<int>& yShape, const std::vector<int>& aShape,
+                               const std::vector<int>& bShape)
+{
+    auto padded = [](const std::vector<int>& s, size_t dim) {
+        std::vector<long long> out(dim, 1);
+        for (size_t i = 0; i < s.size(); ++i)
+            out[dim - s.size() + i] = s[i];
+        return out;
+    };
+    size_t dim = std::max(std::max(yShape.size(), aShape.size()), std::max(bShape.size(), static_cast<size_t>(2)));
+    const auto y = padded(yShape, dim), a = padded(aShape, dim), b = padded(bShape, dim);
+    const size_t nb = dim - 2;                         // batch dimensions
+    const long long M = y[dim - 2], N = y[dim - 1], K = a[dim - 1];
+    const long long matY = M * N, matA = M * K, matB = K * N;
+
+    // element strides of each batch dimension inside its own tensor
+    auto strides = [&](const std::vector<long long>& s, long long mat) {
+        std::vector<long long> st(nb, 0);
+        long long run = mat;
+        for (size_t i = nb; i-- > 0;) {
+            st[i] = run;
+            run *= s[i];
+        }
+        return st;
+    };
+    const auto sy = strides(y, matY), sa = strides(a, matA), sb = strides(b, matB);
+
+    std::vector<LeafCall> plan;
+    if (nb == 0) {
+        plan.push_back({0, 0, 0, 1, 0, 0});
+        return plan;
+    }
+    // innermost batch dimension becomes the strided batch of one call when each
+    // operand either spans it fully or has extent 1 there
+    const size_t in = nb - 1;
+    const bool foldable = (a[in] == y[in] || a[in] == 1) && (b[in] == y[in] || b[in] == 1);
+    const size_t outer_dims = foldable ? in : nb;
+    long long outer = 1;
+    for (size_t i = 0; i < outer_dims; ++i)
+        outer *= y[i];
+    std::vector<long long> idx(outer_dims, 0);
+    for (long long it = 0; it < outer; ++it) {
+        long long oy = 0, oa = 0, ob = 0;
+        for (size_t i = 0; i < outer_dims; ++i) {
+            oy += idx[i] * sy[i];
+            oa += (idx[i] % a[i]) * sa[i];
+            ob += (idx[i] % b[i]) * sb[i];
+        }
+        if (foldable)
+            plan.push_back({oy, oa, ob, y[in], a[in] == 1 ? 0 : matA, b[in] == 1 ? 0 : matB});
+        else
+            plan.push_back({oy, oa, ob, 1, 0, 0});
+        for (size_t i = outer_dims; i-- > 0;) {
+            if (++idx[i] < y[i])
+                break;
+            idx[i] = 0;
+        }
+    }
+    return plan;
+}
+
+void Gemm(const std::vector<int>& yShape, float* y, const std::vector<int>& aShape,
+          const float* a, const std::vector<int>& bShape, const float* b, int deviceId)
+{
+    auto dimAt = [](const std::vector<int>& s, int fromEnd) {
+        return static_cast<int>(s.size()) >= fromEnd ? s[s.size() - fromEnd] : 1;
+    };
+    const long long M = dimAt(yShape, 2), N = dimAt(yShape, 1), K = dimAt(aShape, 1);
+    sb200_ctx* ctx = ContextFor(deviceId);
+    for (const LeafCall& c : PlanGemm(yShape, aShape, bShape)) {
+        check("sb200_gemm_batched",
+              sb200_gemm_batched(ctx, g_mode, SB200_PATH_AUTO, 0, 0, M, N, K, a + c.offA, K,
+                                 c.strideA, b + c.offB, N, c.strideB, y + c.offY, N, M * N,
+                                 y + c.offY, N, M * N, nullptr, nullptr, 0.0f, c.batch,
+                                 cudaStreamPerThread));
+    }
+}
+
+}  // namespace sb200::compat
+
+namespace Sapphire::Compute::Dense::Cuda {
+
+void Gemm(unsigned int totalSize, float* out, const float* A, const float* B, unsigned int M,
+          unsigned int N, unsigned int K, int deviceId)
+{
+    const unsigned long long per = static_cast<unsigned long long>(M) * N;
+    const long long batch = per ? totalSize / per : 0;
+    sb200_ctx* ctx = sb200::compat::ContextFor(deviceId);
+    check("Dense::Cuda::Gemm",
+          sb200_gemm_batched(ctx, g_mode, SB200_PATH_AUTO, 0, 0, M, N, K, A, K,
+                             static_cast<long long>(M) * K, B, N, static_cast<long long>(K) * N,
+                             out, N, per, out, N, per, nullptr, nullptr, 0.0f, batch,
+                             cudaStreamPerThread));
+}
+
+void GemmMatrixWiseBroadcast(float* out, const float* A, const float* B, unsigned int M,
+                             unsigned int N, unsigned int K, unsigned int batchSize,
+                             bool broadcastA, bool broadcastB, int deviceId)
+{
+    const long long per = static_cast<long long>(M) * N;
+    sb200_ctx* ctx = sb200::compat::ContextFor(deviceId);
+    check("Dense::Cuda::GemmMatrixWiseBroadcast",
+          sb200_gemm_batched(ctx, g_mode, SB200_PATH_AUTO, 0, 0, M, N, K, A, K,
+                             broadcastA ? 0 : static_cast<long long>(M) * K, B, N,
+                             broadcastB ? 0 : static_cast<long long>(K) * N, out, N, per, out, N,
+                             per, nullptr, nullptr, 0.0f, batchSize, cudaStreamPerThread));
+}
+
+}  // namespace Sapphire::Compute::Dense::Cuda
+
+namespace Sapphire::Compute::Sparse::Cuda {
+
+void Gemm(SparseMatrix** hostOutput, SparseMatrix** cudaOutput, SparseMatrix* cudaA,
+          SparseMatrix* cudaB, uint32_t m, uint32_t n, size_t numMatrices, int deviceId,
+          bool copyResultToHost)
+{
+    (void)m;
+    (void)n;
+    sb200_ctx* ctx = sb200::compat::ContextFor(deviceId);
+    std::vector<sb200_csr> hA(numMatrices), hB(numMatrices), hC(numMatrices);
+    auto cu = [](cudaError_t e, const char* what) {
+        if (e != cudaSuccess)
+            throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+    };
+    cu(cudaMemcpy(hA.data(), cudaA, numMatrices * sizeof(sb200_csr), cudaMemcpyDeviceToHost),
+       "copy A descriptors");
+    cu(cudaMemcpy(hB.data(), cudaB, numMatrices * sizeof(sb200_csr), cudaMemcpyDeviceToHost),
+       "copy B descriptors");
+    for (size_t i = 0; i < numMatrices; ++i)
+        check("sb200_spgemm_csr", sb200_spgemm_csr(ctx, &hA[i], &hB[i], &hC[i], cudaStreamPerThread));
+    cu(cudaStreamSynchronize(cudaStreamPerThread), "sync");
+    if (cudaOutput) {
+        void* d = nullptr;
+        cu(cudaMalloc(&d, numMatrices * sizeof(sb200_csr)), "alloc C descriptors");
+        cu(cudaMemcpy(d, hC.data(), numMatrices * sizeof(sb200_csr), cudaMemcpyHostToDevice),
+           "copy C descriptors");
+        *cudaOutput = static_cast<SparseMatrix*>(d);
+    }
+    if (copyResultToHost && hostOutput) {
+        SparseMatrix* h = static_cast<SparseMatrix*>(malloc(numMatrices * sizeof(SparseMatrix)));
+        for (size_t i = 0; i < numMatrices; ++i) {
+            h[i] = hC[i];
+            const size_t nnz = hC[i].NNZ;
+            h[i].V = static_cast<float*>(malloc((nnz ? nnz : 1) * 4));
+            h[i].COL = static_cast<uint32_t*>(malloc((nnz ? nnz : 1) * 4));
+            h[i].ROW = static_cast<uint32_t*>(malloc((static_cast<size_t>(hC[i].M) + 1) * 4));
+            cu(cudaMemcpy(h[i].V, hC[i].V, nnz * 4, cudaMemcpyDeviceToHost), "copy V");
+            cu(cudaMemcpy(h[i].COL, hC[i].COL, nnz * 4, cudaMemcpyDeviceToHost), "copy COL");
+            cu(cudaMemcpy(h[i].ROW, hC[i].ROW, (static_cast<size_t>(hC[i].M) + 1) * 4,
+                          cudaMemcpyDeviceToHost), "copy ROW");
+        }
+        *hostOutput = h;
+    }
+}
+
+}  // namespace Sapphire::Compute::Sparse::Cuda
+
+// ------------------------------------------------------------- C test hooks
+// These forward to the C++ shims and turn exceptions back into status codes so
+// that a ctypes caller can exercise the Sapphire-signature layer.
+extern "C" {
+
+int sb200_compat_set_mode(int mode)
+{
+    if (mode != SB200_MODE_TF32 && mode != SB200_MODE_TF32X3)
+        return SB200_ERR_INVALID_ARG;
+    sb200::compat::SetMode(mode);
+    return SB200_OK;
+}
+
+// Sapphire::Compute::Dense::Cuda::Gemm
+int sb200_compat_dense_gemm(unsigned totalSize, float* out, const float* A, const float* B,
+                            unsigned M, unsigned N, unsigned K, int deviceId)
+{
+    try {
+        Sapphire::Compute::Dense::Cuda::Gemm(totalSize, out, A, B, M, N, K, deviceId);
+        return cudaStreamSynchronize(cudaStreamPerThread) == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+    } catch (const std::exception&) {
+        return SB200_ERR_CUDA;
+    }
+}
+
+// Sapphire::Compute::Dense::Cuda::GemmMatrixWiseBroadcast
+int sb200_compat_dense_gemm_broadcast(float* out, const float* A, const float* B, unsigned M,
+                                      unsigned N, unsigned K, unsigned batch, int bcA, int bcB,
+                                      int deviceId)
+{
+    try {
+        Sapphire::Compute::Dense::Cuda::GemmMatrixWiseBroadcast(out, A, B, M, N, K, batch,
+                                                                bcA != 0, bcB != 0, deviceId);
+        return cudaStreamSynchronize(cudaStreamPerThread) == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+    } catch (const std::exception&) {
+        return SB200_ERR_CUDA;
+    }
+}
+
+// The Compute::Gemm broadcast rules over raw shapes; runs on the device.
+int sb200_compat_compute_gemm(const int* yShape, int yDim, float* y, const int* aShape, int aDim,
+                              const float* a, const int* bShape, int bDim, const float* b,
+                              int deviceId)
+{
+    try {
+        sb200::compat::Gemm(std::vector<int>(yShape, yShape + yDim), y,
+                            std::vector<int>(aShape, aShape + aDim), a,
+                            std::vector<int>(bShape, bShape + bDim), b, deviceId);
+        return cudaStreamSynchronize(cudaStreamPerThread) == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+    } catch (const std::exception&) {
+        return SB200_ERR_CUDA;
+    }
+}
+
+// The planner alone (no GPU needed): writes up to `cap` calls as 6 int64 each
+// (offY, offA, offB, batch, strideA, strideB) and returns the number planned.
+long long sb200_compat_plan_gemm(const int* yShape, int yDim, const int* aShape, int aDim,
+                                 const int* bShape, int bDim, long long* out, long long cap)
+{
+    const auto plan = sb200::compat::PlanGemm(std::vector<int>(yShape, yShape + yDim),
+                                              std::vector<int>(aShape, aShape + aDim),
+                                              std::vector<int>(bShape, bShape + bDim));
+    long long n = 0;
+    for (const auto& c : plan) {
+        if (n < cap) {
+            long long* o = out + 6 * n;
+            o[0] = c.offY; o[1] = c.offA; o[2] = c.offB;
+            o[3] = c.batch; o[4] = c.strideA; o[5] = c.strideB;
+        }
+        ++n;
+    }
+    return n;
+}
+
+// Sapphire::Compute::Sparse::Cuda::Gemm for one matrix pair given as host
+// structs with device arrays; returns the output the same way.
+int sb200_compat_sparse_gemm(const sb200_csr* A, const sb200_csr* B, sb200_csr* C, int deviceId)
+{
+    try {
+        void *dA = nullptr, *dB = nullptr;
+        if (cudaSetDevice(deviceId) != cudaSuccess ||
+            cudaMalloc(&dA, sizeof(sb200_csr)) != cudaSuccess ||
+            cudaMalloc(&dB, sizeof(sb200_csr)) != cudaSuccess)
+            return SB200_ERR_ALLOC;
+        cudaMemcpy(dA, A, sizeof(sb200_csr), cudaMemcpyHostToDevice);
+        cudaMemcpy(dB, B, sizeof(sb200_csr), cudaMemcpyHostToDevice);
+        SparseMatrix* dC = nullptr;
+        Sapphire::Compute::Sparse::Cuda::Gemm(nullptr, &dC, static_cast<SparseMatrix*>(dA),
+                                              static_cast<SparseMatrix*>(dB), A->M, B->N, 1,
+                                              deviceId, false);
+        cudaMemcpy(C, dC, sizeof(sb200_csr), cudaMemcpyDeviceToHost);
+        cudaFree(dA);
+        cudaFree(dB);
+        cudaFree(dC);
+        return SB200_OK;
+    } catch (const std::exception&) {
+        return SB200_ERR_CUDA;
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,510 @@
+// Batched fp32 GEMM  D = (C + bias) + op(A).op(B)  on the sm_100a tensor cores.
+//
+// One persistent CTA per SM walks over 128 x BLOCK_N output tiles.  Warp roles:
+//   warp 0      TMA producer: fills a ring of shared-memory stages with one
+//               128 x 32 tile of op(A) and one 32 x BLOCK_N tile of op(B) per
+//               k-block (32 fp32 = one 128-byte swizzle row)
+//   warp 1      MMA issuer: tcgen05.mma kind::tf32, accumulators in TMEM; two
+//               accumulator buffers so the epilogue of one tile overlaps the
+//               main loop of the next
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, add C and bias, store D
+//   warps 6-9   (3xTF32 mode only) split every landed stage into a TF32 high
+//               part and a TF32 low part; the issuer then runs lo.hi + hi.lo +
+//               hi.hi per k-block into the same accumulator
+//
+// Transposed operands cost nothing extra: a tile whose contiguous dimension is
+// M or N instead of K is loaded by TMA in its natural orientation ("MN-major",
+// 32-element chunks along M/N, each 32 k-rows x 128 B) and the instruction
+// descriptor's major bits tell the tensor core which way to read it.  Row-major
+// B[K, N] -- the forward GEMM of a Linear layer -- is the MN-major case.
+//
+// Every wait on an mbarrier is bounded; when one expires the CTA records a code
+// in the status word, raises a CTA-wide abort flag, and every role falls through
+// to the common exit where TMEM is released.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace sb200 {
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 32;                     // fp32 elements = 128 bytes
+constexpr int UMMA_K = 8;                       // k per tcgen05.mma, kind::tf32
+constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 4;
+constexpr int CHUNK_BYTES = 32 * BLOCK_K * 4;   // one MN-major chunk: 32 k-rows x 128 B
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+struct KernelParams {
+    int M, N, K, batch;
+    int tiles_m, tiles_n, num_kb;
+    long long total_tiles;
+    int a_batched, b_batched;                   // 0: batch stride 0, always read matrix 0
+    const float* C; long long ldc, strideC;
+    float* D; long long ldd, strideD;
+    const float* bias;
+    unsigned* status;
+    int explicit_hi;
+};
+
+template <int BLOCK_N, int STAGES, bool SPLIT>
+struct SmemLayout {
+    static constexpr int B_TILE_BYTES = BLOCK_N * BLOCK_K * 4;
+    static constexpr int STAGE_BYTES = (A_TILE_BYTES + B_TILE_BYTES) * (SPLIT ? 2 : 1);
+    static constexpr int TILES_BYTES = STAGE_BYTES * STAGES;
+    // barriers: full, empty, split_done per stage; tmem_full, tmem_empty per accumulator
+    static constexpr int BAR_BYTES = (3 * STAGES + 4) * 8 + 16;
+    static constexpr int TOTAL = TILES_BYTES + BAR_BYTES + 1024;   // + alignment slack
+};
+
+struct Abort {
+    volatile int* flag;
+    unsigned* status;
+};
+
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, const Abort& ab,
+                                         unsigned code)
+{
+    if (ptx::mbar_try_wait(bar, parity))
+        return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0) {
+            if (*ab.flag)
+                return false;
+            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *ab.flag = 1;
+                atomicCAS(ab.status, 0u, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// hi/lo split of one fp32 value for the 3xTF32 mode.  hi is exactly
+// representable in TF32 (10 explicit mantissa bits), lo = x - hi is exact in
+// fp32 and is itself cut to TF32 by the tensor core.
+__device__ __forceinline__ void split_tf32(float x, bool rounded, float& hi, float& lo)
+{
+    uint32_t h;
+    if (rounded)
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    else
+        h = __float_as_uint(x) & 0xFFFFE000u;
+    hi = __uint_as_float(h);
+    lo = x - hi;
+}
+
+template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? 320 : 192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
+                    const __grid_constant__ CUtensorMap mapB, const KernelParams p)
+{
+    using L = SmemLayout<BLOCK_N, STAGES, SPLIT>;
+    constexpr int B_TILE_BYTES = L::B_TILE_BYTES;
+    constexpr int HALF_STAGE = A_TILE_BYTES + B_TILE_BYTES;       // the hi (raw) tiles
+    constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;                    // 256 or 512: power of two
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::TILES_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* split_bar = empty_bar + STAGES;
+    uint64_t* tmem_full = split_bar + STAGES;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const Abort ab{abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+            ptx::mbar_init(&split_bar[s], 4);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&tmem_full[i], 1);
+            ptx::mbar_init(&tmem_empty[i], 4);
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&mapA);
+        ptx::prefetch_tensormap(&mapB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const long long tiles_per_batch = static_cast<long long>(p.tiles_m) * p.tiles_n;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                const int b = static_cast<int>(t / tiles_per_batch);
+                const int r = static_cast<int>(t % tiles_per_batch);
+                const int m0 = (r % p.tiles_m) * BLOCK_M;
+                const int n0 = (r / p.tiles_m) * BLOCK_N;
+                const int ba = p.a_batched ? b : 0;
+                const int bb = p.b_batched ? b : 0;
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!(ok = wait_bar(&empty_bar[s], ph ^ 1u, ab, FAULT_PRODUCER_WAIT)))
+                        break;
+                    uint8_t* sa = smem + s * L::STAGE_BYTES;
+                    uint8_t* sb = sa + A_TILE_BYTES;
+                    const int k0 = kb * BLOCK_K;
+                    ptx::mbar_arrive_expect_tx(&full_bar[s], HALF_STAGE);
+                    if (A_MN) {
+                        // stored [K, M]: contiguous M, one 32(m) x 32(k) box per chunk
+#pragma unroll
+                        for (int c = 0; c < BLOCK_M / 32; ++c)
+                            ptx::tma_load_3d(sa + c * CHUNK_BYTES, &mapA, &full_bar[s],
+                                             m0 + c * 32, k0, ba);
+                    } else {
+                        // stored [M, K]: contiguous K, one 32(k) x 128(m) box
+                        ptx::tma_load_3d(sa, &mapA, &full_bar[s], k0, m0, ba);
+                    }
+                    if (B_MN) {
+                        // stored [K, N]: contiguous N
+#pragma unroll
+                        for (int c = 0; c < BLOCK_N / 32; ++c)
+                            ptx::tma_load_3d(sb + c * CHUNK_BYTES, &mapB, &full_bar[s],
+                                             n0 + c * 32, k0, bb);
+                    } else {
+                        // stored [N, K]: contiguous K, one 32(k) x BLOCK_N(n) box
+                        ptx::tma_load_3d(sb, &mapB, &full_bar[s], k0, n0, bb);
+                    }
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc_tf32(BLOCK_M, BLOCK_N, A_MN, B_MN);
+            // byte step of the descriptor start address per UMMA_K
+            constexpr uint32_t A_KSTEP = A_MN ? 1024u : UMMA_K * 4u;
+            constexpr uint32_t B_KSTEP = B_MN ? 1024u : UMMA_K * 4u;
+            constexpr uint32_t A_LBO = A_MN ? CHUNK_BYTES : 16u;
+            constexpr uint32_t B_LBO = B_MN ? CHUNK_BYTES : 16u;
+            int s = 0;
+            uint32_t ph = 0;
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                if (!(ok = wait_bar(&tmem_empty[acc], acc_ph ^ 1u, ab, FAULT_MMA_WAIT_TMEM)))
+                    break;
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    uint64_t* ready = SPLIT ? &split_bar[s] : &full_bar[s];
+                    if (!(ok = wait_bar(ready, ph, ab, FAULT_MMA_WAIT_FULL)))
+                        break;
+                    ptx::tc_fence_after_sync();
+                    const uint32_t sa = ptx::smem_u32(smem + s * L::STAGE_BYTES);
+                    const uint32_t sb = sa + A_TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t a_hi =
+                            ptx::make_smem_desc_sw128(sa + k * A_KSTEP, A_LBO, 1024u);
+                        const uint64_t b_hi =
+                            ptx::make_smem_desc_sw128(sb + k * B_KSTEP, B_LBO, 1024u);
+                        const uint32_t first = (kb > 0 || k > 0) ? 1u : 0u;
+                        if (SPLIT) {
+                            const uint64_t a_lo = ptx::make_smem_desc_sw128(
+                                sa + HALF_STAGE + k * A_KSTEP, A_LBO, 1024u);
+                            const uint64_t b_lo = ptx::make_smem_desc_sw128(
+                                sb + HALF_STAGE + k * B_KSTEP, B_LBO, 1024u);
+                            // small terms first
+                            ptx::mma_tf32(d_tmem, a_lo, b_hi, idesc, first);
+                            ptx::mma_tf32(d_tmem, a_hi, b_lo, idesc, 1u);
+                            ptx::mma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
+                        } else {
+                            ptx::mma_tf32(d_tmem, a_hi, b_hi, idesc, first);
+                        }
+                    }
+                    ptx::mma_commit(&empty_bar[s]);       // stage free once these MMAs retire
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+                if (!ok)
+                    break;
+                ptx::mma_commit(&tmem_full[acc]);         // accumulator complete
+                acc ^= 1;
+                if (acc == 0)
+                    acc_ph ^= 1u;
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------- epilogue
+        const int q = warp & 3;                           // TMEM lane quadrant of this warp
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        const bool vec_ok = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
+                            ((p.strideD & 3) == 0) &&
+                            (p.C == nullptr ||
+                             (((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                              ((p.strideC & 3) == 0)));
+        for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+            const int b = static_cast<int>(t / tiles_per_batch);
+            const int r = static_cast<int>(t % tiles_per_batch);
+            const int m0 = (r % p.tiles_m) * BLOCK_M;
+            const int n0 = (r / p.tiles_m) * BLOCK_N;
+            if (!(ok = wait_bar(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
+                break;
+            ptx::tc_fence_after_sync();
+            const int row = m0 + q * 32 + lane;
+            float* drow = p.D + b * p.strideD + static_cast<long long>(row) * p.ldd;
+            const float* crow =
+                p.C ? p.C + b * p.strideC + static_cast<long long>(row) * p.ldc : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < BLOCK_N / 32; ++c) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= p.N)
+                    break;                                 // uniform across the warp
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                       static_cast<uint32_t>(acc * BLOCK_N + c * 32),
+                                   v);
+                ptx::tmem_ld_wait();
+                if (row < p.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const int col = col0 + j;
+                        if (vec_ok && col + 3 < p.N) {
+                            float4 base = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (crow)
+                                base = *reinterpret_cast<const float4*>(crow + col);
+                            if (p.bias) {
+                                base.x = base.x + __ldg(p.bias + col);
+                                base.y = base.y + __ldg(p.bias + col + 1);
+                                base.z = base.z + __ldg(p.bias + col + 2);
+                                base.w = base.w + __ldg(p.bias + col + 3);
+                            }
+                            float4 o;
+                            o.x = base.x + __uint_as_float(v[j]);
+                            o.y = base.y + __uint_as_float(v[j + 1]);
+                            o.z = base.z + __uint_as_float(v[j + 2]);
+                            o.w = base.w + __uint_as_float(v[j + 3]);
+                            *reinterpret_cast<float4*>(drow + col) = o;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                if (col + e < p.N) {
+                                    float base = crow ? crow[col + e] : 0.f;
+                                    if (p.bias)
+                                        base = base + __ldg(p.bias + col + e);
+                                    drow[col + e] = base + __uint_as_float(v[j + e]);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                ptx::mbar_arrive(&tmem_empty[acc]);
+            acc ^= 1;
+            if (acc == 0)
+                acc_ph ^= 1u;
+        }
+    } else if (SPLIT) {
+        // --------------------------------------- hi/lo split (3xTF32 mode)
+        // 128 threads; each float4 of the landed tiles is read once, its low
+        // part is written to the twin tile at the same (swizzled) offset.
+        const int tid = threadIdx.x - 6 * 32;
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        const bool rounded = p.explicit_hi != 0;
+        for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+            for (int kb = 0; kb < p.num_kb; ++kb) {
+                if (!(ok = wait_bar(&full_bar[s], ph, ab, FAULT_SPLIT_WAIT)))
+                    break;
+                float4* hi = reinterpret_cast<float4*>(smem + s * L::STAGE_BYTES);
+                float4* lo = reinterpret_cast<float4*>(smem + s * L::STAGE_BYTES + HALF_STAGE);
+#pragma unroll 4
+                for (int i = tid; i < HALF_STAGE / 16; i += 128) {
+                    const float4 x = hi[i];
+                    float4 h, l;
+                    split_tf32(x.x, rounded, h.x, l.x);
+                    split_tf32(x.y, rounded, h.y, l.y);
+                    split_tf32(x.z, rounded, h.z, l.z);
+                    split_tf32(x.w, rounded, h.w, l.w);
+                    lo[i] = l;
+                    if (rounded)
+                        hi[i] = h;
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(&split_bar[s]);
+                if (++s == STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+        }
+    }
+
+    // common exit: every thread arrives here, also after an abort
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------- host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Tensor map over a stack of row-major matrices: dim0 = contiguous extent,
+// dim1 = rows, dim2 = batch; box = 32 contiguous elements x box_rows x 1,
+// 128-byte swizzle, out-of-range elements read as zero.
+int make_map(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig, int64_t rows,
+             int64_t ld, int64_t batch, int64_t batch_stride, int box_rows)
+{
+    EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    if (!enc)
+        return SB200_ERR_UNSUPPORTED;
+    const int64_t nb = (batch_stride == 0) ? 1 : batch;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(contig), static_cast<cuuint64_t>(rows),
+                          static_cast<cuuint64_t>(nb)};
+    const int64_t bs = (batch_stride == 0 || nb == 1) ? rows * ld : batch_stride;
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4, static_cast<cuuint64_t>(bs) * 4};
+    cuuint32_t box[3] = {32, static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
+}
+
+template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT>
+int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
+{
+    using L = SmemLayout<BLOCK_N, STAGES, SPLIT>;
+    auto kern = gemm_tcgen05_kernel<BLOCK_N, STAGES, A_MN, B_MN, SPLIT>;
+    static bool attr_done[16] = {};
+    if (ctx->device < 16 && !attr_done[ctx->device]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
+            cudaSuccess)
+            return SB200_ERR_CUDA;
+        attr_done[ctx->device] = true;
+    } else if (ctx->device >= 16) {
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    }
+
+    CUtensorMap mapA, mapB;
+    int rc;
+    if (A_MN)   // stored [K, M]
+        rc = make_map(ctx, &mapA, g.A, g.M, g.K, g.lda, g.batch, g.strideA, BLOCK_K);
+    else        // stored [M, K]
+        rc = make_map(ctx, &mapA, g.A, g.K, g.M, g.lda, g.batch, g.strideA, BLOCK_M);
+    if (rc)
+        return rc;
+    if (B_MN)   // stored [K, N]
+        rc = make_map(ctx, &mapB, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, BLOCK_K);
+    else        // stored [N, K]
+        rc = make_map(ctx, &mapB, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, BLOCK_N);
+    if (rc)
+        return rc;
+
+    KernelParams p;
+    p.M = static_cast<int>(g.M);
+    p.N = static_cast<int>(g.N);
+    p.K = static_cast<int>(g.K);
+    p.batch = static_cast<int>(g.batch);
+    p.tiles_m = static_cast<int>((g.M + BLOCK_M - 1) / BLOCK_M);
+    p.tiles_n = static_cast<int>((g.N + BLOCK_N - 1) / BLOCK_N);
+    p.num_kb = static_cast<int>((g.K + BLOCK_K - 1) / BLOCK_K);
+    p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * g.batch;
+    p.a_batched = g.strideA != 0;
+    p.b_batched = g.strideB != 0;
+    p.C = g.C; p.ldc = g.ldc; p.strideC = g.strideC;
+    p.D = g.D; p.ldd = g.ldd; p.strideD = g.strideD;
+    p.bias = g.bias;
+    p.status = ctx->d_status;
+    p.explicit_hi = ctx->split_explicit_hi;
+
+    const long long grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
+    kern<<<static_cast<unsigned>(grid), SPLIT ? 320 : 192, L::TOTAL, stream>>>(mapA, mapB, p);
+    ctx->launches += 1;
+    return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+}
+
+template <int BLOCK_N, int STAGES, bool SPLIT>
+int launch_layout(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
+{
+    const bool a_mn = g.transA != 0;     // stored [K, M]
+    const bool b_mn = g.transB == 0;     // stored [K, N]
+    if (a_mn)
+        return b_mn ? launch_variant<BLOCK_N, STAGES, true, true, SPLIT>(ctx, g, stream)
+                    : launch_variant<BLOCK_N, STAGES, true, false, SPLIT>(ctx, g, stream);
+    return b_mn ? launch_variant<BLOCK_N, STAGES, false, true, SPLIT>(ctx, g, stream)
+                : launch_variant<BLOCK_N, STAGES, false, false, SPLIT>(ctx, g, stream);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// TMA needs 16-byte aligned base addresses and 16-byte multiples for every
+// stride; the tile coordinates the kernel uses are multiples of 32 elements.
+bool tcgen05_eligible(const GemmArgs& g)
+{
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0)
+        return false;
+    if (g.M > INT32_MAX || g.N > INT32_MAX || g.K > INT32_MAX || g.batch > INT32_MAX)
+        return false;
+    if (!aligned16(g.A) || !aligned16(g.B))
+        return false;
+    if ((g.lda & 3) || (g.ldb & 3) || (g.strideA & 3) || (g.strideB & 3))
+        return false;
+    if (g.strideA < 0 || g.strideB < 0)
+        return false;
+    return true;
+}
+
+int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
+{
+    if (!tcgen05_eligible(g))
+        return SB200_ERR_UNSUPPORTED;
+    const bool wide = g.N > 128;
+    if (g.mode == SB200_MODE_TF32X3) {
+        // hi + lo tiles double the stage: 128-wide tiles, three stages
+        return launch_layout<128, 3, true>(ctx, g, stream);
+    }
+    return wide ? launch_layout<256, 4, false>(ctx, g, stream)
+                : launch_layout<128, 6, false>(ctx, g, stream);
+}
+
+}  // namespace sb200

@@ -1,0 +1,204 @@
+"""Host-side front end over the C ABI for torch CUDA tensors.
+
+torch is used for device memory and streams only; every computation below is
+a call into libsapphire_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class Context:
+    """One sb200_ctx: per (device, host thread)."""
+
+    def __init__(self, device: int = 0):
+        if not torch.cuda.is_available():
+            raise RuntimeError("sapphire_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        self.device = int(device)
+        h = C.c_void_p()
+        L.check("sb200_ctx_create", L.lib().sb200_ctx_create(self.device, C.byref(h)))
+        self._h = h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            L.lib().sb200_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def last_path(self) -> int:
+        return L.lib().sb200_last_path(self._h)
+
+    def launch_count(self) -> int:
+        return L.lib().sb200_launch_count(self._h)
+
+    def set_option(self, option: int, value: int) -> None:
+        L.check("sb200_ctx_set_option", L.lib().sb200_ctx_set_option(self._h, option, value))
+
+    def check_device_status(self) -> None:
+        L.check("sb200_check_device_status",
+                L.lib().sb200_check_device_status(self._h, _stream_ptr(self.device)))
+
+
+def _mat_geometry(t: torch.Tensor):
+    """(batch, rows, cols, ld, batch_stride) of a 2-D or 3-D fp32 tensor whose
+    last dimension is contiguous."""
+    if t.dtype != torch.float32:
+        raise TypeError("fp32 only")
+    if t.dim() == 2:
+        t = t.unsqueeze(0)
+    if t.dim() != 3:
+        raise ValueError("expected [rows, cols] or [batch, rows, cols]")
+    if t.shape[2] > 1 and t.stride(2) != 1:
+        raise ValueError("last dimension must be contiguous")
+    ld = t.stride(1) if t.shape[1] > 1 else max(t.shape[2], t.stride(1))
+    bs = t.stride(0) if t.shape[0] > 1 else 0
+    return t.shape[0], t.shape[1], t.shape[2], ld, bs
+
+
+def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None, *, mode: int = L.MODE_TF32, trans_a: bool = False,
+         trans_b: bool = False, bias: Optional[torch.Tensor] = None,
+         colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0,
+         path: int = L.PATH_AUTO) -> torch.Tensor:
+    """out = (c + bias) + op(a).op(b), batched over a leading dimension.
+
+    ``c`` may be ``out`` itself (in-place accumulate, Sapphire's
+    ``y <- y + a.b``).  A tensor with batch extent 1 (or 2-D) is shared by all
+    batches.  Returns ``out``.
+    """
+    ba, ra, ca, lda, sa = _mat_geometry(a)
+    bb, rb, cb, ldb, sb = _mat_geometry(b)
+    M, K = (ca, ra) if trans_a else (ra, ca)
+    K2, N = (cb, rb) if trans_b else (rb, cb)
+    if K != K2:
+        raise ValueError(f"inner dimensions differ: {K} vs {K2}")
+    batch = max(ba, bb)
+    if c is not None:
+        batch = max(batch, c.shape[0] if c.dim() == 3 else 1)
+    if out is None:
+        out = torch.empty((batch, M, N), dtype=torch.float32, device=a.device)
+        if a.dim() == 2 and b.dim() == 2 and (c is None or c.dim() == 2):
+            out = out[0]
+    bo, ro, co, ldd, sd = _mat_geometry(out)
+    batch = max(batch, bo)
+    if (ro, co) != (M, N):
+        raise ValueError("output shape mismatch")
+    if bo != batch:
+        raise ValueError("output batch mismatch")
+    if batch > 1 and sd == 0:
+        sd = out.stride(0)
+    cptr, ldc, sc = None, N, 0
+    if c is not None:
+        bc, rc_, cc, ldc, sc = _mat_geometry(c)
+        if (rc_, cc) != (M, N) or bc != batch:
+            raise ValueError("c must have the output's shape")
+        if batch > 1 and sc == 0:
+            sc = c.stride(0)
+        cptr = c.data_ptr()
+    if ba not in (1, batch) or bb not in (1, batch):
+        raise ValueError("operand batch must be 1 or the output batch")
+    L.check("sb200_gemm_batched", L.lib().sb200_gemm_batched(
+        ctx.handle, mode, path, int(trans_a), int(trans_b), M, N, K,
+        a.data_ptr(), lda, sa if ba == batch and batch > 1 else 0,
+        b.data_ptr(), ldb, sb if bb == batch and batch > 1 else 0,
+        cptr, ldc, sc, out.data_ptr(), ldd, sd,
+        bias.data_ptr() if bias is not None else None,
+        colsum_out.data_ptr() if colsum_out is not None else None, float(colsum_scale),
+        batch, _stream_ptr(ctx.device)))
+    return out
+
+
+# --------------------------------------------------------------------- sparse
+
+@dataclass
+class CsrMatrix:
+    """CSR on the device: ROW int32[M+1], COL int32[nnz], V float32[nnz].
+
+    The 32-bit indices are Sapphire's uint32 (``SparseMatrix``); torch stores
+    them as int32 bit patterns.
+    """
+    row: torch.Tensor
+    col: torch.Tensor
+    val: torch.Tensor
+    M: int
+    N: int
+
+    @property
+    def nnz(self) -> int:
+        return int(self.col.numel())
+
+    def as_struct(self) -> L.Csr:
+        s = L.Csr()
+        s.V = self.val.data_ptr() if self.val.numel() else None
+        s.COL = self.col.data_ptr() if self.col.numel() else None
+        s.ROW = self.row.data_ptr()
+        s.NNZ, s.M, s.N = self.nnz, self.M, self.N
+        return s
+
+    @staticmethod
+    def from_numpy(row, col, val, M, N, device):
+        import numpy as np
+        return CsrMatrix(torch.from_numpy(row.astype(np.int64).astype(np.int32)).to(device),
+                         torch.from_numpy(col.view(np.int32).copy()).to(device),
+                         torch.from_numpy(val.copy()).to(device), int(M), int(N))
+
+    def to_numpy(self):
+        import numpy as np
+        return (self.row.cpu().numpy().view(np.uint32), self.col.cpu().numpy().view(np.uint32),
+                self.val.cpu().numpy())
+
+
+def spgemm(ctx: Context, A: CsrMatrix, B: CsrMatrix) -> CsrMatrix:
+    """C = A.B with caller-owned (torch) output arrays: symbolic pass, allocate,
+    numeric pass."""
+    dev = A.row.device
+    a, b = A.as_struct(), B.as_struct()
+    row_c = torch.empty(A.M + 1, dtype=torch.int32, device=dev)
+    nnz = C.c_int64(0)
+    st = _stream_ptr(ctx.device)
+    L.check("sb200_spgemm_csr_symbolic", L.lib().sb200_spgemm_csr_symbolic(
+        ctx.handle, C.byref(a), C.byref(b), row_c.data_ptr(), C.byref(nnz), st))
+    n = int(nnz.value)
+    col_c = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    val_c = torch.empty(max(n, 1), dtype=torch.float32, device=dev)
+    L.check("sb200_spgemm_csr_numeric", L.lib().sb200_spgemm_csr_numeric(
+        ctx.handle, C.byref(a), C.byref(b), row_c.data_ptr(), col_c.data_ptr(), val_c.data_ptr(),
+        st))
+    return CsrMatrix(row_c, col_c[:n], val_c[:n], A.M, B.N)
+
+
+def spgemm_callee_alloc(ctx: Context, A: CsrMatrix, B: CsrMatrix) -> CsrMatrix:
+    """The drop-in call: the library allocates C (cudaMalloc); the arrays are
+    copied into torch tensors and the library's copies freed."""
+    dev = A.row.device
+    a, b, c = A.as_struct(), B.as_struct(), L.Csr()
+    L.check("sb200_spgemm_csr", L.lib().sb200_spgemm_csr(
+        ctx.handle, C.byref(a), C.byref(b), C.byref(c), _stream_ptr(ctx.device)))
+    n = int(c.NNZ)
+    row = torch.empty(A.M + 1, dtype=torch.int32, device=dev)
+    col = torch.empty(n, dtype=torch.int32, device=dev)
+    val = torch.empty(n, dtype=torch.float32, device=dev)
+    L.check("sb200_csr_copy_out", L.lib().sb200_csr_copy_out(
+        C.byref(c), row.data_ptr(), col.data_ptr() if n else None,
+        val.data_ptr() if n else None, 0, _stream_ptr(ctx.device)))
+    L.lib().sb200_csr_free(C.byref(c))
+    return CsrMatrix(row, col, val, A.M, B.N)

@@ -1,0 +1,73 @@
+"""Generates the golden fixtures of tests/golden from the REFERENCE's own CPU
+code (oracle/_ref/libsapphire_ref.so, compiled from the reference tree by
+oracle/Makefile).  Run where the reference tree is mounted:
+
+    make -C oracle && python tests/golden/make_golden.py
+
+Inputs are not stored: they are regenerated from seeds by
+sapphire_b200.workloads / the small generators below.  Outputs are stored in
+full for small cases and as a strided sample plus a float64 checksum for the
+4 x 256^3 case.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from oracle import oracle as O  # noqa: E402
+from sapphire_b200 import workloads as W  # noqa: E402
+
+# (batch, M, N, K): the reference's Gemm1 test family draws M, N, K from [1, 100]
+# (Tests/UnitTests/Sources/FunctionTest/GemmTest.cpp:20-84)
+SMALL_SHAPES = [(1, 1, 1, 1), (2, 3, 5, 7), (3, 17, 9, 33), (1, 64, 10, 256), (2, 100, 99, 98),
+                (4, 32, 32, 32), (1, 128, 128, 128), (1, 130, 70, 40)]
+
+
+def small_case(idx):
+    b, M, N, K = SMALL_SHAPES[idx]
+    rng = np.random.default_rng(100 + idx)
+    a = rng.normal(10.0, 5.0, size=(b, M, K)).astype(np.float32)   # N(10,5) as in Gemm1
+    bm = rng.normal(10.0, 5.0, size=(b, K, N)).astype(np.float32)
+    c = rng.uniform(-1, 1, size=(b, M, N)).astype(np.float32)
+    return a, bm, c
+
+
+def mlp_reference(steps, impl):
+    Ws, bs = W.mlp_init(0)
+    net = O.MlpOracle(Ws, bs, 0.01, impl=impl)
+    losses = []
+    for t in range(steps):
+        x, onehot = W.mlp_batch(t)
+        losses.append(net.step(x, onehot))
+    return np.stack(losses), net
+
+
+def main():
+    assert O.have_ref(), "build oracle/_ref first (make -C oracle)"
+    out = {}
+    for i in range(len(SMALL_SHAPES)):
+        a, b, c = small_case(i)
+        out[f"small{i}"] = O.gemm(c, a, b, impl="ref")
+    a, b, c = W.dense_batched(0, range(4), 256, 256, 256, "uniform")
+    y = O.gemm(c, a, b, impl="ref")
+    out["c1_sample"] = y.reshape(-1)[::16].copy()
+    out["c1_sum64"] = np.array([y.astype(np.float64).sum()])
+    # transpose leaf
+    rng = np.random.default_rng(7)
+    t_in = rng.uniform(-1, 1, size=(3, 5, 8)).astype(np.float32)
+    out["transpose"] = O.transpose(t_in, impl="ref")
+    # 3 MLP steps through the reference leaves (Gemm via ref; elementwise leaves via ref below)
+    losses, net = mlp_reference(3, "ref")
+    out["mlp_loss3"] = losses
+    out["mlp_w2_after3"] = net.W[2]
+    out["mlp_b0_after3"] = net.b[0]
+    np.savez_compressed(os.path.join(HERE, "dense_golden.npz"), **out)
+    print("wrote", os.path.join(HERE, "dense_golden.npz"),
+          {k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main()
