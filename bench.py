@@ -1,0 +1,383 @@
+#!/usr/bin/env python
+"""Benchmark of the matrix-multiplication path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload dense_tf32|dense_tf32x3|dense4000_tf32|linear_bwd|spgemm|spgemm_zipf]
+                    [--no-extras]
+
+One JSON line on stdout (rank 0).  The headline workload is the large batched
+dense GEMM, 8 x 4096^3 fp32-in / TF32 per GPU (weak scaling: every rank owns 8
+independent batches, no data-path collective).  A "step" is one pass of the
+path over that batch.  `value` is whole-job TFLOP/s with inputs resident in
+HBM; `e2e` is the same metric through the C ABI from pinned HOST buffers with
+the host<->device copies inside the timed region.
+
+`--impl reference` times the reference's own CPU GEMM (oracle/_ref, compiled
+from the reference tree; the oracle port when that build is absent) on a
+bounded row slice of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DENSE = {"dense_tf32": (4096, 0), "dense_tf32x3": (4096, 1), "dense4000_tf32": (4000, 0),
+         "dense4000_tf32x3": (4000, 1)}
+BATCH = 8
+
+
+def peaks():
+    """Roofline denominators: measured on this pool when the file is present."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples of one GPU during a timed region."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.f,
+                stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.f.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        self.f.close()
+        os.unlink(self.f.name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(mx)) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------- reference arm
+
+def cpu_gemm_sample(n: int, rows: int, repeats: int = 1):
+    """Times the reference CPU GEMM on `rows` output rows of one n^3 batch.
+    Returns (seconds per pass, kind, flops per pass)."""
+    from oracle import oracle as O
+    from sapphire_b200 import workloads as W
+    kind = "reference" if O.have_ref() else "port"
+    a = W.normal(0, "a", (rows, n), 1.0, 0)
+    b = W.normal(0, "b", (n, n), 1.0, 0)
+    c = W.uniform_pm1(0, "c", (rows, n), 0)
+    fn = O.ref().ref_gemm if kind == "reference" else O.port().orc_gemm
+    best = None
+    for _ in range(repeats):
+        y = c.copy()
+        t = time.perf_counter()
+        fn(y.size, y.reshape(-1), a.reshape(-1), b.reshape(-1), rows, n, n)
+        dt = time.perf_counter() - t
+        best = dt if best is None else min(best, dt)
+    return best, kind, 2.0 * rows * n * n
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n, mode = DENSE.get(args.workload, (4096, 0))
+    rows = 32
+    times = []
+    kind = None
+    for i in range(args.warmup + args.steps):
+        dt, kind, flops = cpu_gemm_sample(n, rows)
+        if i >= args.warmup:
+            times.append(dt)
+    sec = float(np.mean(times))
+    tflops = flops / sec / 1e12
+    sample = (f"{rows} output rows of one {n}x{n}x{n} batch per step "
+              f"(2*{rows}*{n}^2 FLOP), rate extrapolates to the full 8-batch workload")
+    line = {
+        "impl": "reference", "metric": "batched dense GEMM throughput", "value": tflops,
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"dense batched GEMM batch={BATCH} M=N=K={n} y=a.b+c, CPU row slice",
+                   "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": 1, "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------- our arm
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="dense_tf32")
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from sapphire_b200 import _lib as L
+    from sapphire_b200 import ops
+    from sapphire_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = ops.Context(local)
+    pk = peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, steps, warmup):
+        """CUDA-event time per step on the current stream, max over ranks."""
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        launches0 = ctx.launch_count()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        return max_over_ranks(ms), (ctx.launch_count() - launches0)
+
+    # ---------------------------------------------------------------- dense
+    def dense_inputs(n, on_device=True):
+        # this rank's 8 batches of the global [8*world, n, n] tensors
+        ids = list(range(rank * BATCH, (rank + 1) * BATCH))
+        if on_device:
+            # device-side generation keeps start-up short; the parity tests use the
+            # numpy generators, the timing does not depend on the values
+            g = torch.Generator(device=dev)
+            g.manual_seed(1234 + rank)
+            a = torch.randn(BATCH, n, n, device=dev, generator=g)
+            b = torch.randn(BATCH, n, n, device=dev, generator=g)
+            c = torch.rand(BATCH, n, n, device=dev, generator=g) * 2 - 1
+            return a, b, c
+        return W.dense_batched(0, ids, n, n, n, "normal")
+
+    def bench_dense(n, mode, steps, warmup, sample_clocks):
+        a, b, c = dense_inputs(n)
+        out = torch.empty_like(c)
+        fn = lambda: ops.gemm(ctx, a, b, c, out, mode=mode)
+        sampler = ClockSampler(local) if sample_clocks and rank == 0 else None
+        ms, launches = timed(fn, steps, warmup)
+        clocks = sampler.stop() if sampler else None
+        ctx.check_device_status()
+        flops = 2.0 * BATCH * n * n * n
+        per_gpu = flops / ms / 1e9
+        del a, b, c, out
+        return ms, per_gpu, launches, clocks
+
+    def bench_dense_e2e(n, mode, steps):
+        """Host pinned buffers -> H2D -> GEMM -> D2H, all inside the timed region."""
+        ha = torch.empty(BATCH, n, n).pin_memory()
+        hb = torch.empty(BATCH, n, n).pin_memory()
+        hc = torch.empty(BATCH, n, n).pin_memory()
+        hy = torch.empty(BATCH, n, n).pin_memory()
+        for h in (ha, hb, hc):
+            h.normal_()
+        da, db, dc = (torch.empty(BATCH, n, n, device=dev) for _ in range(3))
+        dy = torch.empty(BATCH, n, n, device=dev)
+
+        def step():
+            da.copy_(ha, non_blocking=True)
+            db.copy_(hb, non_blocking=True)
+            dc.copy_(hc, non_blocking=True)
+            ops.gemm(ctx, da, db, dc, dy, mode=mode)
+            hy.copy_(dy, non_blocking=True)
+
+        ms, _ = timed(step, steps, 1)
+        nbytes = ha.numel() * 4
+        return ms, 2.0 * BATCH * n ** 3 / ms / 1e9, 3 * nbytes, nbytes
+
+    # --------------------------------------------------------------- sparse
+    def bench_spgemm(dist_name, steps, warmup):
+        M = N = 65536
+        rA, cA, vA = W.csr_random(0 + 2 * rank, M, N, 0.001, dist_name)
+        rB, cB, vB = W.csr_random(1, N, N, 0.001, dist_name)
+        A = ops.CsrMatrix.from_numpy(rA, cA, vA, M, N, dev)
+        B = ops.CsrMatrix.from_numpy(rB, cB, vB, N, N, dev)
+        res = {}
+        def fn():
+            res["C"] = ops.spgemm(ctx, A, B)
+        ms, launches = timed(fn, steps, warmup)
+        nnzC = res["C"].nnz
+        prods = int(W.csr_products(rA, cA, rB).sum())
+        nbytes = 8 * (cA.size + cB.size + nnzC) + 4 * 3 * (M + 1)
+        return {"workload": f"csr spgemm 65536^2 0.1% {dist_name}", "ms_per_step": ms,
+                "gflops_per_gpu": 2.0 * prods / ms / 1e6, "nnzC": nnzC, "products": prods,
+                "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6,
+                             "peak": pk["hbm_gbs"], "unit": "GB/s",
+                             "frac": nbytes / ms / 1e6 / pk["hbm_gbs"], "traffic": None,
+                             "peak_source": pk["source"]},
+                "gpu_launches": launches}
+
+    def bench_linear_bwd(steps, warmup):
+        rows, width = 8192, 4096
+        g = torch.Generator(device=dev); g.manual_seed(7 + rank)
+        dy = torch.randn(rows, width, device=dev, generator=g) * 0.02
+        x = torch.randn(rows, width, device=dev, generator=g) * 0.02
+        w = torch.randn(width, width, device=dev, generator=g) * 0.02
+        dx = torch.empty(rows, width, device=dev)
+        dw = torch.empty(width, width, device=dev)
+        db = torch.empty(width, device=dev)
+        def fn():
+            ops.gemm(ctx, dy, w, None, dx, trans_b=True)                    # dx = dy.W^T
+            ops.gemm(ctx, x, dy, None, dw, trans_a=True, colsum_out=db,     # dW = x^T.dy, dB
+                     colsum_scale=1.0 / rows)
+            if world > 1:
+                dist.all_reduce(dw)
+                dist.all_reduce(db)
+        ms, launches = timed(fn, steps, warmup)
+        flops = 2 * 2.0 * rows * width * width
+        return {"workload": "linear backward dY[8192x4096] X[8192x4096] W[4096x4096] per GPU, "
+                            "dW/dB allreduce inside" if world > 1 else
+                            "linear backward dY[8192x4096] X[8192x4096] W[4096x4096]",
+                "ms_per_step": ms, "tflops_per_gpu": flops / ms / 1e9, "gpu_launches": launches}
+
+    # ------------------------------------------------------------- headline
+    if args.workload in DENSE:
+        n, mode = DENSE[args.workload]
+        ms, per_gpu, launches, clocks = bench_dense(n, mode, args.steps, args.warmup, True)
+        value = per_gpu * world
+        tf32_peak = pk["bf16_tflops"] / 2.0
+        line = {
+            "metric": "batched dense GEMM throughput", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "tf32" if mode == 0 else "3xtf32 (fp32-accurate)", "data": "synthetic",
+            "config": {"workload": f"dense batched GEMM y=a.b+c, per GPU batch={BATCH} "
+                                   f"M=N=K={n}, fp32 in/out, a,b~N(0,1) c~U[-1,1)",
+                       "global_batch": BATCH * world, "parallelism": f"batch-sharded x{world}",
+                       "l2": "inputs (3 x %d MiB) larger than the 126 MB L2" % (BATCH * n * n * 4 >> 20)},
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": tf32_peak,
+                         "unit": "TFLOP/s", "frac": per_gpu / tf32_peak, "traffic": None,
+                         "peak_source": f"{pk['source']}: cuBLAS bf16 burst / 2 (TF32 runs at half "
+                                        "the bf16 rate)"},
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        e_ms, e_val, h2d, d2h = bench_dense_e2e(n, mode, max(2, min(args.steps, 5)))
+        line["e2e"] = {"value": e_val * world, "unit": "TFLOP/s", "ms_per_step": e_ms,
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    elif args.workload in ("spgemm", "spgemm_zipf"):
+        r = bench_spgemm("poisson" if args.workload == "spgemm" else "zipf", args.steps,
+                         args.warmup)
+        line = {"metric": "CSR SpGEMM throughput", "value": r["gflops_per_gpu"] * world,
+                "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": r["workload"], "parallelism": f"A row blocks x{world}, B replicated"},
+                "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]}
+    elif args.workload == "linear_bwd":
+        r = bench_linear_bwd(args.steps, args.warmup)
+        tf32_peak = pk["bf16_tflops"] / 2.0
+        line = {"metric": "Linear backward GEMM throughput", "value": r["tflops_per_gpu"] * world,
+                "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+                "config": {"workload": r["workload"]},
+                "roofline": {"bound": "tensor", "achieved": r["tflops_per_gpu"], "peak": tf32_peak,
+                             "unit": "TFLOP/s", "frac": r["tflops_per_gpu"] / tf32_peak,
+                             "traffic": None},
+                "gpu_launches": r["gpu_launches"]}
+    else:
+        raise SystemExit(f"unknown workload {args.workload}")
+
+    if not args.no_extras and args.workload == "dense_tf32":
+        extras = []
+        for name in ("dense_tf32x3", "dense4000_tf32"):
+            n, mode = DENSE[name]
+            ms, per_gpu, _, _ = bench_dense(n, mode, 5, 3, False)
+            extras.append({"workload": f"{name} batch={BATCH} n={n}", "ms_per_step": ms,
+                           "tflops_per_gpu": per_gpu})
+        extras.append(bench_linear_bwd(10, 3))
+        extras.append(bench_spgemm("poisson", 5, 3))
+        extras.append(bench_spgemm("zipf", 5, 3))
+        line["other_workloads"] = extras
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        n = DENSE.get(args.workload, (4096, 0))[0]
+        rows = 96
+        sec, kind, flops = cpu_gemm_sample(n, rows)
+        line["cpu_baseline"] = {
+            "value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": kind,
+            "sample": f"{rows} output rows of one {n}^3 batch, {sec:.1f} s; Sapphire's CPU GEMM "
+                      "is a single-threaded scalar loop"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -34,10 +34,12 @@ constexpr int UMMA_K = 8;                       // k per tcgen05.mma, kind::tf32
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 4;
 constexpr int CHUNK_BYTES = 32 * BLOCK_K * 4;   // one MN-major chunk: 32 k-rows x 128 B
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+constexpr int SPLIT_CHUNK_KB = 8;               // 3xTF32: 256 k per tensor-core accumulation chain
 
 struct KernelParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, num_kb;
+    int chunk_kb;                               // k-blocks per TMEM accumulation chain
     long long total_tiles;
     int a_batched, b_batched;                   // 0: batch stride 0, always read matrix 0
     const float* C; long long ldc, strideC;
@@ -52,8 +54,10 @@ struct SmemLayout {
     static constexpr int B_TILE_BYTES = BLOCK_N * BLOCK_K * 4;
     static constexpr int STAGE_BYTES = (A_TILE_BYTES + B_TILE_BYTES) * (SPLIT ? 2 : 1);
     static constexpr int TILES_BYTES = STAGE_BYTES * STAGES;
+    // accumulator buffers in TMEM (512 columns at most)
+    static constexpr int NUM_ACC = SPLIT ? 4 : 2;
     // barriers: full, empty, split_done per stage; tmem_full, tmem_empty per accumulator
-    static constexpr int BAR_BYTES = (3 * STAGES + 4) * 8 + 16;
+    static constexpr int BAR_BYTES = (3 * STAGES + 2 * NUM_ACC) * 8 + 16;
     static constexpr int TOTAL = TILES_BYTES + BAR_BYTES + 1024;   // + alignment slack
 };
 
@@ -97,6 +101,44 @@ __device__ __forceinline__ void split_tf32(float x, bool rounded, float& hi, flo
     lo = x - hi;
 }
 
+// One thread's 32 consecutive output columns of one row: D = (C + bias) + acc.
+__device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], float* drow,
+                                                const float* crow, const float* bias, int col0,
+                                                int N, bool vec_ok)
+{
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const int col = col0 + j;
+        if (vec_ok && col + 3 < N) {
+            float4 base = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (crow)
+                base = *reinterpret_cast<const float4*>(crow + col);
+            if (bias) {
+                base.x = base.x + __ldg(bias + col);
+                base.y = base.y + __ldg(bias + col + 1);
+                base.z = base.z + __ldg(bias + col + 2);
+                base.w = base.w + __ldg(bias + col + 3);
+            }
+            float4 o;
+            o.x = base.x + __uint_as_float(v[j]);
+            o.y = base.y + __uint_as_float(v[j + 1]);
+            o.z = base.z + __uint_as_float(v[j + 2]);
+            o.w = base.w + __uint_as_float(v[j + 3]);
+            *reinterpret_cast<float4*>(drow + col) = o;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (col + e < N) {
+                    float base = crow ? crow[col + e] : 0.f;
+                    if (bias)
+                        base = base + __ldg(bias + col + e);
+                    drow[col + e] = base + __uint_as_float(v[j + e]);
+                }
+            }
+        }
+    }
+}
+
 template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT>
 __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
@@ -105,7 +147,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
     using L = SmemLayout<BLOCK_N, STAGES, SPLIT>;
     constexpr int B_TILE_BYTES = L::B_TILE_BYTES;
     constexpr int HALF_STAGE = A_TILE_BYTES + B_TILE_BYTES;       // the hi (raw) tiles
-    constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;                    // 256 or 512: power of two
+    constexpr int NUM_ACC = L::NUM_ACC;
+    constexpr uint32_t TMEM_COLS = NUM_ACC * BLOCK_N;              // 256 or 512: power of two
+    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -114,8 +158,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* split_bar = empty_bar + STAGES;
     uint64_t* tmem_full = split_bar + STAGES;
-    uint64_t* tmem_empty = tmem_full + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    uint64_t* tmem_empty = tmem_full + NUM_ACC;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + NUM_ACC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -128,7 +172,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             ptx::mbar_init(&empty_bar[s], 1);
             ptx::mbar_init(&split_bar[s], 4);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NUM_ACC; ++i) {
             ptx::mbar_init(&tmem_full[i], 1);
             ptx::mbar_init(&tmem_empty[i], 4);
         }
@@ -204,55 +248,67 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             constexpr uint32_t B_KSTEP = B_MN ? 1024u : UMMA_K * 4u;
             constexpr uint32_t A_LBO = A_MN ? CHUNK_BYTES : 16u;
             constexpr uint32_t B_LBO = B_MN ? CHUNK_BYTES : 16u;
+            constexpr uint32_t A_SBO = A_MN ? 512u : 1024u;
+            constexpr uint32_t B_SBO = B_MN ? 512u : 1024u;
+            constexpr uint32_t A_LAY = A_MN ? ptx::LAYOUT_SW128_BASE32 : ptx::LAYOUT_SW128;
+            constexpr uint32_t B_LAY = B_MN ? ptx::LAYOUT_SW128_BASE32 : ptx::LAYOUT_SW128;
             int s = 0;
             uint32_t ph = 0;
             int acc = 0;
             uint32_t acc_ph = 0;
             bool ok = true;
             for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
-                if (!(ok = wait_bar(&tmem_empty[acc], acc_ph ^ 1u, ab, FAULT_MMA_WAIT_TMEM)))
-                    break;
-                ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
-                for (int kb = 0; kb < p.num_kb; ++kb) {
-                    uint64_t* ready = SPLIT ? &split_bar[s] : &full_bar[s];
-                    if (!(ok = wait_bar(ready, ph, ab, FAULT_MMA_WAIT_FULL)))
+                // One accumulator buffer per chunk of k-blocks.  In TF32 mode a
+                // tile is a single chunk; in 3xTF32 mode the chain of tensor-core
+                // accumulations is cut every SPLIT_CHUNK_KB k-blocks and the
+                // partial sums are added up in fp32 registers by the epilogue.
+                for (int kb0 = 0; ok && kb0 < p.num_kb; kb0 += p.chunk_kb) {
+                    if (!(ok = wait_bar(&tmem_empty[acc], acc_ph ^ 1u, ab, FAULT_MMA_WAIT_TMEM)))
                         break;
                     ptx::tc_fence_after_sync();
-                    const uint32_t sa = ptx::smem_u32(smem + s * L::STAGE_BYTES);
-                    const uint32_t sb = sa + A_TILE_BYTES;
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+                    const int kb1 = min(kb0 + p.chunk_kb, p.num_kb);
+                    for (int kb = kb0; kb < kb1; ++kb) {
+                        uint64_t* ready = SPLIT ? &split_bar[s] : &full_bar[s];
+                        if (!(ok = wait_bar(ready, ph, ab, FAULT_MMA_WAIT_FULL)))
+                            break;
+                        ptx::tc_fence_after_sync();
+                        const uint32_t sa = ptx::smem_u32(smem + s * L::STAGE_BYTES);
+                        const uint32_t sb = sa + A_TILE_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint64_t a_hi =
-                            ptx::make_smem_desc_sw128(sa + k * A_KSTEP, A_LBO, 1024u);
-                        const uint64_t b_hi =
-                            ptx::make_smem_desc_sw128(sb + k * B_KSTEP, B_LBO, 1024u);
-                        const uint32_t first = (kb > 0 || k > 0) ? 1u : 0u;
-                        if (SPLIT) {
-                            const uint64_t a_lo = ptx::make_smem_desc_sw128(
-                                sa + HALF_STAGE + k * A_KSTEP, A_LBO, 1024u);
-                            const uint64_t b_lo = ptx::make_smem_desc_sw128(
-                                sb + HALF_STAGE + k * B_KSTEP, B_LBO, 1024u);
-                            // small terms first
-                            ptx::mma_tf32(d_tmem, a_lo, b_hi, idesc, first);
-                            ptx::mma_tf32(d_tmem, a_hi, b_lo, idesc, 1u);
-                            ptx::mma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
-                        } else {
-                            ptx::mma_tf32(d_tmem, a_hi, b_hi, idesc, first);
+                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                            const uint64_t a_hi =
+                                ptx::make_smem_desc(sa + k * A_KSTEP, A_LBO, A_SBO, A_LAY);
+                            const uint64_t b_hi =
+                                ptx::make_smem_desc(sb + k * B_KSTEP, B_LBO, B_SBO, B_LAY);
+                            const uint32_t first = (kb > kb0 || k > 0) ? 1u : 0u;
+                            if (SPLIT) {
+                                const uint64_t a_lo = ptx::make_smem_desc(
+                                    sa + HALF_STAGE + k * A_KSTEP, A_LBO, A_SBO, A_LAY);
+                                const uint64_t b_lo = ptx::make_smem_desc(
+                                    sb + HALF_STAGE + k * B_KSTEP, B_LBO, B_SBO, B_LAY);
+                                // small terms first
+                                ptx::mma_tf32(d_tmem, a_lo, b_hi, idesc, first);
+                                ptx::mma_tf32(d_tmem, a_hi, b_lo, idesc, 1u);
+                                ptx::mma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
+                            } else {
+                                ptx::mma_tf32(d_tmem, a_hi, b_hi, idesc, first);
+                            }
+                        }
+                        ptx::mma_commit(&empty_bar[s]);   // stage free once these MMAs retire
+                        if (++s == STAGES) {
+                            s = 0;
+                            ph ^= 1u;
                         }
                     }
-                    ptx::mma_commit(&empty_bar[s]);       // stage free once these MMAs retire
-                    if (++s == STAGES) {
-                        s = 0;
-                        ph ^= 1u;
+                    if (!ok)
+                        break;
+                    ptx::mma_commit(&tmem_full[acc]);     // this chunk's accumulator is complete
+                    if (++acc == NUM_ACC) {
+                        acc = 0;
+                        acc_ph ^= 1u;
                     }
                 }
-                if (!ok)
-                    break;
-                ptx::mma_commit(&tmem_full[acc]);         // accumulator complete
-                acc ^= 1;
-                if (acc == 0)
-                    acc_ph ^= 1u;
             }
         }
     } else if (warp < 6) {
@@ -266,69 +322,89 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                             (p.C == nullptr ||
                              (((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
                               ((p.strideC & 3) == 0)));
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
         for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
             const int b = static_cast<int>(t / tiles_per_batch);
             const int r = static_cast<int>(t % tiles_per_batch);
             const int m0 = (r % p.tiles_m) * BLOCK_M;
             const int n0 = (r / p.tiles_m) * BLOCK_N;
-            if (!(ok = wait_bar(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
-                break;
-            ptx::tc_fence_after_sync();
             const int row = m0 + q * 32 + lane;
             float* drow = p.D + b * p.strideD + static_cast<long long>(row) * p.ldd;
             const float* crow =
                 p.C ? p.C + b * p.strideC + static_cast<long long>(row) * p.ldc : nullptr;
+            if constexpr (!SPLIT) {
+                // one chunk per tile: straight from TMEM to global memory
+                if (!(ok = wait_bar(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
+                    break;
+                ptx::tc_fence_after_sync();
 #pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 32; ++c) {
-                const int col0 = n0 + c * 32;
-                if (col0 >= p.N)
-                    break;                                 // uniform across the warp
-                uint32_t v[32];
-                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                       static_cast<uint32_t>(acc * BLOCK_N + c * 32),
-                                   v);
-                ptx::tmem_ld_wait();
+                for (int c = 0; c < BLOCK_N / 32; ++c) {
+                    const int col0 = n0 + c * 32;
+                    if (col0 >= p.N)
+                        break;                             // uniform across the warp
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(lane_base + static_cast<uint32_t>(acc * BLOCK_N + c * 32), v);
+                    ptx::tmem_ld_wait();
+                    if (row < p.M)
+                        store_row_chunk(v, drow, crow, p.bias, col0, p.N, vec_ok);
+                }
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(&tmem_empty[acc]);
+                if (++acc == NUM_ACC) {
+                    acc = 0;
+                    acc_ph ^= 1u;
+                }
+            } else {
+                // 3xTF32: the tensor core cuts every fp32 accumulation short
+                // (no round-to-nearest), which over thousands of k steps adds up
+                // to ~1e-5 relative.  Each chunk of k-blocks therefore gets a
+                // fresh TMEM accumulator and the chunks are summed here with
+                // round-to-nearest adds.
+                float sum[BLOCK_N];
+#pragma unroll
+                for (int j = 0; j < BLOCK_N; ++j)
+                    sum[j] = 0.0f;
+                for (int kb0 = 0; ok && kb0 < p.num_kb; kb0 += p.chunk_kb) {
+                    if (!(ok = wait_bar(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
+                        break;
+                    ptx::tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < BLOCK_N / 32; ++c) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(lane_base + static_cast<uint32_t>(acc * BLOCK_N + c * 32),
+                                           v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            sum[c * 32 + j] = __fadd_rn(sum[c * 32 + j], __uint_as_float(v[j]));
+                    }
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0)
+                        ptx::mbar_arrive(&tmem_empty[acc]);
+                    if (++acc == NUM_ACC) {
+                        acc = 0;
+                        acc_ph ^= 1u;
+                    }
+                }
+                if (!ok)
+                    break;
                 if (row < p.M) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const int col = col0 + j;
-                        if (vec_ok && col + 3 < p.N) {
-                            float4 base = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (crow)
-                                base = *reinterpret_cast<const float4*>(crow + col);
-                            if (p.bias) {
-                                base.x = base.x + __ldg(p.bias + col);
-                                base.y = base.y + __ldg(p.bias + col + 1);
-                                base.z = base.z + __ldg(p.bias + col + 2);
-                                base.w = base.w + __ldg(p.bias + col + 3);
-                            }
-                            float4 o;
-                            o.x = base.x + __uint_as_float(v[j]);
-                            o.y = base.y + __uint_as_float(v[j + 1]);
-                            o.z = base.z + __uint_as_float(v[j + 2]);
-                            o.w = base.w + __uint_as_float(v[j + 3]);
-                            *reinterpret_cast<float4*>(drow + col) = o;
-                        } else {
+                    for (int c = 0; c < BLOCK_N / 32; ++c) {
+                        const int col0 = n0 + c * 32;
+                        if (col0 < p.N) {
+                            uint32_t v[32];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                if (col + e < p.N) {
-                                    float base = crow ? crow[col + e] : 0.f;
-                                    if (p.bias)
-                                        base = base + __ldg(p.bias + col + e);
-                                    drow[col + e] = base + __uint_as_float(v[j + e]);
-                                }
-                            }
+                            for (int j = 0; j < 32; ++j)
+                                v[j] = __float_as_uint(sum[c * 32 + j]);
+                            store_row_chunk(v, drow, crow, p.bias, col0, p.N, vec_ok);
                         }
                     }
                 }
             }
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0)
-                ptx::mbar_arrive(&tmem_empty[acc]);
-            acc ^= 1;
-            if (acc == 0)
-                acc_ph ^= 1u;
         }
     } else if (SPLIT) {
         // --------------------------------------- hi/lo split (3xTF32 mode)
@@ -388,9 +464,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 // Tensor map over a stack of row-major matrices: dim0 = contiguous extent,
 // dim1 = rows, dim2 = batch; box = 32 contiguous elements x box_rows x 1,
-// 128-byte swizzle, out-of-range elements read as zero.
+// out-of-range elements read as zero.  K-major tiles use the plain 128-byte
+// swizzle; MN-major tiles the 128-byte swizzle with a 32-byte atom, the only
+// MN-major layout the tensor core reads for 32-bit operands.
 int make_map(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig, int64_t rows,
-             int64_t ld, int64_t batch, int64_t batch_stride, int box_rows)
+             int64_t ld, int64_t batch, int64_t batch_stride, int box_rows, bool mn_major)
 {
     EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
     if (!enc)
@@ -403,7 +481,8 @@ int make_map(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig
     cuuint32_t box[3] = {32, static_cast<cuuint32_t>(box_rows), 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
 }
@@ -426,15 +505,15 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     CUtensorMap mapA, mapB;
     int rc;
     if (A_MN)   // stored [K, M]
-        rc = make_map(ctx, &mapA, g.A, g.M, g.K, g.lda, g.batch, g.strideA, BLOCK_K);
+        rc = make_map(ctx, &mapA, g.A, g.M, g.K, g.lda, g.batch, g.strideA, BLOCK_K, true);
     else        // stored [M, K]
-        rc = make_map(ctx, &mapA, g.A, g.K, g.M, g.lda, g.batch, g.strideA, BLOCK_M);
+        rc = make_map(ctx, &mapA, g.A, g.K, g.M, g.lda, g.batch, g.strideA, BLOCK_M, false);
     if (rc)
         return rc;
     if (B_MN)   // stored [K, N]
-        rc = make_map(ctx, &mapB, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, BLOCK_K);
+        rc = make_map(ctx, &mapB, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, BLOCK_K, true);
     else        // stored [N, K]
-        rc = make_map(ctx, &mapB, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, BLOCK_N);
+        rc = make_map(ctx, &mapB, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, BLOCK_N, false);
     if (rc)
         return rc;
 
@@ -446,6 +525,7 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.tiles_m = static_cast<int>((g.M + BLOCK_M - 1) / BLOCK_M);
     p.tiles_n = static_cast<int>((g.N + BLOCK_N - 1) / BLOCK_N);
     p.num_kb = static_cast<int>((g.K + BLOCK_K - 1) / BLOCK_K);
+    p.chunk_kb = SPLIT ? SPLIT_CHUNK_KB : (p.num_kb > 0 ? p.num_kb : 1);
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * g.batch;
     p.a_batched = g.strideA != 0;
     p.b_batched = g.strideB != 0;

@@ -173,22 +173,28 @@ __device__ __forceinline__ void tmem_ld_wait()
 }
 
 // ------------------------------------------------------------ descriptors
-// Shared-memory matrix descriptor, 128-byte swizzle.  Offsets are in bytes
-// and are stored without their 4 low bits.
-//   K-major tile  (row = one M/N index, 128 B of K per row):
+// Shared-memory matrix descriptor.  Offsets are in bytes and are stored
+// without their 4 low bits.
+//   K-major tile  (row = one M/N index, 128 B = 32 fp32 of K per row), layout
+//       SWIZZLE_128B (16-byte units XOR row % 8, pattern of 8 rows = 1024 B):
 //       lbo unused (1), sbo = bytes between groups of 8 rows (1024)
-//   MN-major tile (row = one K index, 128 B of M/N per row):
+//   MN-major tile (row = one K index, 128 B = 32 fp32 of M/N per row).  For
+//       32-bit operands the tensor core takes only the 128-byte swizzle with a
+//       32-byte atom (32-byte units XOR row % 4, pattern of 4 rows = 512 B):
 //       lbo = bytes between 32-element chunks along M/N,
-//       sbo = bytes between groups of 8 K rows (1024)
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                         uint32_t sbo_bytes)
+//       sbo = bytes between groups of 4 K rows (512 when rows are contiguous)
+constexpr uint32_t LAYOUT_SW128 = 2;          // SWIZZLE_128B
+constexpr uint32_t LAYOUT_SW128_BASE32 = 1;   // SWIZZLE_128B, 32-byte atom
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes, uint32_t layout)
 {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);          // bits [0,14)
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;     // bits [16,30)
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;     // bits [32,46)
     d |= static_cast<uint64_t>(1) << 46;                             // descriptor version (sm_100)
-    d |= static_cast<uint64_t>(2) << 61;                             // SWIZZLE_128B
+    d |= static_cast<uint64_t>(layout) << 61;                        // bits [61,64)
     return d;
 }
 

@@ -1,0 +1,281 @@
+"""GPU parity tests of the dense path, through the C ABI, against the CPU
+oracle (bit-exact restatement of Sapphire's CPU loop) on the same seeded inputs.
+
+Tolerances (relative Frobenius error against Sapphire's own CPU result):
+    TF32 mode    <= 2e-3
+    TF32X3 mode  <= 1e-5
+    SIMT path    bit-exact
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from sapphire_b200 import _lib as L
+from sapphire_b200 import ops
+from sapphire_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+TOL = {L.MODE_TF32: 2e-3, L.MODE_TF32X3: 1e-5}
+DEV = "cuda:0"
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "dense_golden.npz"))
+
+
+def rel_fro(got, want):
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    return np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(DEV)
+
+
+def bits(x):
+    return np.ascontiguousarray(x, np.float32).view(np.uint32)
+
+
+# ------------------------------------------------------------------ config 1
+@pytest.mark.parametrize("mode", [L.MODE_TF32, L.MODE_TF32X3])
+@pytest.mark.parametrize("pad", [0, 8])
+def test_config1_4x256(ctx, oracle, mode, pad):
+    """batch 4, M=N=K=256, U[-1,1) seed 0, y <- c + a.b, every element compared;
+    ld = cols (Sapphire's layout) and ld = cols + 8 (padded rows)."""
+    a, b, c = W.dense_batched(0, range(4), 256, 256, 256, "uniform")
+    want = oracle.gemm(c, a, b)
+    ld = 256 + pad
+    ta = torch.zeros(4, 256, ld, device=DEV); ta[:, :, :256] = dev(a)
+    tb = torch.zeros(4, 256, ld, device=DEV); tb[:, :, :256] = dev(b)
+    ty = torch.zeros(4, 256, ld, device=DEV); ty[:, :, :256] = dev(c)
+    y = ty[:, :, :256]
+    ops.gemm(ctx, ta[:, :, :256], tb[:, :, :256], y, y, mode=mode)       # in place: C aliases D
+    ctx.check_device_status()
+    assert ctx.last_path() == L.PATH_TCGEN05
+    assert rel_fro(y.cpu().numpy(), want) <= TOL[mode]
+    if pad:
+        assert float(ty[:, :, 256:].abs().max()) == 0.0                  # padding untouched
+
+
+def test_config1_matches_reference_fixture(ctx):
+    """Against the fixture written by the reference's own CPU build."""
+    a, b, c = W.dense_batched(0, range(4), 256, 256, 256, "uniform")
+    y = ops.gemm(ctx, dev(a), dev(b), dev(c), mode=L.MODE_TF32X3).cpu().numpy()
+    assert rel_fro(y.reshape(-1)[::16], GOLD["c1_sample"]) <= 1e-5
+    assert abs(y.astype(np.float64).sum() - GOLD["c1_sum64"][0]) <= 1e-5 * np.abs(y).sum()
+
+
+# ------------------------------------------------------------ SIMT: bit-exact
+@pytest.mark.parametrize("idx", range(8))
+def test_simt_bit_exact_small_shapes(ctx, idx):
+    """The reference's Gemm1 family (M, N, K in [1,100], N(10,5) inputs,
+    GemmTest.cpp:20-84): the CUDA-core kernel reproduces the CPU loop bit for bit."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "make_golden", os.path.join(os.path.dirname(__file__), "golden", "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    a, b, c = mod.small_case(idx)
+    y = ops.gemm(ctx, dev(a), dev(b), dev(c), path=L.PATH_SIMT).cpu().numpy()
+    assert ctx.last_path() == L.PATH_SIMT
+    assert np.array_equal(bits(y), bits(GOLD[f"small{idx}"]))
+
+
+def test_auto_path_falls_to_simt_for_tma_hostile_rows(ctx, oracle):
+    """[64,256].[256,10]: a 40-byte row pitch breaks TMA's 16-byte rule."""
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((1, 64, 256)).astype(np.float32)
+    b = rng.standard_normal((1, 256, 10)).astype(np.float32)
+    c = np.zeros((1, 64, 10), np.float32)
+    y = ops.gemm(ctx, dev(a), dev(b), dev(c)).cpu().numpy()
+    assert ctx.last_path() == L.PATH_SIMT
+    assert np.array_equal(bits(y), bits(oracle.gemm(c, a, b)))
+    with pytest.raises(L.Sb200Error) as e:
+        ops.gemm(ctx, dev(a), dev(b), dev(c), path=L.PATH_TCGEN05)
+    assert e.value.status == L.ERR_UNSUPPORTED
+
+
+def test_k_zero_and_empty(ctx):
+    c = torch.randn(2, 5, 8, device=DEV)
+    a = torch.empty(2, 5, 0, device=DEV)
+    b = torch.empty(2, 0, 8, device=DEV)
+    bias = torch.randn(8, device=DEV)
+    y = ops.gemm(ctx, a, b, c, bias=bias)
+    assert torch.equal(y, c + bias)
+    # M == 0 is a no-op
+    ops.gemm(ctx, torch.empty(0, 4, device=DEV), torch.empty(4, 8, device=DEV),
+             out=torch.empty(0, 8, device=DEV))
+
+
+# ------------------------------------------- layouts, tails, strides, epilogue
+@pytest.mark.parametrize("mode", [L.MODE_TF32, L.MODE_TF32X3])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K,batch", [(128, 128, 32, 1), (200, 328, 100, 2), (1, 4, 4, 1),
+                                         (130, 260, 36, 3), (384, 512, 1000, 1)])
+def test_layouts_and_tails(ctx, oracle, mode, ta, tb, M, N, K, batch):
+    rng = np.random.default_rng(M * 7 + N * 3 + K + ta * 2 + tb)
+    a = rng.standard_normal((batch, K, M) if ta else (batch, M, K)).astype(np.float32)
+    b = rng.standard_normal((batch, N, K) if tb else (batch, K, N)).astype(np.float32)
+    c = rng.uniform(-1, 1, (batch, M, N)).astype(np.float32)
+    want = oracle.gemm_ex(ta, tb, M, N, K, a, a.shape[2], a.shape[1] * a.shape[2],
+                          b, b.shape[2], b.shape[1] * b.shape[2], c, N, M * N, N, M * N,
+                          None, batch, batch * M * N).reshape(batch, M, N)
+    y = ops.gemm(ctx, dev(a), dev(b), dev(c), mode=mode, trans_a=bool(ta), trans_b=bool(tb),
+                 path=L.PATH_TCGEN05)
+    ctx.check_device_status()
+    assert rel_fro(y.cpu().numpy(), want) <= TOL[mode]
+
+
+def test_long_k_accumulation_tf32x3(ctx, oracle):
+    """K = 4096: the split mode must stay fp32-accurate over a long reduction."""
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((1, 128, 4096)).astype(np.float32)
+    b = rng.standard_normal((1, 4096, 256)).astype(np.float32)
+    c = rng.uniform(-1, 1, (1, 128, 256)).astype(np.float32)
+    want = oracle.gemm(c, a, b)
+    y = ops.gemm(ctx, dev(a), dev(b), dev(c), mode=L.MODE_TF32X3).cpu().numpy()
+    assert rel_fro(y, want) <= 1e-5
+    y64 = c.astype(np.float64) + a.astype(np.float64) @ b.astype(np.float64)
+    assert rel_fro(y, y64) <= 1e-5
+
+
+def test_broadcast_strides(ctx, oracle):
+    """stride 0 re-reads one matrix for every batch (GemmMatrixWiseBroadcast)."""
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((1, 64, 96)).astype(np.float32)
+    b = rng.standard_normal((6, 96, 128)).astype(np.float32)
+    c = rng.standard_normal((6, 64, 128)).astype(np.float32)
+    want = oracle.gemm(c, np.repeat(a, 6, 0), b)
+    y = ops.gemm(ctx, dev(a), dev(b), dev(c), mode=L.MODE_TF32X3, path=L.PATH_TCGEN05)
+    assert rel_fro(y.cpu().numpy(), want) <= 1e-5
+    a2 = rng.standard_normal((6, 64, 96)).astype(np.float32)
+    b2 = rng.standard_normal((1, 96, 128)).astype(np.float32)
+    want = oracle.gemm(c, a2, np.repeat(b2, 6, 0))
+    y = ops.gemm(ctx, dev(a2), dev(b2), dev(c), mode=L.MODE_TF32X3, path=L.PATH_TCGEN05)
+    assert rel_fro(y.cpu().numpy(), want) <= 1e-5
+
+
+@pytest.mark.parametrize("path", [L.PATH_TCGEN05, L.PATH_SIMT])
+def test_bias_epilogue_is_linear_forward(ctx, oracle, path):
+    """y = bias + x.W with W stored [in, out] (Linear.cpp:134-136)."""
+    rng = np.random.default_rng(6)
+    x = rng.uniform(0, 1, (64, 784)).astype(np.float32)
+    w = rng.uniform(-0.1, 0.1, (784, 512)).astype(np.float32)
+    bias = rng.uniform(-1, 1, 512).astype(np.float32)
+    want = oracle.gemm_ex(0, 0, 64, 512, 784, x, 784, 0, w, 512, 0, None, 512, 0, 512, 0, bias, 1,
+                          64 * 512).reshape(64, 512)
+    y = ops.gemm(ctx, dev(x), dev(w), bias=dev(bias), mode=L.MODE_TF32X3, path=path).cpu().numpy()
+    if path == L.PATH_SIMT:
+        assert np.array_equal(bits(y), bits(want))
+    else:
+        assert rel_fro(y, want) <= 1e-5
+
+
+@pytest.mark.parametrize("mode", [L.MODE_TF32, L.MODE_TF32X3])
+def test_linear_backward_gemms_with_fused_bias_grad(ctx, oracle, mode):
+    """dx = dy.W^T, dW = x^T.dy, dB = colsum(dy)/B with transposes done by
+    descriptors (LinearBackward.cpp:27-99 does Transpose + Gemm + ones-Gemm)."""
+    rng = np.random.default_rng(8)
+    B, I, Oo = 256, 192, 320
+    dy = (rng.standard_normal((B, Oo)) * 0.02).astype(np.float32)
+    x = (rng.standard_normal((B, I)) * 0.02).astype(np.float32)
+    w = (rng.standard_normal((I, Oo)) * 0.02).astype(np.float32)
+    z = np.zeros
+    want_dx = oracle.gemm(z((1, B, I), np.float32), dy[None], oracle.transpose(w)[None])[0]
+    want_dw = oracle.gemm(z((1, I, Oo), np.float32), oracle.transpose(x)[None], dy[None])[0]
+    want_db = oracle.colsum(dy, 1.0 / B)
+    dx = ops.gemm(ctx, dev(dy), dev(w), trans_b=True, mode=mode)
+    db = torch.empty(Oo, device=DEV)
+    dw = ops.gemm(ctx, dev(x), dev(dy), trans_a=True, mode=mode, colsum_out=db,
+                  colsum_scale=1.0 / B)
+    ctx.check_device_status()
+    assert rel_fro(dx.cpu().numpy(), want_dx) <= TOL[mode]
+    assert rel_fro(dw.cpu().numpy(), want_dw) <= TOL[mode]
+    assert rel_fro(db.cpu().numpy(), want_db) <= 1e-5
+
+
+# ------------------------------------------------- full-size property checks
+@pytest.mark.parametrize("n", [4096, 4000])
+def test_config3_full_size_row_sample_and_linearity(ctx, oracle, n):
+    """8 x n^3 is an hour of scalar CPU work, so at full size: (1) a sample of
+    output rows of two batches against the CPU loop, (2) linearity
+    gemm(a, b, c) - gemm(a, b, 0) == c, (3) every batch of a batched call equals
+    the same matrices run alone."""
+    batch = 8
+    ids = [0, 7]
+    a2, b2, c2 = W.dense_batched(0, ids, n, n, n, "normal")
+    ta = torch.randn(batch, n, n, device=DEV)
+    tb = torch.randn(batch, n, n, device=DEV)
+    tc = torch.rand(batch, n, n, device=DEV) * 2 - 1
+    for j, bi in enumerate(ids):
+        ta[bi] = dev(a2[j]); tb[bi] = dev(b2[j]); tc[bi] = dev(c2[j])
+    rows = [0, 1, 127, 128, n // 2 + 3, n - 1]
+    for mode in (L.MODE_TF32, L.MODE_TF32X3):
+        y = ops.gemm(ctx, ta, tb, tc, mode=mode)
+        ctx.check_device_status()
+        for j, bi in enumerate(ids):
+            want = oracle.gemm(c2[j][rows][None], a2[j][rows][None], b2[j][None])[0]
+            assert rel_fro(y[bi][rows].cpu().numpy(), want) <= TOL[mode]
+        y0 = ops.gemm(ctx, ta, tb, None, mode=mode)
+        assert float((y - y0 - tc).abs().max()) <= 1e-3
+        alone = ops.gemm(ctx, ta[7], tb[7], tc[7], mode=mode)
+        assert torch.equal(alone, y[7])
+        del y, y0, alone
+
+
+# ------------------------------------------------ Sapphire-signature shims
+def test_compat_dense_gemm_signature(ctx, oracle):
+    """Sapphire::Compute::Dense::Cuda::Gemm(totalSize, out, A, B, M, N, K, deviceId)."""
+    a, b, c = W.dense_batched(3, range(3), 64, 48, 32, "uniform")
+    out, ta, tb = dev(c), dev(a), dev(b)
+    rc = L.lib().sb200_compat_dense_gemm(out.numel(), out.data_ptr(), ta.data_ptr(), tb.data_ptr(),
+                                         64, 48, 32, 0)
+    assert rc == L.OK
+    assert rel_fro(out.cpu().numpy(), oracle.gemm(c, a, b)) <= 2e-3
+
+
+@pytest.mark.parametrize("ys,as_,bs", [
+    ([3, 4, 4, 8], [3, 1, 4, 12], [3, 4, 12, 8]),          # [b,1,M,K].[b,M,K,N]
+    ([4, 4, 8], [4, 12], [4, 12, 8]),                      # [M,K].[M,K,N]
+    ([5, 4, 4, 8], [4, 12], [5, 4, 12, 8]),                # [M,K].[N,M,K,N]
+])
+def test_compat_compute_gemm_broadcast_families(ctx, ys, as_, bs):
+    """The reference's BroadcastTest families (BroadcastTest.cpp:20-202)."""
+    import ctypes as C
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal(as_).astype(np.float32)
+    b = rng.standard_normal(bs).astype(np.float32)
+    y0 = rng.standard_normal(ys).astype(np.float32)
+    ty, ta, tb = dev(y0), dev(a), dev(b)
+    arr = lambda s: (C.c_int * len(s))(*s)
+    L.lib().sb200_compat_set_mode(L.MODE_TF32X3)
+    rc = L.lib().sb200_compat_compute_gemm(arr(ys), len(ys), ty.data_ptr(), arr(as_), len(as_),
+                                           ta.data_ptr(), arr(bs), len(bs), tb.data_ptr(), 0)
+    L.lib().sb200_compat_set_mode(L.MODE_TF32)
+    assert rc == L.OK
+    want = y0.astype(np.float64) + np.matmul(a.astype(np.float64), b.astype(np.float64))
+    assert rel_fro(ty.cpu().numpy(), want) <= 1e-5
+
+
+def test_invalid_arguments(ctx):
+    a = torch.zeros(4, 8, device=DEV)
+    b = torch.zeros(8, 4, device=DEV)
+    out = torch.zeros(4, 4, device=DEV)
+    lib = L.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    def call(**kw):
+        args = dict(mode=0, path=0, ta=0, tb=0, M=4, N=4, K=8, lda=8, ldb=4, ldd=4, batch=1)
+        args.update(kw)
+        return lib.sb200_gemm_batched(ctx.handle, args["mode"], args["path"], args["ta"], args["tb"],
+                                      args["M"], args["N"], args["K"], a.data_ptr(), args["lda"], 0,
+                                      b.data_ptr(), args["ldb"], 0, None, 4, 0, out.data_ptr(),
+                                      args["ldd"], 0, None, None, 1.0, args["batch"], st)
+    assert call() == L.OK
+    assert call(lda=7) == L.ERR_INVALID_ARG
+    assert call(ldb=3) == L.ERR_INVALID_ARG
+    assert call(ldd=3) == L.ERR_INVALID_ARG
+    assert call(mode=5) == L.ERR_INVALID_ARG
+    assert call(M=-1) == L.ERR_INVALID_ARG
+    assert call(batch=2) == L.ERR_INVALID_ARG          # output batches would overlap (stride 0)
+    torch.cuda.synchronize()

@@ -1,0 +1,125 @@
+"""GPU parity tests of the CSR sparse GEMM through the C ABI.
+
+ROW and COL must equal the CPU oracle's bit for bit; values within 1e-5
+(relative to the largest magnitude of the row set, accumulation order on the
+GPU is not fixed).  The oracle is a restatement: the reference ships no sparse
+GEMM, so reference parity for this path is unpinned.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from sapphire_b200 import _lib as L
+from sapphire_b200 import ops
+from sapphire_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_case(ctx, oracle, M, K, N, seedA, seedB, dens, dist, cap=4096, fn=None):
+    rA, cA, vA = W.csr_random(seedA, M, K, dens, dist, zipf_cap=cap)
+    rB, cB, vB = W.csr_random(seedB, K, N, dens, dist, zipf_cap=cap)
+    A = ops.CsrMatrix.from_numpy(rA, cA, vA, M, K, DEV)
+    B = ops.CsrMatrix.from_numpy(rB, cB, vB, K, N, DEV)
+    Cm = (fn or ops.spgemm)(ctx, A, B)
+    torch.cuda.synchronize()
+    rc, cc, vc = Cm.to_numpy()
+    orc, occ, ovc, _ = oracle.spgemm(rA, cA, vA, rB, cB, vB, M, N)
+    assert np.array_equal(rc, orc), "ROW differs"
+    assert np.array_equal(cc, occ), "COL differs"
+    if ovc.size:
+        assert np.abs(vc - ovc).max() <= 1e-5 * max(np.abs(ovc).max(), 1.0)
+        assert not np.any(ovc == 0.0)        # no exact cancellation: either zero policy agrees
+    return Cm
+
+
+@pytest.mark.parametrize("M,K,N,dens,dist,cap", [
+    (64, 64, 64, 0.05, "poisson", 0),            # tiny rows only (<= 32 products)
+    (300, 200, 500, 0.02, "poisson", 0),         # rectangular, ragged N (not a multiple of 32)
+    (2048, 2048, 2048, 0.01, "poisson", 0),      # bitmap rows
+    (4096, 4096, 4096, None, "zipf", 512),       # mixed bins
+    (8192, 8192, 8192, None, "zipf", 4096),      # heavy rows: output wider than the shared buffer
+    (1000, 1000, 70000, 0.0005, "poisson", 0),   # wide N: bitmap larger than 2048 words
+])
+def test_spgemm_matches_oracle(ctx, oracle, M, K, N, dens, dist, cap):
+    run_case(ctx, oracle, M, K, N, 0, 1, dens, dist, cap or 4096)
+
+
+def test_spgemm_callee_allocated_output(ctx, oracle):
+    """The drop-in call: the library allocates C, the caller frees it."""
+    run_case(ctx, oracle, 1500, 1500, 1500, 2, 3, 0.01, "poisson", fn=ops.spgemm_callee_alloc)
+
+
+def test_spgemm_through_sapphire_signature(ctx, oracle):
+    """Sparse::Cuda::Gemm(hostOutput, cudaOutput, cudaA, cudaB, m, n, numMatrices, ...)."""
+    def via_shim(ctx_, A, B):
+        a, b, c = A.as_struct(), B.as_struct(), L.Csr()
+        assert L.lib().sb200_compat_sparse_gemm(C.byref(a), C.byref(b), C.byref(c), 0) == L.OK
+        n = int(c.NNZ)
+        row = torch.empty(A.M + 1, dtype=torch.int32, device=DEV)
+        col = torch.empty(max(n, 1), dtype=torch.int32, device=DEV)
+        val = torch.empty(max(n, 1), dtype=torch.float32, device=DEV)
+        st = torch.cuda.current_stream().cuda_stream
+        assert L.lib().sb200_csr_copy_out(C.byref(c), row.data_ptr(), col.data_ptr(),
+                                          val.data_ptr(), 0, st) == L.OK
+        L.lib().sb200_csr_free(C.byref(c))
+        return ops.CsrMatrix(row, col[:n], val[:n], A.M, B.N)
+    run_case(ctx, oracle, 700, 700, 700, 4, 5, 0.02, "poisson", fn=via_shim)
+
+
+def test_spgemm_empty_and_degenerate(ctx, oracle):
+    # all-empty A
+    M = N = 128
+    rowA = np.zeros(M + 1, np.uint32)
+    A = ops.CsrMatrix.from_numpy(rowA, np.zeros(0, np.uint32), np.zeros(0, np.float32), M, N, DEV)
+    rB, cB, vB = W.csr_random(1, N, N, 0.05)
+    B = ops.CsrMatrix.from_numpy(rB, cB, vB, N, N, DEV)
+    Cm = ops.spgemm(ctx, A, B)
+    assert Cm.nnz == 0 and int(Cm.row.abs().sum()) == 0
+    # identity x B == B
+    eye = ops.CsrMatrix.from_numpy(np.arange(N + 1, dtype=np.uint32), np.arange(N, dtype=np.uint32),
+                                   np.ones(N, np.float32), N, N, DEV)
+    Cm = ops.spgemm(ctx, eye, B)
+    r, c, v = Cm.to_numpy()
+    assert np.array_equal(r, rB) and np.array_equal(c, cB) and np.array_equal(v, vB)
+    # shape mismatch is rejected
+    bad = ops.CsrMatrix.from_numpy(np.zeros(65, np.uint32), np.zeros(0, np.uint32),
+                                   np.zeros(0, np.float32), 64, 64, DEV)
+    with pytest.raises(L.Sb200Error) as e:
+        ops.spgemm(ctx, A, bad)
+    assert e.value.status == L.ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("dist", ["poisson", "zipf"])
+def test_config5_full_size_properties(ctx, dist):
+    """65536 x 65536, 0.1 % density (and the Zipf variant): ROW monotone and
+    consistent with NNZ, COL strictly ascending inside rows, and the checksum
+    C.1 == A.(B.1) in float64."""
+    import scipy.sparse as sp
+    M = N = 65536
+    rA, cA, vA = W.csr_random(0, M, N, 0.001, dist)
+    rB, cB, vB = W.csr_random(1, N, N, 0.001, dist)
+    A = ops.CsrMatrix.from_numpy(rA, cA, vA, M, N, DEV)
+    B = ops.CsrMatrix.from_numpy(rB, cB, vB, N, N, DEV)
+    Cm = ops.spgemm(ctx, A, B)
+    torch.cuda.synchronize()
+    row = Cm.row.long()
+    assert int(row[0]) == 0 and int(row[-1]) == Cm.nnz
+    assert bool((row[1:] >= row[:-1]).all())
+    col = Cm.col.long()
+    asc = col[1:] > col[:-1]
+    starts = torch.zeros(Cm.nnz, dtype=torch.bool, device=DEV)
+    inner = row[1:-1]
+    starts[inner[inner < Cm.nnz]] = True
+    assert bool((asc | starts[1:]).all())
+    assert int(col.max()) < N and int(col.min()) >= 0
+    rowsum = torch.zeros(M, dtype=torch.float64, device=DEV)
+    ridx = torch.repeat_interleave(torch.arange(M, device=DEV), row[1:] - row[:-1])
+    rowsum.index_add_(0, ridx, Cm.val.double())
+    As = sp.csr_matrix((vA.astype(np.float64), cA, rA), shape=(M, N))
+    Bs = sp.csr_matrix((vB.astype(np.float64), cB, rB), shape=(N, N))
+    want = As @ (Bs @ np.ones(N))
+    assert np.abs(rowsum.cpu().numpy() - want).max() <= 1e-4
