@@ -58,10 +58,20 @@ class ClockSampler:
         try:
             self.p = subprocess.Popen(
                 ["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}",
-                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.f,
+                 "--format=csv,noheader,nounits", "-lms", "50"], stdout=self.f,
                 stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
+        # nvidia-smi needs a moment to start: wait for its first line
+        t0 = time.time()
+        while self.p is not None and self.lines() == 0 and time.time() - t0 < 5.0:
+            time.sleep(0.05)
+
+    def lines(self) -> int:
+        try:
+            return sum(1 for _ in open(self.f.name))
+        except OSError:
+            return 0
 
     def stop(self):
         if self.p is None:
@@ -230,8 +240,19 @@ def main():
         out = torch.empty_like(c)
         fn = lambda: ops.gemm(ctx, a, b, c, out, mode=mode)
         sampler = ClockSampler(local) if sample_clocks and rank == 0 else None
+        n0 = sampler.lines() if sampler else 0
         ms, launches = timed(fn, steps, warmup)
-        clocks = sampler.stop() if sampler else None
+        clocks = None
+        if sampler:
+            # a short timed region may end between two samples: keep the same loop
+            # running (untimed) until a few samples under this load exist
+            t0 = time.time()
+            while sampler.lines() - n0 < 8 and time.time() - t0 < 2.0:
+                for _ in range(10):
+                    fn()
+                torch.cuda.synchronize()
+            clocks = sampler.stop()
+            clocks["window"] = "warm-up + timed steps + untimed continuation of the same loop"
         ctx.check_device_status()
         flops = 2.0 * BATCH * n * n * n
         per_gpu = flops / ms / 1e9

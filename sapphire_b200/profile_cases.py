@@ -1,0 +1,68 @@
+"""Small, self-terminating cases of each kernel for `ncu` captures.
+
+    python -m sapphire_b200.profile_cases dense_tf32 | dense_tf32x3 | dense_tn | spgemm | spgemm_zipf
+
+Each case touches more than the 126 MB L2 but holds at most ~1.5 GB on the
+device and launches every kernel a handful of times, so that a full-set
+capture of one or two launches ends by itself within a couple of minutes.
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from . import _lib as L
+from . import ops
+from . import workloads as W
+
+
+def dense(mode: int, ta: bool = False, tb: bool = False, n: int = 2048, batch: int = 4) -> None:
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    a = torch.randn(batch, n, n, device=dev, generator=g)
+    b = torch.randn(batch, n, n, device=dev, generator=g)
+    c = torch.rand(batch, n, n, device=dev, generator=g)
+    out = torch.empty_like(c)
+    for _ in range(3):
+        ops.gemm(ctx, a, b, c, out, mode=mode, trans_a=ta, trans_b=tb)
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    print("dense case done", float(out[0, 0, 0]))
+
+
+def spgemm(dist: str, M: int = 32768, N: int = 65536) -> None:
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    rA, cA, vA = W.csr_random(0, M, N, 0.001, dist)
+    rB, cB, vB = W.csr_random(1, N, N, 0.001, dist)
+    A = ops.CsrMatrix.from_numpy(rA, cA, vA, M, N, dev)
+    B = ops.CsrMatrix.from_numpy(rB, cB, vB, N, N, dev)
+    for _ in range(2):
+        Cm = ops.spgemm(ctx, A, B)
+    torch.cuda.synchronize()
+    print("spgemm case done", Cm.nnz)
+
+
+def main() -> None:
+    case = sys.argv[1] if len(sys.argv) > 1 else "dense_tf32"
+    if case == "dense_tf32":
+        dense(L.MODE_TF32)
+    elif case == "dense_tf32x3":
+        dense(L.MODE_TF32X3)
+    elif case == "dense_tn":
+        dense(L.MODE_TF32, ta=True)
+    elif case == "dense_nt":
+        dense(L.MODE_TF32, tb=True)
+    elif case == "spgemm":
+        spgemm("poisson")
+    elif case == "spgemm_zipf":
+        spgemm("zipf")
+    else:
+        raise SystemExit(f"unknown case {case}")
+
+
+if __name__ == "__main__":
+    main()

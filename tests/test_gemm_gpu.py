@@ -121,9 +121,11 @@ def test_layouts_and_tails(ctx, oracle, mode, ta, tb, M, N, K, batch):
     want = oracle.gemm_ex(ta, tb, M, N, K, a, a.shape[2], a.shape[1] * a.shape[2],
                           b, b.shape[2], b.shape[1] * b.shape[2], c, N, M * N, N, M * N,
                           None, batch, batch * M * N).reshape(batch, M, N)
+    tma_ok = a.shape[2] % 4 == 0 and b.shape[2] % 4 == 0
     y = ops.gemm(ctx, dev(a), dev(b), dev(c), mode=mode, trans_a=bool(ta), trans_b=bool(tb),
-                 path=L.PATH_TCGEN05)
+                 path=L.PATH_TCGEN05 if tma_ok else L.PATH_AUTO)
     ctx.check_device_status()
+    assert ctx.last_path() == (L.PATH_TCGEN05 if tma_ok else L.PATH_SIMT)
     assert rel_fro(y.cpu().numpy(), want) <= TOL[mode]
 
 
