@@ -76,8 +76,11 @@ int64_t sb200_launch_count(const sb200_ctx* ctx);
  * Sources/Sapphire/compute/dense/cuda/Gemm.cu:31).
  *   SB200_OPT_SPLIT_EXPLICIT_HI  (TF32X3 mode) 0, the default: the high part of
  *       an operand is the raw fp32 word, cut to TF32 by the tensor core; 1: the
- *       high part is rounded to nearest TF32 and rewritten in shared memory. */
-enum { SB200_OPT_SPLIT_EXPLICIT_HI = 1 };
+ *       high part is rounded to nearest TF32 and rewritten in shared memory.
+ *   SB200_OPT_MERGE_MN_BOXES  1, the default: an operand tile whose contiguous
+ *       dimension is M or N (extent a multiple of 32) is fetched by one 4-D TMA
+ *       box; 0: by one 32 x 32 box per 32-element chunk. */
+enum { SB200_OPT_SPLIT_EXPLICIT_HI = 1, SB200_OPT_MERGE_MN_BOXES = 2 };
 int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value);
 
 /* Reads (and clears) the device status word after synchronising the stream.

@@ -16,6 +16,7 @@ ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT, ERR_ALLOC, ERR_T
 MODE_TF32, MODE_TF32X3 = 0, 1
 PATH_AUTO, PATH_TCGEN05, PATH_SIMT = 0, 1, 2
 OPT_SPLIT_EXPLICIT_HI = 1
+OPT_MERGE_MN_BOXES = 2
 
 
 class Csr(C.Structure):

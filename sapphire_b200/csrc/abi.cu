@@ -53,6 +53,7 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->d_workspace = nullptr;
     ctx->workspace_bytes = 0;
     ctx->split_explicit_hi = 0;
+    ctx->merge_mn_boxes = 1;
     ctx->encode_tiled = nullptr;
     ctx->d_status = nullptr;
     if (cudaMalloc(&ctx->d_status, sizeof(unsigned)) != cudaSuccess ||
@@ -109,6 +110,9 @@ extern "C" int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value)
     switch (option) {
         case SB200_OPT_SPLIT_EXPLICIT_HI:
             ctx->split_explicit_hi = value != 0;
+            return SB200_OK;
+        case SB200_OPT_MERGE_MN_BOXES:
+            ctx->merge_mn_boxes = value != 0;
             return SB200_OK;
         default:
             return SB200_ERR_INVALID_ARG;

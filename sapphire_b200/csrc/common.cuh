@@ -39,6 +39,7 @@ struct sb200_ctx {
     float* d_workspace;        // scratch for partial column sums / sparse row work
     size_t workspace_bytes;
     int split_explicit_hi;     // 3xTF32: rewrite the high part in shared memory too
+    int merge_mn_boxes;        // fetch an MN-major tile with one 4-D TMA box when possible
     void* encode_tiled;        // cuTensorMapEncodeTiled, resolved at context creation
 };
 

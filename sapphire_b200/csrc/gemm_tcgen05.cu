@@ -42,6 +42,7 @@ struct KernelParams {
     int chunk_kb;                               // k-blocks per TMEM accumulation chain
     long long total_tiles;
     int a_batched, b_batched;                   // 0: batch stride 0, always read matrix 0
+    int a_merged, b_merged;                     // MN-major tile fetched by one 4-D TMA box
     const float* C; long long ldc, strideC;
     float* D; long long ldd, strideD;
     const float* bias;
@@ -212,7 +213,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                     uint8_t* sb = sa + A_TILE_BYTES;
                     const int k0 = kb * BLOCK_K;
                     ptx::mbar_arrive_expect_tx(&full_bar[s], HALF_STAGE);
-                    if (A_MN) {
+                    if (A_MN && p.a_merged) {
+                        // stored [K, M], M % 32 == 0: all chunks in one 4-D box
+                        ptx::tma_load_4d(sa, &mapA, &full_bar[s], 0, k0, m0 / 32, ba);
+                    } else if (A_MN) {
                         // stored [K, M]: contiguous M, one 32(m) x 32(k) box per chunk
 #pragma unroll
                         for (int c = 0; c < BLOCK_M / 32; ++c)
@@ -222,7 +226,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                         // stored [M, K]: contiguous K, one 32(k) x 128(m) box
                         ptx::tma_load_3d(sa, &mapA, &full_bar[s], k0, m0, ba);
                     }
-                    if (B_MN) {
+                    if (B_MN && p.b_merged) {
+                        ptx::tma_load_4d(sb, &mapB, &full_bar[s], 0, k0, n0 / 32, bb);
+                    } else if (B_MN) {
                         // stored [K, N]: contiguous N
 #pragma unroll
                         for (int c = 0; c < BLOCK_N / 32; ++c)
@@ -487,6 +493,31 @@ int make_map(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig
     return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
 }
 
+// MN-major operand whose contiguous extent is a multiple of 32: view it as
+// [batch][chunk = contig / 32][row][32] so that one box of 32 x 32 rows x
+// `chunks` chunks brings a whole tile (same shared-memory image as `chunks`
+// separate 32 x 32 boxes: chunk-major, 32 rows of 128 B each).
+int make_map_merged(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig,
+                    int64_t rows, int64_t ld, int64_t batch, int64_t batch_stride, int chunks)
+{
+    EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    if (!enc)
+        return SB200_ERR_UNSUPPORTED;
+    const int64_t nb = (batch_stride == 0) ? 1 : batch;
+    cuuint64_t dims[4] = {32, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(contig / 32),
+                          static_cast<cuuint64_t>(nb)};
+    const int64_t bs = (batch_stride == 0 || nb == 1) ? rows * ld : batch_stride;
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(ld) * 4, 128,
+                             static_cast<cuuint64_t>(bs) * 4};
+    cuuint32_t box[4] = {32, static_cast<cuuint32_t>(BLOCK_K), static_cast<cuuint32_t>(chunks), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
+}
+
 template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT>
 int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 {
@@ -504,13 +535,19 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 
     CUtensorMap mapA, mapB;
     int rc;
-    if (A_MN)   // stored [K, M]
+    const bool a_merged = A_MN && (g.M % 32 == 0) && ctx->merge_mn_boxes;
+    const bool b_merged = B_MN && (g.N % 32 == 0) && ctx->merge_mn_boxes;
+    if (a_merged)
+        rc = make_map_merged(ctx, &mapA, g.A, g.M, g.K, g.lda, g.batch, g.strideA, BLOCK_M / 32);
+    else if (A_MN)   // stored [K, M]
         rc = make_map(ctx, &mapA, g.A, g.M, g.K, g.lda, g.batch, g.strideA, BLOCK_K, true);
     else        // stored [M, K]
         rc = make_map(ctx, &mapA, g.A, g.K, g.M, g.lda, g.batch, g.strideA, BLOCK_M, false);
     if (rc)
         return rc;
-    if (B_MN)   // stored [K, N]
+    if (b_merged)
+        rc = make_map_merged(ctx, &mapB, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, BLOCK_N / 32);
+    else if (B_MN)   // stored [K, N]
         rc = make_map(ctx, &mapB, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, BLOCK_K, true);
     else        // stored [N, K]
         rc = make_map(ctx, &mapB, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, BLOCK_N, false);
@@ -529,6 +566,8 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * g.batch;
     p.a_batched = g.strideA != 0;
     p.b_batched = g.strideB != 0;
+    p.a_merged = a_merged;
+    p.b_merged = b_merged;
     p.C = g.C; p.ldc = g.ldc; p.strideC = g.strideC;
     p.D = g.D; p.ldd = g.ldd; p.strideD = g.strideD;
     p.bias = g.bias;
