@@ -55,6 +55,9 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->split_explicit_hi = 0;
     ctx->merge_mn_boxes = 1;
     ctx->encode_tiled = nullptr;
+    ctx->d_sp_pattern = nullptr;
+    ctx->sp_pattern_bytes = 0;
+    ctx->sp_valid = 0;
     ctx->d_status = nullptr;
     if (cudaMalloc(&ctx->d_status, sizeof(unsigned)) != cudaSuccess ||
         cudaMemset(ctx->d_status, 0, sizeof(unsigned)) != cudaSuccess) {
@@ -81,6 +84,7 @@ extern "C" int sb200_ctx_destroy(sb200_ctx* ctx)
     cudaSetDevice(ctx->device);
     if (ctx->d_workspace) cudaFree(ctx->d_workspace);
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->d_sp_pattern) cudaFree(ctx->d_sp_pattern);
     delete ctx;
     return SB200_OK;
 }

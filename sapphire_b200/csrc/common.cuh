@@ -30,6 +30,14 @@ struct GemmArgs {
 
 }  // namespace sb200
 
+namespace sb200 {
+// Operand arrays the kept sparse row patterns were computed from.
+struct SpPatternKey {
+    const void *rowA, *colA, *rowB, *colB;
+    uint32_t M, K, N, nnzA, nnzB;
+};
+}  // namespace sb200
+
 struct sb200_ctx {
     int device;
     int sm_count;
@@ -41,6 +49,10 @@ struct sb200_ctx {
     int split_explicit_hi;     // 3xTF32: rewrite the high part in shared memory too
     int merge_mn_boxes;        // fetch an MN-major tile with one 4-D TMA box when possible
     void* encode_tiled;        // cuTensorMapEncodeTiled, resolved at context creation
+    uint32_t* d_sp_pattern;    // sparse GEMM: row bitmaps kept from the symbolic pass
+    size_t sp_pattern_bytes;
+    sb200::SpPatternKey sp_key;
+    int sp_valid;
 };
 
 namespace sb200 {

@@ -33,7 +33,7 @@ namespace {
 constexpr int TINY_MAX = 32;
 constexpr unsigned HEAVY_MIN = 16384;
 constexpr int ROW_THREADS = 256;
-constexpr int VAL_CAP = 8192;            // fp32 accumulators per CTA in shared memory
+constexpr int VAL_CAP = 6144;            // fp32 accumulators per CTA in shared memory
 constexpr uint32_t MAX_COLS = 1u << 20;  // bitmap of N bits must fit in shared memory
 
 struct Csr {
@@ -187,31 +187,16 @@ tiny_rows_kernel(Csr A, Csr B, Work w, const uint32_t* __restrict__ rowC,
 }
 
 // ------------------------------------------------------- CTA-per-row path
-template <typename F>
-__device__ __forceinline__ void for_each_product(const Csr& A, const Csr& B, uint32_t i,
-                                                 uint32_t prod, F f)
-{
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t pa = A.row[i], pe = A.row[i + 1];
-    const uint32_t nnzA = pe - pa;
-    if (prod / nnzA >= 128) {
-        // long rows of B: the whole CTA strides each of them
-        for (uint32_t p = pa; p < pe; ++p) {
-            const uint32_t k = A.col[p];
-            const float av = A.val[p];
-            const uint32_t qe = B.row[k + 1];
-            for (uint32_t q = B.row[k] + threadIdx.x; q < qe; q += ROW_THREADS) f(q, av);
-        }
-    } else {
-        // one warp per nonzero of A
-        for (uint32_t p = pa + warp; p < pe; p += ROW_THREADS / 32) {
-            const uint32_t k = A.col[p];
-            const float av = A.val[p];
-            const uint32_t qe = B.row[k + 1];
-            for (uint32_t q = B.row[k] + lane; q < qe; q += 32) f(q, av);
-        }
-    }
-}
+constexpr int A_CHUNK = 512;             // nonzeros of A's row staged in shared memory at a time
+constexpr int WALK_UNROLL = 4;           // independent loads in flight per thread
+
+// Per-chunk staging of A's row: for nonzero p of the chunk, where B's row
+// starts (qs), the running count of products before it (pref) and A's value.
+struct RowChunk {
+    uint32_t* qs;      // [A_CHUNK]
+    uint32_t* pref;    // [A_CHUNK + 1]
+    float* aval;       // [A_CHUNK]   (numeric only)
+};
 
 __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s_warp,
                                                          uint32_t& total)
@@ -237,36 +222,180 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s
     return warp_off + incl - v;
 }
 
+// Stages nonzeros [p0, p0 + n) of A's row i and returns the chunk's product count.
 template <bool NUMERIC>
-__global__ void __launch_bounds__(ROW_THREADS)
-cta_rows_kernel(Csr A, Csr B, Work w, uint32_t words, const uint32_t* __restrict__ rowC,
-                uint32_t* __restrict__ colC, float* __restrict__ valC)
+__device__ __forceinline__ uint32_t load_chunk(const Csr& A, const Csr& B, uint32_t p0, uint32_t n,
+                                               const RowChunk& ch, uint32_t* s_warp)
+{
+    // two nonzeros per thread (A_CHUNK == 2 * ROW_THREADS)
+    uint32_t len[2], qs[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const uint32_t e = threadIdx.x * 2 + u;
+        len[u] = 0;
+        qs[u] = 0;
+        if (e < n) {
+            const uint32_t k = A.col[p0 + e];
+            qs[u] = B.row[k];
+            len[u] = B.row[k + 1] - qs[u];
+            if (NUMERIC) ch.aval[e] = A.val[p0 + e];
+        }
+    }
+    uint32_t total;
+    const uint32_t off = block_exclusive_scan(len[0] + len[1], s_warp, total);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const uint32_t e = threadIdx.x * 2 + u;
+        if (e < n) {
+            ch.qs[e] = qs[u];
+            ch.pref[e] = off + (u ? len[0] : 0);
+        }
+    }
+    if (threadIdx.x == 0) ch.pref[n] = total;
+    __syncthreads();
+    return total;
+}
+
+// Calls f(column, a_value * b_value) for every product of the staged chunk.
+//
+// Two schedules, chosen per chunk by the mean length of B's rows:
+//  * rows of B of 16+ entries: one warp per nonzero of A, lanes stride B's row
+//    with four loads in flight; no search, ~10 instructions per product;
+//  * short rows: product t of the chunk belongs to the nonzero p with
+//    pref[p] <= t < pref[p+1] (binary search); thread tid takes t = tid,
+//    tid + 256, ... so that no lane idles on a one-entry row.
+template <bool NUMERIC, typename F>
+__device__ __forceinline__ void walk_chunk(const Csr& B, const RowChunk& ch, uint32_t n,
+                                           uint32_t total, F f)
+{
+    if (total >= 16u * n) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        for (uint32_t p = warp; p < n; p += ROW_THREADS / 32) {
+            const uint32_t qs = ch.qs[p];
+            const uint32_t len = ch.pref[p + 1] - ch.pref[p];
+            const float av = NUMERIC ? ch.aval[p] : 0.0f;
+            for (uint32_t o = lane; o < len; o += 32 * WALK_UNROLL) {
+                uint32_t col[WALK_UNROLL];
+                float bv[WALK_UNROLL];
+#pragma unroll
+                for (int u = 0; u < WALK_UNROLL; ++u) {
+                    if (o + 32 * u < len) {
+                        col[u] = __ldg(B.col + qs + o + 32 * u);
+                        if (NUMERIC) bv[u] = __ldg(B.val + qs + o + 32 * u);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < WALK_UNROLL; ++u)
+                    if (o + 32 * u < len) f(col[u], NUMERIC ? __fmul_rn(av, bv[u]) : 0.0f);
+            }
+        }
+        return;
+    }
+    uint32_t p = 0;
+    for (uint32_t base = threadIdx.x; base < total; base += ROW_THREADS * WALK_UNROLL) {
+        uint32_t q[WALK_UNROLL], col[WALK_UNROLL];
+        float av[WALK_UNROLL], bv[WALK_UNROLL];
+#pragma unroll
+        for (int u = 0; u < WALK_UNROLL; ++u) {
+            const uint32_t t = base + u * ROW_THREADS;
+            q[u] = 0xffffffffu;
+            if (t < total) {
+                uint32_t lo = p, hi = n;            // pref[lo] <= t < pref[hi]
+                while (hi - lo > 1) {
+                    const uint32_t mid = (lo + hi) >> 1;
+                    if (ch.pref[mid] <= t) lo = mid; else hi = mid;
+                }
+                p = lo;
+                q[u] = ch.qs[p] + (t - ch.pref[p]);
+                if (NUMERIC) av[u] = ch.aval[p];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < WALK_UNROLL; ++u) {
+            if (q[u] != 0xffffffffu) {
+                col[u] = __ldg(B.col + q[u]);
+                if (NUMERIC) bv[u] = __ldg(B.val + q[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < WALK_UNROLL; ++u)
+            if (q[u] != 0xffffffffu) f(col[u], NUMERIC ? __fmul_rn(av[u], bv[u]) : 0.0f);
+    }
+}
+
+// One CTA per row.
+//   SYMBOLIC (NUMERIC == false): mark the row's columns in a shared-memory
+//       bitmap, count them, and -- when `pattern` is given -- keep the bitmap in
+//       global memory for the numeric pass (words * 4 bytes per row).
+//   NUMERIC: rebuild the bitmap (FROM_PATTERN == false) or read it back,
+//       prefix-sum its popcounts so that rank(j) = prefix[j / 32] +
+//       popc(bits below j) is the position of column j in the sorted output row,
+//       emit the columns in bitmap order, then accumulate every product at its rank.
+template <bool NUMERIC, bool FROM_PATTERN>
+__global__ void __launch_bounds__(ROW_THREADS, 4)
+cta_rows_kernel(Csr A, Csr B, Work w, uint32_t words, uint32_t* __restrict__ pattern,
+                const uint32_t* __restrict__ rowC, uint32_t* __restrict__ colC,
+                float* __restrict__ valC)
 {
     extern __shared__ uint32_t sm[];
-    uint32_t* bitmap = sm;                              // [words]
-    uint32_t* wprefix = sm + words;                     // [words]   (numeric only)
-    float* vals = reinterpret_cast<float*>(sm + 2 * words);   // [VAL_CAP] (numeric only)
+    // symbolic: bitmap[words]; numeric: packed[words] = {bits, prefix}
+    uint32_t* bitmap = sm;
+    uint2* packed = reinterpret_cast<uint2*>(sm);
+    uint32_t* after_map = sm + (NUMERIC ? 2 * words : words);
+    RowChunk ch;
+    ch.qs = after_map;                                           // [A_CHUNK]
+    ch.pref = ch.qs + A_CHUNK;                                   // [A_CHUNK + 1] (+ pad)
+    ch.aval = reinterpret_cast<float*>(ch.pref + A_CHUNK + 4);   // [A_CHUNK]   (numeric)
+    float* vals = ch.aval + A_CHUNK;                             // [VAL_CAP]   (numeric)
     __shared__ uint32_t s_warp[ROW_THREADS / 32];
 
     const uint32_t n_heavy = w.counters[2];
     const uint32_t n_rows = n_heavy + w.counters[1];
     const uint32_t per_thread = (words + ROW_THREADS - 1) / ROW_THREADS;
+    const uint32_t w_lo = threadIdx.x * per_thread;
+    const uint32_t w_hi = min(w_lo + per_thread, words);
 
     for (uint32_t idx = blockIdx.x; idx < n_rows; idx += gridDim.x) {
         const uint32_t i = idx < n_heavy ? w.list_heavy[idx] : w.list_mid[idx - n_heavy];
-        const uint32_t prod = w.prod[i];
-        for (uint32_t x = threadIdx.x; x < words; x += ROW_THREADS) bitmap[x] = 0;
-        __syncthreads();
-        for_each_product(A, B, i, prod, [&](uint32_t q, float) {
-            const uint32_t j = B.col[q];
-            atomicOr(&bitmap[j >> 5], 1u << (j & 31));
-        });
-        __syncthreads();
-        // contiguous slice of bitmap words per thread -> popcount -> scan
-        const uint32_t w_lo = threadIdx.x * per_thread;
-        const uint32_t w_hi = min(w_lo + per_thread, words);
-        uint32_t mine = 0;
-        for (uint32_t x = w_lo; x < w_hi; ++x) mine += __popc(bitmap[x]);
+        const uint32_t pa = A.row[i], pe = A.row[i + 1];
+        const bool one_chunk = (pe - pa) <= A_CHUNK;
+        uint32_t chunk_total = 0;
+        uint32_t mine = 0;                                       // set bits in this thread's words
+
+        if (!(NUMERIC && FROM_PATTERN)) {
+            // ---- pattern: mark every product's column
+            if (NUMERIC) {
+                for (uint32_t x = threadIdx.x; x < words; x += ROW_THREADS)
+                    packed[x] = make_uint2(0u, 0u);
+            } else {
+                for (uint32_t x = threadIdx.x; x < words; x += ROW_THREADS) bitmap[x] = 0;
+            }
+            __syncthreads();
+            for (uint32_t p0 = pa; p0 < pe; p0 += A_CHUNK) {
+                const uint32_t n = min(static_cast<uint32_t>(A_CHUNK), pe - p0);
+                chunk_total = load_chunk<NUMERIC>(A, B, p0, n, ch, s_warp);
+                walk_chunk<false>(B, ch, n, chunk_total, [&](uint32_t j, float) {
+                    if (NUMERIC)
+                        atomicOr(&packed[j >> 5].x, 1u << (j & 31));
+                    else
+                        atomicOr(&bitmap[j >> 5], 1u << (j & 31));
+                });
+                __syncthreads();
+            }
+            if (!NUMERIC && pattern) {
+                // lane-contiguous copy: full 128-byte lines per warp
+                uint32_t* dst = pattern + static_cast<size_t>(i) * words;
+                for (uint32_t x = threadIdx.x; x < words; x += ROW_THREADS) dst[x] = bitmap[x];
+            }
+            for (uint32_t x = w_lo; x < w_hi; ++x)
+                mine += __popc(NUMERIC ? packed[x].x : bitmap[x]);
+        } else {
+            // ---- pattern kept by the symbolic pass
+            const uint32_t* src = pattern + static_cast<size_t>(i) * words;
+            for (uint32_t x = threadIdx.x; x < words; x += ROW_THREADS) packed[x].x = src[x];
+            __syncthreads();
+            for (uint32_t x = w_lo; x < w_hi; ++x) mine += __popc(packed[x].x);
+        }
         uint32_t total;
         uint32_t run = block_exclusive_scan(mine, s_warp, total);
         if (!NUMERIC) {
@@ -276,32 +405,46 @@ cta_rows_kernel(Csr A, Csr B, Work w, uint32_t words, const uint32_t* __restrict
         }
         const uint32_t out0 = rowC[i];
         const bool in_smem = total <= VAL_CAP;
+        // columns come out ascending: word order, then bit order.  They are
+        // staged in the (not yet used) value buffer so that the global store is
+        // lane-contiguous; rows wider than the buffer store them directly.
+        uint32_t* stage = reinterpret_cast<uint32_t*>(vals);
         for (uint32_t x = w_lo; x < w_hi; ++x) {
-            wprefix[x] = run;
-            uint32_t bits = bitmap[x];
-            // columns come out ascending: word order, then bit order
+            uint32_t bits = packed[x].x;
+            packed[x].y = run;
             while (bits) {
                 const int bpos = __ffs(bits) - 1;
                 bits &= bits - 1;
-                colC[out0 + run] = x * 32 + bpos;
+                if (in_smem)
+                    stage[run] = x * 32 + bpos;
+                else
+                    colC[out0 + run] = x * 32 + bpos;
                 ++run;
             }
         }
+        __syncthreads();
         if (in_smem) {
-            for (uint32_t x = threadIdx.x; x < total; x += ROW_THREADS) vals[x] = 0.0f;
+            for (uint32_t x = threadIdx.x; x < total; x += ROW_THREADS) {
+                colC[out0 + x] = stage[x];
+                vals[x] = 0.0f;                    // same word, same thread: no hazard
+            }
         } else {
             for (uint32_t x = threadIdx.x; x < total; x += ROW_THREADS) valC[out0 + x] = 0.0f;
-            __threadfence_block();
         }
         __syncthreads();
+        // ---- values: accumulate every product at the rank of its column
         float* acc = in_smem ? vals : (valC + out0);
-        for_each_product(A, B, i, prod, [&](uint32_t q, float av) {
-            const uint32_t j = B.col[q];
-            const uint32_t word = j >> 5;
-            const uint32_t rank = wprefix[word] + __popc(bitmap[word] & ((1u << (j & 31)) - 1u));
-            atomicAdd(&acc[rank], __fmul_rn(av, B.val[q]));
-        });
-        __syncthreads();
+        for (uint32_t p0 = pa; p0 < pe; p0 += A_CHUNK) {
+            const uint32_t n = min(static_cast<uint32_t>(A_CHUNK), pe - p0);
+            if (FROM_PATTERN || !one_chunk)
+                chunk_total = load_chunk<NUMERIC>(A, B, p0, n, ch, s_warp);
+            walk_chunk<true>(B, ch, n, chunk_total, [&](uint32_t j, float prod) {
+                const uint2 wp = packed[j >> 5];
+                const uint32_t rank = wp.y + __popc(wp.x & ((1u << (j & 31)) - 1u));
+                atomicAdd(&acc[rank], prod);
+            });
+            __syncthreads();
+        }
         if (in_smem)
             for (uint32_t x = threadIdx.x; x < total; x += ROW_THREADS) valC[out0 + x] = vals[x];
         __syncthreads();
@@ -349,6 +492,7 @@ struct Plan {
     uint32_t words;
     size_t smem_symbolic, smem_numeric;
     unsigned long long* d_total;
+    uint32_t* pattern;          // [M][words] row bitmaps kept between the passes, or null
 };
 
 int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
@@ -382,8 +526,10 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
     pl->words = (B->N + 31) / 32;
     if (pl->words == 0)
         pl->words = 1;
-    pl->smem_symbolic = static_cast<size_t>(pl->words) * 4;
-    pl->smem_numeric = static_cast<size_t>(pl->words) * 8 + VAL_CAP * 4;
+    const size_t chunk_bytes = (3 * A_CHUNK + 4) * 4;   // qs, pref (+pad), aval
+    pl->pattern = nullptr;
+    pl->smem_symbolic = static_cast<size_t>(pl->words) * 4 + chunk_bytes;
+    pl->smem_numeric = static_cast<size_t>(pl->words) * 8 + chunk_bytes + VAL_CAP * 4;
     return SB200_OK;
 }
 
@@ -399,14 +545,49 @@ int bin_rows(sb200_ctx* ctx, const Plan& pl, cudaStream_t stream)
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
 
-template <bool NUMERIC>
+// Identity of the operands a kept pattern belongs to.
+bool same_operands(const sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B)
+{
+    const SpPatternKey& k = ctx->sp_key;
+    return ctx->sp_valid && k.rowA == A->ROW && k.colA == A->COL && k.rowB == B->ROW &&
+           k.colB == B->COL && k.M == A->M && k.K == A->N && k.N == B->N && k.nnzA == A->NNZ &&
+           k.nnzB == B->NNZ;
+}
+
+// Row bitmaps are kept when they fit the budget (M * ceil(N / 32) * 4 bytes).
+constexpr size_t PATTERN_BUDGET = static_cast<size_t>(2) << 30;
+
+int prepare_pattern(sb200_ctx* ctx, Plan* pl, const sb200_csr* A, const sb200_csr* B)
+{
+    ctx->sp_valid = 0;
+    const size_t need = static_cast<size_t>(A->M) * pl->words * 4;
+    if (need == 0 || need > PATTERN_BUDGET)
+        return SB200_OK;                       // numeric pass rebuilds the bitmaps
+    if (need > ctx->sp_pattern_bytes) {
+        if (ctx->d_sp_pattern) cudaFree(ctx->d_sp_pattern);
+        ctx->d_sp_pattern = nullptr;
+        ctx->sp_pattern_bytes = 0;
+        void* p = nullptr;
+        if (cudaMalloc(&p, need) != cudaSuccess) {
+            cudaGetLastError();
+            return SB200_OK;                   // no room: fall back to rebuilding
+        }
+        ctx->d_sp_pattern = static_cast<uint32_t*>(p);
+        ctx->sp_pattern_bytes = need;
+    }
+    pl->pattern = ctx->d_sp_pattern;
+    ctx->sp_key = SpPatternKey{A->ROW, A->COL, B->ROW, B->COL, A->M, A->N, B->N, A->NNZ, B->NNZ};
+    return SB200_OK;
+}
+
+template <bool NUMERIC, bool FROM_PATTERN>
 int run_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, uint32_t* colC, float* valC,
              cudaStream_t stream)
 {
     if (pl.A.M == 0)
         return SB200_OK;
     const size_t smem = NUMERIC ? pl.smem_numeric : pl.smem_symbolic;
-    auto kern = cta_rows_kernel<NUMERIC>;
+    auto kern = cta_rows_kernel<NUMERIC, FROM_PATTERN>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
         return SB200_ERR_CUDA;
@@ -415,7 +596,8 @@ int run_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, uint32_t* col
             cudaSuccess || per_sm < 1)
         per_sm = 1;
     const unsigned grid = static_cast<unsigned>(ctx->sm_count) * per_sm;
-    kern<<<grid, ROW_THREADS, smem, stream>>>(pl.A, pl.B, pl.w, pl.words, rowC, colC, valC);
+    kern<<<grid, ROW_THREADS, smem, stream>>>(pl.A, pl.B, pl.w, pl.words, pl.pattern, rowC, colC,
+                                              valC);
     tiny_rows_kernel<NUMERIC><<<static_cast<unsigned>(ctx->sm_count) * 8, 256, 0, stream>>>(
         pl.A, pl.B, pl.w, rowC, colC, valC);
     ctx->launches += 2;
@@ -439,10 +621,11 @@ extern "C" int sb200_spgemm_csr_symbolic(sb200_ctx* ctx, const sb200_csr* A, con
         return rc;
     if (cudaSetDevice(ctx->device) != cudaSuccess)
         return SB200_ERR_CUDA;
-    if ((rc = bin_rows(ctx, pl, stream)))
+    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, stream)))
         return rc;
-    if ((rc = run_rows<false>(ctx, pl, nullptr, nullptr, nullptr, stream)))
+    if ((rc = run_rows<false, false>(ctx, pl, nullptr, nullptr, nullptr, stream)))
         return rc;
+    ctx->sp_valid = pl.pattern != nullptr;
     row_scan_kernel<<<1, 1024, 0, stream>>>(pl.w.cnt, pl.A.M, rowC, pl.d_total);
     ctx->launches += 1;
     unsigned long long total = 0;
@@ -456,8 +639,10 @@ extern "C" int sb200_spgemm_csr_symbolic(sb200_ctx* ctx, const sb200_csr* A, con
     return SB200_OK;
 }
 
-// Requires the row bins left in the context workspace by the symbolic call on
-// the same (A, B); they are rebuilt here so the two calls stay independent.
+// The row bins are rebuilt here, so the call works on its own.  When the
+// immediately preceding symbolic call on this context had the same operand
+// arrays (same pointers and sizes; their contents must not have changed) the
+// row patterns it kept are read back instead of being recomputed.
 extern "C" int sb200_spgemm_csr_numeric(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B,
                                         const uint32_t* rowC, uint32_t* colC, float* valC,
                                         sb200_stream stream_)
@@ -473,7 +658,11 @@ extern "C" int sb200_spgemm_csr_numeric(sb200_ctx* ctx, const sb200_csr* A, cons
         return SB200_ERR_CUDA;
     if ((rc = bin_rows(ctx, pl, stream)))
         return rc;
-    return run_rows<true>(ctx, pl, rowC, colC, valC, stream);
+    if (same_operands(ctx, A, B)) {
+        pl.pattern = ctx->d_sp_pattern;
+        return run_rows<true, true>(ctx, pl, rowC, colC, valC, stream);
+    }
+    return run_rows<true, false>(ctx, pl, rowC, colC, valC, stream);
 }
 
 extern "C" int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B,
@@ -494,8 +683,8 @@ extern "C" int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_
     if (cudaMalloc(&C->ROW, (static_cast<size_t>(A->M) + 1) * 4) != cudaSuccess)
         return SB200_ERR_ALLOC;
     // symbolic: bins stay valid in the workspace for the numeric pass below
-    if ((rc = bin_rows(ctx, pl, stream)) ||
-        (rc = run_rows<false>(ctx, pl, nullptr, nullptr, nullptr, stream))) {
+    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, stream)) ||
+        (rc = run_rows<false, false>(ctx, pl, nullptr, nullptr, nullptr, stream))) {
         sb200_csr_free(C);
         return rc;
     }
@@ -518,7 +707,10 @@ extern "C" int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_
         sb200_csr_free(C);
         return SB200_ERR_ALLOC;
     }
-    if ((rc = run_rows<true>(ctx, pl, C->ROW, C->COL, C->V, stream))) {
+    rc = pl.pattern ? run_rows<true, true>(ctx, pl, C->ROW, C->COL, C->V, stream)
+                    : run_rows<true, false>(ctx, pl, C->ROW, C->COL, C->V, stream);
+    ctx->sp_valid = 0;
+    if (rc) {
         sb200_csr_free(C);
         return rc;
     }
