@@ -181,6 +181,52 @@ int sb200_csr_free(sb200_csr* C);
 int sb200_csr_copy_out(const sb200_csr* src, uint32_t* row, uint32_t* col, float* val,
                        int to_host, sb200_stream stream);
 
+/* ---- elementwise steps of a Linear training step -------------------------
+ * The kernels either side of the GEMMs when Sapphire trains an MLP; same
+ * argument meaning as the reference's device leaves.  All pointers are device
+ * pointers; "accumulates" means dx is read, added to and written back.
+ */
+
+/* out = max(in, 0).  Dense::Cuda::ReLU
+ * (Sources/Sapphire/compute/dense/cuda/kernels/ActivationKernel.cu:11-22). */
+int sb200_relu(sb200_ctx* ctx, float* out, const float* in, int64_t n, sb200_stream stream);
+
+/* dx += x > 0 ? dy : 0 (accumulates).  ReLUBackward
+ * (Sources/Sapphire/compute/dense/cuda/kernels/ActivationBackwardKernel.cu:11-24). */
+int sb200_relu_backward(sb200_ctx* ctx, float* dx, const float* dy, const float* x, int64_t n,
+                        sb200_stream stream);
+
+/* Row softmax over rows of `unit` elements with max subtraction.  SoftMax
+ * (Sources/Sapphire/compute/dense/naive/NaiveBasic.cpp:235-255; device twin
+ * ActivationKernel.cu:38-65). */
+int sb200_softmax(sb200_ctx* ctx, float* out, const float* in, int64_t total, int unit,
+                  sb200_stream stream);
+
+/* dx += J^T dy with the full softmax Jacobian (accumulates).  SoftMaxBackward
+ * (Sources/Sapphire/compute/dense/naive/NaiveBasic.cpp:257-281). */
+int sb200_softmax_backward(sb200_ctx* ctx, float* dx, const float* dy, const float* y,
+                           int64_t total, int unit, sb200_stream stream);
+
+/* loss[i] = -sum_j label[i,j] * log(x[i,j]); x == 0 is replaced by 1.17549e-30;
+ * no batch mean.  CrossEntropy
+ * (Sources/Sapphire/compute/dense/naive/NaiveCrossEntropy.cpp:15-31). */
+int sb200_cross_entropy(sb200_ctx* ctx, float* loss, const float* x, const float* label, int batch,
+                        int unit, sb200_stream stream);
+
+/* dx -= label / x (accumulates).  CrossEntropyBackward (NaiveCrossEntropy.cpp:33-51). */
+int sb200_cross_entropy_backward(sb200_ctx* ctx, float* dx, const float* x, const float* label,
+                                 int batch, int unit, sb200_stream stream);
+
+/* z <- z - lr * dz as one kernel; the reference runs Scale into a temporary and
+ * then Sub (Sources/Sapphire/operations/optimizers/SGD.cpp:22-28). */
+int sb200_sgd_update(sb200_ctx* ctx, float* z, const float* dz, float lr, int64_t n,
+                     sb200_stream stream);
+
+/* out = in * factor.  Dense::Cuda::Scale
+ * (Sources/Sapphire/compute/dense/cuda/kernels/BasicKernel.cu:115-125). */
+int sb200_scale(sb200_ctx* ctx, float* out, const float* in, float factor, int64_t n,
+                sb200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -299,3 +299,29 @@ class MlpOracle:
                 f["relu_bwd"](dpre.reshape(-1), dx.reshape(-1), pre[l - 1].reshape(-1), dx.size)
                 dy = dpre
         return loss
+
+    def gradients(self, x, onehot):
+        """(loss, dWs, dBs) of one batch without touching the parameters: step()
+        with the SGD calls intercepted (dB carries the 1/batch scale).  The
+        backward pass visits the layers last to first and hands first the weight
+        gradient, then the bias gradient, of each layer to the optimizer."""
+        n = len(self.W)
+        saved = ([w.copy() for w in self.W], [b.copy() for b in self.b])
+        dWs, dBs, calls = [None] * n, [None] * n, [0]
+
+        def capture(z, dz):
+            layer = n - 1 - calls[0] // 2
+            if calls[0] % 2 == 0:
+                dWs[layer] = dz.copy()
+            else:
+                dBs[layer] = dz.reshape(-1).copy()
+            calls[0] += 1
+
+        orig = self._sgd
+        self._sgd = capture
+        try:
+            loss = self.step(x, onehot)
+        finally:
+            self._sgd = orig
+            self.W, self.b = saved
+        return loss, dWs, dBs

@@ -61,6 +61,19 @@ SIGNATURES = {
     "sb200_csr_free": (C.c_int, [C.POINTER(Csr)]),
     "sb200_csr_copy_out": (C.c_int, [C.POINTER(Csr), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                      C.c_void_p]),
+    "sb200_relu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "sb200_relu_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                      C.c_void_p]),
+    "sb200_softmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "sb200_softmax_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                         C.c_int, C.c_void_p]),
+    "sb200_cross_entropy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                      C.c_int, C.c_void_p]),
+    "sb200_cross_entropy_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                               C.c_int, C.c_int, C.c_void_p]),
+    "sb200_sgd_update": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64,
+                                   C.c_void_p]),
+    "sb200_scale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_void_p]),
     # Sapphire-signature shims (include/sapphire_b200_compat.h)
     "sb200_compat_set_mode": (C.c_int, [C.c_int]),
     "sb200_compat_dense_gemm": (C.c_int, [C.c_uint, C.c_void_p, C.c_void_p, C.c_void_p,

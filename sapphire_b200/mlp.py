@@ -1,0 +1,77 @@
+"""A Linear -> ReLU -> ... -> Linear -> SoftMax -> CrossEntropy training step on
+the B200 kernels, with the semantics of Sapphire's units:
+
+forward   y = bias + x.W, W stored [in, out]: one GEMM with the bias in its
+          epilogue (the reference runs a rank-1 Gemm for the bias first,
+          Sources/Sapphire/operations/Forward/Linear.cpp:134-136)
+backward  dx = dy.W^T and dW = x^T.dy through descriptor transposes, dB as the
+          fused column sum scaled by 1 / batch
+          (Sources/Sapphire/operations/Backward/LinearBackward.cpp:27-99 materialises both
+          transposes and runs a ones-Gemm for dB)
+update    SGD z <- z - lr * dz (Sources/Sapphire/operations/optimizers/SGD.cpp:22-28), applied
+          after the backward pass (and after the gradient allreduce when the batch
+          is split over ranks); the reference updates inside backward, after dx
+          of the same layer was formed with the old weight, which is the same
+          arithmetic.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib as L
+from . import ops
+from .runner import GradBucket
+
+
+class MlpTrainer:
+    def __init__(self, ctx: ops.Context, weights: Sequence[np.ndarray], biases: Sequence[np.ndarray],
+                 lr: float, mode: int = L.MODE_TF32, world: int = 1):
+        self.ctx, self.lr, self.mode, self.world = ctx, float(lr), mode, world
+        dev = torch.device("cuda", ctx.device)
+        shapes = [w.shape for w in weights]
+        # parameters share the gradient bucket's layout: one SGD kernel updates them all
+        self.params = GradBucket.create(shapes, dev)
+        for dst, w in zip(self.params.dW, weights):
+            dst.copy_(torch.from_numpy(np.ascontiguousarray(w)))
+        for dst, b in zip(self.params.dB, biases):
+            dst.copy_(torch.from_numpy(np.ascontiguousarray(b)))
+        self.grads = GradBucket.create(shapes, dev)
+        self.W, self.b = self.params.dW, self.params.dB
+
+    def forward_backward(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
+        """Fills the gradient bucket with this rank's gradients; returns the
+        per-sample loss."""
+        ctx, mode = self.ctx, self.mode
+        nl = len(self.W)
+        B = x.shape[0]
+        acts: List[torch.Tensor] = [x]
+        pre: List[torch.Tensor] = []
+        for l in range(nl):
+            y = ops.gemm(ctx, acts[-1], self.W[l], bias=self.b[l], mode=mode)
+            pre.append(y)
+            if l < nl - 1:
+                acts.append(ops.relu(ctx, y))
+        prob = ops.softmax(ctx, pre[-1])
+        loss = ops.cross_entropy(ctx, prob, onehot)
+        dprob = torch.zeros_like(prob)
+        ops.cross_entropy_backward(ctx, dprob, prob, onehot)
+        dy = torch.zeros_like(prob)
+        ops.softmax_backward(ctx, dy, dprob, prob)
+        for l in reversed(range(nl)):
+            dx = ops.gemm(ctx, dy, self.W[l], trans_b=True, mode=mode)
+            ops.gemm(ctx, acts[l], dy, out=self.grads.dW[l], trans_a=True, mode=mode,
+                     colsum_out=self.grads.dB[l], colsum_scale=1.0 / B)
+            if l > 0:
+                dpre = torch.zeros_like(pre[l - 1])
+                ops.relu_backward(ctx, dpre, dx, pre[l - 1])
+                dy = dpre
+        return loss
+
+    def step(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
+        loss = self.forward_backward(x, onehot)
+        self.grads.allreduce(self.world, lambda t, f: ops.scale(self.ctx, t, f))
+        ops.sgd_update(self.ctx, self.params.flat, self.grads.flat, self.lr)
+        return loss

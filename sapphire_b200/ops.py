@@ -202,3 +202,56 @@ def spgemm_callee_alloc(ctx: Context, A: CsrMatrix, B: CsrMatrix) -> CsrMatrix:
         val.data_ptr() if n else None, 0, _stream_ptr(ctx.device)))
     L.lib().sb200_csr_free(C.byref(c))
     return CsrMatrix(row, col, val, A.M, B.N)
+
+
+# ---------------------------------------------------------------- elementwise
+
+def _ew(name, ctx, *args):
+    L.check(name, getattr(L.lib(), name)(ctx.handle, *args, _stream_ptr(ctx.device)))
+
+
+def relu(ctx, x, out=None):
+    out = torch.empty_like(x) if out is None else out
+    _ew("sb200_relu", ctx, out.data_ptr(), x.data_ptr(), x.numel())
+    return out
+
+
+def relu_backward(ctx, dx, dy, x):
+    _ew("sb200_relu_backward", ctx, dx.data_ptr(), dy.data_ptr(), x.data_ptr(), x.numel())
+    return dx
+
+
+def softmax(ctx, x, out=None):
+    out = torch.empty_like(x) if out is None else out
+    _ew("sb200_softmax", ctx, out.data_ptr(), x.data_ptr(), x.numel(), x.shape[-1])
+    return out
+
+
+def softmax_backward(ctx, dx, dy, y):
+    _ew("sb200_softmax_backward", ctx, dx.data_ptr(), dy.data_ptr(), y.data_ptr(), y.numel(),
+        y.shape[-1])
+    return dx
+
+
+def cross_entropy(ctx, prob, label, out=None):
+    out = torch.empty(prob.shape[0], dtype=torch.float32, device=prob.device) if out is None else out
+    _ew("sb200_cross_entropy", ctx, out.data_ptr(), prob.data_ptr(), label.data_ptr(),
+        prob.shape[0], prob.shape[1])
+    return out
+
+
+def cross_entropy_backward(ctx, dx, prob, label):
+    _ew("sb200_cross_entropy_backward", ctx, dx.data_ptr(), prob.data_ptr(), label.data_ptr(),
+        prob.shape[0], prob.shape[1])
+    return dx
+
+
+def sgd_update(ctx, z, dz, lr):
+    _ew("sb200_sgd_update", ctx, z.data_ptr(), dz.data_ptr(), float(lr), z.numel())
+    return z
+
+
+def scale(ctx, x, factor, out=None):
+    out = x if out is None else out
+    _ew("sb200_scale", ctx, out.data_ptr(), x.data_ptr(), float(factor), x.numel())
+    return out

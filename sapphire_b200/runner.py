@@ -1,0 +1,123 @@
+"""Multi-GPU runner: one process per GPU, torch.distributed for the plumbing.
+
+Work is partitioned, not replicated:
+
+* batched dense GEMM   contiguous batch ranges per rank, no collective;
+* Linear backward      row blocks of dY / X per rank, W replicated; dX rows are
+                       final, dW and dB partial sums need one allreduce;
+* data-parallel MLP    the batch is split; all gradients travel in one flat
+                       bucket, one allreduce per step;
+* CSR sparse GEMM      row blocks of A balanced by scalar products, B
+                       replicated, no collective (C stays distributed).
+
+Reduction rule of the gradients.  Sapphire's Linear backward leaves dW as the
+plain sum over the samples of the batch and scales dB by 1 / batch
+(Sources/Sapphire/operations/Backward/LinearBackward.cpp:72-73, 93-97).  With the batch
+split over R ranks the single-process result is therefore
+
+    dW = SUM over ranks of dW_local          dB = MEAN over ranks of dB_local
+
+(each local dB already carries 1 / local batch).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import List, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def env_world() -> Tuple[int, int, int]:
+    return (int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")),
+            int(os.environ.get("LOCAL_RANK", "0")))
+
+
+def init_distributed(backend: str) -> Tuple[int, int, int]:
+    world, rank, local = env_world()
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29531")
+        if backend == "nccl":
+            torch.cuda.set_device(local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group(backend)
+    return world, rank, local
+
+
+# ------------------------------------------------------------------ sharding
+
+def contiguous_shard(n_items: int, world: int, rank: int) -> range:
+    """Items [lo, hi) of rank: the first n % world ranks take one extra."""
+    base, extra = divmod(n_items, world)
+    lo = rank * base + min(rank, extra)
+    return range(lo, lo + base + (1 if rank < extra else 0))
+
+
+def row_shard(rows: int, world: int, rank: int, align: int = 1) -> range:
+    """Row block of rank with boundaries at multiples of `align`."""
+    units = (rows + align - 1) // align
+    r = contiguous_shard(units, world, rank)
+    return range(min(r.start * align, rows), min(r.stop * align, rows))
+
+
+def balanced_row_blocks(work: np.ndarray, world: int) -> List[range]:
+    """Contiguous row blocks with near-equal total work (scalar products of the
+    sparse GEMM): block r ends where the running sum passes (r+1)/world of the total."""
+    work = np.asarray(work, dtype=np.int64)
+    cs = np.concatenate([[0], np.cumsum(work)])
+    total = int(cs[-1])
+    cuts = [0]
+    for r in range(1, world):
+        target = total * r / world
+        cut = int(np.searchsorted(cs, target, side="left"))
+        cuts.append(max(cuts[-1], min(cut, work.size)))
+    cuts.append(work.size)
+    return [range(cuts[r], cuts[r + 1]) for r in range(world)]
+
+
+def csr_row_block(row: np.ndarray, col: np.ndarray, val: np.ndarray, rows: range):
+    """The CSR arrays of a block of rows (ROW rebased to start at 0)."""
+    lo, hi = int(row[rows.start]), int(row[rows.stop])
+    return ((row[rows.start:rows.stop + 1].astype(np.int64) - lo).astype(np.uint32),
+            col[lo:hi], val[lo:hi])
+
+
+# ------------------------------------------------------------ gradient bucket
+
+@dataclass
+class GradBucket:
+    """All gradients of the MLP in one flat fp32 buffer: the dW blocks first,
+    then the dB blocks, so that the mean scaling touches one contiguous tail."""
+    flat: torch.Tensor
+    dW: List[torch.Tensor]
+    dB: List[torch.Tensor]
+    n_weight: int
+
+    @staticmethod
+    def create(shapes: Sequence[Tuple[int, int]], device) -> "GradBucket":
+        nW = sum(i * o for i, o in shapes)
+        nB = sum(o for _, o in shapes)
+        flat = torch.zeros(nW + nB, dtype=torch.float32, device=device)
+        dW, dB, off = [], [], 0
+        for i, o in shapes:
+            dW.append(flat[off:off + i * o].view(i, o))
+            off += i * o
+        for _, o in shapes:
+            dB.append(flat[off:off + o])
+            off += o
+        return GradBucket(flat, dW, dB, nW)
+
+    def allreduce(self, world: int, scale_fn=None) -> None:
+        """dW: SUM over ranks.  dB: MEAN over ranks."""
+        if world <= 1:
+            return
+        dist.all_reduce(self.flat, op=dist.ReduceOp.SUM)
+        tail = self.flat[self.n_weight:]
+        if scale_fn is None:
+            tail.mul_(1.0 / world)
+        else:
+            scale_fn(tail, 1.0 / world)

@@ -1,0 +1,95 @@
+"""GPU parity of the elementwise kernels and of the MLP training step (784 ->
+512 -> 256 -> 10, ReLU, softmax cross-entropy, SGD lr 0.01, batch 64) against
+the CPU oracle that restates Sapphire's units call by call."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from sapphire_b200 import _lib as L
+from sapphire_b200 import mlp, ops
+from sapphire_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(DEV)
+
+
+def rel(got, want):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+
+
+def test_elementwise_kernels_match_oracle(ctx, oracle):
+    p = oracle.port()
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((64, 10)).astype(np.float32)
+    x[3, 4] = 0.0
+    # ReLU / backward: exact
+    want = np.empty_like(x); p.orc_relu(want.reshape(-1), x.reshape(-1), x.size)
+    assert np.array_equal(ops.relu(ctx, dev(x)).cpu().numpy(), want)
+    dy = rng.standard_normal(x.shape).astype(np.float32)
+    dx0 = rng.standard_normal(x.shape).astype(np.float32)
+    want = dx0.copy(); p.orc_relu_backward(want.reshape(-1), dy.reshape(-1), x.reshape(-1), x.size)
+    assert np.array_equal(ops.relu_backward(ctx, dev(dx0), dev(dy), dev(x)).cpu().numpy(), want)
+    # softmax: libm vs device exp differ in the last bits
+    want = np.empty_like(x); p.orc_softmax(want.reshape(-1), x.reshape(-1), x.size, 10)
+    prob = ops.softmax(ctx, dev(x))
+    assert rel(prob.cpu().numpy(), want) <= 1e-6
+    lab = np.zeros_like(x); lab[np.arange(64), rng.integers(0, 10, 64)] = 1.0
+    wl = np.zeros(64, np.float32); p.orc_cross_entropy(wl, want.reshape(-1), lab.reshape(-1), 64, 10)
+    assert rel(ops.cross_entropy(ctx, dev(want), dev(lab)).cpu().numpy(), wl) <= 1e-6
+    wdx = np.zeros_like(x); p.orc_cross_entropy_backward(wdx.reshape(-1), want.reshape(-1), lab.reshape(-1), 64, 10)
+    got = ops.cross_entropy_backward(ctx, torch.zeros(64, 10, device=DEV), dev(want), dev(lab))
+    assert np.array_equal(got.cpu().numpy(), wdx)
+    wsb = np.zeros_like(x); p.orc_softmax_backward(wsb.reshape(-1), wdx.reshape(-1), want.reshape(-1), x.size, 10)
+    got = ops.softmax_backward(ctx, torch.zeros(64, 10, device=DEV), dev(wdx), dev(want))
+    assert np.array_equal(got.cpu().numpy(), wsb)
+    # cross entropy of an exact zero probability uses the 1.17549e-30 floor
+    z = np.zeros((1, 2), np.float32); z[0, 1] = 1.0
+    l = ops.cross_entropy(ctx, dev(z), dev(np.array([[1.0, 0.0]], np.float32))).cpu().numpy()
+    assert np.isfinite(l).all() and l[0] > 60.0
+    # SGD: bit-exact (two rounded operations)
+    zv = rng.standard_normal(1000).astype(np.float32); dz = rng.standard_normal(1000).astype(np.float32)
+    tmp = np.empty_like(dz); p.orc_scale(tmp, dz, np.float32(0.01), 1000)
+    out = np.empty_like(zv); p.orc_sub(out, zv, tmp, 1000)
+    assert np.array_equal(ops.sgd_update(ctx, dev(zv), dev(dz), 0.01).cpu().numpy(), out)
+
+
+@pytest.mark.parametrize("mode,tol", [(L.MODE_TF32X3, 1e-5), (L.MODE_TF32, 2e-3)])
+def test_mlp_training_matches_oracle(ctx, oracle, mode, tol):
+    """20 SGD steps: loss curve and final parameters against the single-process oracle."""
+    steps = 20
+    Ws, bs = W.mlp_init(0)
+    net = oracle.MlpOracle(Ws, bs, 0.01)
+    trainer = mlp.MlpTrainer(ctx, Ws, bs, 0.01, mode=mode)
+    want_loss, got_loss = [], []
+    for t in range(steps):
+        x, onehot = W.mlp_batch(t)
+        want_loss.append(net.step(x, onehot))
+        got_loss.append(trainer.step(dev(x), dev(onehot)).cpu().numpy())
+    ctx.check_device_status()
+    assert rel(np.stack(got_loss), np.stack(want_loss)) <= tol
+    for l in range(3):
+        assert rel(trainer.W[l].cpu().numpy(), net.W[l]) <= tol
+        assert rel(trainer.b[l].cpu().numpy(), net.b[l]) <= max(tol, 1e-5)
+    # the loss falls: the step trains
+    assert np.mean(got_loss[-1]) < np.mean(got_loss[0])
+
+
+def test_mlp_fixture_from_reference_build(ctx):
+    """Three steps against the fixture produced by the reference's own CPU leaves."""
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "dense_golden.npz"))
+    Ws, bs = W.mlp_init(0)
+    trainer = mlp.MlpTrainer(ctx, Ws, bs, 0.01, mode=L.MODE_TF32X3)
+    losses = []
+    for t in range(3):
+        x, onehot = W.mlp_batch(t)
+        losses.append(trainer.step(dev(x), dev(onehot)).cpu().numpy())
+    assert rel(np.stack(losses), gold["mlp_loss3"]) <= 1e-5
+    assert rel(trainer.W[2].cpu().numpy(), gold["mlp_w2_after3"]) <= 1e-5
+    assert rel(trainer.b[0].cpu().numpy(), gold["mlp_b0_after3"]) <= 1e-5
