@@ -181,6 +181,33 @@ int sb200_csr_free(sb200_csr* C);
 int sb200_csr_copy_out(const sb200_csr* src, uint32_t* row, uint32_t* col, float* val,
                        int to_host, sb200_stream stream);
 
+/*
+ * Column sums for callers that cannot allocate: out[n] = scale * sum_k op(B)[k, n],
+ * the bias-gradient part of sb200_gemm_batched on its own (same kernels, same
+ * meaning of transB / ldb; B and out are device pointers of the CURRENT device).
+ * This entry point has no counterpart in the reference; it exists for callers
+ * that must not cause a device allocation -- code running underneath an
+ * allocator that assumes it owns the GPU's free memory (Sapphire's
+ * ResourceManager pools, a framework's caching allocator), and code on a
+ * latency path, since cudaMalloc / cudaFree synchronise the device.  It takes
+ * no context (creating one allocates) and calls no cudaMalloc, cudaFree or
+ * allocating library routine: its scratch for the per-slice partial sums is a
+ * fixed 4 MiB array inside the library image, present on every GPU that loads
+ * the library until the process exits.
+ *   Limit: N <= SB200_COLSUM_NOALLOC_MAX_N columns (SB200_ERR_TOO_LARGE beyond);
+ *   K is unlimited.
+ *   The first call on each device looks up the array's device address
+ *   (cudaGetSymbolAddress) and the SM count; make that first call before any
+ *   stream capture begins.
+ *   All calls on a device share the one array.  Nothing needs clearing between
+ *   calls (each call overwrites every cell it later reads), but two calls whose
+ *   kernels overlap on the GPU -- different streams, no dependency -- race on it:
+ *   order them.
+ */
+#define SB200_COLSUM_NOALLOC_MAX_N 16384
+int sb200_colsum_noalloc(const float* B, int transB, int64_t K, int64_t N, int64_t ldb,
+                         float* out, float scale, sb200_stream stream);
+
 /* ---- elementwise steps of a Linear training step -------------------------
  * The kernels either side of the GEMMs when Sapphire trains an MLP; same
  * argument meaning as the reference's device leaves.  All pointers are device
