@@ -2,7 +2,7 @@
 """Benchmark of the matrix-multiplication path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload dense_tf32|dense_tf32x3|dense4000_tf32|linear_bwd|spgemm|spgemm_zipf]
+                    [--workload dense_tf32|dense_tf32x3|dense4000_tf32|linear_bwd|spgemm|spgemm_zipf|mlp]
                     [--no-extras]
 
 One JSON line on stdout (rank 0).  The headline workload is the large batched
@@ -326,6 +326,23 @@ def main():
                             "linear backward dY[8192x4096] X[8192x4096] W[4096x4096]",
                 "ms_per_step": ms, "tflops_per_gpu": flops / ms / 1e9, "gpu_launches": launches}
 
+    def bench_mlp(steps, warmup):
+        """BASELINE config 2: 784-512-256-10 MLP, global batch 64 split over the
+        ranks (strong scaling), one flat gradient allreduce per step.  lr 1e-4: at
+        0.01 Sapphire's un-normalised gradients leave the finite range by step 3."""
+        from sapphire_b200 import mlp as M
+        Ws, bs = W.mlp_init(0)
+        trainer = M.MlpTrainer(ctx, Ws, bs, 1e-4, mode=L.MODE_TF32, world=world)
+        per = 64 // world
+        x, onehot = W.mlp_batch(0)
+        xs = torch.from_numpy(x[rank * per:(rank + 1) * per]).to(dev)
+        ys = torch.from_numpy(onehot[rank * per:(rank + 1) * per]).to(dev)
+        ms, launches = timed(lambda: trainer.step(xs, ys), steps, warmup)
+        flops = 3 * 2.0 * 64 * sum(i * o for i, o in zip(W.MLP_WIDTHS[:-1], W.MLP_WIDTHS[1:]))
+        return {"workload": f"MLP 784-512-256-10 SGD step, global batch 64 over {world} rank(s), "
+                            "gradient allreduce inside", "ms_per_step": ms,
+                "gflops_total": flops / ms / 1e6, "gpu_launches": launches}
+
     # ------------------------------------------------------------- headline
     if args.workload in DENSE:
         n, mode = DENSE[args.workload]
@@ -376,6 +393,13 @@ def main():
                              "unit": "TFLOP/s", "frac": r["tflops_per_gpu"] / tf32_peak,
                              "traffic": None},
                 "gpu_launches": r["gpu_launches"]}
+    elif args.workload == "mlp":
+        r = bench_mlp(args.steps, args.warmup)
+        line = {"metric": "MLP training step time", "value": r["ms_per_step"], "unit": "ms/step",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": r["ms_per_step"], "higher_is_better": False, "scaling": "strong",
+                "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+                "config": {"workload": r["workload"]}, "gpu_launches": r["gpu_launches"]}
     else:
         raise SystemExit(f"unknown workload {args.workload}")
 
@@ -389,6 +413,7 @@ def main():
         extras.append(bench_linear_bwd(10, 3))
         extras.append(bench_spgemm("poisson", 5, 3))
         extras.append(bench_spgemm("zipf", 5, 3))
+        extras.append(bench_mlp(50, 5))
         line["other_workloads"] = extras
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
