@@ -44,40 +44,50 @@ struct Csr {
 };
 
 struct Work {
-    uint32_t* prod;        // [M] scalar products per row, saturating
     uint32_t* cnt;         // [M] nnz of each output row
+    uint32_t* bq;          // [nnzA] for every nonzero (i,k) of A: where B's row k starts
+    uint32_t* blen;        // [nnzA] ... and its length
+    uint4* rows_mid;       // [M] {row, first nonzero, end nonzero, products} per CTA-path row
+    uint4* rows_heavy;     // [M] the same for rows with many products (queued first)
     uint32_t* list_tiny;   // [M]
-    uint32_t* list_mid;    // [M]
-    uint32_t* list_heavy;  // [M]
     uint32_t* counters;    // [4]: tiny, mid, heavy, unused
 };
 
 // ------------------------------------------------------------ row work
+// One warp per row of A: records where each nonzero's row of B lies (so that
+// the row kernels read it with one coalesced load instead of a dependent
+// gather), counts the row's scalar products and queues the row in its bin.
+// In the numeric pass (rowC given) a row whose output is wider than the small
+// value buffer also goes to the heavy bin, whose kernel has a large one.
 __global__ void __launch_bounds__(256)
-row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w)
+row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
+                    const uint32_t* __restrict__ rowC)
 {
     const int lane = threadIdx.x & 31;
     const uint32_t warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const uint32_t nwarps = (gridDim.x * blockDim.x) >> 5;
     for (uint32_t i = warp_global; i < A.M; i += nwarps) {
         unsigned long long s = 0;
-        for (uint32_t p = A.row[i] + lane; p < A.row[i + 1]; p += 32) {
+        const uint32_t pa = A.row[i], pe = A.row[i + 1];
+        for (uint32_t p = pa + lane; p < pe; p += 32) {
             const uint32_t k = A.col[p];
-            s += rowB[k + 1] - rowB[k];
+            const uint32_t q0 = rowB[k], q1 = rowB[k + 1];
+            w.bq[p] = q0;
+            w.blen[p] = q1 - q0;
+            s += q1 - q0;
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (lane == 0) {
             const uint32_t P = s > 0xffffffffull ? 0xffffffffu : static_cast<uint32_t>(s);
-            w.prod[i] = P;
             if (P == 0) {
                 w.cnt[i] = 0;
             } else if (P <= TINY_MAX) {
                 w.list_tiny[atomicAdd(&w.counters[0], 1u)] = i;
-            } else if (P < HEAVY_MIN) {
-                w.list_mid[atomicAdd(&w.counters[1], 1u)] = i;
+            } else if (P < HEAVY_MIN && !(rowC && rowC[i + 1] - rowC[i] > VAL_CAP)) {
+                w.rows_mid[atomicAdd(&w.counters[1], 1u)] = make_uint4(i, pa, pe, P);
             } else {
-                w.list_heavy[atomicAdd(&w.counters[2], 1u)] = i;
+                w.rows_heavy[atomicAdd(&w.counters[2], 1u)] = make_uint4(i, pa, pe, P);
             }
         }
     }
@@ -190,17 +200,18 @@ tiny_rows_kernel(Csr A, Csr B, Work w, const uint32_t* __restrict__ rowC,
 constexpr int A_CHUNK = 512;             // nonzeros of A's row staged in shared memory at a time
 constexpr int WALK_UNROLL = 4;           // independent loads in flight per thread
 
-// Per-chunk staging of A's row: for nonzero p of the chunk, where B's row
-// starts (qs), the running count of products before it (pref) and A's value.
+// Shared-memory staging of a chunk of A's row.
 struct RowChunk {
-    uint32_t* qs;      // [A_CHUNK]
-    uint32_t* pref;    // [A_CHUNK + 1]
-    float* aval;       // [A_CHUNK]   (numeric only)
+    uint32_t* qs;      // [A_CHUNK]     start of B's row
+    uint32_t* len;     // [A_CHUNK]     its length
+    float* aval;       // [A_CHUNK]     A's value (numeric only)
 };
 
+template <int THREADS>
 __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s_warp,
                                                          uint32_t& total)
 {
+    constexpr int NWARPS = THREADS / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t incl = v;
 #pragma unroll
@@ -213,7 +224,7 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s
     __syncthreads();
     uint32_t warp_off = 0, tot = 0;
 #pragma unroll
-    for (int i = 0; i < ROW_THREADS / 32; ++i) {
+    for (int i = 0; i < NWARPS; ++i) {
         const uint32_t x = s_warp[i];
         if (i < warp) warp_off += x;
         tot += x;
@@ -222,104 +233,60 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s
     return warp_off + incl - v;
 }
 
-// Stages nonzeros [p0, p0 + n) of A's row i and returns the chunk's product count.
-template <bool NUMERIC>
-__device__ __forceinline__ uint32_t load_chunk(const Csr& A, const Csr& B, uint32_t p0, uint32_t n,
-                                               const RowChunk& ch, uint32_t* s_warp)
+// Copies nonzeros [p0, p0 + n) of A's row into shared memory (coalesced reads
+// of the arrays the row-work kernel prepared).  No barrier inside.
+template <int THREADS, bool NUMERIC>
+__device__ __forceinline__ void stage_chunk(const Csr& A, const Work& w, uint32_t p0, uint32_t n,
+                                            const RowChunk& ch)
 {
-    // two nonzeros per thread (A_CHUNK == 2 * ROW_THREADS)
-    uint32_t len[2], qs[2];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        const uint32_t e = threadIdx.x * 2 + u;
-        len[u] = 0;
-        qs[u] = 0;
-        if (e < n) {
-            const uint32_t k = A.col[p0 + e];
-            qs[u] = B.row[k];
-            len[u] = B.row[k + 1] - qs[u];
-            if (NUMERIC) ch.aval[e] = A.val[p0 + e];
-        }
+    for (uint32_t e = threadIdx.x; e < n; e += THREADS) {
+        ch.qs[e] = w.bq[p0 + e];
+        ch.len[e] = w.blen[p0 + e];
+        if (NUMERIC) ch.aval[e] = A.val[p0 + e];
     }
-    uint32_t total;
-    const uint32_t off = block_exclusive_scan(len[0] + len[1], s_warp, total);
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        const uint32_t e = threadIdx.x * 2 + u;
-        if (e < n) {
-            ch.qs[e] = qs[u];
-            ch.pref[e] = off + (u ? len[0] : 0);
-        }
-    }
-    if (threadIdx.x == 0) ch.pref[n] = total;
-    __syncthreads();
-    return total;
 }
 
 // Calls f(column, a_value * b_value) for every product of the staged chunk.
-//
-// Two schedules, chosen per chunk by the mean length of B's rows:
-//  * rows of B of 16+ entries: one warp per nonzero of A, lanes stride B's row
-//    with four loads in flight; no search, ~10 instructions per product;
-//  * short rows: product t of the chunk belongs to the nonzero p with
-//    pref[p] <= t < pref[p+1] (binary search); thread tid takes t = tid,
-//    tid + 256, ... so that no lane idles on a one-entry row.
-template <bool NUMERIC, typename F>
-__device__ __forceinline__ void walk_chunk(const Csr& B, const RowChunk& ch, uint32_t n,
-                                           uint32_t total, F f)
+//  * rows of B with more than SHORT_ROW entries: one warp per nonzero of A, lanes
+//    stride B's row with four loads in flight;
+//  * shorter rows: one thread per nonzero, so that a warp is not spent on a
+//    one-entry row (power-law matrices are mostly such rows).
+constexpr uint32_t SHORT_ROW = 8;
+
+template <int THREADS, bool NUMERIC, typename F>
+__device__ __forceinline__ void walk_chunk(const Csr& B, const RowChunk& ch, uint32_t n, F f)
 {
-    if (total >= 16u * n) {
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-        for (uint32_t p = warp; p < n; p += ROW_THREADS / 32) {
-            const uint32_t qs = ch.qs[p];
-            const uint32_t len = ch.pref[p + 1] - ch.pref[p];
-            const float av = NUMERIC ? ch.aval[p] : 0.0f;
-            for (uint32_t o = lane; o < len; o += 32 * WALK_UNROLL) {
-                uint32_t col[WALK_UNROLL];
-                float bv[WALK_UNROLL];
-#pragma unroll
-                for (int u = 0; u < WALK_UNROLL; ++u) {
-                    if (o + 32 * u < len) {
-                        col[u] = __ldg(B.col + qs + o + 32 * u);
-                        if (NUMERIC) bv[u] = __ldg(B.val + qs + o + 32 * u);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < WALK_UNROLL; ++u)
-                    if (o + 32 * u < len) f(col[u], NUMERIC ? __fmul_rn(av, bv[u]) : 0.0f);
-            }
+    constexpr int NWARPS = THREADS / 32;
+    for (uint32_t e = threadIdx.x; e < n; e += THREADS) {
+        const uint32_t len = ch.len[e];
+        if (len <= SHORT_ROW) {
+            const uint32_t qs = ch.qs[e];
+            const float av = NUMERIC ? ch.aval[e] : 0.0f;
+            for (uint32_t q = 0; q < len; ++q)
+                f(__ldg(B.col + qs + q), NUMERIC ? __fmul_rn(av, __ldg(B.val + qs + q)) : 0.0f);
         }
-        return;
     }
-    uint32_t p = 0;
-    for (uint32_t base = threadIdx.x; base < total; base += ROW_THREADS * WALK_UNROLL) {
-        uint32_t q[WALK_UNROLL], col[WALK_UNROLL];
-        float av[WALK_UNROLL], bv[WALK_UNROLL];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t p = warp; p < n; p += NWARPS) {
+        const uint32_t len = ch.len[p];
+        if (len <= SHORT_ROW)
+            continue;
+        const uint32_t qs = ch.qs[p];
+        const float av = NUMERIC ? ch.aval[p] : 0.0f;
+        for (uint32_t o = lane; o < len; o += 32 * WALK_UNROLL) {
+            uint32_t col[WALK_UNROLL];
+            float bv[WALK_UNROLL];
 #pragma unroll
-        for (int u = 0; u < WALK_UNROLL; ++u) {
-            const uint32_t t = base + u * ROW_THREADS;
-            q[u] = 0xffffffffu;
-            if (t < total) {
-                uint32_t lo = p, hi = n;            // pref[lo] <= t < pref[hi]
-                while (hi - lo > 1) {
-                    const uint32_t mid = (lo + hi) >> 1;
-                    if (ch.pref[mid] <= t) lo = mid; else hi = mid;
+            for (int u = 0; u < WALK_UNROLL; ++u) {
+                if (o + 32 * u < len) {
+                    col[u] = __ldg(B.col + qs + o + 32 * u);
+                    if (NUMERIC) bv[u] = __ldg(B.val + qs + o + 32 * u);
                 }
-                p = lo;
-                q[u] = ch.qs[p] + (t - ch.pref[p]);
-                if (NUMERIC) av[u] = ch.aval[p];
             }
-        }
 #pragma unroll
-        for (int u = 0; u < WALK_UNROLL; ++u) {
-            if (q[u] != 0xffffffffu) {
-                col[u] = __ldg(B.col + q[u]);
-                if (NUMERIC) bv[u] = __ldg(B.val + q[u]);
-            }
+            for (int u = 0; u < WALK_UNROLL; ++u)
+                if (o + 32 * u < len) f(col[u], NUMERIC ? __fmul_rn(av, bv[u]) : 0.0f);
         }
-#pragma unroll
-        for (int u = 0; u < WALK_UNROLL; ++u)
-            if (q[u] != 0xffffffffu) f(col[u], NUMERIC ? __fmul_rn(av[u], bv[u]) : 0.0f);
     }
 }
 
@@ -331,50 +298,68 @@ __device__ __forceinline__ void walk_chunk(const Csr& B, const RowChunk& ch, uin
 //       prefix-sum its popcounts so that rank(j) = prefix[j / 32] +
 //       popc(bits below j) is the position of column j in the sorted output row,
 //       emit the columns in bitmap order, then accumulate every product at its rank.
-template <bool NUMERIC, bool FROM_PATTERN>
-__global__ void __launch_bounds__(ROW_THREADS, 4)
-cta_rows_kernel(Csr A, Csr B, Work w, uint32_t words, uint32_t* __restrict__ pattern,
+// The bitmap is split into one contiguous range of `wpw` words per warp; inside
+// a range lane l owns words l, l + 32, ... so every shared-memory access of the
+// scans is conflict-free and the prefix needs only warp shuffles.
+template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN>
+__global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
+cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
+                const uint32_t* __restrict__ n_rows_ptr, uint32_t words, uint32_t wpw,
+                uint32_t val_cap, uint32_t* __restrict__ pattern,
                 const uint32_t* __restrict__ rowC, uint32_t* __restrict__ colC,
                 float* __restrict__ valC)
 {
+    constexpr int NWARPS = THREADS / 32;
     extern __shared__ uint32_t sm[];
-    // symbolic: bitmap[words]; numeric: packed[words] = {bits, prefix}
+    const uint32_t padded = wpw * NWARPS;                        // >= words
+    // symbolic: bitmap[padded]; numeric: packed[padded] = {bits, prefix}
     uint32_t* bitmap = sm;
     uint2* packed = reinterpret_cast<uint2*>(sm);
-    uint32_t* after_map = sm + (NUMERIC ? 2 * words : words);
+    uint32_t* after_map = sm + (NUMERIC ? 2 * padded : padded);
     RowChunk ch;
-    ch.qs = after_map;                                           // [A_CHUNK]
-    ch.pref = ch.qs + A_CHUNK;                                   // [A_CHUNK + 1] (+ pad)
-    ch.aval = reinterpret_cast<float*>(ch.pref + A_CHUNK + 4);   // [A_CHUNK]   (numeric)
-    float* vals = ch.aval + A_CHUNK;                             // [VAL_CAP]   (numeric)
-    __shared__ uint32_t s_warp[ROW_THREADS / 32];
+    ch.qs = after_map;
+    ch.len = ch.qs + A_CHUNK;
+    ch.aval = reinterpret_cast<float*>(ch.len + A_CHUNK);
+    float* vals = ch.aval + A_CHUNK;                             // [val_cap]   (numeric)
+    __shared__ uint32_t s_warp[NWARPS];
+    __shared__ uint32_t s_tot[NWARPS];
 
-    const uint32_t n_heavy = w.counters[2];
-    const uint32_t n_rows = n_heavy + w.counters[1];
-    const uint32_t per_thread = (words + ROW_THREADS - 1) / ROW_THREADS;
-    const uint32_t w_lo = threadIdx.x * per_thread;
-    const uint32_t w_hi = min(w_lo + per_thread, words);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t n_rows = *n_rows_ptr;
+    const uint32_t wbase = warp * wpw;                           // this warp's word range
+
+    auto bits_at = [&](uint32_t x) -> uint32_t { return NUMERIC ? packed[x].x : bitmap[x]; };
 
     for (uint32_t idx = blockIdx.x; idx < n_rows; idx += gridDim.x) {
-        const uint32_t i = idx < n_heavy ? w.list_heavy[idx] : w.list_mid[idx - n_heavy];
-        const uint32_t pa = A.row[i], pe = A.row[i + 1];
-        const bool one_chunk = (pe - pa) <= A_CHUNK;
-        uint32_t chunk_total = 0;
-        uint32_t mine = 0;                                       // set bits in this thread's words
+        const uint4 d = rows[idx];
+        const uint32_t i = d.x, pa = d.y, pe = d.z;
+        const uint32_t nnzA = pe - pa;
+        const bool one_chunk = nnzA <= A_CHUNK;
+        const uint32_t out0 = NUMERIC ? rowC[i] : 0;
+
+        const uint32_t n0 = min(static_cast<uint32_t>(A_CHUNK), nnzA);
+        stage_chunk<THREADS, NUMERIC>(A, w, pa, n0, ch);
+        if (NUMERIC && FROM_PATTERN) {
+            const uint32_t* src = pattern + static_cast<size_t>(i) * words;
+            for (uint32_t x = threadIdx.x; x < padded; x += THREADS)
+                packed[x].x = x < words ? src[x] : 0u;
+        } else if (NUMERIC) {
+            for (uint32_t x = threadIdx.x; x < padded; x += THREADS)
+                packed[x] = make_uint2(0u, 0u);
+        } else {
+            for (uint32_t x = threadIdx.x; x < padded; x += THREADS) bitmap[x] = 0;
+        }
+        __syncthreads();
 
         if (!(NUMERIC && FROM_PATTERN)) {
             // ---- pattern: mark every product's column
-            if (NUMERIC) {
-                for (uint32_t x = threadIdx.x; x < words; x += ROW_THREADS)
-                    packed[x] = make_uint2(0u, 0u);
-            } else {
-                for (uint32_t x = threadIdx.x; x < words; x += ROW_THREADS) bitmap[x] = 0;
-            }
-            __syncthreads();
             for (uint32_t p0 = pa; p0 < pe; p0 += A_CHUNK) {
                 const uint32_t n = min(static_cast<uint32_t>(A_CHUNK), pe - p0);
-                chunk_total = load_chunk<NUMERIC>(A, B, p0, n, ch, s_warp);
-                walk_chunk<false>(B, ch, n, chunk_total, [&](uint32_t j, float) {
+                if (p0 != pa) {
+                    stage_chunk<THREADS, NUMERIC>(A, w, p0, n, ch);
+                    __syncthreads();
+                }
+                walk_chunk<THREADS, false>(B, ch, n, [&](uint32_t j, float) {
                     if (NUMERIC)
                         atomicOr(&packed[j >> 5].x, 1u << (j & 31));
                     else
@@ -383,39 +368,55 @@ cta_rows_kernel(Csr A, Csr B, Work w, uint32_t words, uint32_t* __restrict__ pat
                 __syncthreads();
             }
             if (!NUMERIC && pattern) {
-                // lane-contiguous copy: full 128-byte lines per warp
                 uint32_t* dst = pattern + static_cast<size_t>(i) * words;
-                for (uint32_t x = threadIdx.x; x < words; x += ROW_THREADS) dst[x] = bitmap[x];
+                for (uint32_t x = threadIdx.x; x < words; x += THREADS) dst[x] = bitmap[x];
             }
-            for (uint32_t x = w_lo; x < w_hi; ++x)
-                mine += __popc(NUMERIC ? packed[x].x : bitmap[x]);
-        } else {
-            // ---- pattern kept by the symbolic pass
-            const uint32_t* src = pattern + static_cast<size_t>(i) * words;
-            for (uint32_t x = threadIdx.x; x < words; x += ROW_THREADS) packed[x].x = src[x];
-            __syncthreads();
-            for (uint32_t x = w_lo; x < w_hi; ++x) mine += __popc(packed[x].x);
         }
-        uint32_t total;
-        uint32_t run = block_exclusive_scan(mine, s_warp, total);
+
+        // ---- popcounts: warp-local running prefix over this warp's word range
+        uint32_t carry = 0;
+        for (uint32_t m = 0; m < wpw; m += 32) {
+            const uint32_t x = wbase + m + lane;
+            const uint32_t c = __popc(bits_at(x));
+            uint32_t incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            if (NUMERIC) packed[x].y = carry + incl - c;          // relative to the warp's range
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) s_tot[warp] = carry;
+        __syncthreads();
+        uint32_t woff = 0, total = 0;
+#pragma unroll
+        for (int v = 0; v < NWARPS; ++v) {
+            const uint32_t t = s_tot[v];
+            if (v < warp) woff += t;
+            total += t;
+        }
         if (!NUMERIC) {
             if (threadIdx.x == 0) w.cnt[i] = total;
-            __syncthreads();
+            __syncthreads();                                      // s_tot, bitmap reused next row
             continue;
         }
-        const uint32_t out0 = rowC[i];
-        const bool in_smem = total <= VAL_CAP;
-        // columns come out ascending: word order, then bit order.  They are
-        // staged in the (not yet used) value buffer so that the global store is
-        // lane-contiguous; rows wider than the buffer store them directly.
+
+        // ---- columns: ascending = word order, then bit order.  Staged in the (not
+        // yet used) value buffer so that the global store is lane-contiguous; rows
+        // wider than the buffer store them directly.
+        const bool staged = total <= val_cap;
         uint32_t* stage = reinterpret_cast<uint32_t*>(vals);
-        for (uint32_t x = w_lo; x < w_hi; ++x) {
-            uint32_t bits = packed[x].x;
-            packed[x].y = run;
+        for (uint32_t m = 0; m < wpw; m += 32) {
+            const uint32_t x = wbase + m + lane;
+            uint2 wp = packed[x];
+            wp.y += woff;
+            packed[x].y = wp.y;
+            uint32_t bits = wp.x, run = wp.y;
             while (bits) {
                 const int bpos = __ffs(bits) - 1;
                 bits &= bits - 1;
-                if (in_smem)
+                if (staged)
                     stage[run] = x * 32 + bpos;
                 else
                     colC[out0 + run] = x * 32 + bpos;
@@ -423,30 +424,33 @@ cta_rows_kernel(Csr A, Csr B, Work w, uint32_t words, uint32_t* __restrict__ pat
             }
         }
         __syncthreads();
-        if (in_smem) {
-            for (uint32_t x = threadIdx.x; x < total; x += ROW_THREADS) {
-                colC[out0 + x] = stage[x];
-                vals[x] = 0.0f;                    // same word, same thread: no hazard
-            }
-        } else {
-            for (uint32_t x = threadIdx.x; x < total; x += ROW_THREADS) valC[out0 + x] = 0.0f;
-        }
-        __syncthreads();
-        // ---- values: accumulate every product at the rank of its column
-        float* acc = in_smem ? vals : (valC + out0);
-        for (uint32_t p0 = pa; p0 < pe; p0 += A_CHUNK) {
-            const uint32_t n = min(static_cast<uint32_t>(A_CHUNK), pe - p0);
-            if (FROM_PATTERN || !one_chunk)
-                chunk_total = load_chunk<NUMERIC>(A, B, p0, n, ch, s_warp);
-            walk_chunk<true>(B, ch, n, chunk_total, [&](uint32_t j, float prod) {
-                const uint2 wp = packed[j >> 5];
-                const uint32_t rank = wp.y + __popc(wp.x & ((1u << (j & 31)) - 1u));
-                atomicAdd(&acc[rank], prod);
-            });
+        if (staged)
+            for (uint32_t x = threadIdx.x; x < total; x += THREADS) colC[out0 + x] = stage[x];
+
+        // ---- values: accumulate every product at the rank of its column.  Rows
+        // with more output entries than the value buffer take one pass over the
+        // products per buffer-sized window of ranks.
+        for (uint32_t r0 = 0; r0 < total; r0 += val_cap) {
+            const uint32_t span = min(val_cap, total - r0);
             __syncthreads();
+            for (uint32_t x = threadIdx.x; x < span; x += THREADS) vals[x] = 0.0f;
+            __syncthreads();
+            for (uint32_t p0 = pa; p0 < pe; p0 += A_CHUNK) {
+                const uint32_t n = min(static_cast<uint32_t>(A_CHUNK), pe - p0);
+                if (!one_chunk) {
+                    __syncthreads();
+                    stage_chunk<THREADS, NUMERIC>(A, w, p0, n, ch);
+                    __syncthreads();
+                }
+                walk_chunk<THREADS, true>(B, ch, n, [&](uint32_t j, float prod) {
+                    const uint2 wp = packed[j >> 5];
+                    const uint32_t rank = wp.y + __popc(wp.x & ((1u << (j & 31)) - 1u)) - r0;
+                    if (rank < span) atomicAdd(&vals[rank], prod);
+                });
+            }
+            __syncthreads();
+            for (uint32_t x = threadIdx.x; x < span; x += THREADS) valC[out0 + r0 + x] = vals[x];
         }
-        if (in_smem)
-            for (uint32_t x = threadIdx.x; x < total; x += ROW_THREADS) valC[out0 + x] = vals[x];
         __syncthreads();
     }
 }
@@ -489,8 +493,7 @@ row_scan_kernel(const uint32_t* __restrict__ cnt, uint32_t M, uint32_t* __restri
 struct Plan {
     Csr A, B;
     Work w;
-    uint32_t words;
-    size_t smem_symbolic, smem_numeric;
+    uint32_t words;             // bitmap words per row
     unsigned long long* d_total;
     uint32_t* pattern;          // [M][words] row bitmaps kept between the passes, or null
 };
@@ -507,40 +510,41 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
         return SB200_ERR_TOO_LARGE;
     pl->A = Csr{A->ROW, A->COL, A->V, A->M, A->N};
     pl->B = Csr{B->ROW, B->COL, B->V, B->M, B->N};
-    const size_t M = A->M;
-    const size_t words32 = 5 * M + 8;        // prod, cnt, 3 lists, counters
-    const int rc = ensure_workspace(ctx, words32 * 4 + 16);
+    const size_t M = A->M, nnzA = A->NNZ;
+    // cnt[M] | bq[nnzA] | blen[nnzA] | list_tiny[M] | counters[4] | total (8 B) | pad |
+    // rows_mid[M] (16 B each) | rows_heavy[M]
+    const size_t head_words = (2 * M + 2 * nnzA + 4 + 2 + 3) & ~static_cast<size_t>(3);
+    const size_t bytes = head_words * 4 + 2 * M * sizeof(uint4) + 64;
+    const int rc = ensure_workspace(ctx, bytes);
     if (rc)
         return rc;
     uint32_t* base = reinterpret_cast<uint32_t*>(ctx->d_workspace);
-    pl->w.prod = base;
-    pl->w.cnt = base + M;
-    pl->w.list_tiny = base + 2 * M;
-    pl->w.list_mid = base + 3 * M;
-    pl->w.list_heavy = base + 4 * M;
-    pl->w.counters = base + 5 * M;
-    pl->d_total = reinterpret_cast<unsigned long long*>(base + 5 * M + 4);
-    // keep the 64-bit total 8-byte aligned
-    if (reinterpret_cast<uintptr_t>(pl->d_total) & 7)
-        pl->d_total = reinterpret_cast<unsigned long long*>(base + 5 * M + 5);
+    pl->w.cnt = base;
+    pl->w.bq = base + M;
+    pl->w.blen = base + M + nnzA;
+    pl->w.list_tiny = base + M + 2 * nnzA;
+    pl->w.counters = base + 2 * M + 2 * nnzA;
+    uintptr_t tot = reinterpret_cast<uintptr_t>(pl->w.counters + 4);
+    tot = (tot + 7) & ~static_cast<uintptr_t>(7);
+    pl->d_total = reinterpret_cast<unsigned long long*>(tot);
+    uintptr_t desc = (reinterpret_cast<uintptr_t>(base + head_words) + 15) & ~static_cast<uintptr_t>(15);
+    pl->w.rows_mid = reinterpret_cast<uint4*>(desc);
+    pl->w.rows_heavy = pl->w.rows_mid + M;
     pl->words = (B->N + 31) / 32;
     if (pl->words == 0)
         pl->words = 1;
-    const size_t chunk_bytes = (3 * A_CHUNK + 4) * 4;   // qs, pref (+pad), aval
     pl->pattern = nullptr;
-    pl->smem_symbolic = static_cast<size_t>(pl->words) * 4 + chunk_bytes;
-    pl->smem_numeric = static_cast<size_t>(pl->words) * 8 + chunk_bytes + VAL_CAP * 4;
     return SB200_OK;
 }
 
-int bin_rows(sb200_ctx* ctx, const Plan& pl, cudaStream_t stream)
+int bin_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, cudaStream_t stream)
 {
     if (cudaMemsetAsync(pl.w.counters, 0, 16, stream) != cudaSuccess)
         return SB200_ERR_CUDA;
     if (pl.A.M == 0)
         return SB200_OK;
     const unsigned blocks = static_cast<unsigned>(ctx->sm_count) * 8;
-    row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w);
+    row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w, rowC);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
@@ -580,27 +584,53 @@ int prepare_pattern(sb200_ctx* ctx, Plan* pl, const sb200_csr* A, const sb200_cs
     return SB200_OK;
 }
 
+constexpr int HEAVY_THREADS = 1024;
+constexpr uint32_t HEAVY_VAL_CAP = 40960;     // 160 KB of fp32 accumulators, one CTA per SM
+
+template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN>
+int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_t* n_rows,
+                uint32_t val_cap, const uint32_t* rowC, uint32_t* colC, float* valC,
+                cudaStream_t stream)
+{
+    constexpr int NWARPS = THREADS / 32;
+    const uint32_t wpw = ((pl.words + NWARPS - 1) / NWARPS + 31) & ~31u;
+    const size_t padded = static_cast<size_t>(wpw) * NWARPS;
+    const size_t chunk_bytes = 3 * A_CHUNK * 4;                // qs, len, aval
+    const size_t smem = NUMERIC ? padded * 8 + chunk_bytes + static_cast<size_t>(val_cap) * 4
+                                : padded * 4 + chunk_bytes;
+    auto kern = cta_rows_kernel<THREADS, MIN_BLOCKS, NUMERIC, FROM_PATTERN>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+        return SB200_ERR_TOO_LARGE;                             // bitmap beyond shared memory
+    int per_sm = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem) !=
+            cudaSuccess || per_sm < 1)
+        per_sm = 1;
+    const unsigned grid = static_cast<unsigned>(ctx->sm_count) * per_sm;
+    kern<<<grid, THREADS, smem, stream>>>(pl.A, pl.B, pl.w, rows, n_rows, pl.words, wpw, val_cap,
+                                          pl.pattern, rowC, colC, valC);
+    ctx->launches += 1;
+    return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+}
+
 template <bool NUMERIC, bool FROM_PATTERN>
 int run_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, uint32_t* colC, float* valC,
              cudaStream_t stream)
 {
     if (pl.A.M == 0)
         return SB200_OK;
-    const size_t smem = NUMERIC ? pl.smem_numeric : pl.smem_symbolic;
-    auto kern = cta_rows_kernel<NUMERIC, FROM_PATTERN>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-        return SB200_ERR_CUDA;
-    int per_sm = 1;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, ROW_THREADS, smem) !=
-            cudaSuccess || per_sm < 1)
-        per_sm = 1;
-    const unsigned grid = static_cast<unsigned>(ctx->sm_count) * per_sm;
-    kern<<<grid, ROW_THREADS, smem, stream>>>(pl.A, pl.B, pl.w, pl.words, pl.pattern, rowC, colC,
-                                              valC);
+    // heavy rows first: 1024 threads and a large value buffer, one CTA per SM
+    int rc = launch_rows<HEAVY_THREADS, 1, NUMERIC, FROM_PATTERN>(
+        ctx, pl, pl.w.rows_heavy, pl.w.counters + 2, HEAVY_VAL_CAP, rowC, colC, valC, stream);
+    if (rc)
+        return rc;
+    rc = launch_rows<ROW_THREADS, 4, NUMERIC, FROM_PATTERN>(
+        ctx, pl, pl.w.rows_mid, pl.w.counters + 1, VAL_CAP, rowC, colC, valC, stream);
+    if (rc)
+        return rc;
     tiny_rows_kernel<NUMERIC><<<static_cast<unsigned>(ctx->sm_count) * 8, 256, 0, stream>>>(
         pl.A, pl.B, pl.w, rowC, colC, valC);
-    ctx->launches += 2;
+    ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
 
@@ -621,7 +651,7 @@ extern "C" int sb200_spgemm_csr_symbolic(sb200_ctx* ctx, const sb200_csr* A, con
         return rc;
     if (cudaSetDevice(ctx->device) != cudaSuccess)
         return SB200_ERR_CUDA;
-    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, stream)))
+    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, nullptr, stream)))
         return rc;
     if ((rc = run_rows<false, false>(ctx, pl, nullptr, nullptr, nullptr, stream)))
         return rc;
@@ -656,7 +686,7 @@ extern "C" int sb200_spgemm_csr_numeric(sb200_ctx* ctx, const sb200_csr* A, cons
         return rc;
     if (cudaSetDevice(ctx->device) != cudaSuccess)
         return SB200_ERR_CUDA;
-    if ((rc = bin_rows(ctx, pl, stream)))
+    if ((rc = bin_rows(ctx, pl, rowC, stream)))
         return rc;
     if (same_operands(ctx, A, B)) {
         pl.pattern = ctx->d_sp_pattern;
@@ -683,7 +713,7 @@ extern "C" int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_
     if (cudaMalloc(&C->ROW, (static_cast<size_t>(A->M) + 1) * 4) != cudaSuccess)
         return SB200_ERR_ALLOC;
     // symbolic: bins stay valid in the workspace for the numeric pass below
-    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, stream)) ||
+    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, nullptr, stream)) ||
         (rc = run_rows<false, false>(ctx, pl, nullptr, nullptr, nullptr, stream))) {
         sb200_csr_free(C);
         return rc;
@@ -706,6 +736,11 @@ extern "C" int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_
     if (cudaMalloc(&C->COL, n * 4) != cudaSuccess || cudaMalloc(&C->V, n * 4) != cudaSuccess) {
         sb200_csr_free(C);
         return SB200_ERR_ALLOC;
+    }
+    // bin again, now that the output row sizes are known
+    if ((rc = bin_rows(ctx, pl, C->ROW, stream))) {
+        sb200_csr_free(C);
+        return rc;
     }
     rc = pl.pattern ? run_rows<true, true>(ctx, pl, C->ROW, C->COL, C->V, stream)
                     : run_rows<true, false>(ctx, pl, C->ROW, C->COL, C->V, stream);
