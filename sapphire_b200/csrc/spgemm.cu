@@ -50,7 +50,7 @@ struct Work {
     uint4* rows_mid;       // [M] {row, first nonzero, end nonzero, products} per CTA-path row
     uint4* rows_heavy;     // [M] the same for rows with many products (queued first)
     uint32_t* list_tiny;   // [M]
-    uint32_t* counters;    // [4]: tiny, mid, heavy, unused
+    uint32_t* counters;    // [4]: tiny, mid, heavy, next row of the running row kernel
 };
 
 // ------------------------------------------------------------ row work
@@ -205,6 +205,8 @@ struct RowChunk {
     uint32_t* qs;      // [A_CHUNK]     start of B's row
     uint32_t* len;     // [A_CHUNK]     its length
     float* aval;       // [A_CHUNK]     A's value (numeric only)
+    uint32_t* longs;   // [A_CHUNK]     nonzeros whose row of B the whole CTA walks
+    uint32_t* n_long;  // [1]
 };
 
 template <int THREADS>
@@ -234,20 +236,26 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s
 }
 
 // Copies nonzeros [p0, p0 + n) of A's row into shared memory (coalesced reads
-// of the arrays the row-work kernel prepared).  No barrier inside.
+// of the arrays the row-work kernel prepared) and lists the ones whose row of B
+// is long enough for the whole CTA.  *ch.n_long must be zero on entry (a barrier
+// earlier); no barrier inside.
 template <int THREADS, bool NUMERIC>
 __device__ __forceinline__ void stage_chunk(const Csr& A, const Work& w, uint32_t p0, uint32_t n,
                                             const RowChunk& ch)
 {
     for (uint32_t e = threadIdx.x; e < n; e += THREADS) {
+        const uint32_t len = w.blen[p0 + e];
         ch.qs[e] = w.bq[p0 + e];
-        ch.len[e] = w.blen[p0 + e];
+        ch.len[e] = len;
         if (NUMERIC) ch.aval[e] = A.val[p0 + e];
+        if (len >= static_cast<uint32_t>(THREADS)) ch.longs[atomicAdd(ch.n_long, 1u)] = e;
     }
 }
 
 // Calls f(column, a_value * b_value) for every product of the staged chunk.
-//  * rows of B with more than SHORT_ROW entries: one warp per nonzero of A, lanes
+//  * rows of B of THREADS or more entries: the whole CTA strides the row (a
+//    4096-entry row would otherwise keep one warp busy while 31 wait);
+//  * rows with more than SHORT_ROW entries: one warp per nonzero of A, lanes
 //    stride B's row with four loads in flight;
 //  * shorter rows: one thread per nonzero, so that a warp is not spent on a
 //    one-entry row (power-law matrices are mostly such rows).
@@ -257,6 +265,24 @@ template <int THREADS, bool NUMERIC, typename F>
 __device__ __forceinline__ void walk_chunk(const Csr& B, const RowChunk& ch, uint32_t n, F f)
 {
     constexpr int NWARPS = THREADS / 32;
+    const uint32_t n_long = *ch.n_long;
+    for (uint32_t l = 0; l < n_long; ++l) {
+        const uint32_t e = ch.longs[l];
+        const uint32_t qs = ch.qs[e], len = ch.len[e];
+        const float av = NUMERIC ? ch.aval[e] : 0.0f;
+        for (uint32_t o = threadIdx.x; o < len; o += THREADS * 2) {
+            const bool second = o + THREADS < len;
+            const uint32_t c0 = __ldg(B.col + qs + o);
+            const uint32_t c1 = second ? __ldg(B.col + qs + o + THREADS) : 0u;
+            float v0 = 0.0f, v1 = 0.0f;
+            if (NUMERIC) {
+                v0 = __ldg(B.val + qs + o);
+                if (second) v1 = __ldg(B.val + qs + o + THREADS);
+            }
+            f(c0, NUMERIC ? __fmul_rn(av, v0) : 0.0f);
+            if (second) f(c1, NUMERIC ? __fmul_rn(av, v1) : 0.0f);
+        }
+    }
     for (uint32_t e = threadIdx.x; e < n; e += THREADS) {
         const uint32_t len = ch.len[e];
         if (len <= SHORT_ROW) {
@@ -269,7 +295,7 @@ __device__ __forceinline__ void walk_chunk(const Csr& B, const RowChunk& ch, uin
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (uint32_t p = warp; p < n; p += NWARPS) {
         const uint32_t len = ch.len[p];
-        if (len <= SHORT_ROW)
+        if (len <= SHORT_ROW || len >= static_cast<uint32_t>(THREADS))
             continue;
         const uint32_t qs = ch.qs[p];
         const float av = NUMERIC ? ch.aval[p] : 0.0f;
@@ -304,7 +330,8 @@ __device__ __forceinline__ void walk_chunk(const Csr& B, const RowChunk& ch, uin
 template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN>
 __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
-                const uint32_t* __restrict__ n_rows_ptr, uint32_t words, uint32_t wpw,
+                const uint32_t* __restrict__ n_rows_ptr, uint32_t* __restrict__ next_row,
+                uint32_t words, uint32_t wpw,
                 uint32_t val_cap, uint32_t* __restrict__ pattern,
                 const uint32_t* __restrict__ rowC, uint32_t* __restrict__ colC,
                 float* __restrict__ valC)
@@ -320,9 +347,12 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
     ch.qs = after_map;
     ch.len = ch.qs + A_CHUNK;
     ch.aval = reinterpret_cast<float*>(ch.len + A_CHUNK);
-    float* vals = ch.aval + A_CHUNK;                             // [val_cap]   (numeric)
-    __shared__ uint32_t s_warp[NWARPS];
+    ch.longs = reinterpret_cast<uint32_t*>(ch.aval + A_CHUNK);
+    float* vals = reinterpret_cast<float*>(ch.longs + A_CHUNK);  // [val_cap]   (numeric)
     __shared__ uint32_t s_tot[NWARPS];
+    __shared__ uint32_t s_n_long;
+    __shared__ uint32_t s_next;
+    ch.n_long = &s_n_long;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t n_rows = *n_rows_ptr;
@@ -330,7 +360,17 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
 
     auto bits_at = [&](uint32_t x) -> uint32_t { return NUMERIC ? packed[x].x : bitmap[x]; };
 
-    for (uint32_t idx = blockIdx.x; idx < n_rows; idx += gridDim.x) {
+    // Rows are handed out through a counter: their cost varies by an order of
+    // magnitude in the heavy bin, a fixed stride would leave SMs idle.
+    for (;;) {
+        if (threadIdx.x == 0) {
+            s_next = atomicAdd(next_row, 1u);
+            s_n_long = 0;
+        }
+        __syncthreads();
+        const uint32_t idx = s_next;
+        if (idx >= n_rows)
+            break;
         const uint4 d = rows[idx];
         const uint32_t i = d.x, pa = d.y, pe = d.z;
         const uint32_t nnzA = pe - pa;
@@ -356,6 +396,8 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
             for (uint32_t p0 = pa; p0 < pe; p0 += A_CHUNK) {
                 const uint32_t n = min(static_cast<uint32_t>(A_CHUNK), pe - p0);
                 if (p0 != pa) {
+                    if (threadIdx.x == 0) s_n_long = 0;          // previous walk ended at a barrier
+                    __syncthreads();
                     stage_chunk<THREADS, NUMERIC>(A, w, p0, n, ch);
                     __syncthreads();
                 }
@@ -438,6 +480,8 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
             for (uint32_t p0 = pa; p0 < pe; p0 += A_CHUNK) {
                 const uint32_t n = min(static_cast<uint32_t>(A_CHUNK), pe - p0);
                 if (!one_chunk) {
+                    __syncthreads();
+                    if (threadIdx.x == 0) s_n_long = 0;
                     __syncthreads();
                     stage_chunk<THREADS, NUMERIC>(A, w, p0, n, ch);
                     __syncthreads();
@@ -589,25 +633,38 @@ constexpr uint32_t HEAVY_VAL_CAP = 40960;     // 160 KB of fp32 accumulators, on
 
 template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN>
 int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_t* n_rows,
-                uint32_t val_cap, const uint32_t* rowC, uint32_t* colC, float* valC,
+                uint32_t* next_row, uint32_t val_cap, const uint32_t* rowC, uint32_t* colC, float* valC,
                 cudaStream_t stream)
 {
     constexpr int NWARPS = THREADS / 32;
     const uint32_t wpw = ((pl.words + NWARPS - 1) / NWARPS + 31) & ~31u;
     const size_t padded = static_cast<size_t>(wpw) * NWARPS;
-    const size_t chunk_bytes = 3 * A_CHUNK * 4;                // qs, len, aval
+    const size_t chunk_bytes = 4 * A_CHUNK * 4;                // qs, len, aval, longs
     const size_t smem = NUMERIC ? padded * 8 + chunk_bytes + static_cast<size_t>(val_cap) * 4
                                 : padded * 4 + chunk_bytes;
     auto kern = cta_rows_kernel<THREADS, MIN_BLOCKS, NUMERIC, FROM_PATTERN>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-        return SB200_ERR_TOO_LARGE;                             // bitmap beyond shared memory
-    int per_sm = 1;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem) !=
-            cudaSuccess || per_sm < 1)
-        per_sm = 1;
+    // attribute and occupancy of this instance, remembered per (device, smem size)
+    static thread_local int cached_dev = -1, cached_per_sm = 1;
+    static thread_local size_t cached_smem = 0;
+    if (cached_dev != ctx->device || cached_smem != smem) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)) != cudaSuccess) {
+            cudaGetLastError();
+            return SB200_ERR_TOO_LARGE;                         // bitmap beyond shared memory
+        }
+        int n = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, THREADS, smem) !=
+                cudaSuccess || n < 1)
+            n = 1;
+        cached_dev = ctx->device;
+        cached_smem = smem;
+        cached_per_sm = n;
+    }
+    const int per_sm = cached_per_sm;
     const unsigned grid = static_cast<unsigned>(ctx->sm_count) * per_sm;
-    kern<<<grid, THREADS, smem, stream>>>(pl.A, pl.B, pl.w, rows, n_rows, pl.words, wpw, val_cap,
+    if (cudaMemsetAsync(next_row, 0, 4, stream) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    kern<<<grid, THREADS, smem, stream>>>(pl.A, pl.B, pl.w, rows, n_rows, next_row, pl.words, wpw, val_cap,
                                           pl.pattern, rowC, colC, valC);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
@@ -621,11 +678,11 @@ int run_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, uint32_t* col
         return SB200_OK;
     // heavy rows first: 1024 threads and a large value buffer, one CTA per SM
     int rc = launch_rows<HEAVY_THREADS, 1, NUMERIC, FROM_PATTERN>(
-        ctx, pl, pl.w.rows_heavy, pl.w.counters + 2, HEAVY_VAL_CAP, rowC, colC, valC, stream);
+        ctx, pl, pl.w.rows_heavy, pl.w.counters + 2, pl.w.counters + 3, HEAVY_VAL_CAP, rowC, colC, valC, stream);
     if (rc)
         return rc;
     rc = launch_rows<ROW_THREADS, 4, NUMERIC, FROM_PATTERN>(
-        ctx, pl, pl.w.rows_mid, pl.w.counters + 1, VAL_CAP, rowC, colC, valC, stream);
+        ctx, pl, pl.w.rows_mid, pl.w.counters + 1, pl.w.counters + 3, VAL_CAP, rowC, colC, valC, stream);
     if (rc)
         return rc;
     tiny_rows_kernel<NUMERIC><<<static_cast<unsigned>(ctx->sm_count) * 8, 256, 0, stream>>>(
