@@ -79,8 +79,11 @@ int64_t sb200_launch_count(const sb200_ctx* ctx);
  *       high part is rounded to nearest TF32 and rewritten in shared memory.
  *   SB200_OPT_MERGE_MN_BOXES  1, the default: an operand tile whose contiguous
  *       dimension is M or N (extent a multiple of 32) is fetched by one 4-D TMA
- *       box; 0: by one 32 x 32 box per 32-element chunk. */
-enum { SB200_OPT_SPLIT_EXPLICIT_HI = 1, SB200_OPT_MERGE_MN_BOXES = 2 };
+ *       box; 0: by one 32 x 32 box per 32-element chunk.
+ *   SB200_OPT_CTA_PAIRS  1, the default: TF32 problems with at least one
+ *       256 x 256 tile per pair of SMs run on the two-CTA kernel (clusters of two,
+ *       tcgen05 cta_group::2); 0: always the one-CTA kernel. */
+enum { SB200_OPT_SPLIT_EXPLICIT_HI = 1, SB200_OPT_MERGE_MN_BOXES = 2, SB200_OPT_CTA_PAIRS = 3 };
 int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value);
 
 /* Reads (and clears) the device status word after synchronising the stream.
@@ -157,7 +160,8 @@ typedef struct sb200_csr {
  * host to size the output).
  * Replaces Sparse::Cuda::Gemm (Includes/Sapphire/compute/sparse/cuda/SparseGemm.cuh:16-41:
  * "Required memory is automatically allocated", caller frees), one matrix per call.
- * Limit: B->N <= 1048576 columns (SB200_ERR_TOO_LARGE beyond).
+ * Limit: B->N <= 524288 columns (SB200_ERR_TOO_LARGE beyond): a row's column bitmap and its
+ * prefix sums live in shared memory.
  */
 int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, sb200_csr* C,
                      sb200_stream stream);

@@ -17,6 +17,7 @@ MODE_TF32, MODE_TF32X3 = 0, 1
 PATH_AUTO, PATH_TCGEN05, PATH_SIMT = 0, 1, 2
 OPT_SPLIT_EXPLICIT_HI = 1
 OPT_MERGE_MN_BOXES = 2
+OPT_CTA_PAIRS = 3
 
 
 class Csr(C.Structure):

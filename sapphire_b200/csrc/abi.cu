@@ -54,6 +54,7 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->workspace_bytes = 0;
     ctx->split_explicit_hi = 0;
     ctx->merge_mn_boxes = 1;
+    ctx->use_cta_pairs = 1;
     ctx->encode_tiled = nullptr;
     ctx->d_sp_pattern = nullptr;
     ctx->sp_pattern_bytes = 0;
@@ -117,6 +118,9 @@ extern "C" int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value)
             return SB200_OK;
         case SB200_OPT_MERGE_MN_BOXES:
             ctx->merge_mn_boxes = value != 0;
+            return SB200_OK;
+        case SB200_OPT_CTA_PAIRS:
+            ctx->use_cta_pairs = value != 0;
             return SB200_OK;
         default:
             return SB200_ERR_INVALID_ARG;

@@ -48,6 +48,7 @@ struct sb200_ctx {
     size_t workspace_bytes;
     int split_explicit_hi;     // 3xTF32: rewrite the high part in shared memory too
     int merge_mn_boxes;        // fetch an MN-major tile with one 4-D TMA box when possible
+    int use_cta_pairs;         // large TF32 problems run on the two-CTA (cta_group::2) kernel
     void* encode_tiled;        // cuTensorMapEncodeTiled, resolved at context creation
     uint32_t* d_sp_pattern;    // sparse GEMM: row bitmaps kept from the symbolic pass
     size_t sp_pattern_bytes;
@@ -60,6 +61,9 @@ namespace sb200 {
 // gemm_tcgen05.cu
 bool tcgen05_eligible(const GemmArgs& g);
 int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream);
+// gemm_tcgen05_2cta.cu
+bool pair_kernel_preferred(const sb200_ctx* ctx, const GemmArgs& g);
+int launch_gemm_tcgen05_pair(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream);
 // gemm_simt.cu
 int launch_gemm_simt(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream);
 int launch_colsum(sb200_ctx* ctx, const float* B, int transB, int64_t K, int64_t N, int64_t ldb,

@@ -1,0 +1,218 @@
+// Pieces shared by the one-CTA and the two-CTA tensor-core GEMM kernels:
+// tile constants, kernel parameters, the bounded mbarrier wait, the epilogue
+// store and the tensor-map builders.
+#pragma once
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace sb200 {
+namespace gemm {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 32;                     // fp32 elements = 128 bytes
+constexpr int UMMA_K = 8;                       // k per tcgen05.mma, kind::tf32
+constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 4;
+constexpr int CHUNK_BYTES = 32 * BLOCK_K * 4;   // one MN-major chunk: 32 k-rows x 128 B
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+constexpr int SPLIT_CHUNK_KB = 8;               // 3xTF32: 256 k per tensor-core accumulation chain
+
+struct KernelParams {
+    int M, N, K, batch;
+    int tiles_m, tiles_n, num_kb;
+    int chunk_kb;                               // k-blocks per TMEM accumulation chain
+    long long total_tiles;
+    int a_batched, b_batched;                   // 0: batch stride 0, always read matrix 0
+    int a_merged, b_merged;                     // MN-major tile fetched by one 4-D TMA box
+    const float* C; long long ldc, strideC;
+    float* D; long long ldd, strideD;
+    const float* bias;
+    unsigned* status;
+    int explicit_hi;
+};
+
+struct Abort {
+    volatile int* flag;
+    unsigned* status;
+};
+
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, const Abort& ab,
+                                         unsigned code)
+{
+    if (ptx::mbar_try_wait(bar, parity))
+        return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0) {
+            if (*ab.flag)
+                return false;
+            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *ab.flag = 1;
+                atomicCAS(ab.status, 0u, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// One thread's 32 consecutive output columns of one row: D = (C + bias) + acc.
+__device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], float* drow,
+                                                const float* crow, const float* bias, int col0,
+                                                int N, bool vec_ok)
+{
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const int col = col0 + j;
+        if (vec_ok && col + 3 < N) {
+            float4 base = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (crow)
+                base = *reinterpret_cast<const float4*>(crow + col);
+            if (bias) {
+                base.x = base.x + __ldg(bias + col);
+                base.y = base.y + __ldg(bias + col + 1);
+                base.z = base.z + __ldg(bias + col + 2);
+                base.w = base.w + __ldg(bias + col + 3);
+            }
+            float4 o;
+            o.x = base.x + __uint_as_float(v[j]);
+            o.y = base.y + __uint_as_float(v[j + 1]);
+            o.z = base.z + __uint_as_float(v[j + 2]);
+            o.w = base.w + __uint_as_float(v[j + 3]);
+            *reinterpret_cast<float4*>(drow + col) = o;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (col + e < N) {
+                    float base = crow ? crow[col + e] : 0.f;
+                    if (bias)
+                        base = base + __ldg(bias + col + e);
+                    drow[col + e] = base + __uint_as_float(v[j + e]);
+                }
+            }
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Tensor map over a stack of row-major matrices: dim0 = contiguous extent,
+// dim1 = rows, dim2 = batch; box = 32 contiguous elements x box_rows x 1,
+// out-of-range elements read as zero.  K-major tiles use the plain 128-byte
+// swizzle; MN-major tiles the 128-byte swizzle with a 32-byte atom, the only
+// MN-major layout the tensor core reads for 32-bit operands.
+// The same for one warp's 32 rows x 32 columns, with lane-contiguous global
+// accesses.  After tcgen05.ld lane l holds 32 columns of row l; going through a
+// per-warp shared-memory tile (32 rows x 36 floats) the warp instead moves
+// 4 rows x 128 contiguous bytes per instruction: 8 lanes per row, one float4
+// each.  `row0` is the global row of lane 0; D / C point at the matrix origin of
+// the batch.  Requires 16-byte aligned rows (vec path of store_row_chunk).
+constexpr int EPI_STAGE_LD = 36;                                 // floats per staged row
+constexpr int EPI_STAGE_BYTES_PER_WARP = 32 * EPI_STAGE_LD * 4;
+
+__device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], float* stage,
+                                                      float* D, long long ldd, const float* C,
+                                                      long long ldc, const float* bias, int row0,
+                                                      int col0, int M, int N)
+{
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + j) =
+            make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                        __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+    __syncwarp();
+    const int sub = lane >> 3, cq = (lane & 7) * 4;
+    const int col = col0 + cq;
+    float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (bias) {
+        if (col + 3 < N) {
+            bv = make_float4(__ldg(bias + col), __ldg(bias + col + 1), __ldg(bias + col + 2),
+                             __ldg(bias + col + 3));
+        } else {
+            if (col < N) bv.x = __ldg(bias + col);
+            if (col + 1 < N) bv.y = __ldg(bias + col + 1);
+            if (col + 2 < N) bv.z = __ldg(bias + col + 2);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = i * 4 + sub;
+        const int grow = row0 + r;
+        const float4 a = *reinterpret_cast<const float4*>(stage + r * EPI_STAGE_LD + cq);
+        if (grow < M && col < N) {
+            float* drow = D + static_cast<long long>(grow) * ldd;
+            const float* crow = C ? C + static_cast<long long>(grow) * ldc : nullptr;
+            if (col + 3 < N) {
+                float4 base = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (crow)
+                    base = *reinterpret_cast<const float4*>(crow + col);
+                float4 o;
+                o.x = (base.x + bv.x) + a.x;
+                o.y = (base.y + bv.y) + a.y;
+                o.z = (base.z + bv.z) + a.z;
+                o.w = (base.w + bv.w) + a.w;
+                *reinterpret_cast<float4*>(drow + col) = o;
+            } else {
+                const float av[4] = {a.x, a.y, a.z, a.w};
+                const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (col + e < N)
+                        drow[col + e] = ((crow ? crow[col + e] : 0.f) + bb[e]) + av[e];
+            }
+        }
+    }
+    __syncwarp();
+}
+
+inline int make_map(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig, int64_t rows,
+             int64_t ld, int64_t batch, int64_t batch_stride, int box_rows, bool mn_major)
+{
+    EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    if (!enc)
+        return SB200_ERR_UNSUPPORTED;
+    const int64_t nb = (batch_stride == 0) ? 1 : batch;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(contig), static_cast<cuuint64_t>(rows),
+                          static_cast<cuuint64_t>(nb)};
+    const int64_t bs = (batch_stride == 0 || nb == 1) ? rows * ld : batch_stride;
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4, static_cast<cuuint64_t>(bs) * 4};
+    cuuint32_t box[3] = {32, static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
+}
+
+// MN-major operand whose contiguous extent is a multiple of 32: view it as
+// [batch][chunk = contig / 32][row][32] so that one box of 32 x 32 rows x
+// `chunks` chunks brings a whole tile (same shared-memory image as `chunks`
+// separate 32 x 32 boxes: chunk-major, 32 rows of 128 B each).
+inline int make_map_merged(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig,
+                    int64_t rows, int64_t ld, int64_t batch, int64_t batch_stride, int chunks)
+{
+    EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    if (!enc)
+        return SB200_ERR_UNSUPPORTED;
+    const int64_t nb = (batch_stride == 0) ? 1 : batch;
+    cuuint64_t dims[4] = {32, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(contig / 32),
+                          static_cast<cuuint64_t>(nb)};
+    const int64_t bs = (batch_stride == 0 || nb == 1) ? rows * ld : batch_stride;
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(ld) * 4, 128,
+                             static_cast<cuuint64_t>(bs) * 4};
+    cuuint32_t box[4] = {32, static_cast<cuuint32_t>(BLOCK_K), static_cast<cuuint32_t>(chunks), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
+}
+
+}  // namespace gemm
+}  // namespace sb200

@@ -21,34 +21,13 @@
 // Every wait on an mbarrier is bounded; when one expires the CTA records a code
 // in the status word, raises a CTA-wide abort flag, and every role falls through
 // to the common exit where TMEM is released.
-#include "common.cuh"
-#include "ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace sb200 {
 
+using namespace gemm;
+
 namespace {
-
-constexpr int BLOCK_M = 128;
-constexpr int BLOCK_K = 32;                     // fp32 elements = 128 bytes
-constexpr int UMMA_K = 8;                       // k per tcgen05.mma, kind::tf32
-constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 4;
-constexpr int CHUNK_BYTES = 32 * BLOCK_K * 4;   // one MN-major chunk: 32 k-rows x 128 B
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
-constexpr int SPLIT_CHUNK_KB = 8;               // 3xTF32: 256 k per tensor-core accumulation chain
-
-struct KernelParams {
-    int M, N, K, batch;
-    int tiles_m, tiles_n, num_kb;
-    int chunk_kb;                               // k-blocks per TMEM accumulation chain
-    long long total_tiles;
-    int a_batched, b_batched;                   // 0: batch stride 0, always read matrix 0
-    int a_merged, b_merged;                     // MN-major tile fetched by one 4-D TMA box
-    const float* C; long long ldc, strideC;
-    float* D; long long ldd, strideD;
-    const float* bias;
-    unsigned* status;
-    int explicit_hi;
-};
 
 template <int BLOCK_N, int STAGES, bool SPLIT>
 struct SmemLayout {
@@ -58,35 +37,11 @@ struct SmemLayout {
     // accumulator buffers in TMEM (512 columns at most)
     static constexpr int NUM_ACC = SPLIT ? 4 : 2;
     // barriers: full, empty, split_done per stage; tmem_full, tmem_empty per accumulator
-    static constexpr int BAR_BYTES = (3 * STAGES + 2 * NUM_ACC) * 8 + 16;
-    static constexpr int TOTAL = TILES_BYTES + BAR_BYTES + 1024;   // + alignment slack
+    // (rounded to 16 bytes: the epilogue staging tiles that follow take float4 accesses)
+    static constexpr int BAR_BYTES = ((3 * STAGES + 2 * NUM_ACC) * 8 + 16 + 15) & ~15;
+    // + epilogue staging tiles (4 warps) + alignment slack
+    static constexpr int TOTAL = TILES_BYTES + BAR_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP + 1024;
 };
-
-struct Abort {
-    volatile int* flag;
-    unsigned* status;
-};
-
-__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, const Abort& ab,
-                                         unsigned code)
-{
-    if (ptx::mbar_try_wait(bar, parity))
-        return true;
-    const uint64_t t0 = ptx::globaltimer_ns();
-    uint32_t spins = 0;
-    while (!ptx::mbar_try_wait(bar, parity)) {
-        if ((++spins & 63u) == 0) {
-            if (*ab.flag)
-                return false;
-            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-                *ab.flag = 1;
-                atomicCAS(ab.status, 0u, code);
-                return false;
-            }
-        }
-    }
-    return true;
-}
 
 // hi/lo split of one fp32 value for the 3xTF32 mode.  hi is exactly
 // representable in TF32 (10 explicit mantissa bits), lo = x - hi is exact in
@@ -100,44 +55,6 @@ __device__ __forceinline__ void split_tf32(float x, bool rounded, float& hi, flo
         h = __float_as_uint(x) & 0xFFFFE000u;
     hi = __uint_as_float(h);
     lo = x - hi;
-}
-
-// One thread's 32 consecutive output columns of one row: D = (C + bias) + acc.
-__device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], float* drow,
-                                                const float* crow, const float* bias, int col0,
-                                                int N, bool vec_ok)
-{
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-        const int col = col0 + j;
-        if (vec_ok && col + 3 < N) {
-            float4 base = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (crow)
-                base = *reinterpret_cast<const float4*>(crow + col);
-            if (bias) {
-                base.x = base.x + __ldg(bias + col);
-                base.y = base.y + __ldg(bias + col + 1);
-                base.z = base.z + __ldg(bias + col + 2);
-                base.w = base.w + __ldg(bias + col + 3);
-            }
-            float4 o;
-            o.x = base.x + __uint_as_float(v[j]);
-            o.y = base.y + __uint_as_float(v[j + 1]);
-            o.z = base.z + __uint_as_float(v[j + 2]);
-            o.w = base.w + __uint_as_float(v[j + 3]);
-            *reinterpret_cast<float4*>(drow + col) = o;
-        } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (col + e < N) {
-                    float base = crow ? crow[col + e] : 0.f;
-                    if (bias)
-                        base = base + __ldg(bias + col + e);
-                    drow[col + e] = base + __uint_as_float(v[j + e]);
-                }
-            }
-        }
-    }
 }
 
 template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT>
@@ -162,6 +79,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
     uint64_t* tmem_empty = tmem_full + NUM_ACC;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + NUM_ACC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* epi_stage = reinterpret_cast<float*>(smem + L::TILES_BYTES + L::BAR_BYTES);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -335,9 +253,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             const int m0 = (r % p.tiles_m) * BLOCK_M;
             const int n0 = (r / p.tiles_m) * BLOCK_N;
             const int row = m0 + q * 32 + lane;
-            float* drow = p.D + b * p.strideD + static_cast<long long>(row) * p.ldd;
-            const float* crow =
-                p.C ? p.C + b * p.strideC + static_cast<long long>(row) * p.ldc : nullptr;
+            float* dmat = p.D + b * p.strideD;
+            const float* cmat = p.C ? p.C + b * p.strideC : nullptr;
+            float* drow = dmat + static_cast<long long>(row) * p.ldd;
+            const float* crow = cmat ? cmat + static_cast<long long>(row) * p.ldc : nullptr;
+            float* my_stage = epi_stage + q * (EPI_STAGE_BYTES_PER_WARP / 4);
             if constexpr (!SPLIT) {
                 // one chunk per tile: straight from TMEM to global memory
                 if (!(ok = wait_bar(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
@@ -351,8 +271,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                     uint32_t v[32];
                     ptx::tmem_ld_32x32(lane_base + static_cast<uint32_t>(acc * BLOCK_N + c * 32), v);
                     ptx::tmem_ld_wait();
-                    if (row < p.M)
-                        store_row_chunk(v, drow, crow, p.bias, col0, p.N, vec_ok);
+                    if (vec_ok)
+                        store_chunk_coalesced(v, my_stage, dmat, p.ldd, cmat, p.ldc, p.bias,
+                                              m0 + q * 32, col0, p.M, p.N);
+                    else if (row < p.M)
+                        store_row_chunk(v, drow, crow, p.bias, col0, p.N, false);
                 }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
@@ -397,17 +320,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                 }
                 if (!ok)
                     break;
-                if (row < p.M) {
 #pragma unroll
-                    for (int c = 0; c < BLOCK_N / 32; ++c) {
-                        const int col0 = n0 + c * 32;
-                        if (col0 < p.N) {
-                            uint32_t v[32];
+                for (int c = 0; c < BLOCK_N / 32; ++c) {
+                    const int col0 = n0 + c * 32;
+                    if (col0 < p.N) {                      // uniform across the warp
+                        uint32_t v[32];
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                v[j] = __float_as_uint(sum[c * 32 + j]);
-                            store_row_chunk(v, drow, crow, p.bias, col0, p.N, vec_ok);
-                        }
+                        for (int j = 0; j < 32; ++j)
+                            v[j] = __float_as_uint(sum[c * 32 + j]);
+                        if (vec_ok)
+                            store_chunk_coalesced(v, my_stage, dmat, p.ldd, cmat, p.ldc, p.bias,
+                                                  m0 + q * 32, col0, p.M, p.N);
+                        else if (row < p.M)
+                            store_row_chunk(v, drow, crow, p.bias, col0, p.N, false);
                     }
                 }
             }
@@ -462,61 +387,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
 }
 
 // ------------------------------------------------------------------- host
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// Tensor map over a stack of row-major matrices: dim0 = contiguous extent,
-// dim1 = rows, dim2 = batch; box = 32 contiguous elements x box_rows x 1,
-// out-of-range elements read as zero.  K-major tiles use the plain 128-byte
-// swizzle; MN-major tiles the 128-byte swizzle with a 32-byte atom, the only
-// MN-major layout the tensor core reads for 32-bit operands.
-int make_map(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig, int64_t rows,
-             int64_t ld, int64_t batch, int64_t batch_stride, int box_rows, bool mn_major)
-{
-    EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
-    if (!enc)
-        return SB200_ERR_UNSUPPORTED;
-    const int64_t nb = (batch_stride == 0) ? 1 : batch;
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(contig), static_cast<cuuint64_t>(rows),
-                          static_cast<cuuint64_t>(nb)};
-    const int64_t bs = (batch_stride == 0 || nb == 1) ? rows * ld : batch_stride;
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4, static_cast<cuuint64_t>(bs) * 4};
-    cuuint32_t box[3] = {32, static_cast<cuuint32_t>(box_rows), 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
-}
-
-// MN-major operand whose contiguous extent is a multiple of 32: view it as
-// [batch][chunk = contig / 32][row][32] so that one box of 32 x 32 rows x
-// `chunks` chunks brings a whole tile (same shared-memory image as `chunks`
-// separate 32 x 32 boxes: chunk-major, 32 rows of 128 B each).
-int make_map_merged(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig,
-                    int64_t rows, int64_t ld, int64_t batch, int64_t batch_stride, int chunks)
-{
-    EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
-    if (!enc)
-        return SB200_ERR_UNSUPPORTED;
-    const int64_t nb = (batch_stride == 0) ? 1 : batch;
-    cuuint64_t dims[4] = {32, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(contig / 32),
-                          static_cast<cuuint64_t>(nb)};
-    const int64_t bs = (batch_stride == 0 || nb == 1) ? rows * ld : batch_stride;
-    cuuint64_t strides[3] = {static_cast<cuuint64_t>(ld) * 4, 128,
-                             static_cast<cuuint64_t>(bs) * 4};
-    cuuint32_t box[4] = {32, static_cast<cuuint32_t>(BLOCK_K), static_cast<cuuint32_t>(chunks), 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
-}
 
 template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT>
 int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
@@ -617,6 +487,8 @@ int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 {
     if (!tcgen05_eligible(g))
         return SB200_ERR_UNSUPPORTED;
+    if (pair_kernel_preferred(ctx, g))
+        return launch_gemm_tcgen05_pair(ctx, g, stream);
     const bool wide = g.N > 128;
     if (g.mode == SB200_MODE_TF32X3) {
         // hi + lo tiles double the stage: 128-wide tiles, three stages

@@ -34,7 +34,7 @@ constexpr int TINY_MAX = 32;
 constexpr unsigned HEAVY_MIN = 16384;
 constexpr int ROW_THREADS = 256;
 constexpr int VAL_CAP = 6144;            // fp32 accumulators per CTA in shared memory
-constexpr uint32_t MAX_COLS = 1u << 20;  // bitmap of N bits must fit in shared memory
+constexpr uint32_t MAX_COLS = 1u << 19;  // bitmap + prefix of N columns must fit in shared memory
 
 struct Csr {
     const uint32_t* row;
@@ -640,6 +640,14 @@ int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_
     const uint32_t wpw = ((pl.words + NWARPS - 1) / NWARPS + 31) & ~31u;
     const size_t padded = static_cast<size_t>(wpw) * NWARPS;
     const size_t chunk_bytes = 4 * A_CHUNK * 4;                // qs, len, aval, longs
+    if (NUMERIC) {
+        // the value buffer takes what the bitmap leaves of the 227 KB per CTA
+        const size_t budget = 226 * 1024, fixed = padded * 8 + chunk_bytes;
+        if (fixed + 1024 * 4 > budget)
+            return SB200_ERR_TOO_LARGE;
+        if (fixed + static_cast<size_t>(val_cap) * 4 > budget)
+            val_cap = static_cast<uint32_t>((budget - fixed) / 4);
+    }
     const size_t smem = NUMERIC ? padded * 8 + chunk_bytes + static_cast<size_t>(val_cap) * 4
                                 : padded * 4 + chunk_bytes;
     auto kern = cta_rows_kernel<THREADS, MIN_BLOCKS, NUMERIC, FROM_PATTERN>;
