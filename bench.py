@@ -270,12 +270,29 @@ def main():
         da, db, dc = (torch.empty(BATCH, n, n, device=dev) for _ in range(3))
         dy = torch.empty(BATCH, n, n, device=dev)
 
+        # per batch: H2D on one stream, GEMM on the compute stream, D2H on a third,
+        # chained by events, so that the copies of batch i+1 overlap the GEMM of batch i
+        h2d, d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        ev_in = [torch.cuda.Event() for _ in range(BATCH)]
+        ev_out = [torch.cuda.Event() for _ in range(BATCH)]
+
         def step():
-            da.copy_(ha, non_blocking=True)
-            db.copy_(hb, non_blocking=True)
-            dc.copy_(hc, non_blocking=True)
-            ops.gemm(ctx, da, db, dc, dy, mode=mode)
-            hy.copy_(dy, non_blocking=True)
+            main = torch.cuda.current_stream(dev)
+            h2d.wait_stream(main)
+            d2h.wait_stream(main)
+            for i in range(BATCH):
+                with torch.cuda.stream(h2d):
+                    da[i].copy_(ha[i], non_blocking=True)
+                    db[i].copy_(hb[i], non_blocking=True)
+                    dc[i].copy_(hc[i], non_blocking=True)
+                    ev_in[i].record(h2d)
+                main.wait_event(ev_in[i])
+                ops.gemm(ctx, da[i], db[i], dc[i], dy[i], mode=mode)
+                ev_out[i].record(main)
+                with torch.cuda.stream(d2h):
+                    d2h.wait_event(ev_out[i])
+                    hy[i].copy_(dy[i], non_blocking=True)
+            main.wait_stream(d2h)
 
         ms, _ = timed(step, steps, 1)
         nbytes = ha.numel() * 4

@@ -328,11 +328,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             v[j] = __float_as_uint(sum[c * 32 + j]);
-                        if (vec_ok)
-                            store_chunk_coalesced(v, my_stage, dmat, p.ldd, cmat, p.ldc, p.bias,
-                                                  m0 + q * 32, col0, p.M, p.N);
-                        else if (row < p.M)
-                            store_row_chunk(v, drow, crow, p.bias, col0, p.N, false);
+                        // one store per tile after many chunk drains: the plain row
+                        // store keeps this path's register count down
+                        if (row < p.M)
+                            store_row_chunk(v, drow, crow, p.bias, col0, p.N, vec_ok);
                     }
                 }
             }

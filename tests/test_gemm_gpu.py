@@ -197,6 +197,33 @@ def test_linear_backward_gemms_with_fused_bias_grad(ctx, oracle, mode):
     assert rel_fro(db.cpu().numpy(), want_db) <= 1e-5
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K,batch", [(1024, 512, 256, 40), (1000, 520, 100, 38), (512, 256, 64, 80)])
+def test_two_cta_kernel_matches_one_cta_and_oracle(ctx, oracle, ta, tb, M, N, K, batch):
+    """Problems with enough 256 x 256 tiles run on pairs of SMs (cta_group::2);
+    the same request with pairs switched off runs on the one-CTA kernel.  Both
+    must meet the TF32 bar against the CPU loop (checked on one batch) and agree
+    with each other on all batches."""
+    rng = np.random.default_rng(M + N + K + ta * 2 + tb)
+    a = rng.standard_normal((batch, K, M) if ta else (batch, M, K)).astype(np.float32)
+    b = rng.standard_normal((batch, N, K) if tb else (batch, K, N)).astype(np.float32)
+    c = rng.uniform(-1, 1, (batch, M, N)).astype(np.float32)
+    ta_, tb_, tc_ = dev(a), dev(b), dev(c)
+    outs = []
+    for pairs in (1, 0):
+        ctx.set_option(L.OPT_CTA_PAIRS, pairs)
+        outs.append(ops.gemm(ctx, ta_, tb_, tc_, trans_a=bool(ta), trans_b=bool(tb)))
+        ctx.check_device_status()
+    ctx.set_option(L.OPT_CTA_PAIRS, 1)
+    bi = batch - 1
+    want = oracle.gemm_ex(ta, tb, M, N, K, a[bi], a.shape[2], 0, b[bi], b.shape[2], 0, c[bi], N, 0,
+                          N, 0, None, 1, M * N).reshape(M, N)
+    assert rel_fro(outs[0][bi].cpu().numpy(), want) <= 2e-3
+    assert rel_fro(outs[1][bi].cpu().numpy(), want) <= 2e-3
+    # same products, same k order per output: the two kernels agree to rounding of the accumulation
+    assert rel_fro(outs[0].cpu().numpy(), outs[1].cpu().numpy()) <= 1e-5
+
+
 # ------------------------------------------------- full-size property checks
 @pytest.mark.parametrize("n", [4096, 4000])
 def test_config3_full_size_row_sample_and_linearity(ctx, oracle, n):

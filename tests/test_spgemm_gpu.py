@@ -42,6 +42,7 @@ def run_case(ctx, oracle, M, K, N, seedA, seedB, dens, dist, cap=4096, fn=None):
     (4096, 4096, 4096, None, "zipf", 512),       # mixed bins
     (8192, 8192, 8192, None, "zipf", 4096),      # heavy rows: output wider than the shared buffer
     (1000, 1000, 70000, 0.0005, "poisson", 0),   # wide N: bitmap larger than 2048 words
+    (300, 400, 400000, 0.01, "poisson", 0),      # very wide N, long rows of B: heavy bin, rank windows
 ])
 def test_spgemm_matches_oracle(ctx, oracle, M, K, N, dens, dist, cap):
     run_case(ctx, oracle, M, K, N, 0, 1, dens, dist, cap or 4096)
