@@ -75,3 +75,38 @@ class MlpTrainer:
         self.grads.allreduce(self.world, lambda t, f: ops.scale(self.ctx, t, f))
         ops.sgd_update(self.ctx, self.params.flat, self.grads.flat, self.lr)
         return loss
+
+    # ------------------------------------------------------------ CUDA graph
+    def capture(self, batch: int) -> None:
+        """Records one whole step (forward, backward, gradient allreduce, SGD) into
+        a CUDA graph over static input buffers: the step is ~25 small kernels and
+        launch-bound, a graph replays them with one launch.  Two eager steps run
+        first so that every lazily created resource (kernel attributes, the
+        column-sum scratch) exists before capture begins; the parameters are
+        restored afterwards."""
+        dev = self.params.flat.device
+        n_in, n_out = self.W[0].shape[0], self.W[-1].shape[1]
+        self._gx = torch.zeros(batch, n_in, device=dev)
+        self._gy = torch.zeros(batch, n_out, device=dev)
+        self._gy[:, 0] = 1.0
+        saved = self.params.flat.clone()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.step(self._gx, self._gy)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.params.flat.copy_(saved)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._gloss = self.step(self._gx, self._gy)
+        self.params.flat.copy_(saved)
+
+    def step_graph(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
+        """One step through the captured graph; returns the per-sample loss buffer
+        (overwritten by the next replay)."""
+        self._gx.copy_(x, non_blocking=True)
+        self._gy.copy_(onehot, non_blocking=True)
+        self._graph.replay()
+        return self._gloss

@@ -122,3 +122,18 @@ def test_mlp_fixture_from_reference_build(ctx):
     assert rel(np.stack(losses), gold["mlp_loss3"]) <= 1e-5
     assert rel(trainer.W[2].cpu().numpy(), gold["mlp_w2_after3"]) <= 1e-5
     assert rel(trainer.b[0].cpu().numpy(), gold["mlp_b0_after3"]) <= 1e-5
+
+
+def test_mlp_cuda_graph_step_equals_eager_step(ctx):
+    """The captured step replays the same kernels: identical parameters after 5 steps."""
+    Ws, bs = W.mlp_init(0)
+    eager = mlp.MlpTrainer(ctx, Ws, bs, 1e-4, mode=L.MODE_TF32X3)
+    graph = mlp.MlpTrainer(ctx, Ws, bs, 1e-4, mode=L.MODE_TF32X3)
+    graph.capture(64)
+    for t in range(5):
+        x, onehot = W.mlp_batch(t)
+        le = eager.step(dev(x), dev(onehot)).clone()
+        lg = graph.step_graph(dev(x), dev(onehot)).clone()
+        assert torch.equal(le, lg)
+    torch.cuda.synchronize()
+    assert torch.equal(eager.params.flat, graph.params.flat)
