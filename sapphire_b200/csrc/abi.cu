@@ -192,12 +192,20 @@ extern "C" int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA
     g.C = C; g.ldc = ldc; g.strideC = strideC;
     g.D = D; g.ldd = ldd; g.strideD = strideD;
     g.bias = bias;
+    g.colsum_out = nullptr;
+    g.colsum_scale = colsum_scale;
 
     const bool tc_ok = tcgen05_eligible(g);
     int rc;
     if (path == SB200_PATH_TCGEN05 && !tc_ok)
         return SB200_ERR_UNSUPPORTED;
+    bool fused_colsum = false;
     if ((path == SB200_PATH_AUTO && tc_ok) || path == SB200_PATH_TCGEN05) {
+        // the TF32 tensor-core kernel takes the column sums along (extra warps read
+        // the B tiles already in shared memory); other paths run them separately
+        fused_colsum = colsum_out && mode == SB200_MODE_TF32 && K > 0;
+        if (fused_colsum)
+            g.colsum_out = colsum_out;
         rc = launch_gemm_tcgen05(ctx, g, stream);
         ctx->last_path = SB200_PATH_TCGEN05;
     } else {
@@ -206,7 +214,7 @@ extern "C" int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA
     }
     if (rc)
         return rc;
-    if (colsum_out)
+    if (colsum_out && !fused_colsum)
         rc = launch_colsum(ctx, B, g.transB, K, N, ldb, colsum_out, colsum_scale, stream);
     return rc;
 }

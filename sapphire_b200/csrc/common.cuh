@@ -26,6 +26,8 @@ struct GemmArgs {
     const float* C; int64_t ldc, strideC;
     float* D; int64_t ldd, strideD;
     const float* bias;
+    float* colsum_out;         // fused column sums of op(B) (tensor-core path, TF32 mode), or null
+    float colsum_scale;
 };
 
 }  // namespace sb200

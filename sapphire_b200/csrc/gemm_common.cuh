@@ -28,6 +28,8 @@ struct KernelParams {
     const float* bias;
     unsigned* status;
     int explicit_hi;
+    float* colsum_out;                          // column sums of op(B) (fused bias gradient) or null
+    float colsum_scale;
 };
 
 struct Abort {
@@ -167,6 +169,85 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
         }
     }
     __syncwarp();
+}
+
+// ---------------------------------------------------------------- column sums
+// Column sums of op(B) taken from the B tiles as they pass through shared
+// memory (the bias gradient of a Linear layer: B = dy).  Four extra warps (128
+// threads) consume every stage next to the tensor core; only the CTAs of the
+// first row of tiles add anything up, so the sums cost no extra global traffic.
+constexpr int COLSUM_THREADS = 128;
+constexpr int COLSUM_SCRATCH_BYTES = 2048;
+
+// Adds one k-block (32 k) of the staged B tile to this thread's partial sums.
+//   MN-major tile ([chunk][32 k rows][128 B], 32-byte-atom swizzle): thread owns
+//     one 16-byte unit (4 columns) and a share of the k rows -> acc4;
+//   K-major tile ([column][128 B of k], 16-byte swizzle): thread owns whole
+//     rows (= columns of op(B)), tid and tid + 128 -> acc4.x / acc4.y.
+template <bool B_MN, int NCOLS>
+__device__ __forceinline__ void colsum_accumulate(const uint8_t* sb, int tid, float4& acc4)
+{
+    if (B_MN) {
+        constexpr int UNITS = NCOLS / 4;                  // 16-byte units across the tile
+        constexpr int PARTS = COLSUM_THREADS / UNITS;     // k shares
+        constexpr int ROWS = BLOCK_K / PARTS;
+        const int u = tid % UNITS, part = tid / UNITS;
+        const uint8_t* base = sb + (u >> 3) * CHUNK_BYTES;
+        const int uu = u & 7;
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            const int k = part * ROWS + i;
+            const int phys = uu ^ ((k & 3) << 1);
+            const float4 x = *reinterpret_cast<const float4*>(base + k * 128 + phys * 16);
+            acc4.x += x.x; acc4.y += x.y; acc4.z += x.z; acc4.w += x.w;
+        }
+    } else {
+#pragma unroll
+        for (int h = 0; h < NCOLS / COLSUM_THREADS; ++h) {
+            const int row = tid + h * COLSUM_THREADS;
+            const uint8_t* r = sb + row * 128;
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float4 x = *reinterpret_cast<const float4*>(r + (((i + row) & 7) << 4));
+                s += (x.x + x.y) + (x.z + x.w);
+            }
+            if (h == 0) acc4.x += s; else acc4.y += s;
+        }
+    }
+}
+
+// Combines the threads' partial sums and writes scale * sum for columns
+// [n0, n0 + NCOLS) below N.  `scratch`: COLSUM_SCRATCH_BYTES of shared memory.
+// Uses named barrier 1 among the 128 column-sum threads.
+template <bool B_MN, int NCOLS>
+__device__ __forceinline__ void colsum_finish(float4 acc4, float* scratch, int tid, float* out,
+                                              float scale, int n0, int N)
+{
+    if (B_MN) {
+        constexpr int UNITS = NCOLS / 4;
+        constexpr int PARTS = COLSUM_THREADS / UNITS;
+        reinterpret_cast<float4*>(scratch)[tid] = acc4;   // [part][unit]
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid < UNITS) {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int q = 0; q < PARTS; ++q) {
+                const float4 x = reinterpret_cast<const float4*>(scratch)[q * UNITS + tid];
+                s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+            }
+            const int col = n0 + tid * 4;
+            const float v[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (col + e < N) out[col + e] = v[e] * scale;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+    } else {
+        if (n0 + tid < N) out[n0 + tid] = acc4.x * scale;
+        if (NCOLS > COLSUM_THREADS && n0 + tid + COLSUM_THREADS < N)
+            out[n0 + tid + COLSUM_THREADS] = acc4.y * scale;
+    }
 }
 
 inline int make_map(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig, int64_t rows,

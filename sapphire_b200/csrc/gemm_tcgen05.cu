@@ -40,7 +40,8 @@ struct SmemLayout {
     // (rounded to 16 bytes: the epilogue staging tiles that follow take float4 accesses)
     static constexpr int BAR_BYTES = ((3 * STAGES + 2 * NUM_ACC) * 8 + 16 + 15) & ~15;
     // + epilogue staging tiles (4 warps) + alignment slack
-    static constexpr int TOTAL = TILES_BYTES + BAR_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP + 1024;
+    static constexpr int TOTAL = TILES_BYTES + BAR_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP +
+                                 COLSUM_SCRATCH_BYTES + 1024;
 };
 
 // hi/lo split of one fp32 value for the 3xTF32 mode.  hi is exactly
@@ -57,8 +58,8 @@ __device__ __forceinline__ void split_tf32(float x, bool rounded, float& hi, flo
     lo = x - hi;
 }
 
-template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT>
-__global__ void __launch_bounds__(SPLIT ? 320 : 192, 1)
+template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT, bool COLSUM>
+__global__ void __launch_bounds__((SPLIT || COLSUM) ? 320 : 192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                     const __grid_constant__ CUtensorMap mapB, const KernelParams p)
 {
@@ -80,6 +81,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + NUM_ACC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* epi_stage = reinterpret_cast<float*>(smem + L::TILES_BYTES + L::BAR_BYTES);
+    float* colsum_scratch = epi_stage + 4 * (EPI_STAGE_BYTES_PER_WARP / 4);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -88,7 +90,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
-            ptx::mbar_init(&empty_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], COLSUM ? 5 : 1);   // MMA commit (+ 4 column-sum warps)
             ptx::mbar_init(&split_bar[s], 4);
         }
         for (int i = 0; i < NUM_ACC; ++i) {
@@ -336,7 +338,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                 }
             }
         }
-    } else if (SPLIT) {
+    } else if (SPLIT && warp < 10) {
         // --------------------------------------- hi/lo split (3xTF32 mode)
         // 128 threads; each float4 of the landed tiles is read once, its low
         // part is written to the twin tile at the same (swizzled) offset.
@@ -375,6 +377,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
         }
     }
 
+    if constexpr (COLSUM) {
+        if (warp >= 6) {
+            // ---------------------- column sums of op(B) (fused bias gradient)
+            static_assert(!SPLIT, "column sums ride on the TF32 kernel");
+            const int tid = threadIdx.x - 6 * 32;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                const int r = static_cast<int>(t % tiles_per_batch);
+                const bool mine = (t / tiles_per_batch == 0) && (r % p.tiles_m == 0);
+                const int n0 = (r / p.tiles_m) * BLOCK_N;
+                float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!(ok = wait_bar(&full_bar[s], ph, ab, FAULT_SPLIT_WAIT)))
+                        break;
+                    if (mine)
+                        colsum_accumulate<B_MN, BLOCK_N>(smem + s * L::STAGE_BYTES + A_TILE_BYTES,
+                                                         tid, acc4);
+                    __syncwarp();
+                    if (lane == 0)
+                        ptx::mbar_arrive(&empty_bar[s]);
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+                if (!ok)
+                    break;
+                if (mine)
+                    colsum_finish<B_MN, BLOCK_N>(acc4, colsum_scratch, tid, p.colsum_out,
+                                                 p.colsum_scale, n0, p.N);
+            }
+        }
+    }
+
     // common exit: every thread arrives here, also after an abort
     ptx::tc_fence_before_sync();
     __syncthreads();
@@ -387,11 +425,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
 
 // ------------------------------------------------------------------- host
 
-template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT>
+template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT, bool COLSUM>
 int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 {
     using L = SmemLayout<BLOCK_N, STAGES, SPLIT>;
-    auto kern = gemm_tcgen05_kernel<BLOCK_N, STAGES, A_MN, B_MN, SPLIT>;
+    auto kern = gemm_tcgen05_kernel<BLOCK_N, STAGES, A_MN, B_MN, SPLIT, COLSUM>;
     static bool attr_done[16] = {};
     if (ctx->device < 16 && !attr_done[ctx->device]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
@@ -442,23 +480,26 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.bias = g.bias;
     p.status = ctx->d_status;
     p.explicit_hi = ctx->split_explicit_hi;
+    p.colsum_out = COLSUM ? g.colsum_out : nullptr;
+    p.colsum_scale = g.colsum_scale;
 
     const long long grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
-    kern<<<static_cast<unsigned>(grid), SPLIT ? 320 : 192, L::TOTAL, stream>>>(mapA, mapB, p);
+    kern<<<static_cast<unsigned>(grid), (SPLIT || COLSUM) ? 320 : 192, L::TOTAL, stream>>>(mapA, mapB,
+                                                                                          p);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
 
-template <int BLOCK_N, int STAGES, bool SPLIT>
+template <int BLOCK_N, int STAGES, bool SPLIT, bool COLSUM>
 int launch_layout(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 {
     const bool a_mn = g.transA != 0;     // stored [K, M]
     const bool b_mn = g.transB == 0;     // stored [K, N]
     if (a_mn)
-        return b_mn ? launch_variant<BLOCK_N, STAGES, true, true, SPLIT>(ctx, g, stream)
-                    : launch_variant<BLOCK_N, STAGES, true, false, SPLIT>(ctx, g, stream);
-    return b_mn ? launch_variant<BLOCK_N, STAGES, false, true, SPLIT>(ctx, g, stream)
-                : launch_variant<BLOCK_N, STAGES, false, false, SPLIT>(ctx, g, stream);
+        return b_mn ? launch_variant<BLOCK_N, STAGES, true, true, SPLIT, COLSUM>(ctx, g, stream)
+                    : launch_variant<BLOCK_N, STAGES, true, false, SPLIT, COLSUM>(ctx, g, stream);
+    return b_mn ? launch_variant<BLOCK_N, STAGES, false, true, SPLIT, COLSUM>(ctx, g, stream)
+                : launch_variant<BLOCK_N, STAGES, false, false, SPLIT, COLSUM>(ctx, g, stream);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -491,10 +532,13 @@ int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     const bool wide = g.N > 128;
     if (g.mode == SB200_MODE_TF32X3) {
         // hi + lo tiles double the stage: 128-wide tiles, three stages
-        return launch_layout<128, 3, true>(ctx, g, stream);
+        return launch_layout<128, 3, true, false>(ctx, g, stream);
     }
-    return wide ? launch_layout<256, 4, false>(ctx, g, stream)
-                : launch_layout<128, 6, false>(ctx, g, stream);
+    if (g.colsum_out)
+        return wide ? launch_layout<256, 4, false, true>(ctx, g, stream)
+                    : launch_layout<128, 6, false, true>(ctx, g, stream);
+    return wide ? launch_layout<256, 4, false, false>(ctx, g, stream)
+                : launch_layout<128, 6, false, false>(ctx, g, stream);
 }
 
 }  // namespace sb200

@@ -325,6 +325,8 @@ int launch_pair_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.bias = g.bias;
     p.status = ctx->d_status;
     p.explicit_hi = 0;
+    p.colsum_out = nullptr;
+    p.colsum_scale = 0.0f;
 
     // a persistent grid must be fully co-resident: ask how many pairs fit at once
     static int cached_pairs[16] = {};
@@ -366,6 +368,11 @@ int launch_pair_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 bool pair_kernel_preferred(const sb200_ctx* ctx, const GemmArgs& g)
 {
     if (g.mode != SB200_MODE_TF32 || !ctx->use_cta_pairs)
+        return false;
+    // Fused column sums need a "stage filled" signal inside the CTA that holds the
+    // B tile; in a pair that barrier lives in the leader only, so such requests
+    // stay on the one-CTA kernel.
+    if (g.colsum_out)
         return false;
     if (g.M < 2 * PAIR_M || g.N < PAIR_N)
         return false;
