@@ -110,15 +110,48 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 // accesses.  After tcgen05.ld lane l holds 32 columns of row l; going through a
 // per-warp shared-memory tile (32 rows x 36 floats) the warp instead moves
 // 4 rows x 128 contiguous bytes per instruction: 8 lanes per row, one float4
-// each.  `row0` is the global row of lane 0; D / C point at the matrix origin of
-// the batch.  Requires 16-byte aligned rows (vec path of store_row_chunk).
+// each: lane l handles rows 4 i + l / 8 (i = 0..7), columns col0 + 4 (l % 8) .. + 3.
+// `row0` is the global row of lane 0's TMEM lane; D / C point at the matrix
+// origin of the batch.  Requires 16-byte aligned rows.
+//
+// C is read by load_c_chunk BEFORE the stores of the previous chunk are issued:
+// C may alias D (in-place y <- y + a.b), so the compiler keeps every load of C
+// behind every earlier store to D, and a load issued only when its value is
+// needed costs a full memory round trip per float4.  Fetching the next chunk's
+// C ahead keeps eight loads per lane in flight across the stores.
 constexpr int EPI_STAGE_LD = 36;                                 // floats per staged row
 constexpr int EPI_STAGE_BYTES_PER_WARP = 32 * EPI_STAGE_LD * 4;
 
+struct CChunk {
+    float4 v[8];
+};
+
+__device__ __forceinline__ void load_c_chunk(CChunk& cc, const float* C, long long ldc, int row0,
+                                             int col0, int M, int N)
+{
+    const int lane = threadIdx.x & 31;
+    const int sub = lane >> 3, col = col0 + (lane & 7) * 4;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int grow = row0 + i * 4 + sub;
+        cc.v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (C && grow < M) {
+            const float* crow = C + static_cast<long long>(grow) * ldc;
+            if (col + 3 < N) {
+                cc.v[i] = *reinterpret_cast<const float4*>(crow + col);
+            } else {
+                if (col < N) cc.v[i].x = crow[col];
+                if (col + 1 < N) cc.v[i].y = crow[col + 1];
+                if (col + 2 < N) cc.v[i].z = crow[col + 2];
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], float* stage,
-                                                      float* D, long long ldd, const float* C,
-                                                      long long ldc, const float* bias, int row0,
-                                                      int col0, int M, int N)
+                                                      float* D, long long ldd, const CChunk& cc,
+                                                      const float* bias, int row0, int col0, int M,
+                                                      int N)
 {
     const int lane = threadIdx.x & 31;
 #pragma unroll
@@ -131,14 +164,10 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
     const int col = col0 + cq;
     float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
     if (bias) {
-        if (col + 3 < N) {
-            bv = make_float4(__ldg(bias + col), __ldg(bias + col + 1), __ldg(bias + col + 2),
-                             __ldg(bias + col + 3));
-        } else {
-            if (col < N) bv.x = __ldg(bias + col);
-            if (col + 1 < N) bv.y = __ldg(bias + col + 1);
-            if (col + 2 < N) bv.z = __ldg(bias + col + 2);
-        }
+        if (col < N) bv.x = __ldg(bias + col);
+        if (col + 1 < N) bv.y = __ldg(bias + col + 1);
+        if (col + 2 < N) bv.z = __ldg(bias + col + 2);
+        if (col + 3 < N) bv.w = __ldg(bias + col + 3);
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -147,24 +176,17 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
         const float4 a = *reinterpret_cast<const float4*>(stage + r * EPI_STAGE_LD + cq);
         if (grow < M && col < N) {
             float* drow = D + static_cast<long long>(grow) * ldd;
-            const float* crow = C ? C + static_cast<long long>(grow) * ldc : nullptr;
+            float4 o;
+            o.x = (cc.v[i].x + bv.x) + a.x;
+            o.y = (cc.v[i].y + bv.y) + a.y;
+            o.z = (cc.v[i].z + bv.z) + a.z;
+            o.w = (cc.v[i].w + bv.w) + a.w;
             if (col + 3 < N) {
-                float4 base = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (crow)
-                    base = *reinterpret_cast<const float4*>(crow + col);
-                float4 o;
-                o.x = (base.x + bv.x) + a.x;
-                o.y = (base.y + bv.y) + a.y;
-                o.z = (base.z + bv.z) + a.z;
-                o.w = (base.w + bv.w) + a.w;
                 *reinterpret_cast<float4*>(drow + col) = o;
             } else {
-                const float av[4] = {a.x, a.y, a.z, a.w};
-                const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (col + e < N)
-                        drow[col + e] = ((crow ? crow[col + e] : 0.f) + bb[e]) + av[e];
+                drow[col] = o.x;
+                if (col + 1 < N) drow[col + 1] = o.y;
+                if (col + 2 < N) drow[col + 2] = o.z;
             }
         }
     }

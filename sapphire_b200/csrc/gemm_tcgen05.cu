@@ -265,6 +265,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                 if (!(ok = wait_bar(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
                     break;
                 ptx::tc_fence_after_sync();
+                CChunk c_now, c_next;
+                if (vec_ok)
+                    load_c_chunk(c_next, cmat, p.ldc, m0 + q * 32, n0, p.M, p.N);
 #pragma unroll 1
                 for (int c = 0; c < BLOCK_N / 32; ++c) {
                     const int col0 = n0 + c * 32;
@@ -272,10 +275,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                         break;                             // uniform across the warp
                     uint32_t v[32];
                     ptx::tmem_ld_32x32(lane_base + static_cast<uint32_t>(acc * BLOCK_N + c * 32), v);
+                    if (vec_ok) {
+                        c_now = c_next;
+                        if (c + 1 < BLOCK_N / 32 && col0 + 32 < p.N)     // next chunk's C, ahead of the stores
+                            load_c_chunk(c_next, cmat, p.ldc, m0 + q * 32, col0 + 32, p.M, p.N);
+                    }
                     ptx::tmem_ld_wait();
                     if (vec_ok)
-                        store_chunk_coalesced(v, my_stage, dmat, p.ldd, cmat, p.ldc, p.bias,
-                                              m0 + q * 32, col0, p.M, p.N);
+                        store_chunk_coalesced(v, my_stage, dmat, p.ldd, c_now, p.bias, m0 + q * 32,
+                                              col0, p.M, p.N);
                     else if (row < p.M)
                         store_row_chunk(v, drow, crow, p.bias, col0, p.N, false);
                 }
