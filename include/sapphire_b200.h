@@ -186,6 +186,23 @@ int sb200_csr_copy_out(const sb200_csr* src, uint32_t* row, uint32_t* col, float
                        int to_host, sb200_stream stream);
 
 /*
+ * Dense -> CSR on the device.  `dense` is M x N row-major with row pitch ld >= N
+ * (the reference's `paddedN`); an entry is kept when it is not exactly 0.0f;
+ * columns ascend inside a row.  The callee allocates out->V / COL / ROW
+ * (caller frees with sb200_csr_free); the call synchronises the stream once.
+ * Device counterpart of CreateSparseMatrixWithDenseMatrix
+ * (Includes/Sapphire/compute/sparse/Sparse.hpp:154-157, declared without a definition).
+ */
+int sb200_dense_to_csr(sb200_ctx* ctx, const float* dense, uint32_t M, uint32_t N, int64_t ld,
+                       sb200_csr* out, sb200_stream stream);
+
+/* CSR -> dense: zero-fills the M x N window of `dense` (row pitch ld >= N) and
+ * scatters the entries.  Device counterpart of ConvertSparseMatrixToDenseMatrix
+ * (Includes/Sapphire/compute/sparse/Sparse.hpp:159-162). */
+int sb200_csr_to_dense(sb200_ctx* ctx, const sb200_csr* src, float* dense, int64_t ld,
+                       sb200_stream stream);
+
+/*
  * Column sums for callers that cannot allocate: out[n] = scale * sum_k op(B)[k, n],
  * the bias-gradient part of sb200_gemm_batched on its own (same kernels, same
  * meaning of transB / ldb; B and out are device pointers of the CURRENT device).

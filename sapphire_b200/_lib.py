@@ -62,6 +62,9 @@ SIGNATURES = {
     "sb200_csr_free": (C.c_int, [C.POINTER(Csr)]),
     "sb200_csr_copy_out": (C.c_int, [C.POINTER(Csr), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                      C.c_void_p]),
+    "sb200_dense_to_csr": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_int64,
+                                     C.POINTER(Csr), C.c_void_p]),
+    "sb200_csr_to_dense": (C.c_int, [C.c_void_p, C.POINTER(Csr), C.c_void_p, C.c_int64, C.c_void_p]),
     "sb200_colsum_noalloc": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64,
                                        C.c_void_p, C.c_float, C.c_void_p]),
     "sb200_relu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),

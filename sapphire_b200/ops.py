@@ -204,6 +204,35 @@ def spgemm_callee_alloc(ctx: Context, A: CsrMatrix, B: CsrMatrix) -> CsrMatrix:
     return CsrMatrix(row, col, val, A.M, B.N)
 
 
+def dense_to_csr(ctx: Context, dense: torch.Tensor) -> CsrMatrix:
+    """2-D fp32 tensor (last dimension contiguous, any row pitch) -> CSR."""
+    M, N = dense.shape
+    c = L.Csr()
+    L.check("sb200_dense_to_csr", L.lib().sb200_dense_to_csr(
+        ctx.handle, dense.data_ptr(), M, N, dense.stride(0) if M > 1 else max(N, dense.stride(0)),
+        C.byref(c), _stream_ptr(ctx.device)))
+    n = int(c.NNZ)
+    dev = dense.device
+    row = torch.empty(M + 1, dtype=torch.int32, device=dev)
+    col = torch.empty(n, dtype=torch.int32, device=dev)
+    val = torch.empty(n, dtype=torch.float32, device=dev)
+    L.check("sb200_csr_copy_out", L.lib().sb200_csr_copy_out(
+        C.byref(c), row.data_ptr(), col.data_ptr() if n else None, val.data_ptr() if n else None, 0,
+        _stream_ptr(ctx.device)))
+    L.lib().sb200_csr_free(C.byref(c))
+    return CsrMatrix(row, col, val, M, N)
+
+
+def csr_to_dense(ctx: Context, A: CsrMatrix, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(A.M, A.N, dtype=torch.float32, device=A.row.device)
+    s = A.as_struct()
+    L.check("sb200_csr_to_dense", L.lib().sb200_csr_to_dense(
+        ctx.handle, C.byref(s), out.data_ptr(), out.stride(0) if A.M > 1 else max(A.N, out.stride(0)),
+        _stream_ptr(ctx.device)))
+    return out
+
+
 # ---------------------------------------------------------------- elementwise
 
 def _ew(name, ctx, *args):

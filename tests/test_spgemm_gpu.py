@@ -142,3 +142,30 @@ def test_config5_full_size_properties(ctx, dist):
     Bs = sp.csr_matrix((vB.astype(np.float64), cB, rB), shape=(N, N))
     want = As @ (Bs @ np.ones(N))
     assert np.abs(rowsum.cpu().numpy() - want).max() <= 1e-4
+
+
+def test_dense_csr_round_trip_and_product(ctx, oracle):
+    """dense -> CSR -> dense is the identity (also with a padded row pitch), the
+    CSR arrays equal numpy's, and CSR(A).CSR(B) densified equals the dense GEMM."""
+    rng = np.random.default_rng(12)
+    M, K, N = 96, 130, 75
+    a = rng.standard_normal((M, K)).astype(np.float32) * (rng.random((M, K)) < 0.1)
+    b = rng.standard_normal((K, N)).astype(np.float32) * (rng.random((K, N)) < 0.2)
+    a[5] = 0.0                                                     # an empty row
+    pitch = torch.zeros(M, K + 6, device=DEV)
+    pitch[:, :K] = torch.from_numpy(a).to(DEV)
+    A = ops.dense_to_csr(ctx, pitch[:, :K])
+    r, c, v = A.to_numpy()
+    want_r = np.concatenate([[0], np.cumsum((a != 0).sum(1))]).astype(np.uint32)
+    rows, cols = np.nonzero(a)
+    assert np.array_equal(r, want_r) and np.array_equal(c, cols.astype(np.uint32))
+    assert np.array_equal(v, a[rows, cols])
+    back = torch.full((M, K + 2), 7.0, device=DEV)
+    ops.csr_to_dense(ctx, A, back[:, :K])
+    assert np.array_equal(back[:, :K].cpu().numpy(), a)
+    assert float(back[:, K:].min()) == 7.0                         # pitch padding untouched
+    B = ops.dense_to_csr(ctx, torch.from_numpy(b).to(DEV))
+    Cm = ops.spgemm(ctx, A, B)
+    dense_c = ops.csr_to_dense(ctx, Cm).cpu().numpy()
+    want = oracle.gemm(np.zeros((1, M, N), np.float32), a[None], b[None])[0]
+    assert np.abs(dense_c - want).max() <= 1e-5 * max(np.abs(want).max(), 1.0)
