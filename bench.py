@@ -175,6 +175,10 @@ def main():
         run_reference_arm(args)
         return
 
+    # NCCL and others print to stdout: keep fd 1 for the one JSON line only
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
     from sapphire_b200 import _lib as L
@@ -453,10 +457,11 @@ def main():
             "value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": kind,
             "sample": f"{rows} output rows of one {n}^3 batch, {sec:.1f} s; Sapphire's CPU GEMM "
                       "is a single-threaded scalar loop"}
-    if rank == 0:
-        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if rank == 0:
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
 
 
 if __name__ == "__main__":
