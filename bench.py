@@ -333,13 +333,23 @@ def main():
         dx = torch.empty(rows, width, device=dev)
         dw = torch.empty(width, width, device=dev)
         db = torch.empty(width, device=dev)
+        comm = torch.cuda.Stream(dev) if world > 1 else None
+        done = torch.cuda.Event() if world > 1 else None
+
         def fn():
-            ops.gemm(ctx, dy, w, None, dx, trans_b=True)                    # dx = dy.W^T
+            # dW first: its allreduce then travels while dX, which needs no exchange, computes
             ops.gemm(ctx, x, dy, None, dw, trans_a=True, colsum_out=db,     # dW = x^T.dy, dB
                      colsum_scale=1.0 / rows)
             if world > 1:
-                dist.all_reduce(dw)
-                dist.all_reduce(db)
+                main = torch.cuda.current_stream(dev)
+                done.record(main)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    dist.all_reduce(dw)
+                    dist.all_reduce(db)
+            ops.gemm(ctx, dy, w, None, dx, trans_b=True)                    # dx = dy.W^T
+            if world > 1:
+                torch.cuda.current_stream(dev).wait_stream(comm)
         ms, launches = timed(fn, steps, warmup)
         flops = 2 * 2.0 * rows * width * width
         return {"workload": "linear backward dY[8192x4096] X[8192x4096] W[4096x4096] per GPU, "
