@@ -602,14 +602,14 @@ bool same_operands(const sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B)
            k.nnzB == B->NNZ;
 }
 
-// Row bitmaps are kept when they fit the budget (M * ceil(N / 32) * 4 bytes).
-constexpr size_t PATTERN_BUDGET = static_cast<size_t>(2) << 30;
+// Row bitmaps are kept when they fit the limit (M * ceil(N / 32) * 4 bytes).
+constexpr size_t PATTERN_LIMIT = static_cast<size_t>(2) << 30;
 
 int prepare_pattern(sb200_ctx* ctx, Plan* pl, const sb200_csr* A, const sb200_csr* B)
 {
     ctx->sp_valid = 0;
     const size_t need = static_cast<size_t>(A->M) * pl->words * 4;
-    if (need == 0 || need > PATTERN_BUDGET)
+    if (need == 0 || need > PATTERN_LIMIT)
         return SB200_OK;                       // numeric pass rebuilds the bitmaps
     if (need > ctx->sp_pattern_bytes) {
         if (ctx->d_sp_pattern) cudaFree(ctx->d_sp_pattern);
@@ -642,11 +642,11 @@ int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_
     const size_t chunk_bytes = 4 * A_CHUNK * 4;                // qs, len, aval, longs
     if (NUMERIC) {
         // the value buffer takes what the bitmap leaves of the 227 KB per CTA
-        const size_t budget = 226 * 1024, fixed = padded * 8 + chunk_bytes;
-        if (fixed + 1024 * 4 > budget)
+        const size_t room = 226 * 1024, fixed = padded * 8 + chunk_bytes;
+        if (fixed + 1024 * 4 > room)
             return SB200_ERR_TOO_LARGE;
-        if (fixed + static_cast<size_t>(val_cap) * 4 > budget)
-            val_cap = static_cast<uint32_t>((budget - fixed) / 4);
+        if (fixed + static_cast<size_t>(val_cap) * 4 > room)
+            val_cap = static_cast<uint32_t>((room - fixed) / 4);
     }
     const size_t smem = NUMERIC ? padded * 8 + chunk_bytes + static_cast<size_t>(val_cap) * 4
                                 : padded * 4 + chunk_bytes;

@@ -1,5 +1,5 @@
 """GPU test of sb200_colsum_noalloc, the entry point for callers that must not
-allocate device memory (they live under another allocator's memory budget, or
+allocate device memory (they live under another allocator's share of the device memory, or
 on a latency path where cudaMalloc would synchronise the device).
 
 It is compared with the column sums the regular entry point
