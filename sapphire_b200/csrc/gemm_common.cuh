@@ -225,8 +225,10 @@ __device__ __forceinline__ void colsum_accumulate(const uint8_t* sb, int tid, fl
         }
     } else {
 #pragma unroll
-        for (int h = 0; h < NCOLS / COLSUM_THREADS; ++h) {
+        for (int h = 0; h < (NCOLS + COLSUM_THREADS - 1) / COLSUM_THREADS; ++h) {
             const int row = tid + h * COLSUM_THREADS;
+            if (row >= NCOLS)
+                break;
             const uint8_t* r = sb + row * 128;
             float s = 0.f;
 #pragma unroll
@@ -266,7 +268,7 @@ __device__ __forceinline__ void colsum_finish(float4 acc4, float* scratch, int t
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
     } else {
-        if (n0 + tid < N) out[n0 + tid] = acc4.x * scale;
+        if (tid < NCOLS && n0 + tid < N) out[n0 + tid] = acc4.x * scale;
         if (NCOLS > COLSUM_THREADS && n0 + tid + COLSUM_THREADS < N)
             out[n0 + tid + COLSUM_THREADS] = acc4.y * scale;
     }

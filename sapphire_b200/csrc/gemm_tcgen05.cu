@@ -68,7 +68,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
     constexpr int HALF_STAGE = A_TILE_BYTES + B_TILE_BYTES;       // the hi (raw) tiles
     constexpr int NUM_ACC = L::NUM_ACC;
     constexpr uint32_t TMEM_COLS = NUM_ACC * BLOCK_N;              // 256 or 512: power of two
-    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
+    static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
+                  "TMEM allocation must be a power of two");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -537,16 +538,29 @@ int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
         return SB200_ERR_UNSUPPORTED;
     if (pair_kernel_preferred(ctx, g))
         return launch_gemm_tcgen05_pair(ctx, g, stream);
-    const bool wide = g.N > 128;
     if (g.mode == SB200_MODE_TF32X3) {
         // hi + lo tiles double the stage: 128-wide tiles, three stages
         return launch_layout<128, 3, true, false>(ctx, g, stream);
     }
-    if (g.colsum_out)
-        return wide ? launch_layout<256, 4, false, true>(ctx, g, stream)
-                    : launch_layout<128, 6, false, true>(ctx, g, stream);
-    return wide ? launch_layout<256, 4, false, false>(ctx, g, stream)
-                : launch_layout<128, 6, false, false>(ctx, g, stream);
+    // Tile width: the widest of 256 / 128 / 64 columns that still gives every
+    // second SM a tile.  Small problems are latency-bound; narrower tiles spread
+    // them over more SMs and leave room for more stages (8 x 24 KB at width 64).
+    const long long tiles_m = (g.M + BLOCK_M - 1) / BLOCK_M;
+    auto tiles = [&](int bn) { return tiles_m * ((g.N + bn - 1) / bn) * g.batch; };
+    const long long want = ctx->sm_count / 2;
+    int bn = 256;
+    if (g.N <= 64 || (tiles(128) < want && g.N > 64))
+        bn = 64;
+    else if (g.N <= 128 || tiles(256) < want)
+        bn = 128;
+    if (g.colsum_out) {
+        if (bn == 256) return launch_layout<256, 4, false, true>(ctx, g, stream);
+        if (bn == 128) return launch_layout<128, 6, false, true>(ctx, g, stream);
+        return launch_layout<64, 8, false, true>(ctx, g, stream);
+    }
+    if (bn == 256) return launch_layout<256, 4, false, false>(ctx, g, stream);
+    if (bn == 128) return launch_layout<128, 6, false, false>(ctx, g, stream);
+    return launch_layout<64, 8, false, false>(ctx, g, stream);
 }
 
 }  // namespace sb200
