@@ -32,13 +32,19 @@ namespace {
 template <int BLOCK_N, int STAGES, bool SPLIT>
 struct SmemLayout {
     static constexpr int B_TILE_BYTES = BLOCK_N * BLOCK_K * 4;
-    static constexpr int STAGE_BYTES = (A_TILE_BYTES + B_TILE_BYTES) * (SPLIT ? 2 : 1);
-    static constexpr int TILES_BYTES = STAGE_BYTES * STAGES;
+    static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;   // one raw k-block (A + B)
+    // 3xTF32: the low parts live in a ring of their own.  Only raw stages
+    // have to cover the ~2 us from TMA issue to landed data; a low-part tile exists
+    // just between the split warps and the MMAs that consume it (measured: 4 raw + 2 low
+    // stages are slower than 3 + 3, the split warps need the slack).
+    static constexpr int LO_STAGES = SPLIT ? 3 : 0;
+    static constexpr int TILES_BYTES = STAGE_BYTES * (STAGES + LO_STAGES);
     // accumulator buffers in TMEM (512 columns at most)
     static constexpr int NUM_ACC = SPLIT ? 4 : 2;
-    // barriers: full, empty, split_done per stage; tmem_full, tmem_empty per accumulator
+    // barriers: full, empty per raw stage; lo_full, lo_empty per low-part stage; tmem_full,
+    // tmem_empty per accumulator
     // (rounded to 16 bytes: the epilogue staging tiles that follow take float4 accesses)
-    static constexpr int BAR_BYTES = ((3 * STAGES + 2 * NUM_ACC) * 8 + 16 + 15) & ~15;
+    static constexpr int BAR_BYTES = ((2 * STAGES + 2 * LO_STAGES + 2 * NUM_ACC) * 8 + 16 + 15) & ~15;
     // + epilogue staging tiles (4 warps) + alignment slack
     static constexpr int TOTAL = TILES_BYTES + BAR_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP +
                                  COLSUM_SCRATCH_BYTES + 1024;
@@ -66,6 +72,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
     using L = SmemLayout<BLOCK_N, STAGES, SPLIT>;
     constexpr int B_TILE_BYTES = L::B_TILE_BYTES;
     constexpr int HALF_STAGE = A_TILE_BYTES + B_TILE_BYTES;       // the hi (raw) tiles
+    constexpr int LO_STAGES = L::LO_STAGES;
     constexpr int NUM_ACC = L::NUM_ACC;
     constexpr uint32_t TMEM_COLS = NUM_ACC * BLOCK_N;              // 256 or 512: power of two
     static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
@@ -76,8 +83,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::TILES_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* split_bar = empty_bar + STAGES;
-    uint64_t* tmem_full = split_bar + STAGES;
+    uint64_t* split_bar = empty_bar + STAGES;                     // "low parts written" per lo stage
+    uint64_t* lo_empty = split_bar + LO_STAGES;                   // "low parts consumed" per lo stage
+    uint64_t* tmem_full = lo_empty + LO_STAGES;
+    uint8_t* lo_ring = smem + STAGES * L::STAGE_BYTES;            // LO_STAGES x (A + B) low-part tiles
     uint64_t* tmem_empty = tmem_full + NUM_ACC;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + NUM_ACC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -92,7 +101,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
             ptx::mbar_init(&empty_bar[s], COLSUM ? 5 : 1);   // MMA commit (+ 4 column-sum warps)
+        }
+        for (int s = 0; s < LO_STAGES; ++s) {
             ptx::mbar_init(&split_bar[s], 4);
+            ptx::mbar_init(&lo_empty[s], 1);
         }
         for (int i = 0; i < NUM_ACC; ++i) {
             ptx::mbar_init(&tmem_full[i], 1);
@@ -181,6 +193,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             constexpr uint32_t B_LAY = B_MN ? ptx::LAYOUT_SW128_BASE32 : ptx::LAYOUT_SW128;
             int s = 0;
             uint32_t ph = 0;
+            int ls = 0;                                   // low-part stage (3xTF32)
+            uint32_t lph = 0;
             int acc = 0;
             uint32_t acc_ph = 0;
             bool ok = true;
@@ -196,8 +210,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                     const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
                     const int kb1 = min(kb0 + p.chunk_kb, p.num_kb);
                     for (int kb = kb0; kb < kb1; ++kb) {
-                        uint64_t* ready = SPLIT ? &split_bar[s] : &full_bar[s];
-                        if (!(ok = wait_bar(ready, ph, ab, FAULT_MMA_WAIT_FULL)))
+                        // 3xTF32: the split warps signal once the low parts are written,
+                        // which they do only after the raw stage has landed
+                        if (!(ok = SPLIT ? wait_bar(&split_bar[ls], lph, ab, FAULT_MMA_WAIT_FULL)
+                                         : wait_bar(&full_bar[s], ph, ab, FAULT_MMA_WAIT_FULL)))
                             break;
                         ptx::tc_fence_after_sync();
                         const uint32_t sa = ptx::smem_u32(smem + s * L::STAGE_BYTES);
@@ -210,10 +226,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                                 ptx::make_smem_desc(sb + k * B_KSTEP, B_LBO, B_SBO, B_LAY);
                             const uint32_t first = (kb > kb0 || k > 0) ? 1u : 0u;
                             if (SPLIT) {
+                                const uint32_t la = ptx::smem_u32(lo_ring + ls * HALF_STAGE);
                                 const uint64_t a_lo = ptx::make_smem_desc(
-                                    sa + HALF_STAGE + k * A_KSTEP, A_LBO, A_SBO, A_LAY);
+                                    la + k * A_KSTEP, A_LBO, A_SBO, A_LAY);
                                 const uint64_t b_lo = ptx::make_smem_desc(
-                                    sb + HALF_STAGE + k * B_KSTEP, B_LBO, B_SBO, B_LAY);
+                                    la + A_TILE_BYTES + k * B_KSTEP, B_LBO, B_SBO, B_LAY);
                                 // small terms first
                                 ptx::mma_tf32(d_tmem, a_lo, b_hi, idesc, first);
                                 ptx::mma_tf32(d_tmem, a_hi, b_lo, idesc, 1u);
@@ -226,6 +243,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                         if (++s == STAGES) {
                             s = 0;
                             ph ^= 1u;
+                        }
+                        if (SPLIT) {
+                            ptx::mma_commit(&lo_empty[ls]);
+                            if (++ls == LO_STAGES) {
+                                ls = 0;
+                                lph ^= 1u;
+                            }
                         }
                     }
                     if (!ok)
@@ -354,33 +378,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
         const int tid = threadIdx.x - 6 * 32;
         int s = 0;
         uint32_t ph = 0;
+        int ls = 0;
+        uint32_t lph = 0;
         bool ok = true;
         const bool rounded = p.explicit_hi != 0;
         for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
             for (int kb = 0; kb < p.num_kb; ++kb) {
                 if (!(ok = wait_bar(&full_bar[s], ph, ab, FAULT_SPLIT_WAIT)))
                     break;
+                if (!(ok = wait_bar(&lo_empty[ls], lph ^ 1u, ab, FAULT_SPLIT_WAIT)))
+                    break;
                 float4* hi = reinterpret_cast<float4*>(smem + s * L::STAGE_BYTES);
-                float4* lo = reinterpret_cast<float4*>(smem + s * L::STAGE_BYTES + HALF_STAGE);
-#pragma unroll 4
-                for (int i = tid; i < HALF_STAGE / 16; i += 128) {
-                    const float4 x = hi[i];
-                    float4 h, l;
-                    split_tf32(x.x, rounded, h.x, l.x);
-                    split_tf32(x.y, rounded, h.y, l.y);
-                    split_tf32(x.z, rounded, h.z, l.z);
-                    split_tf32(x.w, rounded, h.w, l.w);
-                    lo[i] = l;
-                    if (rounded)
-                        hi[i] = h;
+                float4* lo = reinterpret_cast<float4*>(lo_ring + ls * HALF_STAGE);
+                // all loads of a batch first, then the arithmetic, then the stores: the
+                // split must finish well inside one k-block of tensor-core time
+                constexpr int PER_THREAD = HALF_STAGE / 16 / 128;          // float4 per thread
+                constexpr int BATCH = 8;
+                static_assert(!SPLIT || PER_THREAD % BATCH == 0, "split batches");
+#pragma unroll
+                for (int b0 = 0; b0 < PER_THREAD; b0 += BATCH) {
+                    float4 x[BATCH];
+#pragma unroll
+                    for (int j = 0; j < BATCH; ++j)
+                        x[j] = hi[tid + (b0 + j) * 128];
+#pragma unroll
+                    for (int j = 0; j < BATCH; ++j) {
+                        float4 h, l;
+                        split_tf32(x[j].x, rounded, h.x, l.x);
+                        split_tf32(x[j].y, rounded, h.y, l.y);
+                        split_tf32(x[j].z, rounded, h.z, l.z);
+                        split_tf32(x[j].w, rounded, h.w, l.w);
+                        lo[tid + (b0 + j) * 128] = l;
+                        if (rounded)
+                            hi[tid + (b0 + j) * 128] = h;
+                    }
                 }
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0)
-                    ptx::mbar_arrive(&split_bar[s]);
+                    ptx::mbar_arrive(&split_bar[ls]);
                 if (++s == STAGES) {
                     s = 0;
                     ph ^= 1u;
+                }
+                if (++ls == LO_STAGES) {
+                    ls = 0;
+                    lph ^= 1u;
                 }
             }
         }
@@ -539,7 +582,7 @@ int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     if (pair_kernel_preferred(ctx, g))
         return launch_gemm_tcgen05_pair(ctx, g, stream);
     if (g.mode == SB200_MODE_TF32X3) {
-        // hi + lo tiles double the stage: 128-wide tiles, three stages
+        // 128-wide tiles: three raw stages plus a three-deep ring of low-part tiles
         return launch_layout<128, 3, true, false>(ctx, g, stream);
     }
     // Tile width: the widest of 256 / 128 / 64 columns that still gives every
