@@ -153,6 +153,7 @@ extern "C" int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA
                                   const float* bias, float* colsum_out, float colsum_scale,
                                   int64_t batch, sb200_stream stream_)
 {
+    TraceRange trace("sb200_gemm_batched");
     if (!ctx)
         return SB200_ERR_INVALID_ARG;
     if (mode != SB200_MODE_TF32 && mode != SB200_MODE_TF32X3)

@@ -4,9 +4,19 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/sapphire_b200.h"
 
 namespace sb200 {
+
+// NVTX range over one ABI call (header-only NVTX: free when no tool is attached).
+struct TraceRange {
+    explicit TraceRange(const char* name) { nvtxRangePushA(name); }
+    ~TraceRange() { nvtxRangePop(); }
+    TraceRange(const TraceRange&) = delete;
+    TraceRange& operator=(const TraceRange&) = delete;
+};
 
 // Codes written to the device status word by a bounded wait that gave up.
 enum DeviceFault : unsigned {

@@ -707,6 +707,7 @@ using namespace sb200;
 extern "C" int sb200_spgemm_csr_symbolic(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B,
                                          uint32_t* rowC, int64_t* nnzC, sb200_stream stream_)
 {
+    TraceRange trace("sb200_spgemm_csr_symbolic");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!rowC || !nnzC)
         return SB200_ERR_INVALID_ARG;
@@ -742,6 +743,7 @@ extern "C" int sb200_spgemm_csr_numeric(sb200_ctx* ctx, const sb200_csr* A, cons
                                         const uint32_t* rowC, uint32_t* colC, float* valC,
                                         sb200_stream stream_)
 {
+    TraceRange trace("sb200_spgemm_csr_numeric");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!rowC)
         return SB200_ERR_INVALID_ARG;
@@ -763,6 +765,7 @@ extern "C" int sb200_spgemm_csr_numeric(sb200_ctx* ctx, const sb200_csr* A, cons
 extern "C" int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B,
                                 sb200_csr* C, sb200_stream stream_)
 {
+    TraceRange trace("sb200_spgemm_csr");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!C)
         return SB200_ERR_INVALID_ARG;

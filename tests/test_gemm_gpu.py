@@ -129,6 +129,37 @@ def test_layouts_and_tails(ctx, oracle, mode, ta, tb, M, N, K, batch):
     assert rel_fro(y.cpu().numpy(), want) <= TOL[mode]
 
 
+def test_random_small_shapes_on_the_tensor_core_path(ctx, oracle):
+    """The reference's Gemm1 family (M, N, K in [1, 100], batch up to 30, inputs
+    N(10, 5), GemmTest.cpp:20-84) with rows padded to a multiple of 4 floats so
+    that TMA can fetch them: 40 seeded random cases over all four operand
+    orientations and both arithmetic modes, every output element compared."""
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        M, N, K = (int(x) for x in rng.integers(1, 131, 3))
+        batch = int(rng.integers(1, 6))
+        ta, tb = int(rng.integers(0, 2)), int(rng.integers(0, 2))
+        mode = L.MODE_TF32X3 if case % 2 else L.MODE_TF32
+        pad4 = lambda n: (n + 3) // 4 * 4
+        ar, ac = (K, M) if ta else (M, K)
+        br, bc = (N, K) if tb else (K, N)
+        a = rng.normal(10.0, 5.0, (batch, ar, ac)).astype(np.float32)
+        b = rng.normal(10.0, 5.0, (batch, br, bc)).astype(np.float32)
+        c = rng.uniform(-1, 1, (batch, M, N)).astype(np.float32)
+        want = oracle.gemm_ex(ta, tb, M, N, K, a, ac, ar * ac, b, bc, br * bc, c, N, M * N, N, M * N,
+                              None, batch, batch * M * N).reshape(batch, M, N)
+        pa = torch.zeros(batch, ar, pad4(ac), device=DEV); pa[:, :, :ac] = dev(a)
+        pb = torch.zeros(batch, br, pad4(bc), device=DEV); pb[:, :, :bc] = dev(b)
+        py = torch.zeros(batch, M, pad4(N), device=DEV); py[:, :, :N] = dev(c)
+        y = py[:, :, :N]
+        ops.gemm(ctx, pa[:, :, :ac], pb[:, :, :bc], y, y, mode=mode, trans_a=bool(ta),
+                 trans_b=bool(tb), path=L.PATH_TCGEN05)
+        ctx.check_device_status()
+        err = rel_fro(y.cpu().numpy(), want)
+        assert err <= TOL[mode], (case, M, N, K, batch, ta, tb, mode, err)
+        assert float(py[:, :, N:].abs().max()) == 0.0 if pad4(N) > N else True
+
+
 def test_long_k_accumulation_tf32x3(ctx, oracle):
     """K = 4096: the split mode must stay fp32-accurate over a long reduction."""
     rng = np.random.default_rng(11)
