@@ -36,6 +36,15 @@ DENSE = {"dense_tf32": (4096, 0), "dense_tf32x3": (4096, 1), "dense4000_tf32": (
 BATCH = 8
 
 
+def dense_workload_text(n: int) -> str:
+    return (f"dense batched GEMM y=a.b+c, per GPU batch={BATCH} M=N=K={n}, fp32 in/out, "
+            "a,b~N(0,1) c~U[-1,1)")
+
+
+def spgemm_workload_text(dist_name: str) -> str:
+    return f"csr spgemm 65536^2 0.1% {dist_name}"
+
+
 def peaks():
     """Roofline denominators: measured on this pool when the file is present."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -125,33 +134,63 @@ def cpu_gemm_sample(n: int, rows: int, repeats: int = 1):
     return best, kind, 2.0 * rows * n * n
 
 
+def cpu_spgemm_sample(dist_name: str, rows: int):
+    """Times the CPU sparse oracle (the reference ships no sparse GEMM to time) on
+    the first `rows` rows of the benchmark's A against the full B.
+    Returns (seconds, flops)."""
+    from oracle import oracle as O
+    from sapphire_b200 import workloads as W
+    from sapphire_b200 import runner
+    M = N = 65536
+    rA, cA, vA = W.csr_random(0, M, N, 0.001, dist_name)
+    rB, cB, vB = W.csr_random(1, N, N, 0.001, dist_name)
+    rb, cb, vb = runner.csr_row_block(rA, cA, vA, range(0, rows))
+    t = time.perf_counter()
+    _, _, _, prods = O.spgemm(rb, cb, vb, rB, cB, vB, rows, N)
+    return time.perf_counter() - t, 2.0 * prods
+
+
 def run_reference_arm(args):
+    """The reference's own CPU implementation of the path on this host: for the
+    dense workloads Sapphire's Dense::Naive::Gemm (single-threaded: the reference
+    has no threading), for the sparse workloads the CPU oracle (the reference
+    declares its sparse GEMM without defining it)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    n, mode = DENSE.get(args.workload, (4096, 0))
-    rows = 32
     times = []
-    kind = None
-    for i in range(args.warmup + args.steps):
-        dt, kind, flops = cpu_gemm_sample(n, rows)
-        if i >= args.warmup:
-            times.append(dt)
-    sec = float(np.mean(times))
-    tflops = flops / sec / 1e12
-    sample = (f"{rows} output rows of one {n}x{n}x{n} batch per step "
-              f"(2*{rows}*{n}^2 FLOP), rate extrapolates to the full 8-batch workload")
+    if args.workload in ("spgemm", "spgemm_zipf"):
+        dist_name = "poisson" if args.workload == "spgemm" else "zipf"
+        rows = 4096
+        for i in range(args.warmup + args.steps):
+            dt, flops = cpu_spgemm_sample(dist_name, rows)
+            if i >= args.warmup:
+                times.append(dt)
+        sec = float(np.mean(times))
+        value, unit, metric, kind = flops / sec / 1e9, "GFLOP/s", "CSR SpGEMM throughput", "port"
+        workload = spgemm_workload_text(dist_name)
+        sample = f"first {rows} rows of A against the full B per step, Gustavson CPU oracle"
+    else:
+        n, _ = DENSE.get(args.workload, (4096, 0))
+        rows = 32
+        kind = None
+        for i in range(args.warmup + args.steps):
+            dt, kind, flops = cpu_gemm_sample(n, rows)
+            if i >= args.warmup:
+                times.append(dt)
+        sec = float(np.mean(times))
+        value, unit, metric = flops / sec / 1e12, "TFLOP/s", "batched dense GEMM throughput"
+        workload = dense_workload_text(n)
+        sample = (f"{rows} output rows of one {n}x{n}x{n} batch per step "
+                  f"(2*{rows}*{n}^2 FLOP); the rate extrapolates to the full workload")
     line = {
-        "impl": "reference", "metric": "batched dense GEMM throughput", "value": tflops,
-        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "impl": "reference", "metric": metric, "value": value, "unit": unit,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"dense batched GEMM batch={BATCH} M=N=K={n} y=a.b+c, CPU row slice",
-                   "sample": sample},
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": 1, "kind": kind,
-                         "sample": sample},
-        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
-                "d2h_bytes_per_step": 0},
+        "config": {"workload": workload, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": 1, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -316,7 +355,7 @@ def main():
         nnzC = res["C"].nnz
         prods = int(W.csr_products(rA, cA, rB).sum())
         nbytes = 8 * (cA.size + cB.size + nnzC) + 4 * 3 * (M + 1)
-        return {"workload": f"csr spgemm 65536^2 0.1% {dist_name}", "ms_per_step": ms,
+        return {"workload": spgemm_workload_text(dist_name), "ms_per_step": ms,
                 "gflops_per_gpu": 2.0 * prods / ms / 1e6, "nnzC": nnzC, "products": prods,
                 "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6,
                              "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -393,8 +432,7 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "tf32" if mode == 0 else "3xtf32 (fp32-accurate)", "data": "synthetic",
-            "config": {"workload": f"dense batched GEMM y=a.b+c, per GPU batch={BATCH} "
-                                   f"M=N=K={n}, fp32 in/out, a,b~N(0,1) c~U[-1,1)",
+            "config": {"workload": dense_workload_text(n),
                        "global_batch": BATCH * world, "parallelism": f"batch-sharded x{world}",
                        "l2": "inputs (3 x %d MiB) larger than the 126 MB L2" % (BATCH * n * n * 4 >> 20)},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": tf32_peak,
@@ -460,13 +498,21 @@ def main():
         line["other_workloads"] = extras
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        n = DENSE.get(args.workload, (4096, 0))[0]
-        rows = 96
-        sec, kind, flops = cpu_gemm_sample(n, rows)
-        line["cpu_baseline"] = {
-            "value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": kind,
-            "sample": f"{rows} output rows of one {n}^3 batch, {sec:.1f} s; Sapphire's CPU GEMM "
-                      "is a single-threaded scalar loop"}
+        if args.workload in ("spgemm", "spgemm_zipf"):
+            dist_name = "poisson" if args.workload == "spgemm" else "zipf"
+            sec, flops = cpu_spgemm_sample(dist_name, 8192)
+            line["cpu_baseline"] = {
+                "value": flops / sec / 1e9, "unit": "GFLOP/s", "cores": 1, "kind": "port",
+                "sample": f"first 8192 rows of A against the full B, {sec:.1f} s; CPU Gustavson "
+                          "oracle (the reference ships no sparse GEMM implementation)"}
+        else:
+            n = DENSE.get(args.workload, (4096, 0))[0]
+            rows = 96
+            sec, kind, flops = cpu_gemm_sample(n, rows)
+            line["cpu_baseline"] = {
+                "value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": kind,
+                "sample": f"{rows} output rows of one {n}^3 batch, {sec:.1f} s; Sapphire's CPU GEMM "
+                          "is a single-threaded scalar loop"}
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:
