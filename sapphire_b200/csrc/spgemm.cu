@@ -11,14 +11,15 @@
 //   otherwise       one CTA per row with a dense accumulator in shared memory:
 //                   a bitmap of the N columns marks the row's pattern
 //                   (atomicOr), a prefix sum of the bitmap's popcounts turns a
-//                   column into its rank inside the sorted output row, and the
-//                   values are accumulated with shared-memory atomicAdd at that
-//                   rank.  Reading the bitmap back in word order yields the
-//                   columns already sorted, so no sort is needed.  Rows whose
-//                   output exceeds the shared value buffer accumulate straight
-//                   into their slice of C.V in global memory.
-//   rows with P above a threshold are queued first so that the longest CTAs
-//   start early.
+//                   column into its rank inside the sorted output row, and every
+//                   product stores its column and adds its value at that rank in
+//                   a shared-memory window, which is then copied to C with
+//                   16-byte stores: the columns come out sorted without a sort.
+//                   Rows with more output entries than the window take one walk
+//                   over their products per window (no global atomics).
+//   rows with many products, or with an output wider than the small window, go
+//   to a second instance of the same kernel with 1024 threads, one CTA per SM
+//   and a large window.
 //
 // The symbolic pass runs the pattern part only (tiny: count distinct sorted
 // keys; CTA: popcount of the bitmap); an exclusive scan of the counts gives ROW.
@@ -33,7 +34,9 @@ namespace {
 constexpr int TINY_MAX = 32;
 constexpr unsigned HEAVY_MIN = 16384;
 constexpr int ROW_THREADS = 256;
-constexpr int VAL_CAP = 6144;            // fp32 accumulators per CTA in shared memory
+// Output entries a mid-bin CTA holds in shared memory (wider rows go to the heavy
+// bin): with 16-bit staged columns four CTAs fit on an SM, with 32-bit ones three.
+__host__ __device__ constexpr uint32_t mid_cap(uint32_t n_cols) { return n_cols <= 65536 ? 5376u : 6144u; }
 constexpr uint32_t MAX_COLS = 1u << 19;  // bitmap + prefix of N columns must fit in shared memory
 
 struct Csr {
@@ -61,9 +64,10 @@ struct Work {
 // value buffer also goes to the heavy bin, whose kernel has a large one.
 __global__ void __launch_bounds__(256)
 row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
-                    const uint32_t* __restrict__ rowC)
+                    const uint32_t* __restrict__ rowC, uint32_t n_cols)
 {
     const int lane = threadIdx.x & 31;
+    const uint32_t cap = mid_cap(n_cols);
     const uint32_t warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const uint32_t nwarps = (gridDim.x * blockDim.x) >> 5;
     for (uint32_t i = warp_global; i < A.M; i += nwarps) {
@@ -84,7 +88,7 @@ row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
                 w.cnt[i] = 0;
             } else if (P <= TINY_MAX) {
                 w.list_tiny[atomicAdd(&w.counters[0], 1u)] = i;
-            } else if (P < HEAVY_MIN && !(rowC && rowC[i + 1] - rowC[i] > VAL_CAP)) {
+            } else if (P < HEAVY_MIN && !(rowC && rowC[i + 1] - rowC[i] > cap)) {
                 w.rows_mid[atomicAdd(&w.counters[1], 1u)] = make_uint4(i, pa, pe, P);
             } else {
                 w.rows_heavy[atomicAdd(&w.counters[2], 1u)] = make_uint4(i, pa, pe, P);
@@ -197,16 +201,25 @@ tiny_rows_kernel(Csr A, Csr B, Work w, const uint32_t* __restrict__ rowC,
 }
 
 // ------------------------------------------------------- CTA-per-row path
-constexpr int A_CHUNK = 512;             // nonzeros of A's row staged in shared memory at a time
-constexpr int WALK_UNROLL = 4;           // independent loads in flight per thread
+constexpr uint32_t SHORT_ROW = 8;        // rows of B up to this length are walked by one thread
+constexpr uint32_t SUB = 8;              // lanes that share one descriptor (a piece of a row of B)
+constexpr uint32_t TILE_WORDS = 2048;    // bitmap words covered by one block-wide prefix step
+constexpr int PIECES_IN_FLIGHT = 4;      // descriptors a lane group loads before it accumulates
 
-// Shared-memory staging of a chunk of A's row.
-struct RowChunk {
-    uint32_t* qs;      // [A_CHUNK]     start of B's row
-    uint32_t* len;     // [A_CHUNK]     its length
-    float* aval;       // [A_CHUNK]     A's value (numeric only)
-    uint32_t* longs;   // [A_CHUNK]     nonzeros whose row of B the whole CTA walks
-    uint32_t* n_long;  // [1]
+// Shared-memory work lists of the product walk.  A nonzero (i,k) of A whose
+// row of B has SHORT_ROW < len < THREADS entries is cut into pieces of SUB
+// entries; every piece gets a descriptor and SUB adjacent lanes take one piece
+// at a time, so that a warp works on four pieces with (nearly) all lanes busy
+// whatever the row lengths are.  Rows of THREADS or more entries are listed in
+// the same arrays (used before the descriptors) and walked by the whole CTA.
+template <int THREADS>
+struct WalkLists {
+    static constexpr uint32_t CAP = 3 * THREADS;                 // descriptors per round
+    static constexpr size_t BYTES = CAP * 4 + CAP * 4 + CAP;     // off, aval, n
+    uint32_t* off;     // [CAP]  first entry of the piece in B.col / B.val
+                       //        (long rows: [0, THREADS) starts, [THREADS, 2 THREADS) lengths)
+    float* aval;       // [CAP]  A's value
+    uint8_t* n;        // [CAP]  entries in the piece (1..SUB)
 };
 
 template <int THREADS>
@@ -235,134 +248,168 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s
     return warp_off + incl - v;
 }
 
-// Copies nonzeros [p0, p0 + n) of A's row into shared memory (coalesced reads
-// of the arrays the row-work kernel prepared) and lists the ones whose row of B
-// is long enough for the whole CTA.  *ch.n_long must be zero on entry (a barrier
-// earlier); no barrier inside.
-template <int THREADS, bool NUMERIC>
-__device__ __forceinline__ void stage_chunk(const Csr& A, const Work& w, uint32_t p0, uint32_t n,
-                                            const RowChunk& ch)
+// Calls f(column, a_value * b_value) for every scalar product of A's nonzeros
+// [pa, pe).  The whole CTA must call it; *n_long must be zero on entry and is
+// zero again on return; the lists must not be in use (a barrier earlier).  No
+// barrier after the last call of f.
+template <int THREADS, bool WITH_VALUES, typename F>
+__device__ __forceinline__ void walk_products(const Csr& A, const Csr& B, const Work& w,
+                                              uint32_t pa, uint32_t pe, const WalkLists<THREADS>& wl,
+                                              uint32_t* n_long, uint32_t* s_warp, F f)
 {
-    for (uint32_t e = threadIdx.x; e < n; e += THREADS) {
-        const uint32_t len = w.blen[p0 + e];
-        ch.qs[e] = w.bq[p0 + e];
-        ch.len[e] = len;
-        if (NUMERIC) ch.aval[e] = A.val[p0 + e];
-        if (len >= static_cast<uint32_t>(THREADS)) ch.longs[atomicAdd(ch.n_long, 1u)] = e;
-    }
-}
+    constexpr uint32_t CAP = WalkLists<THREADS>::CAP;
+    constexpr uint32_t NGROUPS = THREADS / SUB;
+    const uint32_t sub = threadIdx.x & (SUB - 1), group = threadIdx.x / SUB;
+    uint32_t* long_len = wl.off + THREADS;
 
-// Calls f(column, a_value * b_value) for every product of the staged chunk.
-//  * rows of B of THREADS or more entries: the whole CTA strides the row (a
-//    4096-entry row would otherwise keep one warp busy while 31 wait);
-//  * rows with more than SHORT_ROW entries: one warp per nonzero of A, lanes
-//    stride B's row with four loads in flight;
-//  * shorter rows: one thread per nonzero, so that a warp is not spent on a
-//    one-entry row (power-law matrices are mostly such rows).
-constexpr uint32_t SHORT_ROW = 8;
+    for (uint32_t p0 = pa; p0 < pe; p0 += THREADS) {
+        const uint32_t e = p0 + threadIdx.x;
+        uint32_t len = 0, qs = 0;
+        float av = 0.0f;
+        if (e < pe) {
+            len = w.blen[e];
+            qs = w.bq[e];
+            if (WITH_VALUES) av = A.val[e];
+        }
+        const bool is_long = len >= static_cast<uint32_t>(THREADS);
+        const bool is_mid = len > SHORT_ROW && !is_long;
+        if (is_long) {
+            const uint32_t s = atomicAdd(n_long, 1u);
+            wl.off[s] = qs;
+            long_len[s] = len;
+            if (WITH_VALUES) wl.aval[s] = av;
+        }
+        const uint32_t pieces = is_mid ? (len + SUB - 1) / SUB : 0u;
+        uint32_t total_pieces;
+        const uint32_t first = block_exclusive_scan<THREADS>(pieces, s_warp, total_pieces);
 
-template <int THREADS, bool NUMERIC, typename F>
-__device__ __forceinline__ void walk_chunk(const Csr& B, const RowChunk& ch, uint32_t n, F f)
-{
-    constexpr int NWARPS = THREADS / 32;
-    const uint32_t n_long = *ch.n_long;
-    for (uint32_t l = 0; l < n_long; ++l) {
-        const uint32_t e = ch.longs[l];
-        const uint32_t qs = ch.qs[e], len = ch.len[e];
-        const float av = NUMERIC ? ch.aval[e] : 0.0f;
-        for (uint32_t o = threadIdx.x; o < len; o += THREADS * 2) {
-            const bool second = o + THREADS < len;
-            const uint32_t c0 = __ldg(B.col + qs + o);
-            const uint32_t c1 = second ? __ldg(B.col + qs + o + THREADS) : 0u;
-            float v0 = 0.0f, v1 = 0.0f;
-            if (NUMERIC) {
-                v0 = __ldg(B.val + qs + o);
-                if (second) v1 = __ldg(B.val + qs + o + THREADS);
-            }
-            f(c0, NUMERIC ? __fmul_rn(av, v0) : 0.0f);
-            if (second) f(c1, NUMERIC ? __fmul_rn(av, v1) : 0.0f);
-        }
-    }
-    for (uint32_t e = threadIdx.x; e < n; e += THREADS) {
-        const uint32_t len = ch.len[e];
-        if (len <= SHORT_ROW) {
-            const uint32_t qs = ch.qs[e];
-            const float av = NUMERIC ? ch.aval[e] : 0.0f;
-            for (uint32_t q = 0; q < len; ++q)
-                f(__ldg(B.col + qs + q), NUMERIC ? __fmul_rn(av, __ldg(B.val + qs + q)) : 0.0f);
-        }
-    }
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (uint32_t p = warp; p < n; p += NWARPS) {
-        const uint32_t len = ch.len[p];
-        if (len <= SHORT_ROW || len >= static_cast<uint32_t>(THREADS))
-            continue;
-        const uint32_t qs = ch.qs[p];
-        const float av = NUMERIC ? ch.aval[p] : 0.0f;
-        for (uint32_t o = lane; o < len; o += 32 * WALK_UNROLL) {
-            uint32_t col[WALK_UNROLL];
-            float bv[WALK_UNROLL];
-#pragma unroll
-            for (int u = 0; u < WALK_UNROLL; ++u) {
-                if (o + 32 * u < len) {
-                    col[u] = __ldg(B.col + qs + o + 32 * u);
-                    if (NUMERIC) bv[u] = __ldg(B.val + qs + o + 32 * u);
+        // ---- rows of B walked by the whole CTA
+        const uint32_t nl = *n_long;
+        if (nl) {
+            for (uint32_t l = 0; l < nl; ++l) {
+                const uint32_t lq = wl.off[l], ll = long_len[l];
+                const float la = WITH_VALUES ? wl.aval[l] : 0.0f;
+                for (uint32_t o = threadIdx.x; o < ll; o += THREADS * 2) {
+                    const bool second = o + THREADS < ll;
+                    const uint32_t c0 = __ldg(B.col + lq + o);
+                    const uint32_t c1 = second ? __ldg(B.col + lq + o + THREADS) : 0u;
+                    float v0 = 0.0f, v1 = 0.0f;
+                    if (WITH_VALUES) {
+                        v0 = __ldg(B.val + lq + o);
+                        if (second) v1 = __ldg(B.val + lq + o + THREADS);
+                    }
+                    const uint32_t cc[2] = {c0, c1};
+                    const float pp[2] = {WITH_VALUES ? __fmul_rn(la, v0) : 0.0f,
+                                         WITH_VALUES ? __fmul_rn(la, v1) : 0.0f};
+                    const bool aa[2] = {true, second};
+                    f(cc, pp, aa);
                 }
             }
-#pragma unroll
-            for (int u = 0; u < WALK_UNROLL; ++u)
-                if (o + 32 * u < len) f(col[u], NUMERIC ? __fmul_rn(av, bv[u]) : 0.0f);
+            __syncthreads();                                      // the lists become descriptors
+            if (threadIdx.x == 0) *n_long = 0;
         }
+
+        // ---- short rows: one thread each, straight from registers
+        if (len <= SHORT_ROW)
+            for (uint32_t q = 0; q < len; ++q) {
+                const uint32_t cc[1] = {__ldg(B.col + qs + q)};
+                const float pp[1] = {WITH_VALUES ? __fmul_rn(av, __ldg(B.val + qs + q)) : 0.0f};
+                const bool aa[1] = {true};
+                f(cc, pp, aa);
+            }
+
+        // ---- everything between: pieces of SUB entries, SUB lanes per piece
+        for (uint32_t base = 0; base < total_pieces; base += CAP) {
+            if (base) __syncthreads();                            // previous round consumed
+            if (pieces) {
+                const uint32_t c_lo = base > first ? base - first : 0u;
+                const uint32_t c_hi = min(pieces, base + CAP > first ? base + CAP - first : 0u);
+                for (uint32_t c = c_lo; c < c_hi; ++c) {
+                    const uint32_t slot = first + c - base;
+                    wl.off[slot] = qs + c * SUB;
+                    wl.n[slot] = static_cast<uint8_t>(min(SUB, len - c * SUB));
+                    if (WITH_VALUES) wl.aval[slot] = av;
+                }
+            }
+            __syncthreads();
+            const uint32_t nd = min(CAP, total_pieces - base);
+            for (uint32_t d = group; d < nd; d += PIECES_IN_FLIGHT * NGROUPS) {
+                uint32_t o[PIECES_IN_FLIGHT], cc[PIECES_IN_FLIGHT];
+                float pp[PIECES_IN_FLIGHT];
+                bool aa[PIECES_IN_FLIGHT];
+#pragma unroll
+                for (int u = 0; u < PIECES_IN_FLIGHT; ++u) {
+                    const uint32_t du = d + u * NGROUPS;
+                    aa[u] = du < nd && sub < wl.n[du];
+                    o[u] = aa[u] ? wl.off[du] + sub : 0u;
+                }
+#pragma unroll
+                for (int u = 0; u < PIECES_IN_FLIGHT; ++u) {
+                    cc[u] = aa[u] ? __ldg(B.col + o[u]) : 0u;
+                    pp[u] = (WITH_VALUES && aa[u]) ? __ldg(B.val + o[u]) : 0.0f;
+                }
+                if (WITH_VALUES) {
+#pragma unroll
+                    for (int u = 0; u < PIECES_IN_FLIGHT; ++u)
+                        if (aa[u]) pp[u] = __fmul_rn(wl.aval[d + u * NGROUPS], pp[u]);
+                }
+                f(cc, pp, aa);
+            }
+        }
+        if (p0 + THREADS < pe) __syncthreads();                   // lists reused by the next group
     }
 }
 
 // One CTA per row.
 //   SYMBOLIC (NUMERIC == false): mark the row's columns in a shared-memory
 //       bitmap, count them, and -- when `pattern` is given -- keep the bitmap in
-//       global memory for the numeric pass (words * 4 bytes per row).
+//       global memory for the numeric pass (`pitch` words per row).
 //   NUMERIC: rebuild the bitmap (FROM_PATTERN == false) or read it back,
 //       prefix-sum its popcounts so that rank(j) = prefix[j / 32] +
 //       popc(bits below j) is the position of column j in the sorted output row,
-//       emit the columns in bitmap order, then accumulate every product at its rank.
-// The bitmap is split into one contiguous range of `wpw` words per warp; inside
-// a range lane l owns words l, l + 32, ... so every shared-memory access of the
-// scans is conflict-free and the prefix needs only warp shuffles.
-template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN>
+//       then walk the products once per window of `val_cap` ranks: each product
+//       stores its column and adds its value at its rank in shared memory, and
+//       the window is copied to C with 16-byte stores.  The rank carries the
+//       row's misalignment (first output index mod 4) so that the shared-memory
+//       and the global side of that copy are aligned alike.
+// ColT is the shared-memory type of a staged column: 16 bits when N <= 65536
+// (a smaller window buffer lets a fourth CTA fit on the SM), else 32.
+// Thread t owns WPT consecutive bitmap words per tile of TILE_WORDS words.
+template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN, typename ColT>
 __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
                 const uint32_t* __restrict__ n_rows_ptr, uint32_t* __restrict__ next_row,
-                uint32_t words, uint32_t wpw,
-                uint32_t val_cap, uint32_t* __restrict__ pattern,
-                const uint32_t* __restrict__ rowC, uint32_t* __restrict__ colC,
-                float* __restrict__ valC)
+                uint32_t pitch, uint32_t tiles, uint32_t val_cap, int vec_ok,
+                uint32_t* __restrict__ pattern, const uint32_t* __restrict__ rowC,
+                uint32_t* __restrict__ colC, float* __restrict__ valC)
 {
     constexpr int NWARPS = THREADS / 32;
-    extern __shared__ uint32_t sm[];
-    const uint32_t padded = wpw * NWARPS;                        // >= words
-    // symbolic: bitmap[padded]; numeric: packed[padded] = {bits, prefix}
+    constexpr uint32_t WPT = TILE_WORDS / THREADS;               // 8, 4 or 2
+    static_assert(WPT >= 2 && WPT * THREADS == TILE_WORDS, "tile must divide among the threads");
+    extern __shared__ uint4 sm4[];
+    uint32_t* sm = reinterpret_cast<uint32_t*>(sm4);
+    const uint32_t padded = tiles * TILE_WORDS;                  // >= pitch
+    // symbolic: bitmap[pitch]; numeric: packed[padded] = {bits, prefix}
     uint32_t* bitmap = sm;
     uint2* packed = reinterpret_cast<uint2*>(sm);
-    uint32_t* after_map = sm + (NUMERIC ? 2 * padded : padded);
-    RowChunk ch;
-    ch.qs = after_map;
-    ch.len = ch.qs + A_CHUNK;
-    ch.aval = reinterpret_cast<float*>(ch.len + A_CHUNK);
-    ch.longs = reinterpret_cast<uint32_t*>(ch.aval + A_CHUNK);
-    float* vals = reinterpret_cast<float*>(ch.longs + A_CHUNK);  // [val_cap]   (numeric)
-    __shared__ uint32_t s_tot[NWARPS];
+    uint32_t* after_map = sm + (NUMERIC ? 2 * padded : pitch);
+    WalkLists<THREADS> wl;
+    wl.off = after_map;
+    wl.aval = reinterpret_cast<float*>(wl.off + WalkLists<THREADS>::CAP);
+    wl.n = reinterpret_cast<uint8_t*>(wl.aval + WalkLists<THREADS>::CAP);
+    float* vals = reinterpret_cast<float*>(wl.n + WalkLists<THREADS>::CAP);   // [val_cap + 4]
+    ColT* cols = reinterpret_cast<ColT*>(vals + val_cap + 4);                 // [val_cap + 4]
+    __shared__ uint32_t s_warp[NWARPS];
     __shared__ uint32_t s_n_long;
     __shared__ uint32_t s_next;
-    ch.n_long = &s_n_long;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t n_rows = *n_rows_ptr;
-    const uint32_t wbase = warp * wpw;                           // this warp's word range
-
-    auto bits_at = [&](uint32_t x) -> uint32_t { return NUMERIC ? packed[x].x : bitmap[x]; };
 
     // Rows are handed out through a counter: their cost varies by an order of
     // magnitude in the heavy bin, a fixed stride would leave SMs idle.
     for (;;) {
+        __syncthreads();                                          // previous row done with shared memory
         if (threadIdx.x == 0) {
             s_next = atomicAdd(next_row, 1u);
             s_n_long = 0;
@@ -373,129 +420,144 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
             break;
         const uint4 d = rows[idx];
         const uint32_t i = d.x, pa = d.y, pe = d.z;
-        const uint32_t nnzA = pe - pa;
-        const bool one_chunk = nnzA <= A_CHUNK;
         const uint32_t out0 = NUMERIC ? rowC[i] : 0;
-
-        const uint32_t n0 = min(static_cast<uint32_t>(A_CHUNK), nnzA);
-        stage_chunk<THREADS, NUMERIC>(A, w, pa, n0, ch);
-        if (NUMERIC && FROM_PATTERN) {
-            const uint32_t* src = pattern + static_cast<size_t>(i) * words;
-            for (uint32_t x = threadIdx.x; x < padded; x += THREADS)
-                packed[x].x = x < words ? src[x] : 0u;
-        } else if (NUMERIC) {
-            for (uint32_t x = threadIdx.x; x < padded; x += THREADS)
-                packed[x] = make_uint2(0u, 0u);
-        } else {
-            for (uint32_t x = threadIdx.x; x < padded; x += THREADS) bitmap[x] = 0;
-        }
-        __syncthreads();
 
         if (!(NUMERIC && FROM_PATTERN)) {
             // ---- pattern: mark every product's column
-            for (uint32_t p0 = pa; p0 < pe; p0 += A_CHUNK) {
-                const uint32_t n = min(static_cast<uint32_t>(A_CHUNK), pe - p0);
-                if (p0 != pa) {
-                    if (threadIdx.x == 0) s_n_long = 0;          // previous walk ended at a barrier
-                    __syncthreads();
-                    stage_chunk<THREADS, NUMERIC>(A, w, p0, n, ch);
-                    __syncthreads();
-                }
-                walk_chunk<THREADS, false>(B, ch, n, [&](uint32_t j, float) {
+            const uint32_t n4 = (NUMERIC ? 2 * padded : pitch) / 4;
+            for (uint32_t x = threadIdx.x; x < n4; x += THREADS) sm4[x] = make_uint4(0u, 0u, 0u, 0u);
+            __syncthreads();
+            walk_products<THREADS, false>(A, B, w, pa, pe, wl, &s_n_long, s_warp, [&](const auto& col, const auto&, const auto& act) {
+                constexpr int U = sizeof(col) / sizeof(col[0]);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (!act[u]) continue;
+                    const uint32_t j = col[u];
                     if (NUMERIC)
                         atomicOr(&packed[j >> 5].x, 1u << (j & 31));
                     else
                         atomicOr(&bitmap[j >> 5], 1u << (j & 31));
-                });
-                __syncthreads();
-            }
-            if (!NUMERIC && pattern) {
-                uint32_t* dst = pattern + static_cast<size_t>(i) * words;
-                for (uint32_t x = threadIdx.x; x < words; x += THREADS) dst[x] = bitmap[x];
-            }
+                }
+            });
+            __syncthreads();
         }
 
-        // ---- popcounts: warp-local running prefix over this warp's word range
-        uint32_t carry = 0;
-        for (uint32_t m = 0; m < wpw; m += 32) {
-            const uint32_t x = wbase + m + lane;
-            const uint32_t c = __popc(bits_at(x));
-            uint32_t incl = c;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += t;
-            }
-            if (NUMERIC) packed[x].y = carry + incl - c;          // relative to the warp's range
-            carry += __shfl_sync(0xffffffffu, incl, 31);
-        }
-        if (lane == 0) s_tot[warp] = carry;
-        __syncthreads();
-        uint32_t woff = 0, total = 0;
-#pragma unroll
-        for (int v = 0; v < NWARPS; ++v) {
-            const uint32_t t = s_tot[v];
-            if (v < warp) woff += t;
-            total += t;
-        }
         if (!NUMERIC) {
-            if (threadIdx.x == 0) w.cnt[i] = total;
-            __syncthreads();                                      // s_tot, bitmap reused next row
+            // ---- count, and keep the bitmap for the numeric pass
+            uint32_t* dst = pattern ? pattern + static_cast<size_t>(i) * pitch : nullptr;
+            uint32_t c = 0;
+            for (uint32_t x = threadIdx.x * 4; x < pitch; x += THREADS * 4) {
+                const uint4 b = *reinterpret_cast<const uint4*>(bitmap + x);
+                c += __popc(b.x) + __popc(b.y) + __popc(b.z) + __popc(b.w);
+                if (dst) *reinterpret_cast<uint4*>(dst + x) = b;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+            if (lane == 0) s_warp[warp] = c;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                uint32_t total = 0;
+#pragma unroll
+                for (int v = 0; v < NWARPS; ++v) total += s_warp[v];
+                w.cnt[i] = total;
+            }
             continue;
         }
 
-        // ---- columns: ascending = word order, then bit order.  Staged in the (not
-        // yet used) value buffer so that the global store is lane-contiguous; rows
-        // wider than the buffer store them directly.
-        const bool staged = total <= val_cap;
-        uint32_t* stage = reinterpret_cast<uint32_t*>(vals);
-        for (uint32_t m = 0; m < wpw; m += 32) {
-            const uint32_t x = wbase + m + lane;
-            uint2 wp = packed[x];
-            wp.y += woff;
-            packed[x].y = wp.y;
-            uint32_t bits = wp.x, run = wp.y;
-            while (bits) {
-                const int bpos = __ffs(bits) - 1;
-                bits &= bits - 1;
-                if (staged)
-                    stage[run] = x * 32 + bpos;
-                else
-                    colC[out0 + run] = x * 32 + bpos;
-                ++run;
+        // ---- ranks: prefix[word] = set bits before it (+ the row's misalignment)
+        const uint32_t shift = out0 & 3u;
+        uint32_t carry = shift;
+        const uint32_t* src = FROM_PATTERN ? pattern + static_cast<size_t>(i) * pitch : nullptr;
+        for (uint32_t t = 0; t < tiles; ++t) {
+            const uint32_t x0 = (t * THREADS + threadIdx.x) * WPT;
+            uint32_t bits[WPT];
+            if (FROM_PATTERN) {
+                if (x0 < pitch) {                                  // pitch is a multiple of 8 >= WPT
+                    if constexpr (WPT == 2) {
+                        const uint2 v = *reinterpret_cast<const uint2*>(src + x0);
+                        bits[0] = v.x; bits[1] = v.y;
+                    } else {
+#pragma unroll
+                        for (uint32_t k = 0; k < WPT; k += 4) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(src + x0 + k);
+                            bits[k] = v.x; bits[k + 1] = v.y; bits[k + 2] = v.z; bits[k + 3] = v.w;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (uint32_t k = 0; k < WPT; ++k) bits[k] = 0;
+                }
+            } else {
+#pragma unroll
+                for (uint32_t k = 0; k < WPT; k += 2) {
+                    const uint4 two = *reinterpret_cast<const uint4*>(packed + x0 + k);
+                    bits[k] = two.x;
+                    bits[k + 1] = two.z;
+                }
             }
+            uint32_t c = 0;
+#pragma unroll
+            for (uint32_t k = 0; k < WPT; ++k) c += __popc(bits[k]);
+            uint32_t tile_total;
+            uint32_t run = carry + block_exclusive_scan<THREADS>(c, s_warp, tile_total);
+#pragma unroll
+            for (uint32_t k = 0; k < WPT; k += 2) {
+                const uint32_t r1 = run + __popc(bits[k]);
+                *reinterpret_cast<uint4*>(packed + x0 + k) = make_uint4(bits[k], run, bits[k + 1], r1);
+                run = r1 + __popc(bits[k + 1]);
+            }
+            carry += tile_total;
         }
-        __syncthreads();
-        if (staged)
-            for (uint32_t x = threadIdx.x; x < total; x += THREADS) colC[out0 + x] = stage[x];
+        const uint32_t total = carry - shift;
 
-        // ---- values: accumulate every product at the rank of its column.  Rows
-        // with more output entries than the value buffer take one pass over the
-        // products per buffer-sized window of ranks.
+        // ---- columns and values, one window of ranks at a time
         for (uint32_t r0 = 0; r0 < total; r0 += val_cap) {
             const uint32_t span = min(val_cap, total - r0);
+            const uint32_t lim = span + shift;                    // slots [shift, lim) are this window
+            __syncthreads();                                      // ranks written; previous window copied out
+            for (uint32_t x = threadIdx.x; x < (lim + 3) / 4; x += THREADS)
+                reinterpret_cast<float4*>(vals)[x] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             __syncthreads();
-            for (uint32_t x = threadIdx.x; x < span; x += THREADS) vals[x] = 0.0f;
-            __syncthreads();
-            for (uint32_t p0 = pa; p0 < pe; p0 += A_CHUNK) {
-                const uint32_t n = min(static_cast<uint32_t>(A_CHUNK), pe - p0);
-                if (!one_chunk) {
-                    __syncthreads();
-                    if (threadIdx.x == 0) s_n_long = 0;
-                    __syncthreads();
-                    stage_chunk<THREADS, NUMERIC>(A, w, p0, n, ch);
-                    __syncthreads();
-                }
-                walk_chunk<THREADS, true>(B, ch, n, [&](uint32_t j, float prod) {
+            walk_products<THREADS, true>(A, B, w, pa, pe, wl, &s_n_long, s_warp, [&](const auto& col, const auto& prod, const auto& act) {
+                // all rank lookups first, then the stores, then the atomics: the
+                // shared-memory round trips of a batch overlap instead of chaining
+                constexpr int U = sizeof(col) / sizeof(col[0]);
+                uint32_t slot[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const uint32_t j = col[u];
                     const uint2 wp = packed[j >> 5];
-                    const uint32_t rank = wp.y + __popc(wp.x & ((1u << (j & 31)) - 1u)) - r0;
-                    if (rank < span) atomicAdd(&vals[rank], prod);
-                });
-            }
+                    slot[u] = act[u] ? wp.y + __popc(wp.x & ((1u << (j & 31)) - 1u)) - r0 : 0xffffffffu;
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (slot[u] < lim) cols[slot[u]] = static_cast<ColT>(col[u]);   // slots below `shift`: never copied out
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (slot[u] < lim) atomicAdd(&vals[slot[u]], prod[u]);
+            });
             __syncthreads();
-            for (uint32_t x = threadIdx.x; x < span; x += THREADS) valC[out0 + r0 + x] = vals[x];
+            uint32_t* gcol = colC + (out0 + r0 - shift);          // slot s <-> gcol[s]; 16-byte aligned
+            float* gval = valC + (out0 + r0 - shift);
+            for (uint32_t q = threadIdx.x; q < (lim + 3) / 4; q += THREADS) {
+                const uint32_t s0 = q * 4;
+                if (vec_ok && s0 >= shift && s0 + 4 <= lim) {
+                    if constexpr (sizeof(ColT) == 2) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(cols + s0);
+                        *reinterpret_cast<uint4*>(gcol + s0) =
+                            make_uint4(raw.x & 0xffffu, raw.x >> 16, raw.y & 0xffffu, raw.y >> 16);
+                    } else {
+                        *reinterpret_cast<uint4*>(gcol + s0) = *reinterpret_cast<const uint4*>(cols + s0);
+                    }
+                    *reinterpret_cast<float4*>(gval + s0) = *reinterpret_cast<const float4*>(vals + s0);
+                } else {
+                    for (uint32_t s = max(s0, shift); s < min(s0 + 4, lim); ++s) {
+                        gcol[s] = cols[s];
+                        gval[s] = vals[s];
+                    }
+                }
+            }
         }
-        __syncthreads();
     }
 }
 
@@ -537,9 +599,9 @@ row_scan_kernel(const uint32_t* __restrict__ cnt, uint32_t M, uint32_t* __restri
 struct Plan {
     Csr A, B;
     Work w;
-    uint32_t words;             // bitmap words per row
+    uint32_t pitch;             // bitmap words per row, a multiple of 8 (rows stay 32-byte aligned)
     unsigned long long* d_total;
-    uint32_t* pattern;          // [M][words] row bitmaps kept between the passes, or null
+    uint32_t* pattern;          // [M][pitch] row bitmaps kept between the passes, or null
 };
 
 int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
@@ -574,9 +636,9 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
     uintptr_t desc = (reinterpret_cast<uintptr_t>(base + head_words) + 15) & ~static_cast<uintptr_t>(15);
     pl->w.rows_mid = reinterpret_cast<uint4*>(desc);
     pl->w.rows_heavy = pl->w.rows_mid + M;
-    pl->words = (B->N + 31) / 32;
-    if (pl->words == 0)
-        pl->words = 1;
+    pl->pitch = ((B->N + 31) / 32 + 7) & ~7u;
+    if (pl->pitch == 0)
+        pl->pitch = 8;
     pl->pattern = nullptr;
     return SB200_OK;
 }
@@ -588,7 +650,7 @@ int bin_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, cudaStream_t 
     if (pl.A.M == 0)
         return SB200_OK;
     const unsigned blocks = static_cast<unsigned>(ctx->sm_count) * 8;
-    row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w, rowC);
+    row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w, rowC, pl.B.N);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
@@ -602,13 +664,13 @@ bool same_operands(const sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B)
            k.nnzB == B->NNZ;
 }
 
-// Row bitmaps are kept when they fit the limit (M * ceil(N / 32) * 4 bytes).
+// Row bitmaps are kept when they fit the limit (M * pitch * 4 bytes).
 constexpr size_t PATTERN_LIMIT = static_cast<size_t>(2) << 30;
 
 int prepare_pattern(sb200_ctx* ctx, Plan* pl, const sb200_csr* A, const sb200_csr* B)
 {
     ctx->sp_valid = 0;
-    const size_t need = static_cast<size_t>(A->M) * pl->words * 4;
+    const size_t need = static_cast<size_t>(A->M) * pl->pitch * 4;
     if (need == 0 || need > PATTERN_LIMIT)
         return SB200_OK;                       // numeric pass rebuilds the bitmaps
     if (need > ctx->sp_pattern_bytes) {
@@ -629,28 +691,29 @@ int prepare_pattern(sb200_ctx* ctx, Plan* pl, const sb200_csr* A, const sb200_cs
 }
 
 constexpr int HEAVY_THREADS = 1024;
-constexpr uint32_t HEAVY_VAL_CAP = 40960;     // 160 KB of fp32 accumulators, one CTA per SM
+constexpr uint32_t HEAVY_VAL_CAP = 20480;     // 160 KB of columns + fp32 accumulators, one CTA per SM
 
-template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN>
+template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN, typename ColT>
 int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_t* n_rows,
                 uint32_t* next_row, uint32_t val_cap, const uint32_t* rowC, uint32_t* colC, float* valC,
                 cudaStream_t stream)
 {
-    constexpr int NWARPS = THREADS / 32;
-    const uint32_t wpw = ((pl.words + NWARPS - 1) / NWARPS + 31) & ~31u;
-    const size_t padded = static_cast<size_t>(wpw) * NWARPS;
-    const size_t chunk_bytes = 4 * A_CHUNK * 4;                // qs, len, aval, longs
+    const uint32_t tiles = (pl.pitch + TILE_WORDS - 1) / TILE_WORDS;
+    const size_t padded = static_cast<size_t>(tiles) * TILE_WORDS;
+    const size_t lists = WalkLists<THREADS>::BYTES;
+    constexpr size_t per_entry = 4 + sizeof(ColT);              // accumulator + staged column
     if (NUMERIC) {
-        // the value buffer takes what the bitmap leaves of the 227 KB per CTA
-        const size_t room = 226 * 1024, fixed = padded * 8 + chunk_bytes;
-        if (fixed + 1024 * 4 > room)
+        // columns + values take what the bitmap leaves of the 227 KB per CTA
+        const size_t room = 226 * 1024, fixed = padded * 8 + lists + 4 * per_entry;
+        if (fixed + 1024 * per_entry > room)
             return SB200_ERR_TOO_LARGE;
-        if (fixed + static_cast<size_t>(val_cap) * 4 > room)
-            val_cap = static_cast<uint32_t>((room - fixed) / 4);
+        if (fixed + static_cast<size_t>(val_cap) * per_entry > room)
+            val_cap = static_cast<uint32_t>((room - fixed) / per_entry);
+        val_cap &= ~3u;                                         // windows start on 16-byte boundaries
     }
-    const size_t smem = NUMERIC ? padded * 8 + chunk_bytes + static_cast<size_t>(val_cap) * 4
-                                : padded * 4 + chunk_bytes;
-    auto kern = cta_rows_kernel<THREADS, MIN_BLOCKS, NUMERIC, FROM_PATTERN>;
+    const size_t smem = NUMERIC ? padded * 8 + lists + (static_cast<size_t>(val_cap) + 4) * per_entry
+                                : static_cast<size_t>(pl.pitch) * 4 + lists;
+    auto kern = cta_rows_kernel<THREADS, MIN_BLOCKS, NUMERIC, FROM_PATTERN, ColT>;
     // attribute and occupancy of this instance, remembered per (device, smem size)
     static thread_local int cached_dev = -1, cached_per_sm = 1;
     static thread_local size_t cached_smem = 0;
@@ -667,13 +730,17 @@ int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_
         cached_dev = ctx->device;
         cached_smem = smem;
         cached_per_sm = n;
+        if (getenv("SB200_VERBOSE"))
+            fprintf(stderr, "sb200: cta_rows<%d,%d,%d> smem %zu B, %d CTAs/SM, val_cap %u\n", THREADS,
+                    int(NUMERIC), int(FROM_PATTERN), smem, n, val_cap);
     }
     const int per_sm = cached_per_sm;
     const unsigned grid = static_cast<unsigned>(ctx->sm_count) * per_sm;
     if (cudaMemsetAsync(next_row, 0, 4, stream) != cudaSuccess)
         return SB200_ERR_CUDA;
-    kern<<<grid, THREADS, smem, stream>>>(pl.A, pl.B, pl.w, rows, n_rows, next_row, pl.words, wpw, val_cap,
-                                          pl.pattern, rowC, colC, valC);
+    const int vec_ok = ((reinterpret_cast<uintptr_t>(colC) | reinterpret_cast<uintptr_t>(valC)) & 15) == 0;
+    kern<<<grid, THREADS, smem, stream>>>(pl.A, pl.B, pl.w, rows, n_rows, next_row, pl.pitch, tiles, val_cap,
+                                          vec_ok, pl.pattern, rowC, colC, valC);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
@@ -684,13 +751,22 @@ int run_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, uint32_t* col
 {
     if (pl.A.M == 0)
         return SB200_OK;
-    // heavy rows first: 1024 threads and a large value buffer, one CTA per SM
-    int rc = launch_rows<HEAVY_THREADS, 1, NUMERIC, FROM_PATTERN>(
+    // heavy rows first: 1024 threads and a large window buffer, one CTA per SM
+    int rc = launch_rows<HEAVY_THREADS, 1, NUMERIC, FROM_PATTERN, uint32_t>(
         ctx, pl, pl.w.rows_heavy, pl.w.counters + 2, pl.w.counters + 3, HEAVY_VAL_CAP, rowC, colC, valC, stream);
     if (rc)
         return rc;
-    rc = launch_rows<ROW_THREADS, 4, NUMERIC, FROM_PATTERN>(
-        ctx, pl, pl.w.rows_mid, pl.w.counters + 1, pl.w.counters + 3, VAL_CAP, rowC, colC, valC, stream);
+    if constexpr (!NUMERIC)
+        rc = launch_rows<ROW_THREADS, 6, false, false, uint32_t>(
+            ctx, pl, pl.w.rows_mid, pl.w.counters + 1, pl.w.counters + 3, 0, rowC, colC, valC, stream);
+    else if (pl.B.N <= 65536)
+        rc = launch_rows<ROW_THREADS, 4, NUMERIC, FROM_PATTERN, uint16_t>(
+            ctx, pl, pl.w.rows_mid, pl.w.counters + 1, pl.w.counters + 3, mid_cap(pl.B.N), rowC, colC, valC,
+            stream);
+    else
+        rc = launch_rows<ROW_THREADS, 3, NUMERIC, FROM_PATTERN, uint32_t>(
+            ctx, pl, pl.w.rows_mid, pl.w.counters + 1, pl.w.counters + 3, mid_cap(pl.B.N), rowC, colC, valC,
+            stream);
     if (rc)
         return rc;
     tiny_rows_kernel<NUMERIC><<<static_cast<unsigned>(ctx->sm_count) * 8, 256, 0, stream>>>(
