@@ -10,6 +10,7 @@ namespace sb200 {
 
 int ensure_workspace(sb200_ctx* ctx, size_t bytes)
 {
+    ctx->sp_work_valid = 0;                // whoever asks is about to overwrite the buffer
     if (bytes <= ctx->workspace_bytes)
         return SB200_OK;
     // cudaFree waits for work that may still use the old buffer
@@ -59,6 +60,7 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->d_sp_pattern = nullptr;
     ctx->sp_pattern_bytes = 0;
     ctx->sp_valid = 0;
+    ctx->sp_work_valid = 0;
     ctx->d_status = nullptr;
     if (cudaMalloc(&ctx->d_status, sizeof(unsigned)) != cudaSuccess ||
         cudaMemset(ctx->d_status, 0, sizeof(unsigned)) != cudaSuccess) {

@@ -66,6 +66,7 @@ struct sb200_ctx {
     size_t sp_pattern_bytes;
     sb200::SpPatternKey sp_key;
     int sp_valid;
+    int sp_work_valid;         // ... and its per-row / per-nonzero arrays are still in the workspace
 };
 
 namespace sb200 {

@@ -28,6 +28,10 @@
 // values agree with a sequential sum to rounding, while ROW and COL are exact.
 #include "common.cuh"
 
+// the symbolic instance of the row kernel folds the output offset to zero, which
+// turns a bounds check of its (dead) numeric half into "unsigned >= 0"
+#pragma nv_diag_suppress 186
+
 namespace sb200 {
 namespace {
 
@@ -48,6 +52,7 @@ struct Csr {
 
 struct Work {
     uint32_t* cnt;         // [M] nnz of each output row
+    uint32_t* prod;        // [M] scalar products of each row (saturating)
     uint32_t* bq;          // [nnzA] for every nonzero (i,k) of A: where B's row k starts
     uint32_t* blen;        // [nnzA] ... and its length
     uint4* rows_mid;       // [M] {row, first nonzero, end nonzero, products} per CTA-path row
@@ -84,6 +89,7 @@ row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (lane == 0) {
             const uint32_t P = s > 0xffffffffull ? 0xffffffffu : static_cast<uint32_t>(s);
+            w.prod[i] = P;
             if (P == 0) {
                 w.cnt[i] = 0;
             } else if (P <= TINY_MAX) {
@@ -94,6 +100,25 @@ row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
                 w.rows_heavy[atomicAdd(&w.counters[2], 1u)] = make_uint4(i, pa, pe, P);
             }
         }
+    }
+}
+
+// The bins again, from the product counts a previous row_products_kernel left in
+// the workspace, now that the output row sizes are known (one thread per row).
+__global__ void __launch_bounds__(256)
+rebin_kernel(Csr A, Work w, const uint32_t* __restrict__ rowC, uint32_t n_cols)
+{
+    const uint32_t cap = mid_cap(n_cols);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < A.M; i += gridDim.x * blockDim.x) {
+        const uint32_t P = w.prod[i];
+        if (P == 0)
+            continue;
+        if (P <= TINY_MAX)
+            w.list_tiny[atomicAdd(&w.counters[0], 1u)] = i;
+        else if (P < HEAVY_MIN && rowC[i + 1] - rowC[i] <= cap)
+            w.rows_mid[atomicAdd(&w.counters[1], 1u)] = make_uint4(i, A.row[i], A.row[i + 1], P);
+        else
+            w.rows_heavy[atomicAdd(&w.counters[2], 1u)] = make_uint4(i, A.row[i], A.row[i + 1], P);
     }
 }
 
@@ -221,6 +246,11 @@ struct WalkLists {
     float* aval;       // [CAP]  A's value
     uint8_t* n;        // [CAP]  entries in the piece (1..SUB)
 };
+
+__device__ __forceinline__ void prefetch_l2(const void* p)
+{
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 
 template <int THREADS>
 __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s_warp,
@@ -406,21 +436,40 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t n_rows = *n_rows_ptr;
 
-    // Rows are handed out through a counter: their cost varies by an order of
-    // magnitude in the heavy bin, a fixed stride would leave SMs idle.
+    // Rows are handed out through a counter (their cost varies by an order of
+    // magnitude in the heavy bin, a fixed stride would leave SMs idle), a few at
+    // a time where rows are small, so that the next row is known early enough to
+    // pull what its prologue reads into L2 while the current row is worked on.
+    constexpr uint32_t BATCH = THREADS >= 1024 ? 1 : 4;
     for (;;) {
         __syncthreads();                                          // previous row done with shared memory
         if (threadIdx.x == 0) {
-            s_next = atomicAdd(next_row, 1u);
+            s_next = atomicAdd(next_row, BATCH);
             s_n_long = 0;
         }
         __syncthreads();
-        const uint32_t idx = s_next;
-        if (idx >= n_rows)
+        const uint32_t idx_first = s_next;
+        if (idx_first >= n_rows)
             break;
+        const uint32_t idx_end = min(idx_first + BATCH, n_rows);
+      for (uint32_t idx = idx_first; idx < idx_end; ++idx) {
+        if (idx != idx_first) __syncthreads();                    // previous row done with shared memory
         const uint4 d = rows[idx];
         const uint32_t i = d.x, pa = d.y, pe = d.z;
         const uint32_t out0 = NUMERIC ? rowC[i] : 0;
+        if (BATCH > 1 && idx + 1 < idx_end) {
+            const uint4 dn = rows[idx + 1];
+            if ((threadIdx.x & 7) == 0 && dn.y + threadIdx.x < dn.z) {
+                prefetch_l2(w.blen + dn.y + threadIdx.x);
+                prefetch_l2(w.bq + dn.y + threadIdx.x);
+                if (NUMERIC) prefetch_l2(A.val + dn.y + threadIdx.x);
+            }
+            if (NUMERIC && threadIdx.x == 0) prefetch_l2(rowC + dn.x);
+            if (NUMERIC && FROM_PATTERN) {
+                const uint32_t* nsrc = pattern + static_cast<size_t>(dn.x) * pitch;
+                for (uint32_t x = threadIdx.x * 8; x < pitch; x += THREADS * 8) prefetch_l2(nsrc + x);
+            }
+        }
 
         if (!(NUMERIC && FROM_PATTERN)) {
             // ---- pattern: mark every product's column
@@ -558,41 +607,62 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
                 }
             }
         }
+      }
     }
 }
 
 // --------------------------------------------------------------- row scan
-// rowC[0] = 0, rowC[i+1] = sum cnt[0..i]; one CTA, chunks of 1024 with carry.
+// rowC[0] = 0, rowC[i+1] = sum cnt[0..i]; one CTA, chunks of 8192 counts (eight
+// consecutive ones per thread, read with two 16-byte loads) with a carry.
 __global__ void __launch_bounds__(1024)
 row_scan_kernel(const uint32_t* __restrict__ cnt, uint32_t M, uint32_t* __restrict__ rowC,
                 unsigned long long* __restrict__ total_out)
 {
+    constexpr uint32_t PER = 8;
     __shared__ unsigned long long s_warp[32];
-    __shared__ unsigned long long s_carry;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) {
-        s_carry = 0;
-        rowC[0] = 0;
-    }
-    __syncthreads();
-    for (uint32_t base = 0; base < M; base += 1024) {
-        const uint32_t i = base + threadIdx.x;
-        unsigned long long v = i < M ? cnt[i] : 0, incl = v;
+    if (threadIdx.x == 0) rowC[0] = 0;
+    unsigned long long carry = 0;
+    for (uint32_t base = 0; base < M; base += 1024 * PER) {
+        const uint32_t i0 = base + threadIdx.x * PER;
+        uint32_t v[PER];
+        if (i0 + PER <= M) {                                      // cnt is 16-byte aligned
+            const uint4 lo = *reinterpret_cast<const uint4*>(cnt + i0);
+            const uint4 hi = *reinterpret_cast<const uint4*>(cnt + i0 + 4);
+            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+            v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+        } else {
+#pragma unroll
+            for (uint32_t k = 0; k < PER; ++k) v[k] = i0 + k < M ? cnt[i0 + k] : 0u;
+        }
+        unsigned long long mine = 0;
+#pragma unroll
+        for (uint32_t k = 0; k < PER; ++k) mine += v[k];
+        unsigned long long incl = mine;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, o);
             if (lane >= o) incl += t;
         }
+        __syncthreads();                                          // s_warp of the previous chunk read
         if (lane == 31) s_warp[warp] = incl;
         __syncthreads();
-        unsigned long long off = s_carry;
-        for (int x = 0; x < warp; ++x) off += s_warp[x];
-        if (i < M) rowC[i + 1] = static_cast<uint32_t>(off + incl);
-        __syncthreads();
-        if (threadIdx.x == 1023) s_carry = off + incl;
-        __syncthreads();
+        unsigned long long off = carry, chunk_total = 0;
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+            const unsigned long long t = s_warp[x];
+            if (x < warp) off += t;
+            chunk_total += t;
+        }
+        unsigned long long run = off + incl - mine;
+#pragma unroll
+        for (uint32_t k = 0; k < PER; ++k) {
+            run += v[k];
+            if (i0 + k < M) rowC[i0 + k + 1] = static_cast<uint32_t>(run);
+        }
+        carry += chunk_total;
     }
-    if (threadIdx.x == 0) *total_out = s_carry;
+    if (threadIdx.x == 0) *total_out = carry;
 }
 
 // ------------------------------------------------------------------- host
@@ -617,19 +687,24 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
     pl->A = Csr{A->ROW, A->COL, A->V, A->M, A->N};
     pl->B = Csr{B->ROW, B->COL, B->V, B->M, B->N};
     const size_t M = A->M, nnzA = A->NNZ;
-    // cnt[M] | bq[nnzA] | blen[nnzA] | list_tiny[M] | counters[4] | total (8 B) | pad |
+    // cnt[M] | prod[M] | bq[nnzA] | blen[nnzA] | list_tiny[M] | counters[4] | total (8 B) | pad |
     // rows_mid[M] (16 B each) | rows_heavy[M]
-    const size_t head_words = (2 * M + 2 * nnzA + 4 + 2 + 3) & ~static_cast<size_t>(3);
+    const size_t head_words = (3 * M + 2 * nnzA + 4 + 2 + 3) & ~static_cast<size_t>(3);
     const size_t bytes = head_words * 4 + 2 * M * sizeof(uint4) + 64;
+    // what a symbolic pass left in the workspace stays usable if the buffer is not replaced
+    const int work_kept = ctx->sp_work_valid;
+    const float* before = ctx->d_workspace;
     const int rc = ensure_workspace(ctx, bytes);
     if (rc)
         return rc;
+    ctx->sp_work_valid = work_kept && ctx->d_workspace == before;
     uint32_t* base = reinterpret_cast<uint32_t*>(ctx->d_workspace);
     pl->w.cnt = base;
-    pl->w.bq = base + M;
-    pl->w.blen = base + M + nnzA;
-    pl->w.list_tiny = base + M + 2 * nnzA;
-    pl->w.counters = base + 2 * M + 2 * nnzA;
+    pl->w.prod = base + M;
+    pl->w.bq = base + 2 * M;
+    pl->w.blen = base + 2 * M + nnzA;
+    pl->w.list_tiny = base + 2 * M + 2 * nnzA;
+    pl->w.counters = base + 3 * M + 2 * nnzA;
     uintptr_t tot = reinterpret_cast<uintptr_t>(pl->w.counters + 4);
     tot = (tot + 7) & ~static_cast<uintptr_t>(7);
     pl->d_total = reinterpret_cast<unsigned long long*>(tot);
@@ -643,14 +718,19 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
     return SB200_OK;
 }
 
-int bin_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, cudaStream_t stream)
+// `reuse`: the per-nonzero and per-row arrays of an earlier call on the same
+// operands are still in the workspace; only the bins are rebuilt (rowC given).
+int bin_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, bool reuse, cudaStream_t stream)
 {
     if (cudaMemsetAsync(pl.w.counters, 0, 16, stream) != cudaSuccess)
         return SB200_ERR_CUDA;
     if (pl.A.M == 0)
         return SB200_OK;
     const unsigned blocks = static_cast<unsigned>(ctx->sm_count) * 8;
-    row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w, rowC, pl.B.N);
+    if (reuse && rowC)
+        rebin_kernel<<<(pl.A.M + 255) / 256, 256, 0, stream>>>(pl.A, pl.w, rowC, pl.B.N);
+    else
+        row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w, rowC, pl.B.N);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
@@ -670,6 +750,7 @@ constexpr size_t PATTERN_LIMIT = static_cast<size_t>(2) << 30;
 int prepare_pattern(sb200_ctx* ctx, Plan* pl, const sb200_csr* A, const sb200_csr* B)
 {
     ctx->sp_valid = 0;
+    ctx->sp_work_valid = 0;
     const size_t need = static_cast<size_t>(A->M) * pl->pitch * 4;
     if (need == 0 || need > PATTERN_LIMIT)
         return SB200_OK;                       // numeric pass rebuilds the bitmaps
@@ -793,11 +874,12 @@ extern "C" int sb200_spgemm_csr_symbolic(sb200_ctx* ctx, const sb200_csr* A, con
         return rc;
     if (cudaSetDevice(ctx->device) != cudaSuccess)
         return SB200_ERR_CUDA;
-    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, nullptr, stream)))
+    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, nullptr, false, stream)))
         return rc;
     if ((rc = run_rows<false, false>(ctx, pl, nullptr, nullptr, nullptr, stream)))
         return rc;
     ctx->sp_valid = pl.pattern != nullptr;
+    ctx->sp_work_valid = ctx->sp_valid;
     row_scan_kernel<<<1, 1024, 0, stream>>>(pl.w.cnt, pl.A.M, rowC, pl.d_total);
     ctx->launches += 1;
     unsigned long long total = 0;
@@ -829,9 +911,10 @@ extern "C" int sb200_spgemm_csr_numeric(sb200_ctx* ctx, const sb200_csr* A, cons
         return rc;
     if (cudaSetDevice(ctx->device) != cudaSuccess)
         return SB200_ERR_CUDA;
-    if ((rc = bin_rows(ctx, pl, rowC, stream)))
+    const bool same = same_operands(ctx, A, B);
+    if ((rc = bin_rows(ctx, pl, rowC, same && ctx->sp_work_valid, stream)))
         return rc;
-    if (same_operands(ctx, A, B)) {
+    if (same) {
         pl.pattern = ctx->d_sp_pattern;
         return run_rows<true, true>(ctx, pl, rowC, colC, valC, stream);
     }
@@ -857,7 +940,7 @@ extern "C" int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_
     if (cudaMalloc(&C->ROW, (static_cast<size_t>(A->M) + 1) * 4) != cudaSuccess)
         return SB200_ERR_ALLOC;
     // symbolic: bins stay valid in the workspace for the numeric pass below
-    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, nullptr, stream)) ||
+    if ((rc = prepare_pattern(ctx, &pl, A, B)) || (rc = bin_rows(ctx, pl, nullptr, false, stream)) ||
         (rc = run_rows<false, false>(ctx, pl, nullptr, nullptr, nullptr, stream))) {
         sb200_csr_free(C);
         return rc;
@@ -882,13 +965,14 @@ extern "C" int sb200_spgemm_csr(sb200_ctx* ctx, const sb200_csr* A, const sb200_
         return SB200_ERR_ALLOC;
     }
     // bin again, now that the output row sizes are known
-    if ((rc = bin_rows(ctx, pl, C->ROW, stream))) {
+    if ((rc = bin_rows(ctx, pl, C->ROW, true, stream))) {
         sb200_csr_free(C);
         return rc;
     }
     rc = pl.pattern ? run_rows<true, true>(ctx, pl, C->ROW, C->COL, C->V, stream)
                     : run_rows<true, false>(ctx, pl, C->ROW, C->COL, C->V, stream);
     ctx->sp_valid = 0;
+    ctx->sp_work_valid = 0;
     if (rc) {
         sb200_csr_free(C);
         return rc;
