@@ -36,6 +36,7 @@ namespace sb200 {
 namespace {
 
 constexpr int TINY_MAX = 32;
+constexpr uint32_t ALL_WINDOWS = 0xffffffffu;   // work item covers the whole output row
 constexpr unsigned HEAVY_MIN = 16384;
 constexpr int ROW_THREADS = 256;
 // Output entries a mid-bin CTA holds in shared memory (wider rows go to the heavy
@@ -55,11 +56,33 @@ struct Work {
     uint32_t* prod;        // [M] scalar products of each row (saturating)
     uint32_t* bq;          // [nnzA] for every nonzero (i,k) of A: where B's row k starts
     uint32_t* blen;        // [nnzA] ... and its length
-    uint4* rows_mid;       // [M] {row, first nonzero, end nonzero, products} per CTA-path row
-    uint4* rows_heavy;     // [M] the same for rows with many products (queued first)
+    uint4* rows_mid;       // [M] {row, first nonzero, end nonzero, window} per CTA-path row
+    uint4* rows_heavy;     // [2M] the same for rows with many products or a wide output;
+                           //      numeric pass: one entry per window of the output row
     uint32_t* list_tiny;   // [M]
-    uint32_t* counters;    // [4]: tiny, mid, heavy, next row of the running row kernel
+    uint32_t* counters;    // [8]: tiny, mid, heavy, next row of the running row kernel, heavy windows
 };
+
+// Queues a heavy row.  In the numeric pass (width = its output entries) a row
+// wider than one window of `heavy_cap` entries is cut into one work item per
+// window, so that it spreads over several SMs; these items go to the second
+// half of the queue (rows_heavy[M .. 2M), counters[4]).  When that half is full
+// the row stays a single item whose CTA walks the windows itself.
+__device__ __forceinline__ void queue_heavy(const Work& w, uint32_t M, uint32_t i, uint32_t pa,
+                                            uint32_t pe, uint32_t width, uint32_t heavy_cap)
+{
+    const uint32_t nw = heavy_cap ? (width + heavy_cap - 1) / heavy_cap : 1u;
+    if (nw > 1) {
+        const uint32_t at = atomicAdd(&w.counters[4], nw);
+        if (at + nw <= M) {
+            for (uint32_t k = 0; k < nw; ++k) w.rows_heavy[M + at + k] = make_uint4(i, pa, pe, k);
+            return;
+        }
+        for (uint32_t k = 0; k < nw && at + k < M; ++k)           // taken but unused: empty items
+            w.rows_heavy[M + at + k] = make_uint4(ALL_WINDOWS, 0u, 0u, 0u);
+    }
+    w.rows_heavy[atomicAdd(&w.counters[2], 1u)] = make_uint4(i, pa, pe, ALL_WINDOWS);
+}
 
 // ------------------------------------------------------------ row work
 // One warp per row of A: records where each nonzero's row of B lies (so that
@@ -69,7 +92,7 @@ struct Work {
 // value buffer also goes to the heavy bin, whose kernel has a large one.
 __global__ void __launch_bounds__(256)
 row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
-                    const uint32_t* __restrict__ rowC, uint32_t n_cols)
+                    const uint32_t* __restrict__ rowC, uint32_t n_cols, uint32_t heavy_cap)
 {
     const int lane = threadIdx.x & 31;
     const uint32_t cap = mid_cap(n_cols);
@@ -95,9 +118,9 @@ row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
             } else if (P <= TINY_MAX) {
                 w.list_tiny[atomicAdd(&w.counters[0], 1u)] = i;
             } else if (P < HEAVY_MIN && !(rowC && rowC[i + 1] - rowC[i] > cap)) {
-                w.rows_mid[atomicAdd(&w.counters[1], 1u)] = make_uint4(i, pa, pe, P);
+                w.rows_mid[atomicAdd(&w.counters[1], 1u)] = make_uint4(i, pa, pe, ALL_WINDOWS);
             } else {
-                w.rows_heavy[atomicAdd(&w.counters[2], 1u)] = make_uint4(i, pa, pe, P);
+                queue_heavy(w, A.M, i, pa, pe, rowC ? rowC[i + 1] - rowC[i] : 0u, rowC ? heavy_cap : 0u);
             }
         }
     }
@@ -106,7 +129,7 @@ row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
 // The bins again, from the product counts a previous row_products_kernel left in
 // the workspace, now that the output row sizes are known (one thread per row).
 __global__ void __launch_bounds__(256)
-rebin_kernel(Csr A, Work w, const uint32_t* __restrict__ rowC, uint32_t n_cols)
+rebin_kernel(Csr A, Work w, const uint32_t* __restrict__ rowC, uint32_t n_cols, uint32_t heavy_cap)
 {
     const uint32_t cap = mid_cap(n_cols);
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < A.M; i += gridDim.x * blockDim.x) {
@@ -116,9 +139,9 @@ rebin_kernel(Csr A, Work w, const uint32_t* __restrict__ rowC, uint32_t n_cols)
         if (P <= TINY_MAX)
             w.list_tiny[atomicAdd(&w.counters[0], 1u)] = i;
         else if (P < HEAVY_MIN && rowC[i + 1] - rowC[i] <= cap)
-            w.rows_mid[atomicAdd(&w.counters[1], 1u)] = make_uint4(i, A.row[i], A.row[i + 1], P);
+            w.rows_mid[atomicAdd(&w.counters[1], 1u)] = make_uint4(i, A.row[i], A.row[i + 1], ALL_WINDOWS);
         else
-            w.rows_heavy[atomicAdd(&w.counters[2], 1u)] = make_uint4(i, A.row[i], A.row[i + 1], P);
+            queue_heavy(w, A.M, i, A.row[i], A.row[i + 1], rowC[i + 1] - rowC[i], heavy_cap);
     }
 }
 
@@ -408,7 +431,8 @@ __device__ __forceinline__ void walk_products(const Csr& A, const Csr& B, const 
 template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN, typename ColT>
 __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
-                const uint32_t* __restrict__ n_rows_ptr, uint32_t* __restrict__ next_row,
+                const uint32_t* __restrict__ n_rows_ptr, const uint4* __restrict__ rows2,
+                const uint32_t* __restrict__ n_rows2_ptr, uint32_t cap2, uint32_t* __restrict__ next_row,
                 uint32_t pitch, uint32_t tiles, uint32_t val_cap, int vec_ok,
                 uint32_t* __restrict__ pattern, const uint32_t* __restrict__ rowC,
                 uint32_t* __restrict__ colC, float* __restrict__ valC)
@@ -434,7 +458,10 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
     __shared__ uint32_t s_next;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t n_rows = *n_rows_ptr;
+    // the work items: a first list and, when given, a second one of at most cap2 entries
+    const uint32_t n_rows1 = *n_rows_ptr;
+    const uint32_t n_rows = n_rows1 + (rows2 ? min(*n_rows2_ptr, cap2) : 0u);
+    auto item = [&](uint32_t idx) -> uint4 { return idx < n_rows1 ? rows[idx] : rows2[idx - n_rows1]; };
 
     // Rows are handed out through a counter (their cost varies by an order of
     // magnitude in the heavy bin, a fixed stride would leave SMs idle), a few at
@@ -454,11 +481,13 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
         const uint32_t idx_end = min(idx_first + BATCH, n_rows);
       for (uint32_t idx = idx_first; idx < idx_end; ++idx) {
         if (idx != idx_first) __syncthreads();                    // previous row done with shared memory
-        const uint4 d = rows[idx];
+        const uint4 d = item(idx);
         const uint32_t i = d.x, pa = d.y, pe = d.z;
+        if (i == ALL_WINDOWS)
+            continue;                                             // an empty item of the window queue
         const uint32_t out0 = NUMERIC ? rowC[i] : 0;
-        if (BATCH > 1 && idx + 1 < idx_end) {
-            const uint4 dn = rows[idx + 1];
+        if (BATCH > 1 && idx + 1 < idx_end && item(idx + 1).x != ALL_WINDOWS) {
+            const uint4 dn = item(idx + 1);
             if ((threadIdx.x & 7) == 0 && dn.y + threadIdx.x < dn.z) {
                 prefetch_l2(w.blen + dn.y + threadIdx.x);
                 prefetch_l2(w.bq + dn.y + threadIdx.x);
@@ -559,8 +588,11 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
         }
         const uint32_t total = carry - shift;
 
-        // ---- columns and values, one window of ranks at a time
-        for (uint32_t r0 = 0; r0 < total; r0 += val_cap) {
+        // ---- columns and values, one window of ranks at a time: the item's
+        // window, or all of them
+        const uint32_t r_begin = d.w == ALL_WINDOWS ? 0u : d.w * val_cap;
+        const uint32_t r_end = d.w == ALL_WINDOWS ? total : min(total, r_begin + val_cap);
+        for (uint32_t r0 = r_begin; r0 < r_end; r0 += val_cap) {
             const uint32_t span = min(val_cap, total - r0);
             const uint32_t lim = span + shift;                    // slots [shift, lim) are this window
             __syncthreads();                                      // ranks written; previous window copied out
@@ -687,10 +719,10 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
     pl->A = Csr{A->ROW, A->COL, A->V, A->M, A->N};
     pl->B = Csr{B->ROW, B->COL, B->V, B->M, B->N};
     const size_t M = A->M, nnzA = A->NNZ;
-    // cnt[M] | prod[M] | bq[nnzA] | blen[nnzA] | list_tiny[M] | counters[4] | total (8 B) | pad |
-    // rows_mid[M] (16 B each) | rows_heavy[M]
-    const size_t head_words = (3 * M + 2 * nnzA + 4 + 2 + 3) & ~static_cast<size_t>(3);
-    const size_t bytes = head_words * 4 + 2 * M * sizeof(uint4) + 64;
+    // cnt[M] | prod[M] | bq[nnzA] | blen[nnzA] | list_tiny[M] | counters[8] | total (8 B) | pad |
+    // rows_mid[M] (16 B each) | rows_heavy[2M]
+    const size_t head_words = (3 * M + 2 * nnzA + 8 + 2 + 3) & ~static_cast<size_t>(3);
+    const size_t bytes = head_words * 4 + 3 * M * sizeof(uint4) + 64;
     // what a symbolic pass left in the workspace stays usable if the buffer is not replaced
     const int work_kept = ctx->sp_work_valid;
     const float* before = ctx->d_workspace;
@@ -705,7 +737,7 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
     pl->w.blen = base + 2 * M + nnzA;
     pl->w.list_tiny = base + 2 * M + 2 * nnzA;
     pl->w.counters = base + 3 * M + 2 * nnzA;
-    uintptr_t tot = reinterpret_cast<uintptr_t>(pl->w.counters + 4);
+    uintptr_t tot = reinterpret_cast<uintptr_t>(pl->w.counters + 8);
     tot = (tot + 7) & ~static_cast<uintptr_t>(7);
     pl->d_total = reinterpret_cast<unsigned long long*>(tot);
     uintptr_t desc = (reinterpret_cast<uintptr_t>(base + head_words) + 15) & ~static_cast<uintptr_t>(15);
@@ -718,19 +750,47 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
     return SB200_OK;
 }
 
+constexpr int HEAVY_THREADS = 1024;
+constexpr uint32_t HEAVY_VAL_CAP = 1u << 20;  // "as much as fits": one CTA per SM
+
+// Output entries per window of a numeric row kernel with THREADS threads:
+// columns + values take what the bitmap leaves of the 227 KB per CTA.  0 when
+// not even a small window fits.
+template <int THREADS, typename ColT>
+uint32_t window_cap(uint32_t pitch, uint32_t want)
+{
+    const size_t tiles = (pitch + TILE_WORDS - 1) / TILE_WORDS;
+    const size_t per_entry = 4 + sizeof(ColT);                  // accumulator + staged column
+    const size_t room = 226 * 1024;
+    const size_t fixed = tiles * TILE_WORDS * 8 + WalkLists<THREADS>::BYTES + 4 * per_entry;
+    if (fixed + 1024 * per_entry > room)
+        return 0;
+    size_t cap = want;
+    if (fixed + cap * per_entry > room)
+        cap = (room - fixed) / per_entry;
+    return static_cast<uint32_t>(cap) & ~3u;                    // windows start on 16-byte boundaries
+}
+
+uint32_t heavy_window_cap(const Plan& pl)
+{
+    return pl.B.N <= 65536 ? window_cap<HEAVY_THREADS, uint16_t>(pl.pitch, HEAVY_VAL_CAP)
+                           : window_cap<HEAVY_THREADS, uint32_t>(pl.pitch, HEAVY_VAL_CAP);
+}
+
 // `reuse`: the per-nonzero and per-row arrays of an earlier call on the same
 // operands are still in the workspace; only the bins are rebuilt (rowC given).
 int bin_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, bool reuse, cudaStream_t stream)
 {
-    if (cudaMemsetAsync(pl.w.counters, 0, 16, stream) != cudaSuccess)
+    if (cudaMemsetAsync(pl.w.counters, 0, 32, stream) != cudaSuccess)
         return SB200_ERR_CUDA;
     if (pl.A.M == 0)
         return SB200_OK;
     const unsigned blocks = static_cast<unsigned>(ctx->sm_count) * 8;
+    const uint32_t heavy_cap = heavy_window_cap(pl);
     if (reuse && rowC)
-        rebin_kernel<<<(pl.A.M + 255) / 256, 256, 0, stream>>>(pl.A, pl.w, rowC, pl.B.N);
+        rebin_kernel<<<(pl.A.M + 255) / 256, 256, 0, stream>>>(pl.A, pl.w, rowC, pl.B.N, heavy_cap);
     else
-        row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w, rowC, pl.B.N);
+        row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w, rowC, pl.B.N, heavy_cap);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
@@ -771,11 +831,11 @@ int prepare_pattern(sb200_ctx* ctx, Plan* pl, const sb200_csr* A, const sb200_cs
     return SB200_OK;
 }
 
-constexpr int HEAVY_THREADS = 1024;
-constexpr uint32_t HEAVY_VAL_CAP = 20480;     // 160 KB of columns + fp32 accumulators, one CTA per SM
-
+// rows2 / n_rows2 / cap2: an optional second list of work items (the heavy
+// bin's per-window items).
 template <int THREADS, int MIN_BLOCKS, bool NUMERIC, bool FROM_PATTERN, typename ColT>
 int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_t* n_rows,
+                const uint4* rows2, const uint32_t* n_rows2, uint32_t cap2,
                 uint32_t* next_row, uint32_t val_cap, const uint32_t* rowC, uint32_t* colC, float* valC,
                 cudaStream_t stream)
 {
@@ -784,13 +844,9 @@ int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_
     const size_t lists = WalkLists<THREADS>::BYTES;
     constexpr size_t per_entry = 4 + sizeof(ColT);              // accumulator + staged column
     if (NUMERIC) {
-        // columns + values take what the bitmap leaves of the 227 KB per CTA
-        const size_t room = 226 * 1024, fixed = padded * 8 + lists + 4 * per_entry;
-        if (fixed + 1024 * per_entry > room)
+        val_cap = window_cap<THREADS, ColT>(pl.pitch, val_cap);
+        if (val_cap == 0)
             return SB200_ERR_TOO_LARGE;
-        if (fixed + static_cast<size_t>(val_cap) * per_entry > room)
-            val_cap = static_cast<uint32_t>((room - fixed) / per_entry);
-        val_cap &= ~3u;                                         // windows start on 16-byte boundaries
     }
     const size_t smem = NUMERIC ? padded * 8 + lists + (static_cast<size_t>(val_cap) + 4) * per_entry
                                 : static_cast<size_t>(pl.pitch) * 4 + lists;
@@ -820,8 +876,8 @@ int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_
     if (cudaMemsetAsync(next_row, 0, 4, stream) != cudaSuccess)
         return SB200_ERR_CUDA;
     const int vec_ok = ((reinterpret_cast<uintptr_t>(colC) | reinterpret_cast<uintptr_t>(valC)) & 15) == 0;
-    kern<<<grid, THREADS, smem, stream>>>(pl.A, pl.B, pl.w, rows, n_rows, next_row, pl.pitch, tiles, val_cap,
-                                          vec_ok, pl.pattern, rowC, colC, valC);
+    kern<<<grid, THREADS, smem, stream>>>(pl.A, pl.B, pl.w, rows, n_rows, rows2, n_rows2, cap2, next_row,
+                                          pl.pitch, tiles, val_cap, vec_ok, pl.pattern, rowC, colC, valC);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
@@ -833,21 +889,30 @@ int run_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, uint32_t* col
     if (pl.A.M == 0)
         return SB200_OK;
     // heavy rows first: 1024 threads and a large window buffer, one CTA per SM
-    int rc = launch_rows<HEAVY_THREADS, 1, NUMERIC, FROM_PATTERN, uint32_t>(
-        ctx, pl, pl.w.rows_heavy, pl.w.counters + 2, pl.w.counters + 3, HEAVY_VAL_CAP, rowC, colC, valC, stream);
+    const uint4* windows = NUMERIC ? pl.w.rows_heavy + pl.A.M : nullptr;
+    int rc;
+    if (pl.B.N <= 65536)
+        rc = launch_rows<HEAVY_THREADS, 1, NUMERIC, FROM_PATTERN, uint16_t>(
+            ctx, pl, pl.w.rows_heavy, pl.w.counters + 2, windows, pl.w.counters + 4, pl.A.M,
+            pl.w.counters + 3, HEAVY_VAL_CAP, rowC, colC, valC, stream);
+    else
+        rc = launch_rows<HEAVY_THREADS, 1, NUMERIC, FROM_PATTERN, uint32_t>(
+            ctx, pl, pl.w.rows_heavy, pl.w.counters + 2, windows, pl.w.counters + 4, pl.A.M,
+            pl.w.counters + 3, HEAVY_VAL_CAP, rowC, colC, valC, stream);
     if (rc)
         return rc;
     if constexpr (!NUMERIC)
         rc = launch_rows<ROW_THREADS, 6, false, false, uint32_t>(
-            ctx, pl, pl.w.rows_mid, pl.w.counters + 1, pl.w.counters + 3, 0, rowC, colC, valC, stream);
+            ctx, pl, pl.w.rows_mid, pl.w.counters + 1, nullptr, nullptr, 0, pl.w.counters + 3, 0, rowC, colC,
+            valC, stream);
     else if (pl.B.N <= 65536)
         rc = launch_rows<ROW_THREADS, 4, NUMERIC, FROM_PATTERN, uint16_t>(
-            ctx, pl, pl.w.rows_mid, pl.w.counters + 1, pl.w.counters + 3, mid_cap(pl.B.N), rowC, colC, valC,
-            stream);
+            ctx, pl, pl.w.rows_mid, pl.w.counters + 1, nullptr, nullptr, 0, pl.w.counters + 3,
+            mid_cap(pl.B.N), rowC, colC, valC, stream);
     else
         rc = launch_rows<ROW_THREADS, 3, NUMERIC, FROM_PATTERN, uint32_t>(
-            ctx, pl, pl.w.rows_mid, pl.w.counters + 1, pl.w.counters + 3, mid_cap(pl.B.N), rowC, colC, valC,
-            stream);
+            ctx, pl, pl.w.rows_mid, pl.w.counters + 1, nullptr, nullptr, 0, pl.w.counters + 3,
+            mid_cap(pl.B.N), rowC, colC, valC, stream);
     if (rc)
         return rc;
     tiny_rows_kernel<NUMERIC><<<static_cast<unsigned>(ctx->sm_count) * 8, 256, 0, stream>>>(

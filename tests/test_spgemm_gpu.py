@@ -43,6 +43,10 @@ def run_case(ctx, oracle, M, K, N, seedA, seedB, dens, dist, cap=4096, fn=None):
     (8192, 8192, 8192, None, "zipf", 4096),      # heavy rows: output wider than the shared buffer
     (1000, 1000, 70000, 0.0005, "poisson", 0),   # wide N: bitmap larger than 2048 words
     (300, 400, 400000, 0.01, "poisson", 0),      # very wide N, long rows of B: heavy bin, rank windows
+    (64, 2048, 65536, 0.02, "poisson", 0),       # ~37 k entries per output row: two windows each, one
+                                                 # work item per window until the window queue is full
+    (64, 2048, 65536, 0.05, "poisson", 0),       # nearly dense output rows: three windows, a queue
+                                                 # that fills mid-row (empty items), single-item rows
 ])
 def test_spgemm_matches_oracle(ctx, oracle, M, K, N, dens, dist, cap):
     run_case(ctx, oracle, M, K, N, 0, 1, dens, dist, cap or 4096)
