@@ -446,6 +446,18 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
     // symbolic: bitmap[pitch]; numeric: packed[padded] = {bits, prefix}
     uint32_t* bitmap = sm;
     uint2* packed = reinterpret_cast<uint2*>(sm);
+    // Where entry e of the rank table sits.  A thread owns WPT consecutive entries
+    // and writes them two at a time with 16-byte stores; with WPT == 8 the lanes
+    // of a store are 64 bytes apart and would hit two of the eight 16-byte bank
+    // groups, so the 16-byte slot index is XOR-ed with two higher bits.
+    auto at = [](uint32_t e) -> uint32_t {
+        if constexpr (WPT == 8) {
+            const uint32_t slot = e >> 1;
+            return ((slot ^ ((slot >> 3) & 3u)) << 1) | (e & 1u);
+        } else {
+            return e;
+        }
+    };
     uint32_t* after_map = sm + (NUMERIC ? 2 * padded : pitch);
     WalkLists<THREADS> wl;
     wl.off = after_map;
@@ -512,7 +524,7 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
                     if (!act[u]) continue;
                     const uint32_t j = col[u];
                     if (NUMERIC)
-                        atomicOr(&packed[j >> 5].x, 1u << (j & 31));
+                        atomicOr(&packed[at(j >> 5)].x, 1u << (j & 31));
                     else
                         atomicOr(&bitmap[j >> 5], 1u << (j & 31));
                 }
@@ -568,7 +580,7 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
             } else {
 #pragma unroll
                 for (uint32_t k = 0; k < WPT; k += 2) {
-                    const uint4 two = *reinterpret_cast<const uint4*>(packed + x0 + k);
+                    const uint4 two = *reinterpret_cast<const uint4*>(packed + at(x0 + k));
                     bits[k] = two.x;
                     bits[k + 1] = two.z;
                 }
@@ -581,7 +593,7 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
 #pragma unroll
             for (uint32_t k = 0; k < WPT; k += 2) {
                 const uint32_t r1 = run + __popc(bits[k]);
-                *reinterpret_cast<uint4*>(packed + x0 + k) = make_uint4(bits[k], run, bits[k + 1], r1);
+                *reinterpret_cast<uint4*>(packed + at(x0 + k)) = make_uint4(bits[k], run, bits[k + 1], r1);
                 run = r1 + __popc(bits[k + 1]);
             }
             carry += tile_total;
@@ -607,7 +619,7 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const uint32_t j = col[u];
-                    const uint2 wp = packed[j >> 5];
+                    const uint2 wp = packed[at(j >> 5)];
                     slot[u] = act[u] ? wp.y + __popc(wp.x & ((1u << (j & 31)) - 1u)) - r0 : 0xffffffffu;
                 }
 #pragma unroll
