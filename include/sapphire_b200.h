@@ -136,6 +136,47 @@ int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA, int trans
                        int64_t batch, sb200_stream stream);
 
 /*
+ * The same GEMM with the elementwise steps either side of it in a Linear +
+ * ReLU stack folded into its epilogue:
+ *
+ *     D[b] = gate( relu( (C[b] + bias) + op(A[b]) . op(B[b]) ) )
+ *
+ * relu != 0: the result goes through x > 0 ? x : 0, the forward ReLU that
+ * follows a Linear layer (Sources/Sapphire/compute/dense/naive/NaiveBasic.cpp:159-165,
+ * device kernel Sources/Sapphire/compute/dense/cuda/kernels/ActivationKernel.cu:11-22).
+ * Only the activated tensor is written; its sign pattern equals that of the
+ * pre-activation, so it serves as the gate of the backward pass.
+ *
+ * relu_gate (device, [M, N] per batch with leading dimension ld_gate and batch
+ * stride stride_gate, may be NULL): D is kept where relu_gate > 0 and set to 0
+ * elsewhere.  With this call as dx = dy . W^T it replaces the ReLUBackward
+ * kernel that follows (dx += x > 0 ? dy : 0 into a zeroed buffer,
+ * NaiveBasic.cpp:167-174, ActivationBackwardKernel.cu:11-24).  relu_gate must
+ * not overlap D.
+ *
+ * bias, colsum_out and colsum_scale as in sb200_gemm_batched, which is this
+ * call with relu = 0 and relu_gate = NULL.
+ */
+typedef struct sb200_gemm_epilogue {
+    const float* bias;
+    float* colsum_out;
+    float colsum_scale;
+    int relu;
+    const float* relu_gate;
+    int64_t ld_gate;
+    int64_t stride_gate;
+} sb200_gemm_epilogue;
+
+int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int transA, int transB,
+                          int64_t M, int64_t N, int64_t K,
+                          const float* A, int64_t lda, int64_t strideA,
+                          const float* B, int64_t ldb, int64_t strideB,
+                          const float* C, int64_t ldc, int64_t strideC,
+                          float* D, int64_t ldd, int64_t strideD,
+                          const sb200_gemm_epilogue* epilogue,
+                          int64_t batch, sb200_stream stream);
+
+/*
  * CSR matrix, device arrays.  Same fields and order as the reference's
  * SparseMatrix (Includes/Sapphire/compute/sparse/SparseMatrix.hpp:28-38):
  * V values, COL column indices, ROW offsets of length M + 1, then NNZ, M, N
@@ -264,6 +305,21 @@ int sb200_cross_entropy(sb200_ctx* ctx, float* loss, const float* x, const float
 /* dx -= label / x (accumulates).  CrossEntropyBackward (NaiveCrossEntropy.cpp:33-51). */
 int sb200_cross_entropy_backward(sb200_ctx* ctx, float* dx, const float* x, const float* label,
                                  int batch, int unit, sb200_stream stream);
+
+/*
+ * SoftMax, CrossEntropy and both their backward passes over [batch, unit] logits
+ * as one kernel (one warp per sample), with the arithmetic and operation order
+ * of the four separate calls above run on zeroed gradient buffers:
+ *     prob  = softmax(logits)                     (written when prob != NULL)
+ *     loss  = -sum_j label * log(prob)            (written when loss != NULL)
+ *     dlogits = softmax_backward(cross_entropy_backward(prob, label), prob)
+ * It replaces the four leaf calls at the end of a classifier's forward pass and
+ * the start of its backward pass (NaiveBasic.cpp:235-281,
+ * NaiveCrossEntropy.cpp:15-51).  unit <= 1024.
+ */
+int sb200_softmax_cross_entropy(sb200_ctx* ctx, float* prob, float* loss, float* dlogits,
+                                const float* logits, const float* label, int batch, int unit,
+                                sb200_stream stream);
 
 /* z <- z - lr * dz as one kernel; the reference runs Scale into a temporary and
  * then Sub (Sources/Sapphire/operations/optimizers/SGD.cpp:22-28). */

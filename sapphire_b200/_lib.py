@@ -27,6 +27,13 @@ class Csr(C.Structure):
                 ("Padding", C.c_uint32 * 3)]
 
 
+class GemmEpilogue(C.Structure):
+    """Mirror of sb200_gemm_epilogue."""
+    _fields_ = [("bias", C.c_void_p), ("colsum_out", C.c_void_p), ("colsum_scale", C.c_float),
+                ("relu", C.c_int), ("relu_gate", C.c_void_p), ("ld_gate", C.c_int64),
+                ("stride_gate", C.c_int64)]
+
+
 class Sb200Error(RuntimeError):
     def __init__(self, where: str, status: int):
         self.status = status
@@ -53,6 +60,15 @@ SIGNATURES = {
         C.c_void_p, C.c_int64, C.c_int64,
         C.c_void_p, C.c_void_p, C.c_float,
         C.c_int64, C.c_void_p]),
+    "sb200_gemm_batched_ex": (C.c_int, [
+        C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+        C.c_int64, C.c_int64, C.c_int64,
+        C.c_void_p, C.c_int64, C.c_int64,
+        C.c_void_p, C.c_int64, C.c_int64,
+        C.c_void_p, C.c_int64, C.c_int64,
+        C.c_void_p, C.c_int64, C.c_int64,
+        C.POINTER(GemmEpilogue),
+        C.c_int64, C.c_void_p]),
     "sb200_spgemm_csr": (C.c_int, [C.c_void_p, C.POINTER(Csr), C.POINTER(Csr), C.POINTER(Csr),
                                    C.c_void_p]),
     "sb200_spgemm_csr_symbolic": (C.c_int, [C.c_void_p, C.POINTER(Csr), C.POINTER(Csr), C.c_void_p,
@@ -77,6 +93,8 @@ SIGNATURES = {
                                       C.c_int, C.c_void_p]),
     "sb200_cross_entropy_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                C.c_int, C.c_int, C.c_void_p]),
+    "sb200_softmax_cross_entropy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "sb200_sgd_update": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64,
                                    C.c_void_p]),
     "sb200_scale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_void_p]),

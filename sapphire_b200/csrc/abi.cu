@@ -155,8 +155,35 @@ extern "C" int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA
                                   const float* bias, float* colsum_out, float colsum_scale,
                                   int64_t batch, sb200_stream stream_)
 {
+    sb200_gemm_epilogue e;
+    e.bias = bias;
+    e.colsum_out = colsum_out;
+    e.colsum_scale = colsum_scale;
+    e.relu = 0;
+    e.relu_gate = nullptr;
+    e.ld_gate = 0;
+    e.stride_gate = 0;
+    return sb200_gemm_batched_ex(ctx, mode, path, transA, transB, M, N, K, A, lda, strideA, B, ldb, strideB,
+                                 C, ldc, strideC, D, ldd, strideD, &e, batch, stream_);
+}
+
+extern "C" int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int transA, int transB,
+                                     int64_t M, int64_t N, int64_t K,
+                                     const float* A, int64_t lda, int64_t strideA,
+                                     const float* B, int64_t ldb, int64_t strideB,
+                                     const float* C, int64_t ldc, int64_t strideC,
+                                     float* D, int64_t ldd, int64_t strideD,
+                                     const sb200_gemm_epilogue* epilogue,
+                                     int64_t batch, sb200_stream stream_)
+{
     TraceRange trace("sb200_gemm_batched");
-    if (!ctx)
+    if (!ctx || !epilogue)
+        return SB200_ERR_INVALID_ARG;
+    const float* bias = epilogue->bias;
+    float* colsum_out = epilogue->colsum_out;
+    const float colsum_scale = epilogue->colsum_scale;
+    const float* gate = epilogue->relu_gate;
+    if (gate && (epilogue->ld_gate < N || epilogue->stride_gate < 0))
         return SB200_ERR_INVALID_ARG;
     if (mode != SB200_MODE_TF32 && mode != SB200_MODE_TF32X3)
         return SB200_ERR_INVALID_ARG;
@@ -197,6 +224,10 @@ extern "C" int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA
     g.bias = bias;
     g.colsum_out = nullptr;
     g.colsum_scale = colsum_scale;
+    g.relu = epilogue->relu != 0;
+    g.mask = gate;
+    g.ldmask = gate ? epilogue->ld_gate : 0;
+    g.strideMask = gate ? epilogue->stride_gate : 0;
 
     const bool tc_ok = tcgen05_eligible(g);
     int rc;

@@ -38,6 +38,9 @@ struct GemmArgs {
     const float* bias;
     float* colsum_out;         // fused column sums of op(B) (tensor-core path, TF32 mode), or null
     float colsum_scale;
+    int relu;                  // D = D > 0 ? D : 0 after everything else
+    const float* mask;         // [M, N] per batch or null: D = mask > 0 ? D : 0 (ReLU backward gate)
+    int64_t ldmask, strideMask;
 };
 
 }  // namespace sb200

@@ -94,6 +94,69 @@ __global__ void cross_entropy_backward_kernel(float* __restrict__ dx, const floa
     dx[i] = __fsub_rn(dx[i], __fdiv_rn(label[i], v));
 }
 
+// softmax -> cross-entropy -> its backward -> softmax backward for one sample
+// per warp, each stage with the arithmetic of the separate kernels above run on
+// zero-initialised gradients; the probabilities and the cross-entropy gradient
+// stay in shared memory between the stages.  WARPS rows per block; dynamic
+// shared memory = WARPS * 2 * unit floats.
+constexpr int FUSED_WARPS = 4;
+constexpr int FUSED_MAX_UNIT = 1024;
+
+__global__ void __launch_bounds__(FUSED_WARPS * 32)
+softmax_ce_kernel(float* __restrict__ prob, float* __restrict__ loss, float* __restrict__ dlogits,
+                  const float* __restrict__ logits, const float* __restrict__ label, int batch,
+                  int unit)
+{
+    extern __shared__ float sh[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x * FUSED_WARPS + warp;
+    if (r >= batch) return;                       // whole warps leave; only warp-level syncs below
+    float* y = sh + static_cast<size_t>(warp) * 2 * unit;
+    float* dp = y + unit;
+    const float* x = logits + static_cast<int64_t>(r) * unit;
+    const float* lab = label + static_cast<int64_t>(r) * unit;
+
+    float hi = -3.402823466e+38f;
+    for (int i = lane; i < unit; i += 32) hi = fmaxf(hi, x[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    float denom = 0.0f;
+    if (unit <= 64) {
+        for (int i = 0; i < unit; ++i) denom = __fadd_rn(denom, expf(x[i] - hi));
+    } else {
+        for (int i = lane; i < unit; i += 32) denom += expf(x[i] - hi);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    }
+    for (int i = lane; i < unit; i += 32) {
+        const float p = __fdiv_rn(expf(x[i] - hi), denom);
+        y[i] = p;
+        if (prob) prob[static_cast<int64_t>(r) * unit + i] = p;
+        const float v = p == 0.0f ? CE_FLOOR : p;
+        dp[i] = __fsub_rn(0.0f, __fdiv_rn(lab[i], v));
+    }
+    __syncwarp();
+    if (loss && lane == 0) {
+        float s = 0.0f;
+        for (int j = 0; j < unit; ++j) {
+            const float v = y[j] == 0.0f ? CE_FLOOR : y[j];
+            s = __fsub_rn(s, __fmul_rn(lab[j], logf(v)));
+        }
+        loss[r] = s;
+    }
+    for (int i = lane; i < unit; i += 32) {
+        const float yi = y[i];
+        float s = 0.0f;
+        for (int j = 0; j < unit; ++j) {
+            const float yj = y[j];
+            const float t = (i == j) ? __fmul_rn(dp[j], __fmul_rn(yj, __fsub_rn(1.0f, yj)))
+                                     : __fmul_rn(dp[j], __fmul_rn(-yi, yj));
+            s = __fadd_rn(s, t);
+        }
+        dlogits[static_cast<int64_t>(r) * unit + i] = __fadd_rn(0.0f, s);
+    }
+}
+
 // z <- z - (lr * dz), two rounded operations like Scale then Sub
 __global__ void sgd_kernel(float* __restrict__ z, const float* __restrict__ dz, float lr, int64_t n)
 {
@@ -180,6 +243,19 @@ extern "C" int sb200_cross_entropy_backward(sb200_ctx* ctx, float* dx, const flo
     if (batch == 0) return SB200_OK;
     const int64_t n = static_cast<int64_t>(batch) * unit;
     cross_entropy_backward_kernel<<<blocks_for(n, 256), 256, 0, stream>>>(dx, x, label, n);
+    return finish(ctx);
+}
+
+extern "C" int sb200_softmax_cross_entropy(sb200_ctx* ctx, float* prob, float* loss, float* dlogits,
+                                           const float* logits, const float* label, int batch,
+                                           int unit, sb200_stream stream_)
+{
+    SB200_PROLOGUE(batch >= 0 && unit > 0 && (batch == 0 || (dlogits && logits && label)))
+    if (unit > FUSED_MAX_UNIT) return SB200_ERR_TOO_LARGE;
+    if (batch == 0) return SB200_OK;
+    const size_t smem = static_cast<size_t>(FUSED_WARPS) * 2 * unit * sizeof(float);
+    softmax_ce_kernel<<<blocks_for(batch, FUSED_WARPS), FUSED_WARPS * 32, smem, stream>>>(
+        prob, loss, dlogits, logits, label, batch, unit);
     return finish(ctx);
 }
 

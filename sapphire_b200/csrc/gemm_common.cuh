@@ -30,7 +30,27 @@ struct KernelParams {
     int explicit_hi;
     float* colsum_out;                          // column sums of op(B) (fused bias gradient) or null
     float colsum_scale;
+    int relu;                                   // ReLU of the result
+    const float* mask; long long ldm, strideM;  // ReLU-backward gate matrix or null
 };
+
+// What the epilogue does with an accumulator: D = post((C + bias) + acc), where
+// post is the optional ReLU followed by the optional gate "keep where mask > 0,
+// else 0" (the backward pass of a ReLU whose output, or input, is `mask`).
+struct Epilogue {
+    const float* bias;      // [N] or null
+    const float* mask;      // this batch's [M, N] gate matrix or null
+    long long ldm;
+    int relu;
+};
+
+__device__ __forceinline__ float post_op(float o, int relu, const float* m)
+{
+    if (relu) o = o > 0.0f ? o : 0.0f;
+    // 0 + x like the reference's accumulation into a zeroed gradient (turns -0 into +0)
+    if (m) o = __fadd_rn(0.0f, __ldg(m) > 0.0f ? o : 0.0f);
+    return o;
+}
 
 struct Abort {
     volatile int* flag;
@@ -58,11 +78,14 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, const A
     return true;
 }
 
-// One thread's 32 consecutive output columns of one row: D = (C + bias) + acc.
+// One thread's 32 consecutive output columns of one row: D = post((C + bias) + acc);
+// mrow is the row of the gate matrix or null.
 __device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], float* drow,
-                                                const float* crow, const float* bias, int col0,
-                                                int N, bool vec_ok)
+                                                const float* crow, const Epilogue& ep,
+                                                const float* mrow, int col0, int N, bool vec_ok)
 {
+    const float* bias = ep.bias;
+    const bool post = ep.relu || mrow;
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
         const int col = col0 + j;
@@ -81,6 +104,12 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], float* 
             o.y = base.y + __uint_as_float(v[j + 1]);
             o.z = base.z + __uint_as_float(v[j + 2]);
             o.w = base.w + __uint_as_float(v[j + 3]);
+            if (post) {
+                o.x = post_op(o.x, ep.relu, mrow ? mrow + col : nullptr);
+                o.y = post_op(o.y, ep.relu, mrow ? mrow + col + 1 : nullptr);
+                o.z = post_op(o.z, ep.relu, mrow ? mrow + col + 2 : nullptr);
+                o.w = post_op(o.w, ep.relu, mrow ? mrow + col + 3 : nullptr);
+            }
             *reinterpret_cast<float4*>(drow + col) = o;
         } else {
 #pragma unroll
@@ -89,7 +118,9 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], float* 
                     float base = crow ? crow[col + e] : 0.f;
                     if (bias)
                         base = base + __ldg(bias + col + e);
-                    drow[col + e] = base + __uint_as_float(v[j + e]);
+                    float o = base + __uint_as_float(v[j + e]);
+                    if (post) o = post_op(o, ep.relu, mrow ? mrow + col + e : nullptr);
+                    drow[col + e] = o;
                 }
             }
         }
@@ -150,10 +181,12 @@ __device__ __forceinline__ void load_c_chunk(CChunk& cc, const float* C, long lo
 
 __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], float* stage,
                                                       float* D, long long ldd, const CChunk& cc,
-                                                      const float* bias, int row0, int col0, int M,
+                                                      const Epilogue& e, int row0, int col0, int M,
                                                       int N)
 {
     const int lane = threadIdx.x & 31;
+    const float* bias = e.bias;
+    const bool post = e.relu || e.mask;
 #pragma unroll
     for (int j = 0; j < 32; j += 4)
         *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + j) =
@@ -181,6 +214,13 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
             o.y = (cc.v[i].y + bv.y) + a.y;
             o.z = (cc.v[i].z + bv.z) + a.z;
             o.w = (cc.v[i].w + bv.w) + a.w;
+            if (post) {
+                const float* mrow = e.mask ? e.mask + static_cast<long long>(grow) * e.ldm + col : nullptr;
+                o.x = post_op(o.x, e.relu, mrow);
+                if (col + 1 < N) o.y = post_op(o.y, e.relu, mrow ? mrow + 1 : nullptr);
+                if (col + 2 < N) o.z = post_op(o.z, e.relu, mrow ? mrow + 2 : nullptr);
+                if (col + 3 < N) o.w = post_op(o.w, e.relu, mrow ? mrow + 3 : nullptr);
+            }
             if (col + 3 < N) {
                 *reinterpret_cast<float4*>(drow + col) = o;
             } else {

@@ -28,6 +28,8 @@ struct SimtParams {
     const float* C; long long ldc, strideC;
     float* D; long long ldd, strideD;
     const float* bias;
+    int relu;                                    // D = D > 0 ? D : 0
+    const float* mask; long long ldm, strideM;   // gate matrix or null: D = mask > 0 ? D : 0
 };
 
 __global__ void __launch_bounds__(256)
@@ -89,6 +91,7 @@ gemm_simt_kernel(const SimtParams p)
 
     const float* C = p.C ? p.C + b * p.strideC : nullptr;
     float* D = p.D + b * p.strideD;
+    const float* G = p.mask ? p.mask + b * p.strideM : nullptr;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const long long m = m0 + ty + 16 * i;
@@ -99,7 +102,10 @@ gemm_simt_kernel(const SimtParams p)
             if (n >= p.N) continue;
             float base = C ? C[m * p.ldc + n] : 0.0f;
             if (p.bias) base = __fadd_rn(base, p.bias[n]);
-            D[m * p.ldd + n] = __fadd_rn(base, acc[i][j]);
+            float o = __fadd_rn(base, acc[i][j]);
+            if (p.relu) o = o > 0.0f ? o : 0.0f;
+            if (G) o = __fadd_rn(0.0f, G[m * p.ldm + n] > 0.0f ? o : 0.0f);
+            D[m * p.ldd + n] = o;
         }
     }
 }
@@ -151,6 +157,8 @@ int launch_gemm_simt(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.C = g.C; p.ldc = g.ldc; p.strideC = g.strideC;
     p.D = g.D; p.ldd = g.ldd; p.strideD = g.strideD;
     p.bias = g.bias;
+    p.relu = g.relu;
+    p.mask = g.mask; p.ldm = g.ldmask; p.strideM = g.strideMask;
     dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy), static_cast<unsigned>(g.batch));
     gemm_simt_kernel<<<grid, 256, 0, stream>>>(p);
     ctx->launches += 1;

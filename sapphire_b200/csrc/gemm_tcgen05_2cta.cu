@@ -235,6 +235,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
             float* drow = dmat + static_cast<long long>(row) * p.ldd;
             const float* crow = cmat ? cmat + static_cast<long long>(row) * p.ldc : nullptr;
             float* my_stage = epi_stage + q * (EPI_STAGE_BYTES_PER_WARP / 4);
+            const Epilogue epi{p.bias, p.mask ? p.mask + b * p.strideM : nullptr, p.ldm, p.relu};
             if (!(ok = wait_bar_cluster(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
                 break;
             ptx::tc_fence_after_sync();
@@ -255,10 +256,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
                 }
                 ptx::tmem_ld_wait();
                 if (vec_ok)
-                    store_chunk_coalesced(v, my_stage, dmat, p.ldd, c_now, p.bias, m0 + q * 32,
+                    store_chunk_coalesced(v, my_stage, dmat, p.ldd, c_now, epi, m0 + q * 32,
                                           col0, p.M, p.N);
                 else if (row < p.M)
-                    store_row_chunk(v, drow, crow, p.bias, col0, p.N, false);
+                    store_row_chunk(v, drow, crow, epi,
+                                    epi.mask ? epi.mask + static_cast<long long>(row) * p.ldm : nullptr,
+                                    col0, p.N, false);
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -331,6 +334,8 @@ int launch_pair_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.C = g.C; p.ldc = g.ldc; p.strideC = g.strideC;
     p.D = g.D; p.ldd = g.ldd; p.strideD = g.strideD;
     p.bias = g.bias;
+    p.relu = g.relu;
+    p.mask = g.mask; p.ldm = g.ldmask; p.strideM = g.strideMask;
     p.status = ctx->d_status;
     p.explicit_hi = 0;
     p.colsum_out = nullptr;

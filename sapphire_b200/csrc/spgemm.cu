@@ -101,12 +101,25 @@ row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
     for (uint32_t i = warp_global; i < A.M; i += nwarps) {
         unsigned long long s = 0;
         const uint32_t pa = A.row[i], pe = A.row[i + 1];
-        for (uint32_t p = pa + lane; p < pe; p += 32) {
-            const uint32_t k = A.col[p];
-            const uint32_t q0 = rowB[k], q1 = rowB[k + 1];
-            w.bq[p] = q0;
-            w.blen[p] = q1 - q0;
-            s += q1 - q0;
+        // four nonzeros per lane and step: the gathers from B.ROW are dependent
+        // loads, a row of A with thousands of nonzeros would otherwise crawl
+        for (uint32_t p = pa + lane; p < pe; p += 128) {
+            uint32_t k[4], q0[4], q1[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) k[u] = p + 32 * u < pe ? A.col[p + 32 * u] : 0u;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                q0[u] = rowB[k[u]];
+                q1[u] = rowB[k[u] + 1];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (p + 32 * u < pe) {
+                    w.bq[p + 32 * u] = q0[u];
+                    w.blen[p + 32 * u] = q1[u] - q0[u];
+                    s += q1[u] - q0[u];
+                }
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);

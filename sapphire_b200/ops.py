@@ -78,12 +78,15 @@ def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tenso
          out: Optional[torch.Tensor] = None, *, mode: int = L.MODE_TF32, trans_a: bool = False,
          trans_b: bool = False, bias: Optional[torch.Tensor] = None,
          colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0,
-         path: int = L.PATH_AUTO) -> torch.Tensor:
-    """out = (c + bias) + op(a).op(b), batched over a leading dimension.
+         path: int = L.PATH_AUTO, relu: bool = False,
+         relu_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = gate(relu((c + bias) + op(a).op(b))), batched over a leading dimension.
 
     ``c`` may be ``out`` itself (in-place accumulate, Sapphire's
     ``y <- y + a.b``).  A tensor with batch extent 1 (or 2-D) is shared by all
-    batches.  Returns ``out``.
+    batches.  ``relu`` applies x > 0 ? x : 0 to the result; ``relu_gate`` (the
+    output's shape) zeroes the result where the gate is not positive, the
+    backward pass of a ReLU.  Returns ``out``.
     """
     ba, ra, ca, lda, sa = _mat_geometry(a)
     bb, rb, cb, ldb, sb = _mat_geometry(b)
@@ -116,6 +119,25 @@ def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tenso
         cptr = c.data_ptr()
     if ba not in (1, batch) or bb not in (1, batch):
         raise ValueError("operand batch must be 1 or the output batch")
+    if relu or relu_gate is not None:
+        e = L.GemmEpilogue()
+        e.bias = bias.data_ptr() if bias is not None else None
+        e.colsum_out = colsum_out.data_ptr() if colsum_out is not None else None
+        e.colsum_scale = float(colsum_scale)
+        e.relu = int(relu)
+        e.relu_gate, e.ld_gate, e.stride_gate = None, 0, 0
+        if relu_gate is not None:
+            bg, rg, cg, ldg, sg = _mat_geometry(relu_gate)
+            if (rg, cg) != (M, N) or bg != batch:
+                raise ValueError("relu_gate must have the output's shape")
+            e.relu_gate, e.ld_gate = relu_gate.data_ptr(), ldg
+            e.stride_gate = relu_gate.stride(0) if batch > 1 else 0
+        L.check("sb200_gemm_batched_ex", L.lib().sb200_gemm_batched_ex(
+            ctx.handle, mode, path, int(trans_a), int(trans_b), M, N, K,
+            a.data_ptr(), lda, sa if ba == batch and batch > 1 else 0,
+            b.data_ptr(), ldb, sb if bb == batch and batch > 1 else 0,
+            cptr, ldc, sc, out.data_ptr(), ldd, sd, C.byref(e), batch, _stream_ptr(ctx.device)))
+        return out
     L.check("sb200_gemm_batched", L.lib().sb200_gemm_batched(
         ctx.handle, mode, path, int(trans_a), int(trans_b), M, N, K,
         a.data_ptr(), lda, sa if ba == batch and batch > 1 else 0,
@@ -273,6 +295,21 @@ def cross_entropy_backward(ctx, dx, prob, label):
     _ew("sb200_cross_entropy_backward", ctx, dx.data_ptr(), prob.data_ptr(), label.data_ptr(),
         prob.shape[0], prob.shape[1])
     return dx
+
+
+def softmax_cross_entropy(ctx, logits, label, prob=None, loss=None, dlogits=None):
+    """Fused softmax + cross-entropy + both backward passes over [batch, unit]
+    logits; returns (prob, loss, dlogits)."""
+    batch, unit = logits.shape
+    if prob is None:
+        prob = torch.empty_like(logits)
+    if loss is None:
+        loss = torch.empty(batch, dtype=torch.float32, device=logits.device)
+    if dlogits is None:
+        dlogits = torch.empty_like(logits)
+    _ew("sb200_softmax_cross_entropy", ctx, prob.data_ptr(), loss.data_ptr(), dlogits.data_ptr(),
+        logits.data_ptr(), label.data_ptr(), batch, unit)
+    return prob, loss, dlogits
 
 
 def sgd_update(ctx, z, dz, lr):

@@ -6,6 +6,7 @@ Tolerances (relative Frobenius error against Sapphire's own CPU result):
     TF32X3 mode  <= 1e-5
     SIMT path    bit-exact
 """
+import ctypes as C
 import os
 
 import numpy as np
@@ -339,3 +340,51 @@ def test_invalid_arguments(ctx):
     assert call(M=-1) == L.ERR_INVALID_ARG
     assert call(batch=2) == L.ERR_INVALID_ARG          # output batches would overlap (stride 0)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("mode", [L.MODE_TF32, L.MODE_TF32X3])
+@pytest.mark.parametrize("M,N,K,batch,path", [
+    (64, 512, 784, 1, L.PATH_TCGEN05),      # Linear forward of the MLP: one-CTA tensor-core kernel
+    (200, 328, 100, 3, L.PATH_TCGEN05),     # ragged tiles, batch stride of the gate
+    (1024, 512, 256, 40, L.PATH_AUTO),      # large enough for the two-CTA kernel (TF32 mode)
+    (64, 10, 256, 1, L.PATH_AUTO),          # rows of 10 floats: CUDA-core kernel
+    (33, 17, 9, 2, L.PATH_SIMT),
+])
+def test_relu_and_gate_epilogues_equal_the_separate_kernels(ctx, mode, M, N, K, batch, path):
+    """The fused epilogue steps are exact elementwise functions of the unfused
+    GEMM result: relu(x) = x > 0 ? x : 0 (NaiveBasic.cpp:159-165) and the ReLU
+    backward gate 0 + (g > 0 ? x : 0) (NaiveBasic.cpp:167-174), so the fused and
+    the unfused calls must agree bit for bit."""
+    rng = np.random.default_rng(M + N + K)
+    a = dev(rng.standard_normal((batch, M, K)).astype(np.float32))
+    b = dev(rng.standard_normal((batch, K, N)).astype(np.float32))
+    c = dev(rng.uniform(-1, 1, (batch, M, N)).astype(np.float32))
+    bias = dev(rng.uniform(-1, 1, N).astype(np.float32))
+    gate_np = rng.standard_normal((batch, M, N)).astype(np.float32)
+    gate_np[:, ::3, ::5] = 0.0                                  # exact zeros do not pass the gate
+    gate = dev(gate_np)
+    plain = ops.gemm(ctx, a, b, c, bias=bias, mode=mode, path=path)
+    want_relu = torch.where(plain > 0, plain, torch.zeros_like(plain))
+    got = ops.gemm(ctx, a, b, c, bias=bias, mode=mode, path=path, relu=True)
+    assert torch.equal(got, want_relu)
+    want_gate = torch.where(gate > 0, plain, torch.zeros_like(plain)) + 0.0
+    got = ops.gemm(ctx, a, b, c, bias=bias, mode=mode, path=path, relu_gate=gate)
+    assert np.array_equal(bits(got.cpu().numpy()), bits(want_gate.cpu().numpy()))
+    both = ops.gemm(ctx, a, b, c, bias=bias, mode=mode, path=path, relu=True, relu_gate=gate)
+    want_both = torch.where(gate > 0, want_relu, torch.zeros_like(plain)) + 0.0
+    assert np.array_equal(bits(both.cpu().numpy()), bits(want_both.cpu().numpy()))
+    ctx.check_device_status()
+
+
+def test_gate_argument_validation(ctx):
+    a = torch.zeros(8, 8, device=DEV)
+    e = L.GemmEpilogue()
+    e.relu_gate, e.ld_gate, e.stride_gate = a.data_ptr(), 4, 0          # ld_gate < N
+    rc = L.lib().sb200_gemm_batched_ex(ctx.handle, L.MODE_TF32, L.PATH_AUTO, 0, 0, 8, 8, 8,
+                                       a.data_ptr(), 8, 0, a.data_ptr(), 8, 0, None, 8, 0,
+                                       a.data_ptr(), 8, 0, C.byref(e), 1, None)
+    assert rc == L.ERR_INVALID_ARG
+    rc = L.lib().sb200_gemm_batched_ex(ctx.handle, L.MODE_TF32, L.PATH_AUTO, 0, 0, 8, 8, 8,
+                                       a.data_ptr(), 8, 0, a.data_ptr(), 8, 0, None, 8, 0,
+                                       a.data_ptr(), 8, 0, None, 1, None)
+    assert rc == L.ERR_INVALID_ARG

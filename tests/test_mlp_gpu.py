@@ -137,3 +137,51 @@ def test_mlp_cuda_graph_step_equals_eager_step(ctx):
         assert torch.equal(le, lg)
     torch.cuda.synchronize()
     assert torch.equal(eager.params.flat, graph.params.flat)
+
+
+@pytest.mark.parametrize("batch,unit", [(64, 10), (5, 1), (33, 100), (7, 1024)])
+def test_fused_softmax_cross_entropy_equals_the_four_kernels(ctx, batch, unit):
+    """One kernel for SoftMax + CrossEntropy + both backward passes: every output
+    bit-identical to the chain of separate kernels on zeroed gradients."""
+    rng = np.random.default_rng(unit)
+    logits = dev(rng.standard_normal((batch, unit)).astype(np.float32) * 3)
+    lab = np.zeros((batch, unit), np.float32)
+    lab[np.arange(batch), rng.integers(0, unit, batch)] = 1.0
+    lab = dev(lab)
+    prob = ops.softmax(ctx, logits)
+    loss = ops.cross_entropy(ctx, prob, lab)
+    dprob = ops.cross_entropy_backward(ctx, torch.zeros_like(prob), prob, lab)
+    dlogits = ops.softmax_backward(ctx, torch.zeros_like(prob), dprob, prob)
+    fprob, floss, fdl = ops.softmax_cross_entropy(ctx, logits, lab)
+    assert torch.equal(fprob, prob)
+    assert torch.equal(floss, loss)
+    assert torch.equal(fdl.view(torch.int32), dlogits.view(torch.int32))
+
+
+def test_fused_softmax_cross_entropy_rejects_wide_rows(ctx):
+    x = torch.zeros(2, 1025, device=DEV)
+    with pytest.raises(L.Sb200Error) as e:
+        ops.softmax_cross_entropy(ctx, x, x)
+    assert e.value.status == L.ERR_TOO_LARGE
+
+
+@pytest.mark.parametrize("mode", [L.MODE_TF32, L.MODE_TF32X3])
+def test_fused_mlp_step_is_bit_identical_to_the_unfused_step(ctx, mode):
+    """ReLU in the forward epilogue, the ReLU gate in the dx epilogue and the fused
+    SoftMax/CrossEntropy kernel take seven kernels out of the step (two ReLU, two
+    ReLU backward, four SoftMax/CrossEntropy kernels become one) and change not a
+    bit of the parameters."""
+    Ws, bs = W.mlp_init(0)
+    fused = mlp.MlpTrainer(ctx, Ws, bs, 1e-4, mode=mode, fused=True)
+    plain = mlp.MlpTrainer(ctx, Ws, bs, 1e-4, mode=mode, fused=False)
+    for t in range(5):
+        x, onehot = W.mlp_batch(t)
+        n0 = ctx.launch_count()
+        lf = fused.step(dev(x), dev(onehot)).clone()
+        n1 = ctx.launch_count()
+        lp = plain.step(dev(x), dev(onehot)).clone()
+        n2 = ctx.launch_count()
+        assert torch.equal(lf, lp)
+        assert (n2 - n1) - (n1 - n0) == 7
+    torch.cuda.synchronize()
+    assert torch.equal(fused.params.flat.view(torch.int32), plain.params.flat.view(torch.int32))
