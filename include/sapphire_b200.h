@@ -307,6 +307,39 @@ int sb200_cross_entropy_backward(sb200_ctx* ctx, float* dx, const float* x, cons
                                  int batch, int unit, sb200_stream stream);
 
 /*
+ * Convolution lowering for the batched GEMM.  x is [N, C, H, W]; the matrix
+ * `cols` is [N, C*kh*kw, outR*outC] with
+ *     outR = (H + 2 padR - dilR (kh - 1) - 1) / strideR + 1     (outC likewise),
+ * row c*kh*kw + (kh*kw - 1 - (fr*kw + fc)) holding filter tap (fr, fc) of
+ * channel c (reverse tap order: the GEMM below is then a true convolution, the
+ * mode the reference asks of cuDNN) and column orow*outC + ocol the output pixel.
+ *
+ * sb200_im2col fills cols; taps outside the image read pad_value.  Device
+ * counterpart of Dense::Naive::Im2Col
+ * (Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-115), which exists on the host
+ * only.  The forward convolution of Convolution.cpp:217-253 is then
+ *     sb200_gemm_batched(A = filter [Cout, C*kh*kw] with strideA = 0,
+ *                        B = cols, C = D = y [N, Cout, outR*outC])
+ * -- the broadcast-A case of Compute::Gemm.
+ *
+ * sb200_col2im adds to every pixel of x the entries of cols that im2col read
+ * from it (ascending output-pixel order, like the reference's loop): the input
+ * gradient step of Conv2DBackward (Convolution.cpp:117-211, 255-316).
+ */
+typedef struct sb200_conv_geometry {
+    int N, C, H, W;
+    int kh, kw;
+    int strideR, strideC;
+    int padR, padC;
+    int dilR, dilC;
+} sb200_conv_geometry;
+
+int sb200_im2col(sb200_ctx* ctx, float* cols, const float* x,
+                 const sb200_conv_geometry* geometry, float pad_value, sb200_stream stream);
+int sb200_col2im(sb200_ctx* ctx, float* x, const float* cols,
+                 const sb200_conv_geometry* geometry, sb200_stream stream);
+
+/*
  * SoftMax, CrossEntropy and both their backward passes over [batch, unit] logits
  * as one kernel (one warp per sample), with the arithmetic and operation order
  * of the four separate calls above run on zeroed gradient buffers:

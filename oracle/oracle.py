@@ -75,6 +75,9 @@ def port():
                   "orc_softmax", "orc_softmax_backward", "orc_cross_entropy",
                   "orc_cross_entropy_backward"):
             getattr(lib, n).restype = None
+        conv_geom = [C.c_int] * 12
+        lib.orc_im2col.argtypes = [_f32p, _f32p] + conv_geom + [C.c_float]
+        lib.orc_col2im.argtypes = [_f32p, _f32p] + conv_geom
         lib.orc_spgemm_symbolic.argtypes = [C.c_uint32, C.c_uint32, _u32p, _u32p, _u32p, _u32p,
                                             _u32p, C.POINTER(C.c_long)]
         lib.orc_spgemm_symbolic.restype = C.c_long
@@ -173,6 +176,62 @@ def transpose(x, impl: str = "port"):
     fn = port().orc_transpose if impl == "port" else ref().ref_transpose
     fn(out.reshape(-1), x3.reshape(-1), x3.shape[1], x3.shape[2], x3.shape[0], 0)
     return out.reshape(x.shape[:-2] + (x.shape[-1], x.shape[-2]))
+
+
+# ------------------------------------------------------------- convolution
+
+def conv_out(size, pad, dil, k, stride):
+    return (size + 2 * pad - dil * (k - 1) - 1) // stride + 1
+
+
+def im2col(x, kh, kw, stride=(1, 1), pad=(0, 0), dil=(1, 1), pad_value=0.0):
+    """x [N, C, H, W] -> cols [N, C*kh*kw, outR*outC] (taps stored in reverse)."""
+    x = _c(x)
+    N, Cc, H, W = x.shape
+    P = conv_out(H, pad[0], dil[0], kh, stride[0]) * conv_out(W, pad[1], dil[1], kw, stride[1])
+    cols = np.empty((N, Cc * kh * kw, P), dtype=np.float32)
+    port().orc_im2col(cols.reshape(-1), x.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
+                      pad[0], pad[1], dil[0], dil[1], pad_value)
+    return cols
+
+
+def col2im(dx, cols, kh, kw, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
+    """dx [N, C, H, W] += adjoint of im2col applied to cols; returns dx."""
+    assert dx.dtype == np.float32 and dx.flags.c_contiguous
+    cols = _c(cols)
+    N, Cc, H, W = dx.shape
+    port().orc_col2im(dx.reshape(-1), cols.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
+                      pad[0], pad[1], dil[0], dil[1])
+    return dx
+
+
+def conv2d(y, x, filt, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
+    """y [N, Cout, outR, outC] += conv(x, filt) the way the reference's host path
+    composes it: Im2Col, then Gemm(rY[N,Cout,P], rFilter[1,Cout,C*kh*kw], rX)
+    (Sources/Sapphire/compute/dense/naive/Convolution.cpp:217-253)."""
+    N, Cout = y.shape[:2]
+    kh, kw = filt.shape[-2:]
+    cols = im2col(x, kh, kw, stride, pad, dil)
+    f2 = np.repeat(_c(filt).reshape(1, Cout, -1), N, 0)
+    return gemm(_c(y).reshape(N, Cout, -1), f2, cols).reshape(y.shape)
+
+
+def conv2d_backward(dx, dfilt, dy, x, filt, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
+    """dx += ..., dfilt += ... as Conv2DBackward composes them
+    (Convolution.cpp:255-316): drX = filter^T . dY per batch, dFilter += dY_n . rX_n^T
+    over the batches in ascending order, Col2Im(dx, drX).  Returns (dx, dfilt)."""
+    N, Cout = dy.shape[:2]
+    kh, kw = filt.shape[-2:]
+    cols = im2col(x, kh, kw, stride, pad, dil)
+    f2 = _c(filt).reshape(1, Cout, -1)
+    dy3 = _c(dy).reshape(N, Cout, -1)
+    drx = gemm(np.zeros_like(cols), np.repeat(transpose(f2), N, 0), dy3)
+    colsT = transpose(cols)
+    df = _c(dfilt).reshape(1, Cout, -1).copy()
+    for n in range(N):                      # y's batch is 1: the N products accumulate in place
+        df = gemm(df, dy3[n:n + 1], colsT[n:n + 1])
+    dx = col2im(np.ascontiguousarray(dx, dtype=np.float32).copy(), drx, kh, kw, stride, pad, dil)
+    return dx, df.reshape(dfilt.shape)
 
 
 # --------------------------------------------------------------- sparse helpers

@@ -12,6 +12,17 @@
  *                     (oracle/_ref, built from the reference tree by
  *                     oracle/Makefile) and against fixtures generated from it
  *                     (tests/golden).
+ *   orc_im2col/col2im PARITY UNPINNED.  Restated from the reference's host
+ *                     lowering (Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-211);
+ *                     that file needs the reference's TensorData / resource
+ *                     manager stack, which does not build from a few files, and
+ *                     the reference holds no fixture for it (its own test
+ *                     compares the host path with cuDNN at 0.01 absolute,
+ *                     Tests/UnitTests/Sources/FunctionTest/Conv2DTest.cpp).  The tests check the
+ *                     restatement against an independent formulation instead:
+ *                     the lowering + Gemm equals a true (flipped-kernel)
+ *                     convolution, the mode the reference asks of cuDNN
+ *                     (Sources/Sapphire/compute/dense/cuda/Convolution.cu:39).
  *   orc_spgemm_*      PARITY UNPINNED.  The reference declares a CSR sparse
  *                     GEMM (Includes/Sapphire/compute/sparse/naive/SparseGemm.hpp:15-16,
  *                     Includes/Sapphire/compute/sparse/cuda/SparseGemm.cuh:38-41) but ships
@@ -226,6 +237,77 @@ void orc_cross_entropy_backward(float* dx, const float* x, const float* label,
     for (int i = 0; i < batch * unit; ++i) {
         const float v = x[i] == 0.0f ? ORC_CE_FLOOR : x[i];
         dx[i] -= label[i] / v;
+    }
+}
+
+/* ------------------------------------------------------------ convolution */
+
+static int orc_conv_out(int in, int pad, int dil, int k, int stride)
+{
+    return (in + 2 * pad - dil * (k - 1) - 1) / stride + 1;
+}
+
+/*
+ * cols[n][C*kh*kw][outR*outC] from x[n][C][H][W].  Row c*kh*kw + (kh*kw - 1 -
+ * (fr*kw + fc)) of the matrix holds filter tap (fr, fc) of channel c -- the
+ * taps are stored in reverse, which makes Gemm(filter, cols) a true
+ * convolution -- and column orow*outC + ocol the output pixel.  Taps that fall
+ * outside the image read `pad`.
+ * Follows Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-115.
+ */
+void orc_im2col(float* cols, const float* x, int N, int C, int H, int W, int kh, int kw,
+                int strideR, int strideC, int padR, int padC, int dilR, int dilC, float pad)
+{
+    const int outR = orc_conv_out(H, padR, dilR, kh, strideR);
+    const int outC = orc_conv_out(W, padC, dilC, kw, strideC);
+    const long P = (long)outR * outC, taps = (long)kh * kw;
+    for (int n = 0; n < N; ++n) {
+        const float* xn = x + (long)n * C * H * W;
+        float* mn = cols + (long)n * C * taps * P;
+        for (int c = 0; c < C; ++c)
+            for (int fr = 0; fr < kh; ++fr)
+                for (int fc = 0; fc < kw; ++fc) {
+                    float* mrow = mn + (c * taps + taps - 1 - ((long)fr * kw + fc)) * P;
+                    for (int orow = 0; orow < outR; ++orow)
+                        for (int ocol = 0; ocol < outC; ++ocol) {
+                            const int r = orow * strideR + fr * dilR - padR;
+                            const int q = ocol * strideC + fc * dilC - padC;
+                            const int inside = r >= 0 && r < H && q >= 0 && q < W;
+                            mrow[(long)orow * outC + ocol] =
+                                inside ? xn[((long)c * H + r) * W + q] : pad;
+                        }
+                }
+    }
+}
+
+/*
+ * The adjoint: x[n][c][r][q] += every entry of cols that im2col would have read
+ * from that pixel.  The reference walks (c, orow, ocol, fr, fc) in that nesting
+ * and adds in place, so a pixel receives its terms in ascending (orow, ocol)
+ * order; fp32 addition order is part of the result.
+ * Follows Sources/Sapphire/compute/dense/naive/Convolution.cpp:117-211.
+ */
+void orc_col2im(float* x, const float* cols, int N, int C, int H, int W, int kh, int kw,
+                int strideR, int strideC, int padR, int padC, int dilR, int dilC)
+{
+    const int outR = orc_conv_out(H, padR, dilR, kh, strideR);
+    const int outC = orc_conv_out(W, padC, dilC, kw, strideC);
+    const long P = (long)outR * outC, taps = (long)kh * kw;
+    for (int n = 0; n < N; ++n) {
+        float* xn = x + (long)n * C * H * W;
+        const float* mn = cols + (long)n * C * taps * P;
+        for (int c = 0; c < C; ++c)
+            for (int orow = 0; orow < outR; ++orow)
+                for (int ocol = 0; ocol < outC; ++ocol)
+                    for (int fr = 0; fr < kh; ++fr)
+                        for (int fc = 0; fc < kw; ++fc) {
+                            const int r = orow * strideR + fr * dilR - padR;
+                            const int q = ocol * strideC + fc * dilC - padC;
+                            if (r < 0 || r >= H || q < 0 || q >= W)
+                                continue;
+                            const long mrow = c * taps + taps - 1 - ((long)fr * kw + fc);
+                            xn[((long)c * H + r) * W + q] += mn[mrow * P + (long)orow * outC + ocol];
+                        }
     }
 }
 

@@ -34,6 +34,12 @@ class GemmEpilogue(C.Structure):
                 ("stride_gate", C.c_int64)]
 
 
+class ConvGeometry(C.Structure):
+    """Mirror of sb200_conv_geometry."""
+    _fields_ = [(n, C.c_int) for n in ("N", "C", "H", "W", "kh", "kw", "strideR", "strideC",
+                                       "padR", "padC", "dilR", "dilC")]
+
+
 class Sb200Error(RuntimeError):
     def __init__(self, where: str, status: int):
         self.status = status
@@ -93,6 +99,10 @@ SIGNATURES = {
                                       C.c_int, C.c_void_p]),
     "sb200_cross_entropy_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                C.c_int, C.c_int, C.c_void_p]),
+    "sb200_im2col": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(ConvGeometry), C.c_float,
+                               C.c_void_p]),
+    "sb200_col2im": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(ConvGeometry),
+                               C.c_void_p]),
     "sb200_softmax_cross_entropy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "sb200_sgd_update": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64,

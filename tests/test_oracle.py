@@ -144,3 +144,55 @@ def test_csr_generators():
     rz, cz, _ = W.csr_random(2, 2000, 4096, row_dist="zipf", zipf_cap=512)
     d = np.diff(rz.astype(np.int64))
     assert d.min() >= 1 and d.max() <= 512
+
+
+CONV_CASES = [
+    # N, C, H, W, Cout, kh, kw, stride, pad, dil
+    (2, 3, 8, 9, 4, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (1, 2, 11, 7, 5, 3, 2, (2, 1), (0, 1), (1, 2)),
+    (3, 1, 6, 6, 2, 1, 1, (1, 1), (0, 0), (1, 1)),
+    (2, 4, 10, 10, 3, 5, 5, (2, 2), (2, 2), (1, 1)),
+    (1, 2, 9, 12, 2, 2, 3, (3, 2), (1, 0), (2, 1)),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_lowering_is_a_true_convolution(oracle, case):
+    """The restated Im2Col + Gemm and Conv2DBackward (im2col, two Gemms, Col2Im)
+    against an independent formulation: torch's cross-correlation with the kernel
+    flipped in both spatial axes (a true convolution, the mode the reference asks
+    of cuDNN), and its autograd gradients.  fp32 with different summation orders:
+    1e-5 relative."""
+    import torch
+    import torch.nn.functional as F
+    N, Cc, H, Wd, Cout, kh, kw, stride, pad, dil = case
+    rng = np.random.default_rng(sum(case[:7]))
+    x = rng.standard_normal((N, Cc, H, Wd)).astype(np.float32)
+    f = rng.standard_normal((Cout, Cc, kh, kw)).astype(np.float32)
+    outR = oracle.conv_out(H, pad[0], dil[0], kh, stride[0])
+    outC = oracle.conv_out(Wd, pad[1], dil[1], kw, stride[1])
+    y0 = rng.standard_normal((N, Cout, outR, outC)).astype(np.float32)
+    got = oracle.conv2d(y0, x, f, stride, pad, dil)
+    xt = torch.from_numpy(x).requires_grad_(True)
+    ft = torch.from_numpy(f).requires_grad_(True)
+    want = F.conv2d(xt, ft.flip(2, 3), stride=stride, padding=pad, dilation=dil)
+    assert np.abs(got - (y0 + want.detach().numpy())).max() <= 1e-5 * max(1.0, np.abs(got).max())
+    dy = rng.standard_normal(want.shape).astype(np.float32)
+    want.backward(torch.from_numpy(dy))
+    dx0 = rng.standard_normal(x.shape).astype(np.float32)
+    df0 = rng.standard_normal(f.shape).astype(np.float32)
+    dx, df = oracle.conv2d_backward(dx0, df0, dy, x, f, stride, pad, dil)
+    assert np.abs(dx - (dx0 + xt.grad.numpy())).max() <= 1e-5 * max(1.0, np.abs(dx).max())
+    assert np.abs(df - (df0 + ft.grad.numpy())).max() <= 2e-5 * max(1.0, np.abs(df).max())
+
+
+def test_im2col_tap_order_and_padding(oracle):
+    """Row c*kh*kw + (kh*kw - 1 - tap) holds tap (fr, fc); outside pixels read the pad value."""
+    x = np.arange(1, 1 + 2 * 3 * 3, dtype=np.float32).reshape(1, 2, 3, 3)
+    cols = oracle.im2col(x, 2, 2, (1, 1), (1, 1), (1, 1), pad_value=-7.0)
+    assert cols.shape == (1, 8, 16)
+    # output pixel (0, 0): tap (1, 1) reads x[0, 0, 0, 0], the other three are padding
+    assert cols[0, 0, 0] == x[0, 0, 0, 0] and (cols[0, 1:4, 0] == -7.0).all()
+    # output pixel (1, 1): taps (0,0),(0,1),(1,0),(1,1) read x[..,0,0],[0,1],[1,0],[1,1], stored in reverse
+    assert list(cols[0, 0:4, 5]) == [x[0, 0, 1, 1], x[0, 0, 1, 0], x[0, 0, 0, 1], x[0, 0, 0, 0]]
+    assert list(cols[0, 4:8, 5]) == [x[0, 1, 1, 1], x[0, 1, 1, 0], x[0, 1, 0, 1], x[0, 1, 0, 0]]
