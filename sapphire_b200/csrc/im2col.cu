@@ -31,27 +31,49 @@ inline bool make_geom(const sb200_conv_geometry* g, ConvGeom* o)
     return true;
 }
 
-// blockIdx.x = image * rows + matrix row, blockIdx.y = chunk of output pixels
+// One block per (image, channel) plane: a thread takes four consecutive output
+// pixels, works out their input coordinates once and then writes them into each
+// of the channel's kh*kw matrix rows (one 16-byte store per row when the row
+// length allows), so the integer divisions are paid once per 4*kh*kw entries
+// and the plane's re-reads (every pixel is wanted by kh*kw rows) hit L1.
 __global__ void __launch_bounds__(256)
-im2col_kernel(float* __restrict__ cols, const float* __restrict__ x, ConvGeom g, float pad)
+im2col_kernel(float* __restrict__ cols, const float* __restrict__ x, ConvGeom g, float pad, int vec_ok)
 {
     const int taps = g.kh * g.kw;
-    const long long rows = static_cast<long long>(g.C) * taps;
     const long long P = static_cast<long long>(g.outR) * g.outC;
-    const long long n = blockIdx.x / rows;
-    const int row = static_cast<int>(blockIdx.x % rows);
-    const int c = row / taps;
-    const int tap = taps - 1 - row % taps;                    // taps are stored in reverse
-    const int fr = tap / g.kw, fc = tap % g.kw;
-    const float* xc = x + (n * g.C + c) * static_cast<long long>(g.H) * g.W;
-    float* out = cols + (n * rows + row) * P;
-    for (long long p = static_cast<long long>(blockIdx.y) * blockDim.x + threadIdx.x; p < P;
-         p += static_cast<long long>(gridDim.y) * blockDim.x) {
-        const int orow = static_cast<int>(p / g.outC), ocol = static_cast<int>(p % g.outC);
-        const int r = orow * g.strideR + fr * g.dilR - g.padR;
-        const int q = ocol * g.strideC + fc * g.dilC - g.padC;
-        const bool inside = r >= 0 && r < g.H && q >= 0 && q < g.W;
-        out[p] = inside ? __ldg(xc + static_cast<long long>(r) * g.W + q) : pad;
+    const long long nc = blockIdx.x;                           // image * C + channel
+    const float* xc = x + nc * static_cast<long long>(g.H) * g.W;
+    float* out = cols + nc * taps * P;                         // this channel's first matrix row
+    for (long long p0 = 4LL * threadIdx.x; p0 < P; p0 += 4LL * blockDim.x) {
+        int orow = static_cast<int>(p0 / g.outC), ocol = static_cast<int>(p0 % g.outC);
+        int r0[4], q0[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            r0[e] = p0 + e < P ? orow * g.strideR - g.padR : -(1 << 29);   // beyond the row: reads pad
+            q0[e] = ocol * g.strideC - g.padC;
+            if (++ocol == g.outC) {
+                ocol = 0;
+                ++orow;
+            }
+        }
+        for (int fr = 0; fr < g.kh; ++fr)
+            for (int fc = 0; fc < g.kw; ++fc) {
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int r = r0[e] + fr * g.dilR, q = q0[e] + fc * g.dilC;
+                    const bool inside = r >= 0 && r < g.H && q >= 0 && q < g.W;
+                    v[e] = inside ? __ldg(xc + static_cast<long long>(r) * g.W + q) : pad;
+                }
+                float* dst = out + (taps - 1 - (fr * g.kw + fc)) * P + p0;   // taps stored in reverse
+                if (vec_ok) {                                  // P % 4 == 0 and cols 16-byte aligned
+                    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (p0 + e < P) dst[e] = v[e];
+                }
+            }
     }
 }
 
@@ -111,9 +133,11 @@ extern "C" int sb200_im2col(sb200_ctx* ctx, float* cols, const float* x,
     if (cudaSetDevice(ctx->device) != cudaSuccess)
         return SB200_ERR_CUDA;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    const long long chunks = (P + 255) / 256;
-    dim3 grid(static_cast<unsigned>(rows * g.N), static_cast<unsigned>(chunks < 65535 ? chunks : 65535));
-    im2col_kernel<<<grid, 256, 0, stream>>>(cols, x, g, pad_value);
+    const int vec_ok = (P % 4 == 0) && (reinterpret_cast<uintptr_t>(cols) % 16 == 0);
+    const long long quads = (P + 3) / 4;
+    const unsigned threads = quads >= 256 ? 256u : quads >= 128 ? 128u : quads >= 64 ? 64u : 32u;
+    im2col_kernel<<<static_cast<unsigned>(static_cast<long long>(g.N) * g.C), threads, 0, stream>>>(
+        cols, x, g, pad_value, vec_ok);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
