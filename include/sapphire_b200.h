@@ -177,6 +177,48 @@ int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int transA, int tr
                           int64_t batch, sb200_stream stream);
 
 /*
+ * GEMM fused with the reduce-scatter that follows it when a Linear layer's
+ * weight gradient is computed from row shards (one rank per GPU, each holding
+ * a slice of the batch): P = op(A) . op(B) is this rank's partial [M, N]
+ * gradient; its rows are cut into n_owners equal blocks and block o is ADDED,
+ * tile by tile from the kernel's epilogue, into owners[o], an
+ * [M / n_owners, N] buffer (leading dimension ld_out) in the memory of the rank
+ * that owns the block -- a pointer into this GPU's memory for the rank itself,
+ * a peer mapping (sb200_peer_open) for the others.  The adds are fp32
+ * reductions at system scope, so the transfer over NVLink overlaps the tensor
+ * core work of the following tiles and no partial gradient is written to this
+ * rank's HBM.  Once every rank's call has completed (a stream-ordered barrier
+ * across the ranks), owners[rank] on each rank holds its block of the summed
+ * gradient; the caller zeroes that buffer before the first rank starts.
+ *
+ * The reference is single-GPU and has no counterpart; the sum it replaces is the
+ * allreduce of the dW = x^T . dy products of
+ * Sources/Sapphire/operations/Backward/LinearBackward.cpp:70-72 over the ranks.
+ * colsum_out / colsum_scale as in sb200_gemm_batched (this rank's partial bias
+ * gradient, local).  Requires M divisible by n_owners (<= 8) with blocks that are
+ * multiples of 128 rows, ld_out a multiple of 4, 16-byte aligned buffers and
+ * operands the tensor-core kernel accepts (SB200_ERR_UNSUPPORTED otherwise).
+ */
+int sb200_gemm_reduce_scatter(sb200_ctx* ctx, int mode, int transA, int transB,
+                              int64_t M, int64_t N, int64_t K,
+                              const float* A, int64_t lda, const float* B, int64_t ldb,
+                              float* const* owners, int n_owners, int64_t ld_out,
+                              float* colsum_out, float colsum_scale, sb200_stream stream);
+
+/*
+ * Device buffers that other processes on the node map into their address space
+ * (CUDA IPC): sb200_peer_alloc allocates one and fills a 64-byte handle to send
+ * to the other ranks (any byte transport), sb200_peer_open maps a received
+ * handle (enabling peer access to the owning GPU on first use) and
+ * sb200_peer_close / sb200_peer_free undo the two.  No counterpart in the
+ * reference.
+ */
+int sb200_peer_alloc(sb200_ctx* ctx, size_t bytes, void** ptr, unsigned char* handle64);
+int sb200_peer_open(sb200_ctx* ctx, const unsigned char* handle64, void** ptr);
+int sb200_peer_close(sb200_ctx* ctx, void* ptr);
+int sb200_peer_free(sb200_ctx* ctx, void* ptr);
+
+/*
  * CSR matrix, device arrays.  Same fields and order as the reference's
  * SparseMatrix (Includes/Sapphire/compute/sparse/SparseMatrix.hpp:28-38):
  * V values, COL column indices, ROW offsets of length M + 1, then NNZ, M, N

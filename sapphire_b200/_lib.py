@@ -75,6 +75,14 @@ SIGNATURES = {
         C.c_void_p, C.c_int64, C.c_int64,
         C.POINTER(GemmEpilogue),
         C.c_int64, C.c_void_p]),
+    "sb200_gemm_reduce_scatter": (C.c_int, [
+        C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64,
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+        C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_void_p, C.c_float, C.c_void_p]),
+    "sb200_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
+    "sb200_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),
+    "sb200_peer_close": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "sb200_peer_free": (C.c_int, [C.c_void_p, C.c_void_p]),
     "sb200_spgemm_csr": (C.c_int, [C.c_void_p, C.POINTER(Csr), C.POINTER(Csr), C.POINTER(Csr),
                                    C.c_void_p]),
     "sb200_spgemm_csr_symbolic": (C.c_int, [C.c_void_p, C.POINTER(Csr), C.POINTER(Csr), C.c_void_p,

@@ -1,5 +1,6 @@
 // C ABI of libsapphire_b200: context life cycle, argument validation and the
 // choice between the tensor-core kernel and the CUDA-core kernel.
+#include <cstring>
 #include <new>
 
 #include "common.cuh"
@@ -228,6 +229,8 @@ extern "C" int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int tra
     g.mask = gate;
     g.ldmask = gate ? epilogue->ld_gate : 0;
     g.strideMask = gate ? epilogue->stride_gate : 0;
+    for (int o = 0; o < MAX_OWNERS; ++o) g.owner[o] = nullptr;
+    g.rows_per_owner = 0;
 
     const bool tc_ok = tcgen05_eligible(g);
     int rc;
@@ -251,4 +254,117 @@ extern "C" int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int tra
     if (colsum_out && !fused_colsum)
         rc = launch_colsum(ctx, B, g.transB, K, N, ldb, colsum_out, colsum_scale, stream);
     return rc;
+}
+
+// ------------------------------------------------- GEMM -> reduce-scatter
+extern "C" int sb200_gemm_reduce_scatter(sb200_ctx* ctx, int mode, int transA, int transB,
+                                         int64_t M, int64_t N, int64_t K,
+                                         const float* A, int64_t lda, const float* B, int64_t ldb,
+                                         float* const* owners, int n_owners, int64_t ld_out,
+                                         float* colsum_out, float colsum_scale, sb200_stream stream_)
+{
+    TraceRange trace("sb200_gemm_reduce_scatter");
+    if (!ctx || !owners || !A || !B)
+        return SB200_ERR_INVALID_ARG;
+    if (mode != SB200_MODE_TF32 && mode != SB200_MODE_TF32X3)
+        return SB200_ERR_INVALID_ARG;
+    if (M <= 0 || N <= 0 || K <= 0 || n_owners < 1 || n_owners > MAX_OWNERS)
+        return SB200_ERR_INVALID_ARG;
+    if (lda < (transA ? M : K) || ldb < (transB ? K : N) || ld_out < N)
+        return SB200_ERR_INVALID_ARG;
+    // every 128-row tile of the product must lie inside one owner's row block,
+    // and the adds are 16 bytes wide
+    if (M % n_owners || (M / n_owners) % 128 || (ld_out & 3))
+        return SB200_ERR_UNSUPPORTED;
+    for (int o = 0; o < n_owners; ++o)
+        if (!owners[o] || (reinterpret_cast<uintptr_t>(owners[o]) & 15))
+            return SB200_ERR_INVALID_ARG;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (cudaSetDevice(ctx->device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+
+    GemmArgs g;
+    g.mode = mode; g.transA = transA != 0; g.transB = transB != 0;
+    g.M = M; g.N = N; g.K = K; g.batch = 1;
+    g.A = A; g.lda = lda; g.strideA = 0;
+    g.B = B; g.ldb = ldb; g.strideB = 0;
+    g.C = nullptr; g.ldc = N; g.strideC = 0;
+    g.D = owners[0]; g.ldd = ld_out; g.strideD = 0;            // alignment checks only; tiles go to owner[]
+    g.bias = nullptr;
+    g.colsum_out = nullptr;
+    g.colsum_scale = colsum_scale;
+    g.relu = 0;
+    g.mask = nullptr; g.ldmask = 0; g.strideMask = 0;
+    for (int o = 0; o < MAX_OWNERS; ++o) g.owner[o] = o < n_owners ? owners[o] : nullptr;
+    g.rows_per_owner = M / n_owners;
+    if (!tcgen05_eligible(g))
+        return SB200_ERR_UNSUPPORTED;                           // the CUDA-core kernel has no such epilogue
+    const bool fused_colsum = colsum_out && mode == SB200_MODE_TF32;
+    if (fused_colsum)
+        g.colsum_out = colsum_out;
+    int rc = launch_gemm_tcgen05(ctx, g, stream);
+    ctx->last_path = SB200_PATH_TCGEN05;
+    if (rc)
+        return rc;
+    if (colsum_out && !fused_colsum)
+        rc = launch_colsum(ctx, B, g.transB, K, N, ldb, colsum_out, colsum_scale, stream);
+    return rc;
+}
+
+// ------------------------------------------------- buffers other ranks map
+extern "C" int sb200_peer_alloc(sb200_ctx* ctx, size_t bytes, void** ptr, unsigned char* handle64)
+{
+    if (!ctx || !ptr || !handle64 || bytes == 0)
+        return SB200_ERR_INVALID_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+    if (cudaSetDevice(ctx->device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    *ptr = nullptr;
+    if (cudaMalloc(ptr, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return SB200_ERR_ALLOC;
+    }
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, *ptr) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(*ptr);
+        *ptr = nullptr;
+        return SB200_ERR_CUDA;
+    }
+    memcpy(handle64, &h, sizeof(h));
+    return SB200_OK;
+}
+
+extern "C" int sb200_peer_open(sb200_ctx* ctx, const unsigned char* handle64, void** ptr)
+{
+    if (!ctx || !ptr || !handle64)
+        return SB200_ERR_INVALID_ARG;
+    if (cudaSetDevice(ctx->device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    *ptr = nullptr;
+    if (cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        return SB200_ERR_CUDA;
+    }
+    return SB200_OK;
+}
+
+extern "C" int sb200_peer_close(sb200_ctx* ctx, void* ptr)
+{
+    if (!ctx || !ptr)
+        return SB200_ERR_INVALID_ARG;
+    if (cudaSetDevice(ctx->device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+}
+
+extern "C" int sb200_peer_free(sb200_ctx* ctx, void* ptr)
+{
+    if (!ctx || !ptr)
+        return SB200_ERR_INVALID_ARG;
+    if (cudaSetDevice(ctx->device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    return cudaFree(ptr) == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }

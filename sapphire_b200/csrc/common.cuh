@@ -41,7 +41,13 @@ struct GemmArgs {
     int relu;                  // D = D > 0 ? D : 0 after everything else
     const float* mask;         // [M, N] per batch or null: D = mask > 0 ? D : 0 (ReLU backward gate)
     int64_t ldmask, strideMask;
+    // reduce-scatter epilogue: rows [o * rows_per_owner, (o+1) * rows_per_owner) of the product
+    // are ADDED into owner[o] (an [rows_per_owner, N] buffer, possibly another GPU's memory)
+    // instead of being stored to D; rows_per_owner == 0 switches it off
+    float* owner[8];
+    int64_t rows_per_owner;
 };
+constexpr int MAX_OWNERS = 8;
 
 }  // namespace sb200
 

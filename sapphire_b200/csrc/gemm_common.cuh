@@ -32,6 +32,8 @@ struct KernelParams {
     float colsum_scale;
     int relu;                                   // ReLU of the result
     const float* mask; long long ldm, strideM;  // ReLU-backward gate matrix or null
+    float* owner[MAX_OWNERS];                   // reduce-scatter epilogue: row-block owners' buffers
+    int rows_per_owner;                         // 0: plain store to D
 };
 
 // What the epilogue does with an accumulator: D = post((C + bias) + acc), where
@@ -42,6 +44,7 @@ struct Epilogue {
     const float* mask;      // this batch's [M, N] gate matrix or null
     long long ldm;
     int relu;
+    int reduce;             // add the result into D (system-scope reduction) instead of storing it
 };
 
 __device__ __forceinline__ float post_op(float o, int relu, const float* m)
@@ -110,7 +113,10 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], float* 
                 o.z = post_op(o.z, ep.relu, mrow ? mrow + col + 2 : nullptr);
                 o.w = post_op(o.w, ep.relu, mrow ? mrow + col + 3 : nullptr);
             }
-            *reinterpret_cast<float4*>(drow + col) = o;
+            if (ep.reduce)
+                ptx::red_add_sys_v4(drow + col, o);
+            else
+                *reinterpret_cast<float4*>(drow + col) = o;
         } else {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -120,7 +126,10 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], float* 
                         base = base + __ldg(bias + col + e);
                     float o = base + __uint_as_float(v[j + e]);
                     if (post) o = post_op(o, ep.relu, mrow ? mrow + col + e : nullptr);
-                    drow[col + e] = o;
+                    if (ep.reduce)
+                        ptx::red_add_sys(drow + col + e, o);
+                    else
+                        drow[col + e] = o;
                 }
             }
         }
@@ -221,7 +230,15 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
                 if (col + 2 < N) o.z = post_op(o.z, e.relu, mrow ? mrow + 2 : nullptr);
                 if (col + 3 < N) o.w = post_op(o.w, e.relu, mrow ? mrow + 3 : nullptr);
             }
-            if (col + 3 < N) {
+            if (e.reduce) {
+                if (col + 3 < N) {
+                    ptx::red_add_sys_v4(drow + col, o);
+                } else {
+                    ptx::red_add_sys(drow + col, o.x);
+                    if (col + 1 < N) ptx::red_add_sys(drow + col + 1, o.y);
+                    if (col + 2 < N) ptx::red_add_sys(drow + col + 2, o.z);
+                }
+            } else if (col + 3 < N) {
                 *reinterpret_cast<float4*>(drow + col) = o;
             } else {
                 drow[col] = o.x;

@@ -281,11 +281,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             const int n0 = (r / p.tiles_m) * BLOCK_N;
             const int row = m0 + q * 32 + lane;
             float* dmat = p.D + b * p.strideD;
+            if (p.rows_per_owner) {
+                // reduce-scatter: the tile lies inside one owner's row block; shift that
+                // owner's buffer so that absolute row numbers index it
+                const int o = m0 / p.rows_per_owner;
+                dmat = p.owner[o] - static_cast<long long>(o) * p.rows_per_owner * p.ldd;
+            }
             const float* cmat = p.C ? p.C + b * p.strideC : nullptr;
             float* drow = dmat + static_cast<long long>(row) * p.ldd;
             const float* crow = cmat ? cmat + static_cast<long long>(row) * p.ldc : nullptr;
             float* my_stage = epi_stage + q * (EPI_STAGE_BYTES_PER_WARP / 4);
-            const Epilogue epi{p.bias, p.mask ? p.mask + b * p.strideM : nullptr, p.ldm, p.relu};
+            const Epilogue epi{p.bias, p.mask ? p.mask + b * p.strideM : nullptr, p.ldm, p.relu,
+                               p.rows_per_owner != 0};
             const float* mrow = epi.mask ? epi.mask + static_cast<long long>(row) * p.ldm : nullptr;
             if constexpr (!SPLIT) {
                 // one chunk per tile: straight from TMEM to global memory
@@ -534,6 +541,8 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.bias = g.bias;
     p.relu = g.relu;
     p.mask = g.mask; p.ldm = g.ldmask; p.strideM = g.strideMask;
+    for (int o = 0; o < MAX_OWNERS; ++o) p.owner[o] = g.owner[o];
+    p.rows_per_owner = static_cast<int>(g.rows_per_owner);
     p.status = ctx->d_status;
     p.explicit_hi = ctx->split_explicit_hi;
     p.colsum_out = COLSUM ? g.colsum_out : nullptr;

@@ -231,11 +231,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
             const int n0 = (r / p.tiles_m) * PAIR_N;
             const int row = m0 + q * 32 + lane;
             float* dmat = p.D + b * p.strideD;
+            if (p.rows_per_owner) {
+                // reduce-scatter: the tile lies inside one owner's row block; shift that
+                // owner's buffer so that absolute row numbers index it
+                const int o = m0 / p.rows_per_owner;
+                dmat = p.owner[o] - static_cast<long long>(o) * p.rows_per_owner * p.ldd;
+            }
             const float* cmat = p.C ? p.C + b * p.strideC : nullptr;
             float* drow = dmat + static_cast<long long>(row) * p.ldd;
             const float* crow = cmat ? cmat + static_cast<long long>(row) * p.ldc : nullptr;
             float* my_stage = epi_stage + q * (EPI_STAGE_BYTES_PER_WARP / 4);
-            const Epilogue epi{p.bias, p.mask ? p.mask + b * p.strideM : nullptr, p.ldm, p.relu};
+            const Epilogue epi{p.bias, p.mask ? p.mask + b * p.strideM : nullptr, p.ldm, p.relu,
+                               p.rows_per_owner != 0};
             if (!(ok = wait_bar_cluster(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
                 break;
             ptx::tc_fence_after_sync();
@@ -336,6 +343,8 @@ int launch_pair_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.bias = g.bias;
     p.relu = g.relu;
     p.mask = g.mask; p.ldm = g.ldmask; p.strideM = g.strideMask;
+    for (int o = 0; o < MAX_OWNERS; ++o) p.owner[o] = g.owner[o];
+    p.rows_per_owner = static_cast<int>(g.rows_per_owner);
     p.status = ctx->d_status;
     p.explicit_hi = 0;
     p.colsum_out = nullptr;

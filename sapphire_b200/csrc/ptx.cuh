@@ -344,5 +344,19 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, int a_mn_ma
            (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// ---- reductions into memory that may belong to another GPU (peer mapping):
+// fire-and-forget fp32 adds at system scope, performed at the owner's L2.
+__device__ __forceinline__ void red_add_sys(float* p, float v)
+{
+    asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ void red_add_sys_v4(float* p, float4 v)      // p 16-byte aligned
+{
+    asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x),
+                 "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
 }  // namespace ptx
 }  // namespace sb200

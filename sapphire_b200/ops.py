@@ -149,6 +149,24 @@ def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tenso
     return out
 
 
+def gemm_reduce_scatter(ctx: Context, a: torch.Tensor, b: torch.Tensor, owners, ld_out: int, *,
+                        mode: int = L.MODE_TF32, trans_a: bool = False, trans_b: bool = False,
+                        colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0) -> None:
+    """op(a).op(b) with row block o of the product added into the buffer at
+    device address ``owners[o]`` (see ``sb200_gemm_reduce_scatter``)."""
+    _, ra, ca, lda, _ = _mat_geometry(a)
+    _, rb, cb, ldb, _ = _mat_geometry(b)
+    M, K = (ca, ra) if trans_a else (ra, ca)
+    K2, N = (cb, rb) if trans_b else (rb, cb)
+    if K != K2:
+        raise ValueError(f"inner dimensions differ: {K} vs {K2}")
+    arr = (C.c_void_p * len(owners))(*[int(p) for p in owners])
+    L.check("sb200_gemm_reduce_scatter", L.lib().sb200_gemm_reduce_scatter(
+        ctx.handle, mode, int(trans_a), int(trans_b), M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
+        arr, len(owners), int(ld_out), colsum_out.data_ptr() if colsum_out is not None else None,
+        float(colsum_scale), _stream_ptr(ctx.device)))
+
+
 # --------------------------------------------------------------------- sparse
 
 @dataclass

@@ -121,3 +121,83 @@ class GradBucket:
             tail.mul_(1.0 / world)
         else:
             scale_fn(tail, 1.0 / world)
+
+
+# ------------------------------------------- GEMM fused with its reduce-scatter
+
+class PeerWindow:
+    """One [rows, cols] fp32 buffer per rank that every rank of the node can add
+    into: the landing zone of ``ops.gemm_reduce_scatter``.  ``mine`` is this
+    rank's buffer as a tensor; ``pointers[o]`` is rank o's buffer as seen from
+    this process (a CUDA IPC mapping for o != rank).  Handles travel through
+    ``all_gather_object``.  With ``world == 1`` no IPC is involved."""
+
+    def __init__(self, ctx, rows: int, cols: int, rank: int = 0, world: int = 1, group=None):
+        import ctypes as C
+        from . import _lib as L
+        self.ctx, self.rank, self.world, self.rows, self.cols = ctx, rank, world, rows, cols
+        self._lib, self._C = L, C
+        nbytes = rows * cols * 4
+        ptr = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        L.check("sb200_peer_alloc", L.lib().sb200_peer_alloc(ctx.handle, nbytes, C.byref(ptr), handle))
+        self._own = ptr.value
+        self.mine = _tensor_over(self._own, rows, cols, ctx.device, self)
+        self.pointers: List[int] = [0] * world
+        self.pointers[rank] = self._own
+        self._opened: List[int] = []
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            for o in range(world):
+                if o == rank:
+                    continue
+                p = C.c_void_p()
+                L.check("sb200_peer_open", L.lib().sb200_peer_open(ctx.handle, handles[o], C.byref(p)))
+                self.pointers[o] = p.value
+                self._opened.append(p.value)
+            dist.barrier(group=group)          # nobody frees before everybody has mapped
+
+    def close(self, group=None) -> None:
+        """Unmaps the peers' buffers, waits for every rank to have done so, frees
+        this rank's buffer.  ``mine`` must not be used afterwards."""
+        L = self._lib
+        torch.cuda.synchronize(self.ctx.device)
+        for p in self._opened:
+            L.lib().sb200_peer_close(self.ctx.handle, p)
+        self._opened = []
+        if self.world > 1:
+            dist.barrier(group=group)
+        if self._own:
+            L.lib().sb200_peer_free(self.ctx.handle, self._own)
+            self._own = 0
+
+
+def _tensor_over(ptr: int, rows: int, cols: int, device: int, keepalive) -> torch.Tensor:
+    """A torch view of library-owned device memory (no copy, no ownership)."""
+    class _Iface:
+        pass
+    holder = _Iface()
+    holder.__cuda_array_interface__ = {"shape": (rows, cols), "typestr": "<f4", "data": (ptr, False),
+                                       "version": 3, "strides": None}
+    holder._keepalive = keepalive
+    return torch.as_tensor(holder, device=torch.device("cuda", device))
+
+
+def linear_backward_fused(ctx, window: PeerWindow, x: torch.Tensor, dy: torch.Tensor,
+                          dw_full: torch.Tensor, db: torch.Tensor, barrier, mode: int = 0) -> None:
+    """dW = sum over ranks of x_r^T . dy_r with the reduce-scatter inside the
+    GEMM kernel (each rank's tiles are added into the owning rank's window over
+    NVLink) followed by an all-gather of the reduced row blocks; dB the local
+    column sums (still to be summed by the caller).  ``barrier()`` must be a
+    stream-ordered barrier across the ranks (a one-element all-reduce does)."""
+    from . import ops
+    window.mine.zero_()
+    barrier()                                  # every window is zero before anyone adds
+    ops.gemm_reduce_scatter(ctx, x, dy, window.pointers, window.cols, trans_a=True, mode=mode,
+                            colsum_out=db, colsum_scale=1.0 / (x.shape[0] * window.world))
+    barrier()                                  # every rank's adds have landed
+    if window.world > 1:
+        dist.all_gather_into_tensor(dw_full, window.mine)
+    else:
+        dw_full.copy_(window.mine)

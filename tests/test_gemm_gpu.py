@@ -388,3 +388,58 @@ def test_gate_argument_validation(ctx):
                                        a.data_ptr(), 8, 0, a.data_ptr(), 8, 0, None, 8, 0,
                                        a.data_ptr(), 8, 0, None, 1, None)
     assert rc == L.ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("mode,tol", [(L.MODE_TF32, 2e-3), (L.MODE_TF32X3, 1e-5)])
+@pytest.mark.parametrize("M,N,K,owners,ta", [
+    (1024, 512, 256, 4, 1),       # one-CTA kernel, transposed A like dW = x^T.dy
+    (4096, 4096, 512, 8, 1),      # enough tiles for the two-CTA kernel (TF32 mode)
+    (512, 520, 100, 2, 0),        # ragged N and K: scalar tail reductions
+    (256, 64, 64, 1, 0),          # a single owner: plain accumulate
+])
+def test_reduce_scatter_epilogue_on_one_gpu(ctx, oracle, mode, tol, M, N, K, owners, ta):
+    """The reduce-scatter epilogue with every owner's buffer on this GPU: row block o
+    of the product is added into buffer o; a second call adds it again."""
+    rng = np.random.default_rng(M + N + K + owners)
+    a = rng.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    b = rng.standard_normal((K, N)).astype(np.float32)
+    want = (a.T if ta else a).astype(np.float64) @ b.astype(np.float64)
+    bufs = [torch.full((M // owners, N), float(o + 1), device=DEV) for o in range(owners)]
+    colsum = torch.empty(N, device=DEV)
+    for rounds in (1, 2):
+        ops.gemm_reduce_scatter(ctx, dev(a), dev(b), [t.data_ptr() for t in bufs], N, mode=mode,
+                                trans_a=bool(ta), colsum_out=colsum, colsum_scale=0.5)
+        got = torch.cat([t - float(o + 1) for o, t in enumerate(bufs)]).cpu().numpy()
+        assert rel_fro(got, rounds * want) <= tol
+    assert np.abs(colsum.cpu().numpy() - 0.5 * b.astype(np.float64).sum(0)).max() <= 1e-3
+    ctx.check_device_status()
+
+
+def test_reduce_scatter_argument_validation(ctx):
+    a = torch.zeros(256, 64, device=DEV)
+    bufs = [torch.zeros(96, 64, device=DEV) for _ in range(2)]
+    with pytest.raises(L.Sb200Error) as e:           # 192 rows over 2 owners: blocks of 96, not tile-aligned
+        ops.gemm_reduce_scatter(ctx, torch.zeros(192, 64, device=DEV), a[:64], [t.data_ptr() for t in bufs], 64)
+    assert e.value.status == L.ERR_UNSUPPORTED
+    with pytest.raises(L.Sb200Error) as e:
+        ops.gemm_reduce_scatter(ctx, a, a[:64], [bufs[0].data_ptr()] * 9, 64)
+    assert e.value.status == L.ERR_INVALID_ARG
+
+
+def test_peer_window_single_rank_linear_backward(ctx):
+    """world == 1: the window is this GPU's own buffer; dW and dB of the fused
+    route equal the plain GEMM with its fused column sum."""
+    from sapphire_b200 import runner
+    rng = np.random.default_rng(5)
+    x = dev(rng.standard_normal((384, 256)).astype(np.float32))
+    dy = dev(rng.standard_normal((384, 192)).astype(np.float32))
+    window = runner.PeerWindow(ctx, 256, 192)
+    dw = torch.empty(256, 192, device=DEV)
+    db = torch.empty(192, device=DEV)
+    for _ in range(2):
+        runner.linear_backward_fused(ctx, window, x, dy, dw, db, lambda: None, mode=L.MODE_TF32X3)
+    want_db = torch.empty(192, device=DEV)
+    want = ops.gemm(ctx, x, dy, trans_a=True, mode=L.MODE_TF32X3, colsum_out=want_db, colsum_scale=1.0 / 384)
+    assert rel_fro(dw.cpu().numpy(), want.cpu().numpy()) <= 1e-6
+    assert torch.equal(db, want_db)
+    window.close()

@@ -55,3 +55,59 @@ def test_dp_mlp_two_gpus_matches_single_process_oracle(tmp_path):
     want = np.concatenate([w.reshape(-1) for w in net.W] + [b.reshape(-1) for b in net.b])
     err = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
     assert err <= 1e-5, err
+
+
+def _rs_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world),
+                      RANK=str(rank), LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from sapphire_b200 import _lib as L
+    from sapphire_b200 import ops, runner
+    runner.init_distributed("nccl")
+    dev = torch.device("cuda", rank)
+    ctx = ops.Context(rank)
+    rows, n_in, n_out = 512, 1024, 768                 # per-rank batch rows; dW is [n_in, n_out]
+    g = torch.Generator(device=dev); g.manual_seed(100 + rank)
+    x = torch.randn(rows, n_in, device=dev, generator=g)
+    dy = torch.randn(rows, n_out, device=dev, generator=g)
+    window = runner.PeerWindow(ctx, n_in // world, n_out, rank, world)
+    tick = torch.zeros(1, device=dev)
+    dw = torch.empty(n_in, n_out, device=dev)
+    db = torch.empty(n_out, device=dev)
+    for _ in range(2):                                  # the second round checks that re-zeroing works
+        runner.linear_backward_fused(ctx, window, x, dy, dw, db, lambda: dist.all_reduce(tick),
+                                     mode=L.MODE_TF32X3)
+    dist.all_reduce(db)
+    # the unfused route: local product, NCCL all-reduce
+    ref = ops.gemm(ctx, x, dy, trans_a=True, mode=L.MODE_TF32X3)
+    dist.all_reduce(ref)
+    xs = [torch.empty_like(x) for _ in range(world)]
+    dys = [torch.empty_like(dy) for _ in range(world)]
+    dist.all_gather(xs, x); dist.all_gather(dys, dy)
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    if rank == 0:
+        X = torch.cat(xs).double().cpu().numpy(); DY = torch.cat(dys).double().cpu().numpy()
+        np.savez(os.path.join(out_dir, "rs.npz"), dw=dw.cpu().numpy(), ref=ref.cpu().numpy(),
+                 db=db.cpu().numpy(), exact_dw=X.T @ DY, exact_db=DY.mean(0))
+    window.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gemm_fused_with_reduce_scatter_over_peer_memory(tmp_path):
+    """Each rank's dW tiles are added into the owning rank's window from the GEMM
+    epilogue (CUDA IPC peer mappings, system-scope fp32 reductions); after the
+    all-gather every rank holds the sum over ranks, equal to the all-reduce of the
+    local products and to the fp64 product of the gathered operands."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    mp.spawn(_rs_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r = np.load(os.path.join(str(tmp_path), "rs.npz"))
+    scale = np.linalg.norm(r["exact_dw"])
+    assert np.linalg.norm(r["dw"] - r["exact_dw"]) / scale <= 1e-5
+    assert np.linalg.norm(r["dw"].astype(np.float64) - r["ref"]) / scale <= 1e-6
+    assert np.abs(r["db"] - r["exact_db"]).max() <= 1e-5
