@@ -205,6 +205,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="dense_tf32")
+    ap.add_argument("--linear-bwd-comm", default="fused", choices=["fused", "nccl"],
+                    help="how the linear_bwd workload sums dW over ranks (see bench_linear_bwd)")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -363,7 +365,14 @@ def main():
                              "peak_source": pk["source"]},
                 "gpu_launches": launches}
 
-    def bench_linear_bwd(steps, warmup):
+    def bench_linear_bwd(steps, warmup, comm_mode="fused"):
+        """dW = x^T.dy (+ dB) and dx = dy.W^T on this rank's 8192 rows.  With several
+        ranks dW and dB are summed over the ranks inside the timed region:
+          "fused"  the dW GEMM adds its tiles into the owning rank's window over
+                   NVLink from its epilogue (GEMM + reduce-scatter in one kernel),
+                   one tiny all-reduce as barrier, then an all-gather of the
+                   reduced row blocks that overlaps the dx GEMM;
+          "nccl"   plain GEMM, then an NCCL all-reduce of dW that overlaps the dx GEMM."""
         rows, width = 8192, 4096
         g = torch.Generator(device=dev); g.manual_seed(7 + rank)
         dy = torch.randn(rows, width, device=dev, generator=g) * 0.02
@@ -374,27 +383,53 @@ def main():
         db = torch.empty(width, device=dev)
         comm = torch.cuda.Stream(dev) if world > 1 else None
         done = torch.cuda.Event() if world > 1 else None
+        fused = world > 1 and comm_mode == "fused" and width % (world * 128) == 0
+        windows, tick, turn = [], None, [0]
+        if fused:
+            from sapphire_b200 import runner as R
+            windows = [R.PeerWindow(ctx, width // world, width, rank, world) for _ in range(2)]
+            for wd in windows:
+                wd.mine.zero_()
+            tick = torch.zeros(1, device=dev)
+            dist.all_reduce(tick)
 
         def fn():
-            # dW first: its allreduce then travels while dX, which needs no exchange, computes
-            ops.gemm(ctx, x, dy, None, dw, trans_a=True, colsum_out=db,     # dW = x^T.dy, dB
-                     colsum_scale=1.0 / rows)
-            if world > 1:
-                main = torch.cuda.current_stream(dev)
+            main = torch.cuda.current_stream(dev)
+            if fused:
+                cur, nxt = windows[turn[0] % 2], windows[(turn[0] + 1) % 2]
+                turn[0] += 1
+                nxt.mine.zero_()                     # zeroed before this step's barrier, used next step
+                ops.gemm_reduce_scatter(ctx, x, dy, cur.pointers, width, trans_a=True,
+                                        colsum_out=db, colsum_scale=1.0 / (rows * world))
+                dist.all_reduce(tick)                # barrier: every rank's adds have landed
                 done.record(main)
                 with torch.cuda.stream(comm):
                     comm.wait_event(done)
-                    dist.all_reduce(dw)
+                    dist.all_gather_into_tensor(dw, cur.mine)
                     dist.all_reduce(db)
+            else:
+                # dW first: its allreduce then travels while dX, which needs no exchange, computes
+                ops.gemm(ctx, x, dy, None, dw, trans_a=True, colsum_out=db,     # dW = x^T.dy, dB
+                         colsum_scale=1.0 / (rows * world))
+                if world > 1:
+                    done.record(main)
+                    with torch.cuda.stream(comm):
+                        comm.wait_event(done)
+                        dist.all_reduce(dw)
+                        dist.all_reduce(db)
             ops.gemm(ctx, dy, w, None, dx, trans_b=True)                    # dx = dy.W^T
             if world > 1:
-                torch.cuda.current_stream(dev).wait_stream(comm)
+                main.wait_stream(comm)
         ms, launches = timed(fn, steps, warmup)
+        for wd in windows:
+            wd.close()
         flops = 2 * 2.0 * rows * width * width
-        return {"workload": "linear backward dY[8192x4096] X[8192x4096] W[4096x4096] per GPU, "
-                            "dW/dB allreduce inside" if world > 1 else
-                            "linear backward dY[8192x4096] X[8192x4096] W[4096x4096]",
-                "ms_per_step": ms, "tflops_per_gpu": flops / ms / 1e9, "gpu_launches": launches}
+        label = "linear backward dY[8192x4096] X[8192x4096] W[4096x4096]"
+        if world > 1:
+            label += (" per GPU, dW reduce-scatter fused into the GEMM epilogue (peer adds) + all-gather"
+                      if fused else " per GPU, dW/dB NCCL allreduce overlapped with the dx GEMM")
+        return {"workload": label, "ms_per_step": ms, "tflops_per_gpu": flops / ms / 1e9,
+                "gpu_launches": launches}
 
     def bench_mlp(steps, warmup):
         """BASELINE config 2: 784-512-256-10 MLP, global batch 64 split over the
@@ -483,7 +518,7 @@ def main():
                 "config": {"workload": r["workload"], "parallelism": f"A row blocks x{world}, B replicated"},
                 "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]}
     elif args.workload == "linear_bwd":
-        r = bench_linear_bwd(args.steps, args.warmup)
+        r = bench_linear_bwd(args.steps, args.warmup, args.linear_bwd_comm)
         tf32_peak = pk["bf16_tflops"] / 2.0
         line = {"metric": "Linear backward GEMM throughput", "value": r["tflops_per_gpu"] * world,
                 "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -516,6 +551,8 @@ def main():
             extras.append({"workload": f"{name} batch={BATCH} n={n}", "ms_per_step": ms,
                            "tflops_per_gpu": per_gpu})
         extras.append(bench_linear_bwd(10, 3))
+        if world > 1:
+            extras.append(bench_linear_bwd(10, 3, "nccl"))
         extras.append(bench_spgemm("poisson", 5, 3))
         extras.append(bench_spgemm("zipf", 5, 3))
         extras.append(bench_mlp(50, 5))
