@@ -390,11 +390,14 @@ int sb200_col2im(sb200_ctx* ctx, float* x, const float* cols,
  *     dlogits = softmax_backward(cross_entropy_backward(prob, label), prob)
  * It replaces the four leaf calls at the end of a classifier's forward pass and
  * the start of its backward pass (NaiveBasic.cpp:235-281,
- * NaiveCrossEntropy.cpp:15-51).  unit <= 1024.
+ * NaiveCrossEntropy.cpp:15-51).  unit <= 1024.  logits, label and prob are dense
+ * [batch, unit]; dlogits has row pitch ld_dlogits >= unit, so that it can be
+ * written with the 16-byte aligned rows the tensor-core GEMMs of the backward
+ * pass want as an operand.
  */
 int sb200_softmax_cross_entropy(sb200_ctx* ctx, float* prob, float* loss, float* dlogits,
-                                const float* logits, const float* label, int batch, int unit,
-                                sb200_stream stream);
+                                int64_t ld_dlogits, const float* logits, const float* label,
+                                int batch, int unit, sb200_stream stream);
 
 /* z <- z - lr * dz as one kernel; the reference runs Scale into a temporary and
  * then Sub (Sources/Sapphire/operations/optimizers/SGD.cpp:22-28). */

@@ -112,7 +112,8 @@ SIGNATURES = {
     "sb200_col2im": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(ConvGeometry),
                                C.c_void_p]),
     "sb200_softmax_cross_entropy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                              C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+                                              C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                              C.c_void_p]),
     "sb200_sgd_update": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64,
                                    C.c_void_p]),
     "sb200_scale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_void_p]),

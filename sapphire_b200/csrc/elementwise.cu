@@ -104,8 +104,8 @@ constexpr int FUSED_MAX_UNIT = 1024;
 
 __global__ void __launch_bounds__(FUSED_WARPS * 32)
 softmax_ce_kernel(float* __restrict__ prob, float* __restrict__ loss, float* __restrict__ dlogits,
-                  const float* __restrict__ logits, const float* __restrict__ label, int batch,
-                  int unit)
+                  int64_t ld_dlogits, const float* __restrict__ logits,
+                  const float* __restrict__ label, int batch, int unit)
 {
     extern __shared__ float sh[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -153,7 +153,7 @@ softmax_ce_kernel(float* __restrict__ prob, float* __restrict__ loss, float* __r
                                      : __fmul_rn(dp[j], __fmul_rn(-yi, yj));
             s = __fadd_rn(s, t);
         }
-        dlogits[static_cast<int64_t>(r) * unit + i] = __fadd_rn(0.0f, s);
+        dlogits[static_cast<int64_t>(r) * ld_dlogits + i] = __fadd_rn(0.0f, s);
     }
 }
 
@@ -247,15 +247,17 @@ extern "C" int sb200_cross_entropy_backward(sb200_ctx* ctx, float* dx, const flo
 }
 
 extern "C" int sb200_softmax_cross_entropy(sb200_ctx* ctx, float* prob, float* loss, float* dlogits,
-                                           const float* logits, const float* label, int batch,
-                                           int unit, sb200_stream stream_)
+                                           int64_t ld_dlogits, const float* logits,
+                                           const float* label, int batch, int unit,
+                                           sb200_stream stream_)
 {
-    SB200_PROLOGUE(batch >= 0 && unit > 0 && (batch == 0 || (dlogits && logits && label)))
+    SB200_PROLOGUE(batch >= 0 && unit > 0 && ld_dlogits >= unit &&
+                   (batch == 0 || (dlogits && logits && label)))
     if (unit > FUSED_MAX_UNIT) return SB200_ERR_TOO_LARGE;
     if (batch == 0) return SB200_OK;
     const size_t smem = static_cast<size_t>(FUSED_WARPS) * 2 * unit * sizeof(float);
     softmax_ce_kernel<<<blocks_for(batch, FUSED_WARPS), FUSED_WARPS * 32, smem, stream>>>(
-        prob, loss, dlogits, logits, label, batch, unit);
+        prob, loss, dlogits, ld_dlogits, logits, label, batch, unit);
     return finish(ctx);
 }
 

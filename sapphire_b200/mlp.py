@@ -35,18 +35,23 @@ from .runner import GradBucket
 
 class MlpTrainer:
     def __init__(self, ctx: ops.Context, weights: Sequence[np.ndarray], biases: Sequence[np.ndarray],
-                 lr: float, mode: int = L.MODE_TF32, world: int = 1, fused: bool = True):
+                 lr: float, mode: int = L.MODE_TF32, world: int = 1, fused: bool = True,
+                 row_pad: int = 4):
+        """``row_pad``: rows of the parameter / gradient buffers are padded to this
+        many floats.  4 (16 bytes) puts the 10-column output layer on the
+        tensor-core kernel; 1 keeps its rows dense, which sends that layer to the
+        CUDA-core kernel (sequential fp32 sums, bit-identical to the reference)."""
         self.ctx, self.lr, self.mode, self.world = ctx, float(lr), mode, world
-        self.fused = fused
+        self.fused, self.row_pad = fused, row_pad
         dev = torch.device("cuda", ctx.device)
         shapes = [w.shape for w in weights]
         # parameters share the gradient bucket's layout: one SGD kernel updates them all
-        self.params = GradBucket.create(shapes, dev)
+        self.params = GradBucket.create(shapes, dev, row_pad)
         for dst, w in zip(self.params.dW, weights):
             dst.copy_(torch.from_numpy(np.ascontiguousarray(w)))
         for dst, b in zip(self.params.dB, biases):
             dst.copy_(torch.from_numpy(np.ascontiguousarray(b)))
-        self.grads = GradBucket.create(shapes, dev)
+        self.grads = GradBucket.create(shapes, dev, row_pad)
         self.W, self.b = self.params.dW, self.params.dB
 
     def forward_backward(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
@@ -70,6 +75,12 @@ class MlpTrainer:
         ops.cross_entropy_backward(ctx, dprob, prob, onehot)
         dy = torch.zeros_like(prob)
         ops.softmax_backward(ctx, dy, dprob, prob)
+        if self.row_pad > 1 and dy.shape[1] % self.row_pad:
+            # same row pitch as the fused path, so that both run the same GEMM kernels
+            ld = (dy.shape[1] + self.row_pad - 1) // self.row_pad * self.row_pad
+            padded = torch.empty((B, ld), dtype=torch.float32, device=dy.device)[:, :dy.shape[1]]
+            padded.copy_(dy)
+            dy = padded
         for l in reversed(range(nl)):
             dx = ops.gemm(ctx, dy, self.W[l], trans_b=True, mode=mode)
             ops.gemm(ctx, acts[l], dy, out=self.grads.dW[l], trans_a=True, mode=mode,
@@ -87,7 +98,7 @@ class MlpTrainer:
         acts: List[torch.Tensor] = [x]              # acts[l] = input of layer l (ReLU output of l-1)
         for l in range(nl):
             acts.append(ops.gemm(ctx, acts[-1], self.W[l], bias=self.b[l], mode=mode, relu=l < nl - 1))
-        _, loss, dy = ops.softmax_cross_entropy(ctx, acts[-1], onehot)
+        _, loss, dy = ops.softmax_cross_entropy(ctx, acts[-1], onehot, row_pad=self.row_pad)
         for l in reversed(range(nl)):
             # dx first, like the reference; the first layer's dx is computed and dropped as there
             dx = ops.gemm(ctx, dy, self.W[l], trans_b=True, mode=mode,

@@ -315,18 +315,23 @@ def cross_entropy_backward(ctx, dx, prob, label):
     return dx
 
 
-def softmax_cross_entropy(ctx, logits, label, prob=None, loss=None, dlogits=None):
+def softmax_cross_entropy(ctx, logits, label, prob=None, loss=None, dlogits=None, row_pad=4):
     """Fused softmax + cross-entropy + both backward passes over [batch, unit]
-    logits; returns (prob, loss, dlogits)."""
+    logits; returns (prob, loss, dlogits).  A dlogits allocated here gets rows
+    padded to a multiple of ``row_pad`` floats (a view of the logical shape is
+    returned); with 4 it can feed the tensor-core GEMMs of the backward pass."""
     batch, unit = logits.shape
+    logits = logits.contiguous()
     if prob is None:
         prob = torch.empty_like(logits)
     if loss is None:
         loss = torch.empty(batch, dtype=torch.float32, device=logits.device)
     if dlogits is None:
-        dlogits = torch.empty_like(logits)
-    _ew("sb200_softmax_cross_entropy", ctx, prob.data_ptr(), loss.data_ptr(), dlogits.data_ptr(),
-        logits.data_ptr(), label.data_ptr(), batch, unit)
+        ld = (unit + row_pad - 1) // row_pad * row_pad
+        dlogits = torch.empty((batch, ld), dtype=torch.float32, device=logits.device)[:, :unit]
+    ld = dlogits.stride(0) if batch > 1 else max(unit, dlogits.stride(0))
+    _ew("sb200_softmax_cross_entropy", ctx, prob.data_ptr(), loss.data_ptr(), dlogits.data_ptr(), ld,
+        logits.data_ptr(), label.contiguous().data_ptr(), batch, unit)
     return prob, loss, dlogits
 
 

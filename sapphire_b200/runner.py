@@ -90,26 +90,36 @@ def csr_row_block(row: np.ndarray, col: np.ndarray, val: np.ndarray, rows: range
 
 @dataclass
 class GradBucket:
-    """All gradients of the MLP in one flat fp32 buffer: the dW blocks first,
-    then the dB blocks, so that the mean scaling touches one contiguous tail."""
+    """All gradients (or parameters) of the MLP in one flat fp32 buffer: the dW
+    blocks first, then the dB blocks, so that the mean scaling touches one
+    contiguous tail.  Rows are padded to a multiple of four floats (the padding
+    stays zero): a [256, 10] weight then has a 16-byte row pitch, which is what
+    the tensor-core GEMM's TMA loads need -- unpadded it would fall to the
+    CUDA-core kernel.  ``dW[l]`` / ``dB[l]`` are views of the logical shape;
+    ``compact()`` returns the values without the padding."""
     flat: torch.Tensor
     dW: List[torch.Tensor]
     dB: List[torch.Tensor]
     n_weight: int
 
     @staticmethod
-    def create(shapes: Sequence[Tuple[int, int]], device) -> "GradBucket":
-        nW = sum(i * o for i, o in shapes)
-        nB = sum(o for _, o in shapes)
+    def create(shapes: Sequence[Tuple[int, int]], device, pad: int = 4) -> "GradBucket":
+        ld = [(o + pad - 1) // pad * pad for _, o in shapes]
+        nW = sum(i * l for (i, _), l in zip(shapes, ld))
+        nB = sum(ld)
         flat = torch.zeros(nW + nB, dtype=torch.float32, device=device)
         dW, dB, off = [], [], 0
-        for i, o in shapes:
-            dW.append(flat[off:off + i * o].view(i, o))
-            off += i * o
-        for _, o in shapes:
-            dB.append(flat[off:off + o])
-            off += o
+        for (i, o), l in zip(shapes, ld):
+            dW.append(flat[off:off + i * l].view(i, l)[:, :o])
+            off += i * l
+        for (_, o), l in zip(shapes, ld):
+            dB.append(flat[off:off + l][:o])
+            off += l
         return GradBucket(flat, dW, dB, nW)
+
+    def compact(self) -> torch.Tensor:
+        """The dW blocks then the dB blocks, without row padding."""
+        return torch.cat([w.reshape(-1) for w in self.dW] + [b.reshape(-1) for b in self.dB])
 
     def allreduce(self, world: int, scale_fn=None) -> None:
         """dW: SUM over ranks.  dB: MEAN over ranks."""

@@ -110,18 +110,25 @@ def test_mlp_lr_0p01_diverges_like_the_reference(ctx, oracle):
     assert first_bad_want is not None and first_bad_got == first_bad_want
 
 
-def test_mlp_fixture_from_reference_build(ctx):
-    """Three steps against the fixture produced by the reference's own CPU leaves."""
+@pytest.mark.parametrize("row_pad,tol", [(1, 1e-5), (4, 3e-5)])
+def test_mlp_fixture_from_reference_build(ctx, row_pad, tol):
+    """Three steps at the reference's lr 0.01 against the fixture produced by the
+    reference's own CPU leaves.  At this learning rate the un-normalised gradients
+    grow by orders of magnitude per step (the run leaves the finite range at the
+    next one), so rounding differences are amplified: with dense rows the
+    10-column layer runs on the sequential CUDA-core kernel and the run stays
+    within 1e-5; with padded rows that layer also runs in 3xTF32 on the tensor
+    cores (1e-6 per GEMM) and the amplified difference is ~1e-5."""
     gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "dense_golden.npz"))
     Ws, bs = W.mlp_init(0)
-    trainer = mlp.MlpTrainer(ctx, Ws, bs, 0.01, mode=L.MODE_TF32X3)
+    trainer = mlp.MlpTrainer(ctx, Ws, bs, 0.01, mode=L.MODE_TF32X3, row_pad=row_pad)
     losses = []
     for t in range(3):
         x, onehot = W.mlp_batch(t)
         losses.append(trainer.step(dev(x), dev(onehot)).cpu().numpy())
-    assert rel(np.stack(losses), gold["mlp_loss3"]) <= 1e-5
-    assert rel(trainer.W[2].cpu().numpy(), gold["mlp_w2_after3"]) <= 1e-5
-    assert rel(trainer.b[0].cpu().numpy(), gold["mlp_b0_after3"]) <= 1e-5
+    assert rel(np.stack(losses), gold["mlp_loss3"]) <= tol
+    assert rel(trainer.W[2].cpu().numpy(), gold["mlp_w2_after3"]) <= tol
+    assert rel(trainer.b[0].cpu().numpy(), gold["mlp_b0_after3"]) <= tol
 
 
 def test_mlp_cuda_graph_step_equals_eager_step(ctx):

@@ -34,7 +34,7 @@ def _worker(rank, world, port, out_dir):
     torch.cuda.synchronize()
     ctx.check_device_status()
     if rank == 0:
-        np.save(os.path.join(out_dir, "params.npy"), trainer.params.flat.cpu().numpy())
+        np.save(os.path.join(out_dir, "params.npy"), trainer.params.compact().cpu().numpy())
     dist.barrier()
     dist.destroy_process_group()
 

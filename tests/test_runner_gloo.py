@@ -82,7 +82,7 @@ def _dp_worker(rank, world, port, out_dir):
         dst.copy_(torch.from_numpy(g))
     bucket.allreduce(world)
     if rank == 0:
-        np.save(os.path.join(out_dir, "flat.npy"), bucket.flat.numpy())
+        np.save(os.path.join(out_dir, "flat.npy"), bucket.compact().numpy())
     dist.barrier()
     dist.destroy_process_group()
 
