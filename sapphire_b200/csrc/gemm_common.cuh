@@ -55,6 +55,14 @@ __device__ __forceinline__ float post_op(float o, int relu, const float* m)
     return o;
 }
 
+// The same with the gate value already in a register.
+__device__ __forceinline__ float post_op_value(float o, int relu, bool gated, float gate)
+{
+    if (relu) o = o > 0.0f ? o : 0.0f;
+    if (gated) o = __fadd_rn(0.0f, gate > 0.0f ? o : 0.0f);
+    return o;
+}
+
 struct Abort {
     volatile int* flag;
     unsigned* status;
@@ -196,14 +204,38 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
     const int lane = threadIdx.x & 31;
     const float* bias = e.bias;
     const bool post = e.relu || e.mask;
+    const int sub = lane >> 3, cq = (lane & 7) * 4;
+    const int col = col0 + cq;
+    // the gate values of this lane's float4s are fetched four rows at a time, the
+    // four loads in flight together (fetched one by one where they are needed
+    // they would cost a memory round trip each)
+    float4 gate[4];
+    const bool gate_vec = e.mask && ((e.ldm & 3) == 0) && ((reinterpret_cast<uintptr_t>(e.mask) & 15) == 0);
+    auto load_gates = [&](int first) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int grow = row0 + (first + k) * 4 + sub;
+            gate[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (grow < M && col < N) {
+                const float* mp = e.mask + static_cast<long long>(grow) * e.ldm + col;
+                if (gate_vec && col + 3 < N) {
+                    gate[k] = __ldg(reinterpret_cast<const float4*>(mp));
+                } else {
+                    gate[k].x = __ldg(mp);
+                    if (col + 1 < N) gate[k].y = __ldg(mp + 1);
+                    if (col + 2 < N) gate[k].z = __ldg(mp + 2);
+                    if (col + 3 < N) gate[k].w = __ldg(mp + 3);
+                }
+            }
+        }
+    };
+    if (e.mask) load_gates(0);
 #pragma unroll
     for (int j = 0; j < 32; j += 4)
         *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + j) =
             make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
                         __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
     __syncwarp();
-    const int sub = lane >> 3, cq = (lane & 7) * 4;
-    const int col = col0 + cq;
     float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
     if (bias) {
         if (col < N) bv.x = __ldg(bias + col);
@@ -213,6 +245,7 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
+        if (i == 4 && e.mask) load_gates(4);
         const int r = i * 4 + sub;
         const int grow = row0 + r;
         const float4 a = *reinterpret_cast<const float4*>(stage + r * EPI_STAGE_LD + cq);
@@ -224,11 +257,11 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
             o.z = (cc.v[i].z + bv.z) + a.z;
             o.w = (cc.v[i].w + bv.w) + a.w;
             if (post) {
-                const float* mrow = e.mask ? e.mask + static_cast<long long>(grow) * e.ldm + col : nullptr;
-                o.x = post_op(o.x, e.relu, mrow);
-                if (col + 1 < N) o.y = post_op(o.y, e.relu, mrow ? mrow + 1 : nullptr);
-                if (col + 2 < N) o.z = post_op(o.z, e.relu, mrow ? mrow + 2 : nullptr);
-                if (col + 3 < N) o.w = post_op(o.w, e.relu, mrow ? mrow + 3 : nullptr);
+                const bool gated = e.mask != nullptr;
+                o.x = post_op_value(o.x, e.relu, gated, gate[i & 3].x);
+                o.y = post_op_value(o.y, e.relu, gated, gate[i & 3].y);
+                o.z = post_op_value(o.z, e.relu, gated, gate[i & 3].z);
+                o.w = post_op_value(o.w, e.relu, gated, gate[i & 3].w);
             }
             if (e.reduce) {
                 if (col + 3 < N) {

@@ -1,6 +1,7 @@
 """Small, self-terminating cases of each kernel for `ncu` captures.
 
     python -m sapphire_b200.profile_cases dense_tf32 | dense_tf32x3 | dense_tn | spgemm | spgemm_zipf
+                                          | im2col | mlp
 
 Each case touches more than the 126 MB L2 but holds at most ~1.5 GB on the
 device and launches every kernel a handful of times, so that a full-set
@@ -46,6 +47,36 @@ def spgemm(dist: str, M: int = 32768, N: int = 65536) -> None:
     print("spgemm case done", Cm.nnz)
 
 
+def im2col() -> None:
+    """The bench's convolution: 32 x 64 x 56 x 56 input, 3 x 3 taps, padding 1
+    (cols = 231 MB, larger than L2)."""
+    from . import conv
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    x = torch.randn(32, 64, 56, 56, device=dev, generator=g)
+    for _ in range(3):
+        cols = conv.im2col(ctx, x, 3, 3, (1, 1), (1, 1), (1, 1))
+    torch.cuda.synchronize()
+    print("im2col case done", float(cols[0, 0, 0]))
+
+
+def mlp_step() -> None:
+    """Three eager steps of the 784-512-256-10 MLP at batch 64."""
+    from . import mlp
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    Ws, bs = W.mlp_init(0)
+    trainer = mlp.MlpTrainer(ctx, Ws, bs, 1e-4, mode=L.MODE_TF32)
+    x, onehot = W.mlp_batch(0)
+    x, onehot = torch.from_numpy(x).to(dev), torch.from_numpy(onehot).to(dev)
+    for _ in range(3):
+        loss = trainer.step(x, onehot)
+    torch.cuda.synchronize()
+    print("mlp case done", float(loss[0]))
+
+
 def main() -> None:
     case = sys.argv[1] if len(sys.argv) > 1 else "dense_tf32"
     if case == "dense_tf32":
@@ -60,6 +91,10 @@ def main() -> None:
         spgemm("poisson")
     elif case == "spgemm_zipf":
         spgemm("zipf")
+    elif case == "im2col":
+        im2col()
+    elif case == "mlp":
+        mlp_step()
     else:
         raise SystemExit(f"unknown case {case}")
 
