@@ -51,28 +51,45 @@ gemm_simt_kernel(const SimtParams p)
         for (int j = 0; j < 4; ++j)
             acc[i][j] = 0.0f;
 
-    for (long long k0 = 0; k0 < p.K; k0 += TK) {
-        for (int i = threadIdx.x; i < TK * TS; i += 256) {
+    // Tiles go global -> registers -> shared memory; the loads of the next k-step
+    // are issued before the current one is multiplied, so their latency hides
+    // behind the arithmetic (small problems are a handful of CTAs walking K one
+    // step at a time: latency is all there is).
+    constexpr int PER = TK * TS / 256;
+    float ra[PER], rb[PER];
+    auto fetch = [&](long long k0) {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = threadIdx.x + e * 256;
             int kk, mm;
             if (p.transA) { mm = i % TS; kk = i / TS; }     // stored [K, M]: m contiguous
             else          { kk = i % TK; mm = i / TK; }     // stored [M, K]: k contiguous
             const long long m = m0 + mm, k = k0 + kk;
-            float v = 0.0f;
+            ra[e] = 0.0f;
             if (m < p.M && k < p.K)
-                v = p.transA ? A[k * p.lda + m] : A[m * p.lda + k];
-            As[kk][mm] = v;
+                ra[e] = p.transA ? A[k * p.lda + m] : A[m * p.lda + k];
+            int kb, nn;
+            if (p.transB) { kb = i % TK; nn = i / TK; }     // stored [N, K]: k contiguous
+            else          { nn = i % TS; kb = i / TS; }     // stored [K, N]: n contiguous
+            const long long n = n0 + nn, k2 = k0 + kb;
+            rb[e] = 0.0f;
+            if (n < p.N && k2 < p.K)
+                rb[e] = p.transB ? B[n * p.ldb + k2] : B[k2 * p.ldb + n];
         }
-        for (int i = threadIdx.x; i < TK * TS; i += 256) {
-            int kk, nn;
-            if (p.transB) { kk = i % TK; nn = i / TK; }     // stored [N, K]: k contiguous
-            else          { nn = i % TS; kk = i / TS; }     // stored [K, N]: n contiguous
-            const long long n = n0 + nn, k = k0 + kk;
-            float v = 0.0f;
-            if (n < p.N && k < p.K)
-                v = p.transB ? B[n * p.ldb + k] : B[k * p.ldb + n];
-            Bs[kk][nn] = v;
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = threadIdx.x + e * 256;
+            if (p.transA) As[i / TS][i % TS] = ra[e]; else As[i % TK][i / TK] = ra[e];
+            if (p.transB) Bs[i % TK][i / TK] = rb[e]; else Bs[i / TS][i % TS] = rb[e];
         }
+    };
+    if (p.K > 0) fetch(0);
+    for (long long k0 = 0; k0 < p.K; k0 += TK) {
+        stash();
         __syncthreads();
+        if (k0 + TK < p.K) fetch(k0 + TK);
         const int klim = (p.K - k0) < TK ? static_cast<int>(p.K - k0) : TK;
         for (int kk = 0; kk < klim; ++kk) {
             float a[4], bv[4];
