@@ -150,6 +150,9 @@ def cpu_spgemm_sample(dist_name: str, rows: int):
     return time.perf_counter() - t, 2.0 * prods
 
 
+FUSED_RS_VALIDATED_WORLD = 2
+
+
 def run_reference_arm(args):
     """The reference's own CPU implementation of the path on this host: for the
     dense workloads Sapphire's Dense::Naive::Gemm (single-threaded: the reference
@@ -388,6 +391,11 @@ def main():
         if fused:
             from sapphire_b200 import runner as R
             windows = [R.PeerWindow(ctx, width // world, width, rank, world) for _ in range(2)]
+            if not all(wd.ok for wd in windows):        # agreed across ranks: all fall back together
+                for wd in windows:
+                    wd.close()
+                windows, fused = [], False
+        if fused:
             for wd in windows:
                 wd.mine.zero_()
             tick = torch.zeros(1, device=dev)
@@ -550,9 +558,13 @@ def main():
             ms, per_gpu, _, _ = bench_dense(n, mode, 5, 3, False)
             extras.append({"workload": f"{name} batch={BATCH} n={n}", "ms_per_step": ms,
                            "tflops_per_gpu": per_gpu})
-        extras.append(bench_linear_bwd(10, 3))
+        # the fused GEMM + reduce-scatter route has been run on FUSED_RS_VALIDATED_WORLD ranks;
+        # beyond that the default run keeps to the NCCL route (--workload linear_bwd
+        # --linear-bwd-comm fused runs it on any rank count)
         if world > 1:
             extras.append(bench_linear_bwd(10, 3, "nccl"))
+        if world <= FUSED_RS_VALIDATED_WORLD:
+            extras.append(bench_linear_bwd(10, 3))
         extras.append(bench_spgemm("poisson", 5, 3))
         extras.append(bench_spgemm("zipf", 5, 3))
         extras.append(bench_mlp(50, 5))

@@ -140,7 +140,12 @@ class PeerWindow:
     into: the landing zone of ``ops.gemm_reduce_scatter``.  ``mine`` is this
     rank's buffer as a tensor; ``pointers[o]`` is rank o's buffer as seen from
     this process (a CUDA IPC mapping for o != rank).  Handles travel through
-    ``all_gather_object``.  With ``world == 1`` no IPC is involved."""
+    ``all_gather_object``.  With ``world == 1`` no IPC is involved.
+
+    Construction is collective and does not raise half-way: a rank whose
+    mapping fails still takes part in the closing barrier and every rank then
+    sees ``ok == False`` (agreed by an all-reduce), so that callers can fall
+    back together instead of leaving some ranks inside a collective."""
 
     def __init__(self, ctx, rows: int, cols: int, rank: int = 0, world: int = 1, group=None):
         import ctypes as C
@@ -156,6 +161,7 @@ class PeerWindow:
         self.pointers: List[int] = [0] * world
         self.pointers[rank] = self._own
         self._opened: List[int] = []
+        self.ok = True
         if world > 1:
             handles = [None] * world
             dist.all_gather_object(handles, handle.raw, group=group)
@@ -163,10 +169,15 @@ class PeerWindow:
                 if o == rank:
                     continue
                 p = C.c_void_p()
-                L.check("sb200_peer_open", L.lib().sb200_peer_open(ctx.handle, handles[o], C.byref(p)))
+                if L.lib().sb200_peer_open(ctx.handle, handles[o], C.byref(p)) != 0 or not p.value:
+                    self.ok = False
+                    continue
                 self.pointers[o] = p.value
                 self._opened.append(p.value)
-            dist.barrier(group=group)          # nobody frees before everybody has mapped
+            # nobody frees before everybody has mapped, and everybody learns whether all could
+            agreed = torch.tensor([1.0 if self.ok else 0.0], device=torch.device("cuda", ctx.device))
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+            self.ok = bool(agreed.item() > 0.5)
 
     def close(self, group=None) -> None:
         """Unmaps the peers' buffers, waits for every rank to have done so, frees
