@@ -150,7 +150,7 @@ def cpu_spgemm_sample(dist_name: str, rows: int):
     return time.perf_counter() - t, 2.0 * prods
 
 
-FUSED_RS_VALIDATED_WORLD = 2
+FUSED_RS_VALIDATED_WORLD = 8
 
 
 def run_reference_arm(args):
