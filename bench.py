@@ -373,8 +373,9 @@ def main():
         ranks dW and dB are summed over the ranks inside the timed region:
           "fused"  the dW GEMM adds its tiles into the owning rank's window over
                    NVLink from its epilogue (GEMM + reduce-scatter in one kernel),
-                   one tiny all-reduce as barrier, then an all-gather of the
-                   reduced row blocks that overlaps the dx GEMM;
+                   one tiny all-reduce as barrier, then every rank pulls the reduced
+                   row blocks from the owners' windows with copy-engine transfers
+                   while the dx GEMM runs (runner.FusedWeightGradient);
           "nccl"   plain GEMM, then an NCCL all-reduce of dW that overlaps the dx GEMM."""
         rows, width = 8192, 4096
         g = torch.Generator(device=dev); g.manual_seed(7 + rank)
@@ -387,34 +388,18 @@ def main():
         comm = torch.cuda.Stream(dev) if world > 1 else None
         done = torch.cuda.Event() if world > 1 else None
         fused = world > 1 and comm_mode == "fused" and width % (world * 128) == 0
-        windows, tick, turn = [], None, [0]
+        reducer = None
         if fused:
             from sapphire_b200 import runner as R
-            windows = [R.PeerWindow(ctx, width // world, width, rank, world) for _ in range(2)]
-            if not all(wd.ok for wd in windows):        # agreed across ranks: all fall back together
-                for wd in windows:
-                    wd.close()
-                windows, fused = [], False
-        if fused:
-            for wd in windows:
-                wd.mine.zero_()
-            tick = torch.zeros(1, device=dev)
-            dist.all_reduce(tick)
+            reducer = R.FusedWeightGradient(ctx, width, width, rank, world)
+            if not reducer.ok:                           # agreed across ranks: all fall back together
+                reducer.close()
+                reducer, fused = None, False
 
         def fn():
             main = torch.cuda.current_stream(dev)
             if fused:
-                cur, nxt = windows[turn[0] % 2], windows[(turn[0] + 1) % 2]
-                turn[0] += 1
-                nxt.mine.zero_()                     # zeroed before this step's barrier, used next step
-                ops.gemm_reduce_scatter(ctx, x, dy, cur.pointers, width, trans_a=True,
-                                        colsum_out=db, colsum_scale=1.0 / (rows * world))
-                dist.all_reduce(tick)                # barrier: every rank's adds have landed
-                done.record(main)
-                with torch.cuda.stream(comm):
-                    comm.wait_event(done)
-                    dist.all_gather_into_tensor(dw, cur.mine)
-                    dist.all_reduce(db)
+                reducer.start(x, dy, dw, db)
             else:
                 # dW first: its allreduce then travels while dX, which needs no exchange, computes
                 ops.gemm(ctx, x, dy, None, dw, trans_a=True, colsum_out=db,     # dW = x^T.dy, dB
@@ -426,16 +411,18 @@ def main():
                         dist.all_reduce(dw)
                         dist.all_reduce(db)
             ops.gemm(ctx, dy, w, None, dx, trans_b=True)                    # dx = dy.W^T
-            if world > 1:
+            if fused:
+                reducer.wait()
+            elif world > 1:
                 main.wait_stream(comm)
         ms, launches = timed(fn, steps, warmup)
-        for wd in windows:
-            wd.close()
+        if reducer is not None:
+            reducer.close()
         flops = 2 * 2.0 * rows * width * width
         label = "linear backward dY[8192x4096] X[8192x4096] W[4096x4096]"
         if world > 1:
-            label += (" per GPU, dW reduce-scatter fused into the GEMM epilogue (peer adds) + all-gather"
-                      if fused else " per GPU, dW/dB NCCL allreduce overlapped with the dx GEMM")
+            label += (" per GPU, dW reduce-scatter fused into the GEMM epilogue (peer adds) + "
+                      "copy-engine gather" if fused else " per GPU, dW/dB NCCL allreduce overlapped with the dx GEMM")
         return {"workload": label, "ms_per_step": ms, "tflops_per_gpu": flops / ms / 1e9,
                 "gpu_launches": launches}
 

@@ -178,6 +178,12 @@ class PeerWindow:
             agreed = torch.tensor([1.0 if self.ok else 0.0], device=torch.device("cuda", ctx.device))
             dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
             self.ok = bool(agreed.item() > 0.5)
+        # every rank's buffer as a tensor of this process (peer mappings for the others):
+        # sources of copy-engine transfers, never operands of library kernels
+        self.views: List[torch.Tensor] = [
+            self.mine if o == rank else
+            (_tensor_over(self.pointers[o], rows, cols, ctx.device, self) if self.pointers[o] else None)
+            for o in range(world)]
 
     def close(self, group=None) -> None:
         """Unmaps the peers' buffers, waits for every rank to have done so, frees
@@ -205,20 +211,67 @@ def _tensor_over(ptr: int, rows: int, cols: int, device: int, keepalive) -> torc
     return torch.as_tensor(holder, device=torch.device("cuda", device))
 
 
-def linear_backward_fused(ctx, window: PeerWindow, x: torch.Tensor, dy: torch.Tensor,
-                          dw_full: torch.Tensor, db: torch.Tensor, barrier, mode: int = 0) -> None:
-    """dW = sum over ranks of x_r^T . dy_r with the reduce-scatter inside the
-    GEMM kernel (each rank's tiles are added into the owning rank's window over
-    NVLink) followed by an all-gather of the reduced row blocks; dB the local
-    column sums (still to be summed by the caller).  ``barrier()`` must be a
-    stream-ordered barrier across the ranks (a one-element all-reduce does)."""
-    from . import ops
-    window.mine.zero_()
-    barrier()                                  # every window is zero before anyone adds
-    ops.gemm_reduce_scatter(ctx, x, dy, window.pointers, window.cols, trans_a=True, mode=mode,
-                            colsum_out=db, colsum_scale=1.0 / (x.shape[0] * window.world))
-    barrier()                                  # every rank's adds have landed
-    if window.world > 1:
-        dist.all_gather_into_tensor(dw_full, window.mine)
-    else:
-        dw_full.copy_(window.mine)
+class FusedWeightGradient:
+    """dW = sum over ranks of x_r^T . dy_r for a Linear layer whose batch rows are
+    split over the ranks, with the reduce-scatter inside the GEMM kernel:
+
+    start()  zeroes the window of the next step, runs ``sb200_gemm_reduce_scatter``
+             (every rank's tiles are added into the owning rank's window over
+             NVLink from the epilogue), a one-element all-reduce as the barrier
+             "all adds have landed", then on a second stream pulls every owner's
+             reduced row block into ``dw_full`` with copy-engine transfers and
+             all-reduces the bias gradient;
+    wait()   makes the current stream wait for that second stream.
+
+    Work that needs no exchange (the dx GEMM) goes between the two calls.  Three
+    windows rotate: a window is zeroed two steps after its use, when every peer
+    has finished copying it out (each rank passed a barrier after its copies),
+    and one step before its next use, so that every rank has zeroed it before the
+    barrier that precedes the first add.  ``ok`` is False on every rank when any
+    rank could not map a peer's window (callers fall back together)."""
+
+    def __init__(self, ctx, n_in: int, n_out: int, rank: int = 0, world: int = 1, group=None):
+        self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
+        self.n_in, self.n_out = n_in, n_out
+        self.windows = [PeerWindow(ctx, n_in // world, n_out, rank, world, group) for _ in range(3)]
+        self.ok = all(w.ok for w in self.windows)
+        dev = torch.device("cuda", ctx.device)
+        self.side = torch.cuda.Stream(dev)
+        self.done = torch.cuda.Event()
+        self.tick = torch.zeros(1, device=dev)
+        self.turn = 0
+        for w in self.windows:
+            w.mine.zero_()
+        self._barrier()
+
+    def _barrier(self) -> None:
+        if self.world > 1:
+            dist.all_reduce(self.tick, group=self.group)
+
+    def start(self, x: torch.Tensor, dy: torch.Tensor, dw_full: torch.Tensor, db: torch.Tensor,
+              mode: int = 0) -> None:
+        from . import ops
+        cur, nxt = self.windows[self.turn % 3], self.windows[(self.turn + 1) % 3]
+        self.turn += 1
+        dev = torch.device("cuda", self.ctx.device)
+        main = torch.cuda.current_stream(dev)
+        nxt.mine.zero_()
+        # dB: 1 / (global batch), so that the SUM over ranks below is the mean over the batch
+        ops.gemm_reduce_scatter(self.ctx, x, dy, cur.pointers, self.n_out, trans_a=True, mode=mode,
+                                colsum_out=db, colsum_scale=1.0 / (x.shape[0] * self.world))
+        self._barrier()
+        self.done.record(main)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(self.done)
+            rows = self.n_in // self.world
+            for o in range(self.world):
+                dw_full[o * rows:(o + 1) * rows].copy_(cur.views[o], non_blocking=True)
+            if self.world > 1:
+                dist.all_reduce(db, group=self.group)
+
+    def wait(self) -> None:
+        torch.cuda.current_stream(torch.device("cuda", self.ctx.device)).wait_stream(self.side)
+
+    def close(self) -> None:
+        for w in self.windows:
+            w.close(self.group)

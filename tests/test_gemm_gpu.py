@@ -427,19 +427,23 @@ def test_reduce_scatter_argument_validation(ctx):
 
 
 def test_peer_window_single_rank_linear_backward(ctx):
-    """world == 1: the window is this GPU's own buffer; dW and dB of the fused
-    route equal the plain GEMM with its fused column sum."""
+    """world == 1: the windows are this GPU's own buffers; over five steps (the
+    three windows come round again) dW and dB of the fused route equal the plain
+    GEMM with its fused column sum."""
     from sapphire_b200 import runner
     rng = np.random.default_rng(5)
-    x = dev(rng.standard_normal((384, 256)).astype(np.float32))
-    dy = dev(rng.standard_normal((384, 192)).astype(np.float32))
-    window = runner.PeerWindow(ctx, 256, 192)
+    reducer = runner.FusedWeightGradient(ctx, 256, 192)
+    assert reducer.ok
     dw = torch.empty(256, 192, device=DEV)
     db = torch.empty(192, device=DEV)
-    for _ in range(2):
-        runner.linear_backward_fused(ctx, window, x, dy, dw, db, lambda: None, mode=L.MODE_TF32X3)
-    want_db = torch.empty(192, device=DEV)
-    want = ops.gemm(ctx, x, dy, trans_a=True, mode=L.MODE_TF32X3, colsum_out=want_db, colsum_scale=1.0 / 384)
-    assert rel_fro(dw.cpu().numpy(), want.cpu().numpy()) <= 1e-6
-    assert torch.equal(db, want_db)
-    window.close()
+    for _ in range(5):
+        x = dev(rng.standard_normal((384, 256)).astype(np.float32))
+        dy = dev(rng.standard_normal((384, 192)).astype(np.float32))
+        reducer.start(x, dy, dw, db, mode=L.MODE_TF32X3)
+        reducer.wait()
+        want_db = torch.empty(192, device=DEV)
+        want = ops.gemm(ctx, x, dy, trans_a=True, mode=L.MODE_TF32X3, colsum_out=want_db,
+                        colsum_scale=1.0 / 384)
+        assert rel_fro(dw.cpu().numpy(), want.cpu().numpy()) <= 1e-6
+        assert torch.equal(db, want_db)
+    reducer.close()
