@@ -263,15 +263,16 @@ tiny_rows_kernel(Csr A, Csr B, Work w, const uint32_t* __restrict__ rowC,
 
 // ------------------------------------------------------- CTA-per-row path
 constexpr uint32_t SHORT_ROW = 8;        // rows of B up to this length are walked by one thread
-constexpr uint32_t SUB = 8;              // lanes that share one descriptor (a piece of a row of B)
+constexpr uint32_t SUB = 16;             // lanes that share one descriptor (a piece of a row of B)
 constexpr uint32_t TILE_WORDS = 2048;    // bitmap words covered by one block-wide prefix step
 constexpr int PIECES_IN_FLIGHT = 4;      // descriptors a lane group loads before it accumulates
 
 // Shared-memory work lists of the product walk.  A nonzero (i,k) of A whose
 // row of B has SHORT_ROW < len < THREADS entries is cut into pieces of SUB
 // entries; every piece gets a descriptor and SUB adjacent lanes take one piece
-// at a time, so that a warp works on four pieces with (nearly) all lanes busy
-// whatever the row lengths are.  Rows of THREADS or more entries are listed in
+// at a time, so that a warp works on two pieces with most lanes busy whatever
+// the row lengths are (16 and 8 lanes per piece time alike on uniform rows, 16
+// is a few per cent ahead on power-law rows: half the descriptors).  Rows of THREADS or more entries are listed in
 // the same arrays (used before the descriptors) and walked by the whole CTA.
 template <int THREADS>
 struct WalkLists {
