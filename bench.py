@@ -427,7 +427,7 @@ def main():
                 "gpu_launches": launches}
 
     def bench_mlp(steps, warmup):
-        """BASELINE config 2: 784-512-256-10 MLP, global batch 64 split over the
+        """The 784-512-256-10 MLP training step, global batch 64 split over the
         ranks (strong scaling), one flat gradient allreduce per step.  lr 1e-4: at
         0.01 Sapphire's un-normalised gradients leave the finite range by step 3."""
         from sapphire_b200 import mlp as M

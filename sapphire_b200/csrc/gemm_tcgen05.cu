@@ -284,7 +284,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             if (p.rows_per_owner) {
                 // reduce-scatter: the tile lies inside one owner's row block; shift that
                 // owner's buffer so that absolute row numbers index it
-                const int o = m0 / p.rows_per_owner;
+                // (a tile wholly beyond M maps past the last owner: clamp, its rows are masked)
+                const int o = min(m0 / p.rows_per_owner, MAX_OWNERS - 1);
                 dmat = p.owner[o] - static_cast<long long>(o) * p.rows_per_owner * p.ldd;
             }
             const float* cmat = p.C ? p.C + b * p.strideC : nullptr;
