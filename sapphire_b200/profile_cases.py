@@ -1,7 +1,7 @@
 """Small, self-terminating cases of each kernel for `ncu` captures.
 
     python -m sapphire_b200.profile_cases dense_tf32 | dense_tf32x3 | dense_tn | spgemm | spgemm_zipf
-                                          | im2col | mlp
+                                          | im2col | mlp | gemm_rs
 
 Each case touches more than the 126 MB L2 but holds at most ~1.5 GB on the
 device and launches every kernel a handful of times, so that a full-set
@@ -77,6 +77,28 @@ def mlp_step() -> None:
     print("mlp case done", float(loss[0]))
 
 
+def gemm_reduce_scatter() -> None:
+    """dW = x^T.dy for 8192 x 4096 x 4096 twice: a plain GEMM with its fused column
+    sum, then the reduce-scatter variant with eight owners that all live on this
+    GPU (the epilogue is the same code whoever owns the buffers)."""
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    x = torch.randn(8192, 4096, device=dev, generator=g) * 0.02
+    dy = torch.randn(8192, 4096, device=dev, generator=g) * 0.02
+    dw = torch.empty(4096, 4096, device=dev)
+    db = torch.empty(4096, device=dev)
+    owners = [torch.zeros(512, 4096, device=dev) for _ in range(8)]
+    for _ in range(3):
+        ops.gemm(ctx, x, dy, None, dw, trans_a=True, colsum_out=db, colsum_scale=1.0 / 8192)
+    for _ in range(3):
+        ops.gemm_reduce_scatter(ctx, x, dy, [t.data_ptr() for t in owners], 4096, trans_a=True,
+                                colsum_out=db, colsum_scale=1.0 / 8192)
+    torch.cuda.synchronize()
+    print("gemm_rs case done", float(dw[0, 0]), float(owners[0][0, 0]) / 3)
+
+
 def main() -> None:
     case = sys.argv[1] if len(sys.argv) > 1 else "dense_tf32"
     if case == "dense_tf32":
@@ -95,6 +117,8 @@ def main() -> None:
         im2col()
     elif case == "mlp":
         mlp_step()
+    elif case == "gemm_rs":
+        gemm_reduce_scatter()
     else:
         raise SystemExit(f"unknown case {case}")
 
