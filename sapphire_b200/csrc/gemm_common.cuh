@@ -63,6 +63,21 @@ __device__ __forceinline__ float post_op_value(float o, int relu, bool gated, fl
     return o;
 }
 
+// Tile r of a batch -> (row tile, column tile).  Tiles are taken in panels of
+// `panel` row tiles, column tiles fastest inside a panel: the ~150 tiles in
+// flight at any time then cover a near-square patch of the output (panel x ~9
+// tiles), which needs fewer distinct rows of A and columns of B per k-slice --
+// fewer bytes from HBM per wave -- than a full-height stripe a few columns wide.
+__device__ __forceinline__ void tile_coords(int r, int tiles_m, int tiles_n, int panel, int& tm, int& tn)
+{
+    const int per_panel = panel * tiles_n;
+    const int first = (r / per_panel) * panel;                  // first row tile of this panel
+    const int height = min(panel, tiles_m - first);
+    const int within = r - (r / per_panel) * per_panel;
+    tn = within / height;
+    tm = first + within % height;
+}
+
 struct Abort {
     volatile int* flag;
     unsigned* status;

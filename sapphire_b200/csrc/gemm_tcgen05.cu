@@ -29,6 +29,8 @@ using namespace gemm;
 
 namespace {
 
+constexpr int TILE_PANEL = 16;          // row tiles (of 128 rows) per panel of the tile order
+
 template <int BLOCK_N, int STAGES, bool SPLIT>
 struct SmemLayout {
     static constexpr int B_TILE_BYTES = BLOCK_N * BLOCK_K * 4;
@@ -135,8 +137,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                 const int b = static_cast<int>(t / tiles_per_batch);
                 const int r = static_cast<int>(t % tiles_per_batch);
-                const int m0 = (r % p.tiles_m) * BLOCK_M;
-                const int n0 = (r / p.tiles_m) * BLOCK_N;
+                int tm, tn;
+                tile_coords(r, p.tiles_m, p.tiles_n, TILE_PANEL, tm, tn);
+                const int m0 = tm * BLOCK_M;
+                const int n0 = tn * BLOCK_N;
                 const int ba = p.a_batched ? b : 0;
                 const int bb = p.b_batched ? b : 0;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
@@ -277,8 +281,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
         for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
             const int b = static_cast<int>(t / tiles_per_batch);
             const int r = static_cast<int>(t % tiles_per_batch);
-            const int m0 = (r % p.tiles_m) * BLOCK_M;
-            const int n0 = (r / p.tiles_m) * BLOCK_N;
+            int tm, tn;
+            tile_coords(r, p.tiles_m, p.tiles_n, TILE_PANEL, tm, tn);
+            const int m0 = tm * BLOCK_M;
+            const int n0 = tn * BLOCK_N;
             const int row = m0 + q * 32 + lane;
             float* dmat = p.D + b * p.strideD;
             if (p.rows_per_owner) {
@@ -449,8 +455,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             bool ok = true;
             for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                 const int r = static_cast<int>(t % tiles_per_batch);
-                const bool mine = (t / tiles_per_batch == 0) && (r % p.tiles_m == 0);
-                const int n0 = (r / p.tiles_m) * BLOCK_N;
+                int tm, tn;
+                tile_coords(r, p.tiles_m, p.tiles_n, TILE_PANEL, tm, tn);
+                const bool mine = (t / tiles_per_batch == 0) && (tm == 0);
+                const int n0 = tn * BLOCK_N;
                 float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!(ok = wait_bar(&full_bar[s], ph, ab, FAULT_SPLIT_WAIT)))

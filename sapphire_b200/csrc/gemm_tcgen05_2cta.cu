@@ -32,6 +32,7 @@ constexpr int PAIR_M = 256;             // rows per pair tile (128 per CTA)
 constexpr int PAIR_N = 256;             // columns per pair tile (128 loaded per CTA)
 constexpr int HALF_N = PAIR_N / 2;
 constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_PANEL = 8;           // row tiles (of 256 rows) per panel of the tile order
 constexpr int B_HALF_BYTES = HALF_N * BLOCK_K * 4;              // 16 KB
 constexpr int PAIR_STAGE_BYTES = A_TILE_BYTES + B_HALF_BYTES;   // 32 KB
 constexpr int PAIR_TILES_BYTES = PAIR_STAGE_BYTES * PAIR_STAGES;
@@ -120,8 +121,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
             for (long long t = pair_id; ok && t < p.total_tiles; t += n_pairs) {
                 const int b = static_cast<int>(t / tiles_per_batch);
                 const int r = static_cast<int>(t % tiles_per_batch);
-                const int m0 = (r % p.tiles_m) * PAIR_M + static_cast<int>(rank) * BLOCK_M;
-                const int n0 = (r / p.tiles_m) * PAIR_N + static_cast<int>(rank) * HALF_N;
+                int tm, tn;
+                tile_coords(r, p.tiles_m, p.tiles_n, PAIR_PANEL, tm, tn);
+                const int m0 = tm * PAIR_M + static_cast<int>(rank) * BLOCK_M;
+                const int n0 = tn * PAIR_N + static_cast<int>(rank) * HALF_N;
                 const int ba = p.a_batched ? b : 0;
                 const int bb = p.b_batched ? b : 0;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
@@ -227,8 +230,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
         for (long long t = pair_id; ok && t < p.total_tiles; t += n_pairs) {
             const int b = static_cast<int>(t / tiles_per_batch);
             const int r = static_cast<int>(t % tiles_per_batch);
-            const int m0 = (r % p.tiles_m) * PAIR_M + static_cast<int>(rank) * BLOCK_M;
-            const int n0 = (r / p.tiles_m) * PAIR_N;
+            int tm, tn;
+            tile_coords(r, p.tiles_m, p.tiles_n, PAIR_PANEL, tm, tn);
+            const int m0 = tm * PAIR_M + static_cast<int>(rank) * BLOCK_M;
+            const int n0 = tn * PAIR_N;
             const int row = m0 + q * 32 + lane;
             float* dmat = p.D + b * p.strideD;
             if (p.rows_per_owner) {
