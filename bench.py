@@ -360,11 +360,16 @@ def main():
         nnzC = res["C"].nnz
         prods = int(W.csr_products(rA, cA, rB).sum())
         nbytes = 8 * (cA.size + cB.size + nnzC) + 4 * 3 * (M + 1)
+        # dram read + written by the two row kernels of one call, from the ncu capture of the
+        # half-size uniform case (profiles/spgemm_cta_rows_32768x65536.md: symbolic 41 + 217 MB,
+        # numeric 652 + 1034 MB), scaled by the output size; no capture of the Zipf case
+        traffic = (258.0e6 + 1686.0e6) * nnzC / 136.2e6 if dist_name == "poisson" else None
         return {"workload": spgemm_workload_text(dist_name), "ms_per_step": ms,
                 "gflops_per_gpu": 2.0 * prods / ms / 1e6, "nnzC": nnzC, "products": prods,
                 "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6,
                              "peak": pk["hbm_gbs"], "unit": "GB/s",
-                             "frac": nbytes / ms / 1e6 / pk["hbm_gbs"], "traffic": None,
+                             "frac": nbytes / ms / 1e6 / pk["hbm_gbs"], "traffic": traffic,
+                             "traffic_source": "ncu, scaled from the 32768-row capture" if traffic else None,
                              "peak_source": pk["source"]},
                 "gpu_launches": launches}
 
