@@ -194,6 +194,15 @@ __device__ __forceinline__ void load_c_chunk(CChunk& cc, const float* C, long lo
 {
     const int lane = threadIdx.x & 31;
     const int sub = lane >> 3, col = col0 + (lane & 7) * 4;
+    if (C && row0 + 32 <= M && col0 + 32 <= N) {                 // inside the matrix: no predicates
+        const float* cptr = C + static_cast<long long>(row0 + sub) * ldc + col;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            cc.v[i] = *reinterpret_cast<const float4*>(cptr);
+            cptr += 4 * ldc;
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int grow = row0 + i * 4 + sub;
@@ -221,6 +230,29 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
     const bool post = e.relu || e.mask;
     const int sub = lane >> 3, cq = (lane & 7) * 4;
     const int col = col0 + cq;
+    // The common case by far -- a chunk inside the matrix, nothing but (C +) acc
+    // to store -- without a predicate or an address multiplication per element:
+    // the full path below costs ~500 instructions per chunk, and with one warp
+    // per 32 rows of a 256-column tile that, not memory, bounds short-k problems.
+    if (!bias && !post && !e.reduce && row0 + 32 <= M && col0 + 32 <= N) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + j) =
+                make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                            __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+        __syncwarp();
+        float* dptr = D + static_cast<long long>(row0 + sub) * ldd + col;
+        const float* sptr = stage + sub * EPI_STAGE_LD + cq;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 a = *reinterpret_cast<const float4*>(sptr + i * 4 * EPI_STAGE_LD);
+            *reinterpret_cast<float4*>(dptr) =
+                make_float4(cc.v[i].x + a.x, cc.v[i].y + a.y, cc.v[i].z + a.z, cc.v[i].w + a.w);
+            dptr += 4 * ldd;
+        }
+        __syncwarp();
+        return;
+    }
     // the gate values of this lane's float4s are fetched four rows at a time, the
     // four loads in flight together (fetched one by one where they are needed
     // they would cost a memory round trip each)

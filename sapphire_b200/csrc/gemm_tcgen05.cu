@@ -307,7 +307,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                     break;
                 ptx::tc_fence_after_sync();
                 CChunk c_now, c_next;
-                if (vec_ok)
+                if (vec_ok)                                    // zeros when there is no C
                     load_c_chunk(c_next, cmat, p.ldc, m0 + q * 32, n0, p.M, p.N);
 #pragma unroll 1
                 for (int c = 0; c < BLOCK_N / 32; ++c) {
@@ -316,7 +316,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                         break;                             // uniform across the warp
                     uint32_t v[32];
                     ptx::tmem_ld_32x32(lane_base + static_cast<uint32_t>(acc * BLOCK_N + c * 32), v);
-                    if (vec_ok) {
+                    if (vec_ok && (cmat || c == 0)) {
                         c_now = c_next;
                         if (c + 1 < BLOCK_N / 32 && col0 + 32 < p.N)     // next chunk's C, ahead of the stores
                             load_c_chunk(c_next, cmat, p.ldc, m0 + q * 32, col0 + 32, p.M, p.N);

@@ -1,7 +1,7 @@
 """Small, self-terminating cases of each kernel for `ncu` captures.
 
     python -m sapphire_b200.profile_cases dense_tf32 | dense_tf32x3 | dense_tn | spgemm | spgemm_zipf
-                                          | im2col | mlp | gemm_rs
+                                          | im2col | mlp | gemm_rs | dense_epilogue
 
 Each case touches more than the 126 MB L2 but holds at most ~1.5 GB on the
 device and launches every kernel a handful of times, so that a full-set
@@ -18,13 +18,16 @@ from . import ops
 from . import workloads as W
 
 
-def dense(mode: int, ta: bool = False, tb: bool = False, n: int = 2048, batch: int = 4) -> None:
+def dense(mode: int, ta: bool = False, tb: bool = False, n: int = 2048, batch: int = 4, k: int = 0) -> None:
+    """k: inner dimension when it differs from n (k = 32 is one k-block per tile:
+    the kernel is then all epilogue)."""
     dev = torch.device("cuda:0")
     ctx = ops.Context(0)
     g = torch.Generator(device=dev)
     g.manual_seed(0)
-    a = torch.randn(batch, n, n, device=dev, generator=g)
-    b = torch.randn(batch, n, n, device=dev, generator=g)
+    k = k or n
+    a = torch.randn(batch, k, n, device=dev, generator=g) if ta else torch.randn(batch, n, k, device=dev, generator=g)
+    b = torch.randn(batch, n, k, device=dev, generator=g) if tb else torch.randn(batch, k, n, device=dev, generator=g)
     c = torch.rand(batch, n, n, device=dev, generator=g)
     out = torch.empty_like(c)
     for _ in range(3):
@@ -119,6 +122,8 @@ def main() -> None:
         mlp_step()
     elif case == "gemm_rs":
         gemm_reduce_scatter()
+    elif case == "dense_epilogue":
+        dense(L.MODE_TF32, n=8192, batch=1, k=32)
     else:
         raise SystemExit(f"unknown case {case}")
 
