@@ -231,23 +231,34 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
     const int sub = lane >> 3, cq = (lane & 7) * 4;
     const int col = col0 + cq;
     // The common case by far -- a chunk inside the matrix, nothing but (C +) acc
-    // to store -- without a predicate or an address multiplication per element:
+    // (+ bias, ReLU) to store -- without a predicate or an address multiplication per element:
     // the full path below costs ~500 instructions per chunk, and with one warp
     // per 32 rows of a 256-column tile that, not memory, bounds short-k problems.
-    if (!bias && !post && !e.reduce && row0 + 32 <= M && col0 + 32 <= N) {
+    if (!e.mask && !e.reduce && row0 + 32 <= M && col0 + 32 <= N) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
             *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + j) =
                 make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
                             __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
         __syncwarp();
+        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias) bv = make_float4(__ldg(bias + col), __ldg(bias + col + 1), __ldg(bias + col + 2),
+                                   __ldg(bias + col + 3));
         float* dptr = D + static_cast<long long>(row0 + sub) * ldd + col;
         const float* sptr = stage + sub * EPI_STAGE_LD + cq;
+        const bool relu = e.relu != 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float4 a = *reinterpret_cast<const float4*>(sptr + i * 4 * EPI_STAGE_LD);
-            *reinterpret_cast<float4*>(dptr) =
-                make_float4(cc.v[i].x + a.x, cc.v[i].y + a.y, cc.v[i].z + a.z, cc.v[i].w + a.w);
+            float4 o = make_float4((cc.v[i].x + bv.x) + a.x, (cc.v[i].y + bv.y) + a.y,
+                                   (cc.v[i].z + bv.z) + a.z, (cc.v[i].w + bv.w) + a.w);
+            if (relu) {
+                o.x = o.x > 0.0f ? o.x : 0.0f;
+                o.y = o.y > 0.0f ? o.y : 0.0f;
+                o.z = o.z > 0.0f ? o.z : 0.0f;
+                o.w = o.w > 0.0f ? o.w : 0.0f;
+            }
+            *reinterpret_cast<float4*>(dptr) = o;
             dptr += 4 * ldd;
         }
         __syncwarp();
