@@ -230,11 +230,21 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
     const bool post = e.relu || e.mask;
     const int sub = lane >> 3, cq = (lane & 7) * 4;
     const int col = col0 + cq;
-    // The common case by far -- a chunk inside the matrix, nothing but (C +) acc
-    // (+ bias, ReLU) to store -- without a predicate or an address multiplication per element:
+    // The common case by far -- a chunk inside the matrix -- without a predicate or
+    // an address multiplication per element:
     // the full path below costs ~500 instructions per chunk, and with one warp
     // per 32 rows of a 256-column tile that, not memory, bounds short-k problems.
-    if (!e.mask && !e.reduce && row0 + 32 <= M && col0 + 32 <= N) {
+    const bool gate_aligned = !e.mask || (((e.ldm & 3) == 0) && ((reinterpret_cast<uintptr_t>(e.mask) & 15) == 0));
+    if (gate_aligned && row0 + 32 <= M && col0 + 32 <= N) {
+        // gate values: four 16-byte loads in flight at a time, issued before the
+        // shared-memory round trip
+        float4 g4[4];
+        const float* gptr = e.mask ? e.mask + static_cast<long long>(row0 + sub) * e.ldm + col : nullptr;
+        if (gptr) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                g4[k] = __ldg(reinterpret_cast<const float4*>(gptr + static_cast<long long>(k) * 4 * e.ldm));
+        }
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
             *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + j) =
@@ -249,6 +259,11 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
         const bool relu = e.relu != 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+            if (i == 4 && gptr) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    g4[k] = __ldg(reinterpret_cast<const float4*>(gptr + static_cast<long long>(4 + k) * 4 * e.ldm));
+            }
             const float4 a = *reinterpret_cast<const float4*>(sptr + i * 4 * EPI_STAGE_LD);
             float4 o = make_float4((cc.v[i].x + bv.x) + a.x, (cc.v[i].y + bv.y) + a.y,
                                    (cc.v[i].z + bv.z) + a.z, (cc.v[i].w + bv.w) + a.w);
@@ -258,7 +273,17 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
                 o.z = o.z > 0.0f ? o.z : 0.0f;
                 o.w = o.w > 0.0f ? o.w : 0.0f;
             }
-            *reinterpret_cast<float4*>(dptr) = o;
+            if (gptr) {
+                const float4 g = g4[i & 3];
+                o.x = __fadd_rn(0.0f, g.x > 0.0f ? o.x : 0.0f);
+                o.y = __fadd_rn(0.0f, g.y > 0.0f ? o.y : 0.0f);
+                o.z = __fadd_rn(0.0f, g.z > 0.0f ? o.z : 0.0f);
+                o.w = __fadd_rn(0.0f, g.w > 0.0f ? o.w : 0.0f);
+            }
+            if (e.reduce)
+                ptx::red_add_sys_v4(dptr, o);
+            else
+                *reinterpret_cast<float4*>(dptr) = o;
             dptr += 4 * ldd;
         }
         __syncwarp();
