@@ -82,3 +82,9 @@ def test_conv_geometry_validation(ctx):
         geom = L.ConvGeometry(**g)
         rc = L.lib().sb200_im2col(ctx.handle, x.data_ptr(), x.data_ptr(), C.byref(geom), 0.0, None)
         assert rc == L.ERR_INVALID_ARG, change
+
+
+def test_empty_batch_is_a_no_op(ctx):
+    x = torch.zeros(0, 3, 8, 8, device=DEV)
+    cols = conv.im2col(ctx, x, 3, 3, (1, 1), (1, 1), (1, 1))
+    assert cols.shape == (0, 27, 64)

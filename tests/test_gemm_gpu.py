@@ -447,3 +447,17 @@ def test_peer_window_single_rank_linear_backward(ctx):
         assert rel_fro(dw.cpu().numpy(), want.cpu().numpy()) <= 1e-6
         assert torch.equal(db, want_db)
     reducer.close()
+
+
+def test_epilogue_steps_with_k_zero(ctx):
+    """K == 0: D = gate(relu(C + bias)), no product."""
+    rng = np.random.default_rng(9)
+    c = dev(rng.standard_normal((40, 24)).astype(np.float32))
+    bias = dev(rng.standard_normal(24).astype(np.float32))
+    gate = dev(rng.standard_normal((40, 24)).astype(np.float32))
+    a = torch.zeros(40, 0, device=DEV)
+    b = torch.zeros(0, 24, device=DEV)
+    got = ops.gemm(ctx, a, b, c, bias=bias, relu=True, relu_gate=gate)
+    base = c + bias
+    want = torch.where(gate > 0, torch.where(base > 0, base, torch.zeros_like(base)), torch.zeros_like(base)) + 0.0
+    assert torch.equal(got, want)
