@@ -121,6 +121,11 @@ int sb200_check_device_status(sb200_ctx* ctx, sb200_stream stream);
  * bias-gradient Gemm dB = ones[1,B].dy followed by Scale(1/B)
  * (LinearBackward.cpp:93-97) when this call is dW = x^T.dy.  Requires batch == 1.
  *
+ * A single TF32 product with K >= 2048 and so few output tiles that most SMs
+ * would idle has its k range cut into slices that run concurrently and add into
+ * D; the adds arrive in no fixed order, so the last bits of such a result can
+ * differ between runs (the 3xTF32 mode and every other shape are reproducible).
+ *
  * path: SB200_PATH_AUTO picks the tcgen05 kernel when the operands satisfy
  * TMA's alignment rules (16-byte aligned base pointers, ld and batch strides
  * multiples of 4 elements) and the SIMT kernel otherwise; the other two

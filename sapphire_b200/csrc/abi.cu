@@ -147,6 +147,49 @@ extern "C" int sb200_check_device_status(sb200_ctx* ctx, sb200_stream stream_)
     return SB200_ERR_DEVICE_TIMEOUT;
 }
 
+namespace {
+
+// Long-k products with few output tiles (say 256 x 256 x 8192: four tiles, each a
+// serial walk over 256 k-blocks while most SMs idle): the k range is cut into
+// slices that run as the batches of one launch and add their partial products
+// into D through the reduction epilogue.  Returns the number of slices, 1 for
+// "do not split".  fp32 adds in arrival order: the last bits of such a product
+// can differ between runs.
+int split_k_slices(const sb200_ctx* ctx, const GemmArgs& g, bool has_colsum)
+{
+    if (g.mode != SB200_MODE_TF32 || g.batch != 1 || g.relu || g.mask || g.bias || has_colsum)
+        return 1;
+    if (g.K % 32)
+        return 1;
+    const long long kb = g.K / 32;
+    const long long tiles = ((g.M + 127) / 128) * ((g.N + 127) / 128);
+    if (kb < 64 || tiles * 4 > ctx->sm_count)
+        return 1;
+    long long s = ctx->sm_count / tiles;
+    if (s > kb / 16) s = kb / 16;
+    if (s > 32) s = 32;
+    while (s > 1 && kb % s) --s;                     // equal slices of whole k-blocks
+    return static_cast<int>(s);
+}
+
+// D <- C (or 0) ahead of a split-k launch, which only adds.
+int preset_output(const GemmArgs& g, cudaStream_t stream)
+{
+    const size_t row_bytes = static_cast<size_t>(g.N) * 4;
+    cudaError_t e = cudaSuccess;
+    if (g.C == g.D)
+        return SB200_OK;
+    if (g.C)
+        e = cudaMemcpy2DAsync(g.D, static_cast<size_t>(g.ldd) * 4, g.C, static_cast<size_t>(g.ldc) * 4,
+                              row_bytes, static_cast<size_t>(g.M), cudaMemcpyDeviceToDevice, stream);
+    else
+        e = cudaMemset2DAsync(g.D, static_cast<size_t>(g.ldd) * 4, 0, row_bytes, static_cast<size_t>(g.M),
+                              stream);
+    return e == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+}
+
+}  // namespace
+
 extern "C" int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA, int transB,
                                   int64_t M, int64_t N, int64_t K,
                                   const float* A, int64_t lda, int64_t strideA,
@@ -243,6 +286,19 @@ extern "C" int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int tra
         fused_colsum = colsum_out && mode == SB200_MODE_TF32 && K > 0;
         if (fused_colsum)
             g.colsum_out = colsum_out;
+        const int slices = split_k_slices(ctx, g, colsum_out != nullptr);
+        if (slices > 1) {
+            if ((rc = preset_output(g, stream)))
+                return rc;
+            const int64_t ks = K / slices;
+            g.batch = slices;
+            g.K = ks;
+            g.strideA = g.transA ? ks * lda : ks;          // slice s starts ks along k
+            g.strideB = g.transB ? ks : ks * ldb;
+            g.C = nullptr;
+            g.owner[0] = D;                                // every tile adds into D itself
+            g.rows_per_owner = int64_t(1) << 30;
+        }
         rc = launch_gemm_tcgen05(ctx, g, stream);
         ctx->last_path = SB200_PATH_TCGEN05;
     } else {

@@ -461,3 +461,28 @@ def test_epilogue_steps_with_k_zero(ctx):
     base = c + bias
     want = torch.where(gate > 0, torch.where(base > 0, base, torch.zeros_like(base)), torch.zeros_like(base)) + 0.0
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (0, 1)])
+@pytest.mark.parametrize("cmode", ["none", "separate", "in_place"])
+def test_long_k_few_tiles_split_k(ctx, ta, tb, cmode):
+    """256 x 192 x 8192: four output tiles, so the k range is cut into concurrent
+    slices that add into D.  Checked against the fp64 product at the TF32 bound."""
+    rng = np.random.default_rng(31 + ta + 2 * tb)
+    M, N, K = 256, 192, 8192
+    a = rng.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    b = rng.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    c = rng.standard_normal((M, N)).astype(np.float32)
+    want = (a.T if ta else a).astype(np.float64) @ (b.T if tb else b).astype(np.float64)
+    if cmode != "none":
+        want = want + c
+    if cmode == "none":
+        got = ops.gemm(ctx, dev(a), dev(b), trans_a=bool(ta), trans_b=bool(tb))
+    elif cmode == "separate":
+        got = ops.gemm(ctx, dev(a), dev(b), dev(c), trans_a=bool(ta), trans_b=bool(tb))
+    else:
+        y = dev(c)
+        got = ops.gemm(ctx, dev(a), dev(b), y, y, trans_a=bool(ta), trans_b=bool(tb))
+    assert ctx.last_path() == L.PATH_TCGEN05
+    assert rel_fro(got.cpu().numpy(), want) <= 2e-3
+    ctx.check_device_status()
