@@ -125,6 +125,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only shared memory, TMEM and kernel parameters: it may
+    // overlap the tail of the previous kernel in the stream (small problems are a
+    // chain of such prologues).  From here on global memory is read and written.
+    ptx::griddep_launch_dependents();
+    ptx::griddep_wait();
 
     const long long tiles_per_batch = static_cast<long long>(p.tiles_m) * p.tiles_n;
 
@@ -558,10 +563,21 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.colsum_scale = g.colsum_scale;
 
     const long long grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
-    kern<<<static_cast<unsigned>(grid), (SPLIT || COLSUM) ? 320 : 192, L::TOTAL, stream>>>(mapA, mapB,
-                                                                                          p);
+    // programmatic stream serialization: the kernel's prologue may start while the
+    // previous kernel of the stream is finishing (see griddep_wait in the kernel)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3((SPLIT || COLSUM) ? 320 : 192);
+    cfg.dynamicSmemBytes = L::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, mapA, mapB, p);
     ctx->launches += 1;
-    return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+    return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? SB200_OK : SB200_ERR_CUDA;
 }
 
 template <int BLOCK_N, int STAGES, bool SPLIT, bool COLSUM>

@@ -344,6 +344,21 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, int a_mn_ma
            (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// ---- programmatic dependent launch: a kernel launched with the "programmatic
+// stream serialization" attribute may start while its predecessor in the stream
+// still runs; it must not touch global memory before griddep_wait(), which
+// returns once the predecessor has completed and its writes are visible.
+// griddep_launch_dependents() lets the successor of THIS kernel start early.
+__device__ __forceinline__ void griddep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void griddep_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- reductions into memory that may belong to another GPU (peer mapping):
 // fire-and-forget fp32 adds at system scope, performed at the owner's L2.
 __device__ __forceinline__ void red_add_sys(float* p, float v)
