@@ -220,75 +220,92 @@ __device__ __forceinline__ void load_c_chunk(CChunk& cc, const float* C, long lo
     }
 }
 
-__device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], float* stage,
-                                                      float* D, long long ldd, const CChunk& cc,
-                                                      const Epilogue& e, int row0, int col0, int M,
-                                                      int N)
+// A chunk that lies inside the matrix (the common case by far): no predicate and
+// no address multiplication per element.  The general version below costs ~500
+// instructions per chunk, and with one warp per 32 rows of a 256-column tile
+// that, not memory, bounded short-k problems.  The gate matrix, when there is
+// one, must have 16-byte aligned rows.  EXTRAS = false compiles the gate and the
+// reduction variant out: the plain store is the hot case and even their
+// never-taken branches cost it 15 % (registers, scheduling freedom).
+template <bool EXTRAS>
+__device__ __forceinline__ void store_chunk_interior(const uint32_t (&v)[32], float* stage, float* D, long long ldd,
+                                                    const CChunk& cc, const Epilogue& e, int row0, int col0,
+                                                    int M, int N)
 {
     const int lane = threadIdx.x & 31;
     const float* bias = e.bias;
-    const bool post = e.relu || e.mask;
     const int sub = lane >> 3, cq = (lane & 7) * 4;
     const int col = col0 + cq;
-    // The common case by far -- a chunk inside the matrix -- without a predicate or
-    // an address multiplication per element:
-    // the full path below costs ~500 instructions per chunk, and with one warp
-    // per 32 rows of a 256-column tile that, not memory, bounds short-k problems.
-    const bool gate_aligned = !e.mask || (((e.ldm & 3) == 0) && ((reinterpret_cast<uintptr_t>(e.mask) & 15) == 0));
-    if (gate_aligned && row0 + 32 <= M && col0 + 32 <= N) {
-        // gate values: four 16-byte loads in flight at a time, issued before the
-        // shared-memory round trip
-        float4 g4[4];
-        const float* gptr = e.mask ? e.mask + static_cast<long long>(row0 + sub) * e.ldm + col : nullptr;
-        if (gptr) {
+    // gate values: four 16-byte loads in flight at a time, issued before the
+    // shared-memory round trip
+    float4 g4[4];
+    const float* gptr = (EXTRAS && e.mask) ? e.mask + static_cast<long long>(row0 + sub) * e.ldm + col : nullptr;
+    if (gptr) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            g4[k] = __ldg(reinterpret_cast<const float4*>(gptr + static_cast<long long>(k) * 4 * e.ldm));
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + j) =
+            make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                        __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+    __syncwarp();
+    float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (bias) bv = make_float4(__ldg(bias + col), __ldg(bias + col + 1), __ldg(bias + col + 2),
+                               __ldg(bias + col + 3));
+    float* dptr = D + static_cast<long long>(row0 + sub) * ldd + col;
+    const float* sptr = stage + sub * EPI_STAGE_LD + cq;
+    const bool relu = e.relu != 0;
+    // all eight results first, the stores after them: the reduction variant is an
+    // asm statement with a memory clobber, inside this loop it would order every
+    // shared-memory read behind the previous store and serialise the chunk
+    float4 o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (i == 4 && gptr) {
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                g4[k] = __ldg(reinterpret_cast<const float4*>(gptr + static_cast<long long>(k) * 4 * e.ldm));
+                g4[k] = __ldg(reinterpret_cast<const float4*>(gptr + static_cast<long long>(4 + k) * 4 * e.ldm));
         }
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + j) =
-                make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                            __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-        __syncwarp();
-        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (bias) bv = make_float4(__ldg(bias + col), __ldg(bias + col + 1), __ldg(bias + col + 2),
-                                   __ldg(bias + col + 3));
-        float* dptr = D + static_cast<long long>(row0 + sub) * ldd + col;
-        const float* sptr = stage + sub * EPI_STAGE_LD + cq;
-        const bool relu = e.relu != 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (i == 4 && gptr) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    g4[k] = __ldg(reinterpret_cast<const float4*>(gptr + static_cast<long long>(4 + k) * 4 * e.ldm));
-            }
-            const float4 a = *reinterpret_cast<const float4*>(sptr + i * 4 * EPI_STAGE_LD);
-            float4 o = make_float4((cc.v[i].x + bv.x) + a.x, (cc.v[i].y + bv.y) + a.y,
-                                   (cc.v[i].z + bv.z) + a.z, (cc.v[i].w + bv.w) + a.w);
-            if (relu) {
-                o.x = o.x > 0.0f ? o.x : 0.0f;
-                o.y = o.y > 0.0f ? o.y : 0.0f;
-                o.z = o.z > 0.0f ? o.z : 0.0f;
-                o.w = o.w > 0.0f ? o.w : 0.0f;
-            }
-            if (gptr) {
-                const float4 g = g4[i & 3];
-                o.x = __fadd_rn(0.0f, g.x > 0.0f ? o.x : 0.0f);
-                o.y = __fadd_rn(0.0f, g.y > 0.0f ? o.y : 0.0f);
-                o.z = __fadd_rn(0.0f, g.z > 0.0f ? o.z : 0.0f);
-                o.w = __fadd_rn(0.0f, g.w > 0.0f ? o.w : 0.0f);
-            }
-            if (e.reduce)
-                ptx::red_add_sys_v4(dptr, o);
-            else
-                *reinterpret_cast<float4*>(dptr) = o;
-            dptr += 4 * ldd;
+        const float4 a = *reinterpret_cast<const float4*>(sptr + i * 4 * EPI_STAGE_LD);
+        o[i] = make_float4((cc.v[i].x + bv.x) + a.x, (cc.v[i].y + bv.y) + a.y,
+                           (cc.v[i].z + bv.z) + a.z, (cc.v[i].w + bv.w) + a.w);
+        if (relu) {
+            o[i].x = o[i].x > 0.0f ? o[i].x : 0.0f;
+            o[i].y = o[i].y > 0.0f ? o[i].y : 0.0f;
+            o[i].z = o[i].z > 0.0f ? o[i].z : 0.0f;
+            o[i].w = o[i].w > 0.0f ? o[i].w : 0.0f;
         }
-        __syncwarp();
-        return;
+        if (gptr) {
+            const float4 g = g4[i & 3];
+            o[i].x = __fadd_rn(0.0f, g.x > 0.0f ? o[i].x : 0.0f);
+            o[i].y = __fadd_rn(0.0f, g.y > 0.0f ? o[i].y : 0.0f);
+            o[i].z = __fadd_rn(0.0f, g.z > 0.0f ? o[i].z : 0.0f);
+            o[i].w = __fadd_rn(0.0f, g.w > 0.0f ? o[i].w : 0.0f);
+        }
     }
+    if (EXTRAS && e.reduce) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ptx::red_add_sys_v4(dptr + static_cast<long long>(i) * 4 * ldd, o[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(dptr + static_cast<long long>(i) * 4 * ldd) = o[i];
+    }
+    __syncwarp();
+}
+
+// Any chunk: every row and column is checked against M and N.
+__device__ __forceinline__ void store_chunk_edge(const uint32_t (&v)[32], float* stage, float* D, long long ldd,
+                                                    const CChunk& cc, const Epilogue& e, int row0, int col0,
+                                                    int M, int N)
+{
+    const int lane = threadIdx.x & 31;
+    const float* bias = e.bias;
+    const int sub = lane >> 3, cq = (lane & 7) * 4;
+    const int col = col0 + cq;
+    const bool post = e.relu || e.mask;
     // the gate values of this lane's float4s are fetched four rows at a time, the
     // four loads in flight together (fetched one by one where they are needed
     // they would cost a memory round trip each)
@@ -364,6 +381,21 @@ __device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], f
         }
     }
     __syncwarp();
+}
+
+__device__ __forceinline__ void store_chunk_coalesced(const uint32_t (&v)[32], float* stage, float* D, long long ldd,
+                                                    const CChunk& cc, const Epilogue& e, int row0, int col0,
+                                                    int M, int N)
+{
+    const bool gate_aligned =
+        !e.mask || (((e.ldm & 3) == 0) && ((reinterpret_cast<uintptr_t>(e.mask) & 15) == 0));
+    if (gate_aligned && row0 + 32 <= M && col0 + 32 <= N) {
+        if (e.mask || e.reduce)
+            store_chunk_interior<true>(v, stage, D, ldd, cc, e, row0, col0, M, N);
+        else
+            store_chunk_interior<false>(v, stage, D, ldd, cc, e, row0, col0, M, N);
+    } else
+        store_chunk_edge(v, stage, D, ldd, cc, e, row0, col0, M, N);
 }
 
 // ---------------------------------------------------------------- column sums
