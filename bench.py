@@ -496,10 +496,10 @@ def main():
                        "l2": "inputs (3 x %d MiB) larger than the 126 MB L2" % (BATCH * n * n * 4 >> 20)},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": tf32_peak,
                          "unit": "TFLOP/s", "frac": per_gpu / tf32_peak,
-                         # dram read+write of one launch: 276.0 MB measured by ncu on the
+                         # dram read+write of one launch: 280.8 MB measured by ncu on the
                          # 4 x 2048^3 case (profiles/gemm_tcgen05_tf32_4x2048.md), scaled by
                          # the matrix bytes of this launch (traffic == every matrix once)
-                         "traffic": 276.0e6 * (BATCH * n * n) / (4 * 2048 * 2048),
+                         "traffic": 280.8e6 * (BATCH * n * n) / (4 * 2048 * 2048),
                          "traffic_source": "ncu, scaled from the 4x2048^3 capture",
                          "peak_source": f"{pk['source']}: cuBLAS bf16 burst / 2 (TF32 runs at half "
                                         "the bf16 rate)"},
