@@ -2,19 +2,32 @@
 """Benchmark of the matrix-multiplication path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload dense_tf32|dense_tf32x3|dense4000_tf32|linear_bwd|spgemm|spgemm_zipf|mlp]
-                    [--no-extras]
+                    [--workload dense_tf32|dense_tf32x3|dense4000_tf32|dense4000_tf32x3|
+                                linear_bwd|spgemm|spgemm_zipf|mlp]
+                    [--per-gpu-batch B] [--no-extras] [--case NAME]
 
 One JSON line on stdout (rank 0).  The headline workload is the large batched
-dense GEMM, 8 x 4096^3 fp32-in / TF32 per GPU (weak scaling: every rank owns 8
-independent batches, no data-path collective).  A "step" is one pass of the
-path over that batch.  `value` is whole-job TFLOP/s with inputs resident in
-HBM; `e2e` is the same metric through the C ABI from pinned HOST buffers with
-the host<->device copies inside the timed region.
+dense GEMM, GLOBAL batch 8 of 4096^3 fp32-in / TF32, batch-sharded over the
+ranks (rank r of N takes a contiguous range of the 8 batches: strong scaling,
+no data-path collective).  A "step" is one pass of the path over that batch.
+`value` is whole-job TFLOP/s with inputs resident in HBM; `e2e` is the same
+metric through the C ABI from pinned HOST buffers with the host<->device copies
+inside the timed region.  `--per-gpu-batch B` instead gives every rank B
+batches of its own (weak scaling; reported as such).
+
+The other workloads shard the same way the path does: `linear_bwd` cuts the
+8192 rows of dY / X into row blocks (dX rows final, dW / dB summed over the
+ranks inside the timed region), `spgemm` cuts A into row blocks balanced by
+scalar products with B replicated, `mlp` splits the batch of 64.
 
 `--impl reference` times the reference's own CPU GEMM (oracle/_ref, compiled
 from the reference tree; the oracle port when that build is absent) on a
 bounded row slice of the same workload.
+
+`--case NAME` runs one small, self-terminating case of a kernel for a profiler
+capture (more than the 126 MB L2 touched, at most ~1.5 GB held, every kernel
+launched a handful of times) and prints a one-line JSON summary; see
+PROFILE_CASES.
 """
 from __future__ import annotations
 
@@ -31,13 +44,20 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# DRAM bytes (read + written) of one launch, from ncu captures of small cases of the same
+# kernels (`--case dense_tf32`, `--case spgemm`, `--case spgemm_zipf`); the bench
+# scales them to its own launch
+DENSE_TRAFFIC_4x2048 = 280.8e6
+SPGEMM_TRAFFIC_PER_NNZC = {"poisson": (258.0e6 + 1686.0e6) / 136.2e6, "zipf": None}
+
 DENSE = {"dense_tf32": (4096, 0), "dense_tf32x3": (4096, 1), "dense4000_tf32": (4000, 0),
          "dense4000_tf32x3": (4000, 1)}
 BATCH = 8
 
 
-def dense_workload_text(n: int) -> str:
-    return (f"dense batched GEMM y=a.b+c, per GPU batch={BATCH} M=N=K={n}, fp32 in/out, "
+def dense_workload_text(n: int, per_gpu: int = 0) -> str:
+    what = f"per GPU batch={per_gpu}" if per_gpu else f"global batch={BATCH}"
+    return (f"dense batched GEMM y=a.b+c, {what} M=N=K={n}, fp32 in/out, "
             "a,b~N(0,1) c~U[-1,1)")
 
 
@@ -150,8 +170,6 @@ def cpu_spgemm_sample(dist_name: str, rows: int):
     return time.perf_counter() - t, 2.0 * prods
 
 
-FUSED_RS_VALIDATED_WORLD = 8
-
 
 def run_reference_arm(args):
     """The reference's own CPU implementation of the path on this host: for the
@@ -189,7 +207,7 @@ def run_reference_arm(args):
     line = {
         "impl": "reference", "metric": metric, "value": value, "unit": unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "sample": sample},
         "cpu_baseline": {"value": value, "unit": unit, "cores": 1, "kind": kind, "sample": sample},
@@ -197,6 +215,141 @@ def run_reference_arm(args):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------- small profiler cases
+
+def _case_dense(mode, ta=False, tb=False, n=2048, batch=4, k=0):
+    """k: inner dimension when it differs from n (k = 32 is one k-block per tile:
+    the kernel is then all epilogue)."""
+    import torch
+    from sapphire_b200 import ops
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    k = k or n
+    a = torch.randn(batch, k, n, device=dev, generator=g) if ta else torch.randn(batch, n, k, device=dev, generator=g)
+    b = torch.randn(batch, n, k, device=dev, generator=g) if tb else torch.randn(batch, k, n, device=dev, generator=g)
+    c = torch.rand(batch, n, n, device=dev, generator=g)
+    out = torch.empty_like(c)
+    for _ in range(3):
+        ops.gemm(ctx, a, b, c, out, mode=mode, trans_a=ta, trans_b=tb)
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    return {"check": float(out[0, 0, 0]), "launches": ctx.launch_count()}
+
+
+def _case_spgemm(dist_name, M=32768, N=65536):
+    import torch
+    from sapphire_b200 import ops
+    from sapphire_b200 import workloads as W
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    rA, cA, vA = W.csr_random(0, M, N, 0.001, dist_name)
+    rB, cB, vB = W.csr_random(1, N, N, 0.001, dist_name)
+    A = ops.CsrMatrix.from_numpy(rA, cA, vA, M, N, dev)
+    B = ops.CsrMatrix.from_numpy(rB, cB, vB, N, N, dev)
+    for _ in range(2):
+        Cm = ops.spgemm(ctx, A, B)
+    torch.cuda.synchronize()
+    return {"nnzC": Cm.nnz, "nnzA": int(cA.size), "nnzB": int(cB.size),
+            "products": int(W.csr_products(rA, cA, rB).sum()), "launches": ctx.launch_count()}
+
+
+def _case_im2col():
+    """The bench's convolution: 32 x 64 x 56 x 56 input, 3 x 3 taps, padding 1
+    (cols = 231 MB, larger than L2)."""
+    import torch
+    from sapphire_b200 import conv, ops
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    x = torch.randn(32, 64, 56, 56, device=dev, generator=g)
+    for _ in range(3):
+        cols = conv.im2col(ctx, x, 3, 3, (1, 1), (1, 1), (1, 1))
+    torch.cuda.synchronize()
+    return {"check": float(cols[0, 0, 0]), "launches": ctx.launch_count()}
+
+
+def _case_mlp():
+    """Three eager steps of the 784-512-256-10 MLP at batch 64."""
+    import torch
+    from sapphire_b200 import _lib as L
+    from sapphire_b200 import mlp, ops
+    from sapphire_b200 import workloads as W
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    Ws, bs = W.mlp_init(0)
+    trainer = mlp.MlpTrainer(ctx, Ws, bs, 1e-4, mode=L.MODE_TF32)
+    x, onehot = W.mlp_batch(0)
+    x, onehot = torch.from_numpy(x).to(dev), torch.from_numpy(onehot).to(dev)
+    for _ in range(3):
+        loss = trainer.step(x, onehot)
+    torch.cuda.synchronize()
+    return {"check": float(loss[0]), "launches": ctx.launch_count()}
+
+
+def _case_gemm_rs():
+    """dW = x^T.dy for 8192 x 4096 x 4096 twice: a plain GEMM with its fused column
+    sum, then the reduce-scatter variant with eight owners that all live on this
+    GPU (the epilogue is the same code whoever owns the buffers)."""
+    import torch
+    from sapphire_b200 import ops
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    x = torch.randn(8192, 4096, device=dev, generator=g) * 0.02
+    dy = torch.randn(8192, 4096, device=dev, generator=g) * 0.02
+    dw = torch.empty(4096, 4096, device=dev)
+    db = torch.empty(4096, device=dev)
+    owners = [torch.zeros(512, 4096, device=dev) for _ in range(8)]
+    for _ in range(3):
+        ops.gemm(ctx, x, dy, None, dw, trans_a=True, colsum_out=db, colsum_scale=1.0 / 8192)
+    for _ in range(3):
+        ops.gemm_reduce_scatter(ctx, x, dy, [t.data_ptr() for t in owners], 4096, trans_a=True,
+                                colsum_out=db, colsum_scale=1.0 / 8192)
+    torch.cuda.synchronize()
+    return {"check": float(dw[0, 0]), "check_rs": float(owners[0][0, 0]) / 3,
+            "launches": ctx.launch_count()}
+
+
+PROFILE_CASES = {
+    "dense_tf32": lambda: _case_dense(0),                       # 4 x 2048^3, NN, pair kernel
+    "dense_tf32x3": lambda: _case_dense(1),
+    "dense_tn": lambda: _case_dense(0, ta=True),
+    "dense_nt": lambda: _case_dense(0, tb=True),
+    "dense_epilogue": lambda: _case_dense(0, n=8192, batch=1, k=32),
+    "dense_single_4096": lambda: _case_dense(0, n=4096, batch=1),   # tail-wave split: two launches
+    "spgemm": lambda: _case_spgemm("poisson"),                  # 32768 rows of the 65536^2 case
+    "spgemm_zipf": lambda: _case_spgemm("zipf"),
+    "im2col": _case_im2col,
+    "mlp": _case_mlp,
+    "gemm_rs": _case_gemm_rs,
+}
+
+
+def pin_to_gpu_numa_node(local: int):
+    """Binds this process to the CPUs next to its GPU, so that pinned host buffers
+    allocated afterwards (first touch) sit on that NUMA node.  Returns the node
+    number or None when the platform does not say."""
+    try:
+        import torch
+        pr = torch.cuda.get_device_properties(local)
+        bus = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        base = f"/sys/bus/pci/devices/{bus}"
+        node = int(open(base + "/numa_node").read().strip())
+        cpus = set()
+        for part in open(base + "/local_cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        if cpus:
+            os.sched_setaffinity(0, cpus & os.sched_getaffinity(0) or cpus)
+        return node
+    except Exception:
+        return None
 
 
 # --------------------------------------------------------------------- our arm
@@ -208,13 +361,22 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="dense_tf32")
+    ap.add_argument("--per-gpu-batch", type=int, default=0,
+                    help="dense workloads: every rank gets this many batches of its own (weak "
+                         "scaling) instead of its share of the global batch of 8")
     ap.add_argument("--linear-bwd-comm", default="fused", choices=["fused", "nccl"],
                     help="how the linear_bwd workload sums dW over ranks (see bench_linear_bwd)")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, help="run one small profiler case and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    if args.case:
+        if args.case not in PROFILE_CASES:
+            raise SystemExit(f"unknown case {args.case}; one of {sorted(PROFILE_CASES)}")
+        print(json.dumps({"case": args.case, **PROFILE_CASES[args.case]()}), flush=True)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -227,6 +389,7 @@ def main():
     import torch.distributed as dist
     from sapphire_b200 import _lib as L
     from sapphire_b200 import ops
+    from sapphire_b200 import runner as R
     from sapphire_b200 import workloads as W
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -234,6 +397,7 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa_node = pin_to_gpu_numa_node(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -250,6 +414,13 @@ def main():
             return ms
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 
     def timed(fn, steps, warmup):
@@ -269,24 +440,31 @@ def main():
         return max_over_ranks(ms), (ctx.launch_count() - launches0)
 
     # ---------------------------------------------------------------- dense
-    def dense_inputs(n, on_device=True):
-        # this rank's 8 batches of the global [8*world, n, n] tensors
-        ids = list(range(rank * BATCH, (rank + 1) * BATCH))
-        if on_device:
-            # device-side generation keeps start-up short; the parity tests use the
-            # numpy generators, the timing does not depend on the values
-            g = torch.Generator(device=dev)
-            g.manual_seed(1234 + rank)
-            a = torch.randn(BATCH, n, n, device=dev, generator=g)
-            b = torch.randn(BATCH, n, n, device=dev, generator=g)
-            c = torch.rand(BATCH, n, n, device=dev, generator=g) * 2 - 1
-            return a, b, c
-        return W.dense_batched(0, ids, n, n, n, "normal")
+    def my_batches(per_gpu):
+        """(number of batches this rank owns, global batch).  Strong scaling: a
+        contiguous share of the global batch of 8 (a rank beyond the 8th gets none)."""
+        if per_gpu:
+            return per_gpu, per_gpu * world
+        return len(R.contiguous_shard(BATCH, world, rank)), BATCH
 
-    def bench_dense(n, mode, steps, warmup, sample_clocks):
-        a, b, c = dense_inputs(n)
+    def dense_inputs(n, nb):
+        # device-side generation keeps start-up short; the parity tests use the
+        # numpy generators, the timing does not depend on the values
+        g = torch.Generator(device=dev)
+        g.manual_seed(1234 + rank)
+        a = torch.randn(max(nb, 1), n, n, device=dev, generator=g)
+        b = torch.randn(max(nb, 1), n, n, device=dev, generator=g)
+        c = torch.rand(max(nb, 1), n, n, device=dev, generator=g) * 2 - 1
+        return a, b, c
+
+    def bench_dense(n, mode, steps, warmup, sample_clocks, per_gpu=0, yardstick=False):
+        nb, global_batch = my_batches(per_gpu)
+        a, b, c = dense_inputs(n, nb)
         out = torch.empty_like(c)
-        fn = lambda: ops.gemm(ctx, a, b, c, out, mode=mode)
+        if nb:
+            fn = lambda: ops.gemm(ctx, a[:nb], b[:nb], c[:nb], out[:nb], mode=mode)
+        else:
+            fn = lambda: None
         sampler = ClockSampler(local) if sample_clocks and rank == 0 else None
         n0 = sampler.lines() if sampler else 0
         ms, launches = timed(fn, steps, warmup)
@@ -302,33 +480,43 @@ def main():
             clocks = sampler.stop()
             clocks["window"] = "warm-up + timed steps + untimed continuation of the same loop"
         ctx.check_device_status()
-        flops = 2.0 * BATCH * n * n * n
-        per_gpu = flops / ms / 1e9
+        res = {"ms": ms, "tflops_total": 2.0 * global_batch * n ** 3 / ms / 1e9,
+               "launches": launches, "clocks": clocks, "global_batch": global_batch,
+               "local_batch": nb}
+        if yardstick and nb and mode == 0:
+            # the library call the reference makes (cuBLAS TF32 through torch), same inputs
+            prev = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = True
+            yfn = lambda: torch.baddbmm(c[:nb], a[:nb], b[:nb], out=out[:nb])
+            yms, _ = timed(yfn, steps, warmup)
+            torch.backends.cuda.matmul.allow_tf32 = prev
+            res["yardstick"] = {
+                "what": "cuBLAS TF32 (torch.baddbmm, allow_tf32) on the same inputs and batch split; "
+                        "a library call, NOT on the product path",
+                "ms_per_step": yms, "tflops_total": 2.0 * global_batch * n ** 3 / yms / 1e9}
         del a, b, c, out
-        return ms, per_gpu, launches, clocks
+        return res
 
-    def bench_dense_e2e(n, mode, steps):
+    def bench_dense_e2e(n, mode, steps, per_gpu=0):
         """Host pinned buffers -> H2D -> GEMM -> D2H, all inside the timed region."""
-        ha = torch.empty(BATCH, n, n).pin_memory()
-        hb = torch.empty(BATCH, n, n).pin_memory()
-        hc = torch.empty(BATCH, n, n).pin_memory()
-        hy = torch.empty(BATCH, n, n).pin_memory()
+        nb, global_batch = my_batches(per_gpu)
+        m = max(nb, 1)
+        ha, hb, hc, hy = (torch.empty(m, n, n).pin_memory() for _ in range(4))
         for h in (ha, hb, hc):
             h.normal_()
-        da, db, dc = (torch.empty(BATCH, n, n, device=dev) for _ in range(3))
-        dy = torch.empty(BATCH, n, n, device=dev)
+        da, db, dc, dy = (torch.empty(m, n, n, device=dev) for _ in range(4))
 
         # per batch: H2D on one stream, GEMM on the compute stream, D2H on a third,
         # chained by events, so that the copies of batch i+1 overlap the GEMM of batch i
         h2d, d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        ev_in = [torch.cuda.Event() for _ in range(BATCH)]
-        ev_out = [torch.cuda.Event() for _ in range(BATCH)]
+        ev_in = [torch.cuda.Event() for _ in range(m)]
+        ev_out = [torch.cuda.Event() for _ in range(m)]
 
         def step():
             main = torch.cuda.current_stream(dev)
             h2d.wait_stream(main)
             d2h.wait_stream(main)
-            for i in range(BATCH):
+            for i in range(nb):
                 with torch.cuda.stream(h2d):
                     da[i].copy_(ha[i], non_blocking=True)
                     db[i].copy_(hb[i], non_blocking=True)
@@ -343,46 +531,65 @@ def main():
             main.wait_stream(d2h)
 
         ms, _ = timed(step, steps, 1)
-        nbytes = ha.numel() * 4
-        return ms, 2.0 * BATCH * n ** 3 / ms / 1e9, 3 * nbytes, nbytes
+        per_batch = n * n * 4
+        h2d_total = sum_over_ranks(3.0 * nb * per_batch)
+        d2h_total = sum_over_ranks(1.0 * nb * per_batch)
+        return ms, 2.0 * global_batch * n ** 3 / ms / 1e9, int(h2d_total), int(d2h_total)
 
     # --------------------------------------------------------------- sparse
     def bench_spgemm(dist_name, steps, warmup):
+        """One global A (seed 0) and B (seed 1); rank r multiplies its row block of A,
+        the blocks balanced by scalar products, against the whole (replicated) B.
+        No collective: C stays distributed by rows."""
         M = N = 65536
-        rA, cA, vA = W.csr_random(0 + 2 * rank, M, N, 0.001, dist_name)
+        rA, cA, vA = W.csr_random(0, M, N, 0.001, dist_name)
         rB, cB, vB = W.csr_random(1, N, N, 0.001, dist_name)
-        A = ops.CsrMatrix.from_numpy(rA, cA, vA, M, N, dev)
+        work = W.csr_products(rA, cA, rB)
+        rows = R.balanced_row_blocks(work, world)[rank]
+        rb, cb, vb = R.csr_row_block(rA, cA, vA, rows)
+        A = ops.CsrMatrix.from_numpy(rb, cb, vb, len(rows), N, dev)
         B = ops.CsrMatrix.from_numpy(rB, cB, vB, N, N, dev)
         res = {}
         def fn():
             res["C"] = ops.spgemm(ctx, A, B)
         ms, launches = timed(fn, steps, warmup)
-        nnzC = res["C"].nnz
-        prods = int(W.csr_products(rA, cA, rB).sum())
-        nbytes = 8 * (cA.size + cB.size + nnzC) + 4 * 3 * (M + 1)
-        # dram read + written by the two row kernels of one call, from the ncu capture of the
-        # half-size uniform case (profiles/spgemm_cta_rows_32768x65536.md: symbolic 41 + 217 MB,
-        # numeric 652 + 1034 MB), scaled by the output size; no capture of the Zipf case
-        traffic = (258.0e6 + 1686.0e6) * nnzC / 136.2e6 if dist_name == "poisson" else None
+        nnzC_local = res["C"].nnz
+        nnzC = int(sum_over_ranks(float(nnzC_local)))
+        prods = int(work.sum())
+        # what one GPU must move: its rows of A and C, and all of B
+        local_bytes = 8 * (cb.size + cB.size + nnzC_local) + 4 * 3 * (len(rows) + 1)
+        nbytes = sum_over_ranks(float(local_bytes)) / world
+        # dram read + written by one call's kernels, from an ncu capture of the first
+        # 32768 rows of the same product, scaled by the output entries of this launch
+        traffic = SPGEMM_TRAFFIC_PER_NNZC.get(dist_name)
+        traffic = traffic * nnzC / world if traffic else None
         return {"workload": spgemm_workload_text(dist_name), "ms_per_step": ms,
-                "gflops_per_gpu": 2.0 * prods / ms / 1e6, "nnzC": nnzC, "products": prods,
+                "gflops_total": 2.0 * prods / ms / 1e6, "nnzC": nnzC, "products": prods,
+                "rows_of_rank0": len(rows),
                 "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6,
                              "peak": pk["hbm_gbs"], "unit": "GB/s",
                              "frac": nbytes / ms / 1e6 / pk["hbm_gbs"], "traffic": traffic,
-                             "traffic_source": "ncu, scaled from the 32768-row capture" if traffic else None,
+                             "traffic_source": "ncu on the first 32768 rows, scaled by nnz(C)" if traffic else None,
+                             "per": "GPU (mean over ranks of the bytes each must move / max time)",
                              "peak_source": pk["source"]},
                 "gpu_launches": launches}
 
     def bench_linear_bwd(steps, warmup, comm_mode="fused"):
-        """dW = x^T.dy (+ dB) and dx = dy.W^T on this rank's 8192 rows.  With several
-        ranks dW and dB are summed over the ranks inside the timed region:
+        """Backward GEMMs of one Linear layer, global dY / X of 8192 rows cut into row
+        blocks over the ranks (boundaries at multiples of 128): dx = dy.W^T is final
+        per rank; dW = x^T.dy and dB are partial sums, added up over the ranks inside
+        the timed region:
           "fused"  the dW GEMM adds its tiles into the owning rank's window over
                    NVLink from its epilogue (GEMM + reduce-scatter in one kernel),
                    one tiny all-reduce as barrier, then every rank pulls the reduced
                    row blocks from the owners' windows with copy-engine transfers
                    while the dx GEMM runs (runner.FusedWeightGradient);
-          "nccl"   plain GEMM, then an NCCL all-reduce of dW that overlaps the dx GEMM."""
-        rows, width = 8192, 4096
+          "nccl"   plain GEMM, then an NCCL all-reduce of dW that overlaps the dx GEMM.
+        With several ranks the fused dW is checked against the NCCL route once,
+        outside the timed region."""
+        total_rows, width = 8192, 4096
+        mine = R.row_shard(total_rows, world, rank, 128)
+        rows = max(len(mine), 1)
         g = torch.Generator(device=dev); g.manual_seed(7 + rank)
         dy = torch.randn(rows, width, device=dev, generator=g) * 0.02
         x = torch.randn(rows, width, device=dev, generator=g) * 0.02
@@ -395,41 +602,56 @@ def main():
         fused = world > 1 and comm_mode == "fused" and width % (world * 128) == 0
         reducer = None
         if fused:
-            from sapphire_b200 import runner as R
             reducer = R.FusedWeightGradient(ctx, width, width, rank, world)
             if not reducer.ok:                           # agreed across ranks: all fall back together
                 reducer.close()
                 reducer, fused = None, False
 
-        def fn():
+        def nccl_route():
             main = torch.cuda.current_stream(dev)
-            if fused:
-                reducer.start(x, dy, dw, db)
-            else:
-                # dW first: its allreduce then travels while dX, which needs no exchange, computes
-                ops.gemm(ctx, x, dy, None, dw, trans_a=True, colsum_out=db,     # dW = x^T.dy, dB
-                         colsum_scale=1.0 / (rows * world))
-                if world > 1:
-                    done.record(main)
-                    with torch.cuda.stream(comm):
-                        comm.wait_event(done)
-                        dist.all_reduce(dw)
-                        dist.all_reduce(db)
+            # dW first: its allreduce then travels while dX, which needs no exchange, computes
+            ops.gemm(ctx, x, dy, None, dw, trans_a=True, colsum_out=db,     # dW = x^T.dy, dB
+                     colsum_scale=1.0 / total_rows)
+            if world > 1:
+                done.record(main)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    dist.all_reduce(dw)
+                    dist.all_reduce(db)
             ops.gemm(ctx, dy, w, None, dx, trans_b=True)                    # dx = dy.W^T
-            if fused:
-                reducer.wait()
-            elif world > 1:
+            if world > 1:
                 main.wait_stream(comm)
+
+        def fused_route():
+            reducer.start(x, dy, dw, db, total_rows=total_rows)
+            ops.gemm(ctx, dy, w, None, dx, trans_b=True)
+            reducer.wait()
+
+        check = None
+        if fused:
+            nccl_route()
+            torch.cuda.synchronize()
+            want_dw, want_db = dw.clone(), db.clone()
+            fused_route()
+            torch.cuda.synchronize()
+            err_w = float((dw - want_dw).norm() / want_dw.norm())
+            err_b = float((db - want_db).norm() / want_db.norm())
+            check = {"dw_rel_err_fused_vs_nccl": max_over_ranks(err_w),
+                     "db_rel_err_fused_vs_nccl": max_over_ranks(err_b)}
+        fn = fused_route if fused else nccl_route
         ms, launches = timed(fn, steps, warmup)
         if reducer is not None:
             reducer.close()
-        flops = 2 * 2.0 * rows * width * width
-        label = "linear backward dY[8192x4096] X[8192x4096] W[4096x4096]"
+        flops = 2 * 2.0 * total_rows * width * width
+        label = f"linear backward dY[8192x4096] X[8192x4096] W[4096x4096], rows sharded x{world}"
         if world > 1:
-            label += (" per GPU, dW reduce-scatter fused into the GEMM epilogue (peer adds) + "
-                      "copy-engine gather" if fused else " per GPU, dW/dB NCCL allreduce overlapped with the dx GEMM")
-        return {"workload": label, "ms_per_step": ms, "tflops_per_gpu": flops / ms / 1e9,
-                "gpu_launches": launches}
+            label += (", dW reduce-scatter fused into the GEMM epilogue (peer adds) + "
+                      "copy-engine gather" if fused else ", dW/dB NCCL allreduce overlapped with the dx GEMM")
+        out = {"workload": label, "ms_per_step": ms, "tflops_total": flops / ms / 1e9,
+               "gpu_launches": launches}
+        if check:
+            out["check"] = check
+        return out
 
     def bench_mlp(steps, warmup):
         """The 784-512-256-10 MLP training step, global batch 64 split over the
@@ -472,7 +694,8 @@ def main():
         P, rows = H * Wd, Cc * k * k
         col_bytes = 4.0 * N * (Cc * H * Wd + rows * P)            # x read once, cols written once
         flops = 2.0 * N * Cout * rows * P
-        return {"workload": "conv2d forward 32x64x56x56, 128 filters 3x3 pad 1 (im2col + batched GEMM)",
+        return {"workload": "conv2d forward 32x64x56x56, 128 filters 3x3 pad 1 (im2col + batched GEMM), "
+                            "replicated per rank",
                 "ms_per_step": ms_all, "tflops_per_gpu": flops / ms_all / 1e9,
                 "im2col_ms": ms_cols,
                 "im2col_roofline": {"bound": "hbm", "achieved": col_bytes / ms_cols / 1e6,
@@ -481,53 +704,67 @@ def main():
                 "gpu_launches": launches}
 
     # ------------------------------------------------------------- headline
+    tf32_peak = pk["bf16_tflops"] / 2.0
+    peak_note = f"{pk['source']}: cuBLAS bf16 burst / 2 (TF32 runs at half the bf16 rate)"
     if args.workload in DENSE:
         n, mode = DENSE[args.workload]
-        ms, per_gpu, launches, clocks = bench_dense(n, mode, args.steps, args.warmup, True)
-        value = per_gpu * world
-        tf32_peak = pk["bf16_tflops"] / 2.0
+        r = bench_dense(n, mode, args.steps, args.warmup, True, args.per_gpu_batch, yardstick=True)
+        ms = r["ms"]
+        # the slowest rank bounds the step: its share of the global batch is what one GPU achieved
+        busiest = args.per_gpu_batch or -(-BATCH // world)
+        per_gpu = 2.0 * busiest * n ** 3 / ms / 1e9
         line = {
-            "metric": "batched dense GEMM throughput", "value": value, "unit": "TFLOP/s",
+            "metric": "batched dense GEMM throughput", "value": r["tflops_total"], "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "weak" if args.per_gpu_batch else "strong",
+            "vs_baseline": None,
             "dtype": "tf32" if mode == 0 else "3xtf32 (fp32-accurate)", "data": "synthetic",
-            "config": {"workload": dense_workload_text(n),
-                       "global_batch": BATCH * world, "parallelism": f"batch-sharded x{world}",
-                       "l2": "inputs (3 x %d MiB) larger than the 126 MB L2" % (BATCH * n * n * 4 >> 20)},
+            "config": {"workload": dense_workload_text(n, args.per_gpu_batch),
+                       "global_batch": r["global_batch"],
+                       "parallelism": f"batch-sharded x{world} ({busiest} batch(es) on the busiest GPU)",
+                       "l2": "working set per step (4 x %d MiB on the busiest GPU) larger than the "
+                             "126 MB L2" % (busiest * n * n * 4 >> 20)},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": tf32_peak,
                          "unit": "TFLOP/s", "frac": per_gpu / tf32_peak,
-                         # dram read+write of one launch: 280.8 MB measured by ncu on the
-                         # 4 x 2048^3 case (profiles/gemm_tcgen05_tf32_4x2048.md), scaled by
-                         # the matrix bytes of this launch (traffic == every matrix once)
-                         "traffic": 280.8e6 * (BATCH * n * n) / (4 * 2048 * 2048),
+                         # dram read + write of one launch: measured by ncu on the 4 x 2048^3
+                         # case, scaled by the matrix bytes of this launch (the capture shows
+                         # traffic == every matrix once)
+                         "traffic": DENSE_TRAFFIC_4x2048 * (busiest * n * n) / (4 * 2048 * 2048),
                          "traffic_source": "ncu, scaled from the 4x2048^3 capture",
-                         "peak_source": f"{pk['source']}: cuBLAS bf16 burst / 2 (TF32 runs at half "
-                                        "the bf16 rate)"},
-            "gpu_launches": launches, "clocks": clocks,
+                         "per": "GPU (the busiest rank's FLOPs / max-over-ranks time)",
+                         "peak_source": peak_note},
+            "gpu_launches": r["launches"], "clocks": r["clocks"],
         }
-        e_ms, e_val, h2d, d2h = bench_dense_e2e(n, mode, max(2, min(args.steps, 5)))
-        line["e2e"] = {"value": e_val * world, "unit": "TFLOP/s", "ms_per_step": e_ms,
-                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        if "yardstick" in r:
+            line["yardstick"] = r["yardstick"]
+        e_ms, e_val, h2d, d2h = bench_dense_e2e(n, mode, max(2, min(args.steps, 5)), args.per_gpu_batch)
+        line["e2e"] = {"value": e_val, "unit": "TFLOP/s", "ms_per_step": e_ms,
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "host_numa_node_of_rank0": numa_node,
+                       "note": "pinned host buffers allocated after binding each rank to the CPUs "
+                               "next to its GPU; PCIe / host-memory bound"}
     elif args.workload in ("spgemm", "spgemm_zipf"):
         r = bench_spgemm("poisson" if args.workload == "spgemm" else "zipf", args.steps,
                          args.warmup)
-        line = {"metric": "CSR SpGEMM throughput", "value": r["gflops_per_gpu"] * world,
+        line = {"metric": "CSR SpGEMM throughput", "value": r["gflops_total"],
                 "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": r["workload"], "parallelism": f"A row blocks x{world}, B replicated"},
+                "config": {"workload": r["workload"],
+                           "parallelism": f"A row blocks x{world} balanced by scalar products, B replicated",
+                           "nnzC": r["nnzC"], "products": r["products"]},
                 "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]}
     elif args.workload == "linear_bwd":
         r = bench_linear_bwd(args.steps, args.warmup, args.linear_bwd_comm)
-        tf32_peak = pk["bf16_tflops"] / 2.0
-        line = {"metric": "Linear backward GEMM throughput", "value": r["tflops_per_gpu"] * world,
+        per_gpu = r["tflops_total"] / world
+        line = {"metric": "Linear backward GEMM throughput", "value": r["tflops_total"],
                 "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
-                "config": {"workload": r["workload"]},
-                "roofline": {"bound": "tensor", "achieved": r["tflops_per_gpu"], "peak": tf32_peak,
-                             "unit": "TFLOP/s", "frac": r["tflops_per_gpu"] / tf32_peak,
-                             "traffic": None},
+                "config": {"workload": r["workload"], "check": r.get("check")},
+                "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": tf32_peak,
+                             "unit": "TFLOP/s", "frac": per_gpu / tf32_peak, "traffic": None,
+                             "per": "GPU", "peak_source": peak_note},
                 "gpu_launches": r["gpu_launches"]}
     elif args.workload == "mlp":
         r = bench_mlp(args.steps, args.warmup)
@@ -543,20 +780,20 @@ def main():
     else:
         raise SystemExit(f"unknown workload {args.workload}")
 
-    if not args.no_extras and args.workload == "dense_tf32":
+    if not args.no_extras and args.workload == "dense_tf32" and not args.per_gpu_batch:
         extras = []
         for name in ("dense_tf32x3", "dense4000_tf32"):
             n, mode = DENSE[name]
-            ms, per_gpu, _, _ = bench_dense(n, mode, 5, 3, False)
-            extras.append({"workload": f"{name} batch={BATCH} n={n}", "ms_per_step": ms,
-                           "tflops_per_gpu": per_gpu})
-        # the fused GEMM + reduce-scatter route has been run on FUSED_RS_VALIDATED_WORLD ranks;
-        # beyond that the default run keeps to the NCCL route (--workload linear_bwd
-        # --linear-bwd-comm fused runs it on any rank count)
+            r = bench_dense(n, mode, 5, 3, False)
+            extras.append({"workload": f"{name} global batch={BATCH} n={n}, batch-sharded x{world}",
+                           "scaling": "strong", "ms_per_step": r["ms"], "tflops_total": r["tflops_total"]})
         if world > 1:
+            # every rank with 8 batches of its own: shows that the ranks do not disturb each other
+            r = bench_dense(4096, 0, 5, 3, False, per_gpu=BATCH)
+            extras.append({"workload": f"dense_tf32 per GPU batch={BATCH} n=4096", "scaling": "weak",
+                           "ms_per_step": r["ms"], "tflops_total": r["tflops_total"]})
             extras.append(bench_linear_bwd(10, 3, "nccl"))
-        if world <= FUSED_RS_VALIDATED_WORLD:
-            extras.append(bench_linear_bwd(10, 3))
+        extras.append(bench_linear_bwd(10, 3))
         extras.append(bench_spgemm("poisson", 5, 3))
         extras.append(bench_spgemm("zipf", 5, 3))
         extras.append(bench_mlp(50, 5))

@@ -56,10 +56,17 @@ typedef void* sb200_stream;
 
 /*
  * One context per (device, host thread); it owns the per-device workspace,
- * the device status word and the tensor-map cache.  Replaces the per
- * (device, thread) cuBLAS handle map of the reference
+ * the device status word and a cache of encoded TMA descriptors (64 entries,
+ * least recently used replaced, keyed by base address, extents, leading
+ * dimension, batch stride and box shape: a GEMM on operands the context has
+ * seen before encodes nothing).  Replaces the per (device, thread) cuBLAS
+ * handle map of the reference
  * (Sources/Sapphire/compute/dense/cuda/Gemm.cu:24-30,
  *  Sources/Sapphire/util/ResourceManager.cpp:209-214).
+ *
+ * A context is not thread-safe, and its one workspace is not ordered between
+ * streams: calls that share a context must be stream-ordered with respect to
+ * each other (one stream per context, or event dependencies between streams).
  */
 int sb200_ctx_create(int device, sb200_ctx** out);
 int sb200_ctx_destroy(sb200_ctx* ctx);
@@ -72,6 +79,12 @@ const char* sb200_status_string(int status);
 int sb200_last_path(const sb200_ctx* ctx);
 int64_t sb200_launch_count(const sb200_ctx* ctx);
 
+/* Running counters of a context: kernels launched, TMA descriptors served from
+ * the cache, TMA descriptors encoded.  -1 for an unknown counter. */
+enum { SB200_COUNTER_LAUNCHES = 0, SB200_COUNTER_TENSOR_MAP_HITS = 1,
+       SB200_COUNTER_TENSOR_MAP_MISSES = 2 };
+int64_t sb200_ctx_counter(const sb200_ctx* ctx, int which);
+
 /* Tuning knobs of a context (the counterpart of cublasSetMathMode at
  * Sources/Sapphire/compute/dense/cuda/Gemm.cu:31).
  *   SB200_OPT_SPLIT_EXPLICIT_HI  (TF32X3 mode) 0, the default: the high part of
@@ -82,8 +95,22 @@ int64_t sb200_launch_count(const sb200_ctx* ctx);
  *       box; 0: by one 32 x 32 box per 32-element chunk.
  *   SB200_OPT_CTA_PAIRS  1, the default: TF32 problems with at least one
  *       256 x 256 tile per pair of SMs run on the two-CTA kernel (clusters of two,
- *       tcgen05 cta_group::2); 0: always the one-CTA kernel. */
-enum { SB200_OPT_SPLIT_EXPLICIT_HI = 1, SB200_OPT_MERGE_MN_BOXES = 2, SB200_OPT_CTA_PAIRS = 3 };
+ *       tcgen05 cta_group::2); 0: always the one-CTA kernel.
+ *   SB200_OPT_SPLIT_TAIL_WAVE  1, the default: when the 256 x 256 tiles of a problem
+ *       would leave the last wave over the SM pairs mostly empty (one 4096^3
+ *       product: 3.46 waves of work in the time of 4), the bottom rows of the
+ *       product run as a second launch of the one-CTA kernel; 0: one launch.
+ *   SB200_OPT_WAIT_LIMIT_US  bound of every wait inside the GEMM kernels in
+ *       microseconds (default 2,000,000; at least 100).  A wait that runs out ends
+ *       the launch with SB200_ERR_DEVICE_TIMEOUT from sb200_check_device_status --
+ *       the counterpart of the reference's CHECK_CUBLAS
+ *       (Includes/Sapphire/compute/cudaUtil/CudaParams.cuh:51-58).
+ *   SB200_OPT_TEST_STALL_KBLOCKS  test hook, -1 = off, the default: the TMA
+ *       producers of the next launches stop after this many k-blocks, so that
+ *       every other role's wait runs out and the abort path executes. */
+enum { SB200_OPT_SPLIT_EXPLICIT_HI = 1, SB200_OPT_MERGE_MN_BOXES = 2, SB200_OPT_CTA_PAIRS = 3,
+       SB200_OPT_SPLIT_TAIL_WAVE = 4, SB200_OPT_WAIT_LIMIT_US = 5,
+       SB200_OPT_TEST_STALL_KBLOCKS = 6 };
 int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value);
 
 /* Reads (and clears) the device status word after synchronising the stream.

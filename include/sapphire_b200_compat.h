@@ -48,6 +48,34 @@ long long sb200_compat_plan_gemm(const int* yShape, int yDim, const int* aShape,
  * pair given as host structs holding device arrays. */
 int sb200_compat_sparse_gemm(const sb200_csr* A, const sb200_csr* B, sb200_csr* C, int deviceId);
 
+/* Sapphire::Compute::Sparse::Naive::Gemm
+ * (Includes/Sapphire/compute/sparse/naive/SparseGemm.hpp:15-16): a and b are host
+ * arrays of numMatrices structs holding HOST arrays; *output is a host array
+ * allocated by the call (free it with sb200_compat_deep_free_sparse_host).  The
+ * product itself runs on the current CUDA device; there is no CPU path. */
+int sb200_compat_sparse_naive_gemm(sb200_csr** output, sb200_csr* a, sb200_csr* b, unsigned m,
+                                   unsigned n, size_t numMatrices);
+
+/* The deep allocate / free / copy family for arrays of sparse matrices
+ * (Includes/Sapphire/compute/sparse/Sparse.hpp:20-25, 36, 49-51, 69-71, 92-94,
+ * 119-121, 135-137, 149-150; declared there, defined nowhere in the reference).
+ * "host array": numMatrices structs in host memory with host member arrays;
+ * "device array": numMatrices structs in device memory with device member arrays. */
+int sb200_compat_deep_allocate_sparse_host(sb200_csr** array, unsigned m, unsigned n,
+                                           const unsigned* nnz, unsigned numMatrices);
+int sb200_compat_deep_free_sparse_host(sb200_csr* array, unsigned numMatrices);
+int sb200_compat_deep_allocate_sparse_cuda(sb200_csr** deviceArray, const sb200_csr* hostArray,
+                                           unsigned numMatrices, int deviceId);
+int sb200_compat_deep_free_sparse_cuda(sb200_csr* deviceArray, unsigned numMatrices, int deviceId);
+int sb200_compat_deep_copy_host_to_device(sb200_csr* deviceDst, const sb200_csr* hostSrc,
+                                          unsigned numMatrices, int deviceId);
+int sb200_compat_deep_copy_device_to_host(sb200_csr* hostDst, sb200_csr* deviceSrc,
+                                          unsigned numMatrices, int deviceId);
+int sb200_compat_deep_copy_device_to_device(sb200_csr* deviceDst, sb200_csr* deviceSrc,
+                                            unsigned numMatrices, int deviceId);
+int sb200_compat_deep_copy_host_to_host(sb200_csr* hostDst, sb200_csr* hostSrc,
+                                        unsigned numMatrices);
+
 #ifdef __cplusplus
 }
 #endif

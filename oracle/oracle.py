@@ -280,6 +280,10 @@ class MlpOracle:
         self.b = [_c(b).copy() for b in biases]
         self.lr = np.float32(lr)
         self.impl = impl
+        # per layer: sum over the steps of lr * mean_i |dy[i, :]|, the distance a bias
+        # would have travelled had its per-sample gradients not cancelled (float64);
+        # the scale against which a bias error is a relative error of the gradients
+        self.bias_travel = [np.zeros(b.size, np.float64) for b in biases]
 
     # leaf dispatch: identical results either way; `ref` proves it
     def _gemm_acc(self, y, a, b):
@@ -351,6 +355,7 @@ class MlpOracle:
             dbs = np.empty_like(db)
             f["scale"](dbs.reshape(-1), db.reshape(-1), np.float32(1.0 / B), db.size)
             bl = self.b[l].reshape(1, -1)
+            self.bias_travel[l] += float(self.lr) * np.abs(dy.astype(np.float64)).sum(0) / B
             self._sgd(bl, dbs)
             self.b[l] = bl.reshape(-1)
             if l > 0:

@@ -18,6 +18,10 @@ PATH_AUTO, PATH_TCGEN05, PATH_SIMT = 0, 1, 2
 OPT_SPLIT_EXPLICIT_HI = 1
 OPT_MERGE_MN_BOXES = 2
 OPT_CTA_PAIRS = 3
+OPT_SPLIT_TAIL_WAVE = 4
+OPT_WAIT_LIMIT_US = 5
+OPT_TEST_STALL_KBLOCKS = 6
+COUNTER_LAUNCHES, COUNTER_TENSOR_MAP_HITS, COUNTER_TENSOR_MAP_MISSES = 0, 1, 2
 
 
 class Csr(C.Structure):
@@ -55,6 +59,7 @@ SIGNATURES = {
     "sb200_status_string": (C.c_char_p, [C.c_int]),
     "sb200_last_path": (C.c_int, [C.c_void_p]),
     "sb200_launch_count": (C.c_int64, [C.c_void_p]),
+    "sb200_ctx_counter": (C.c_int64, [C.c_void_p, C.c_int]),
     "sb200_ctx_set_option": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "sb200_check_device_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "sb200_gemm_batched": (C.c_int, [
@@ -131,6 +136,18 @@ SIGNATURES = {
                                               C.c_int, C.POINTER(C.c_int), C.c_int,
                                               C.POINTER(C.c_longlong), C.c_longlong]),
     "sb200_compat_sparse_gemm": (C.c_int, [C.POINTER(Csr), C.POINTER(Csr), C.POINTER(Csr), C.c_int]),
+    "sb200_compat_sparse_naive_gemm": (C.c_int, [C.POINTER(C.POINTER(Csr)), C.POINTER(Csr),
+                                                 C.POINTER(Csr), C.c_uint, C.c_uint, C.c_size_t]),
+    "sb200_compat_deep_allocate_sparse_host": (C.c_int, [C.POINTER(C.POINTER(Csr)), C.c_uint, C.c_uint,
+                                                         C.POINTER(C.c_uint), C.c_uint]),
+    "sb200_compat_deep_free_sparse_host": (C.c_int, [C.POINTER(Csr), C.c_uint]),
+    "sb200_compat_deep_allocate_sparse_cuda": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(Csr),
+                                                         C.c_uint, C.c_int]),
+    "sb200_compat_deep_free_sparse_cuda": (C.c_int, [C.c_void_p, C.c_uint, C.c_int]),
+    "sb200_compat_deep_copy_host_to_device": (C.c_int, [C.c_void_p, C.POINTER(Csr), C.c_uint, C.c_int]),
+    "sb200_compat_deep_copy_device_to_host": (C.c_int, [C.POINTER(Csr), C.c_void_p, C.c_uint, C.c_int]),
+    "sb200_compat_deep_copy_device_to_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint, C.c_int]),
+    "sb200_compat_deep_copy_host_to_host": (C.c_int, [C.POINTER(Csr), C.POINTER(Csr), C.c_uint]),
 }
 
 

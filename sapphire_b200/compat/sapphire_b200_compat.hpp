@@ -44,6 +44,46 @@ void Gemm(SparseMatrix** hostOutput, SparseMatrix** cudaOutput,
           size_t numMatrices, int deviceId, bool copyResultToHost);
 }  // namespace Sapphire::Compute::Sparse::Cuda
 
+namespace Sapphire::Compute::Sparse::Naive
+{
+// Includes/Sapphire/compute/sparse/naive/SparseGemm.hpp:15-16 -- a / b are HOST
+// arrays of numMatrices structs whose V/COL/ROW are host arrays; *output is
+// allocated here (DeepAllocateSparseHost layout, freed with DeepFreeSparseHost).
+// The reference declares this entry point without defining it.  Here it is the
+// device path behind the host signature: operands are deep-copied to the
+// current device, multiplied by Sparse::Cuda::Gemm and the result is deep-copied
+// back; there is no CPU implementation behind it.
+void Gemm(SparseMatrix** output, SparseMatrix* a, SparseMatrix* b, uint32_t m,
+          uint32_t n, size_t numMatrices);
+}  // namespace Sapphire::Compute::Sparse::Naive
+
+namespace Sapphire::Compute
+{
+// The deep allocate / free / copy family of
+// Includes/Sapphire/compute/sparse/Sparse.hpp:20-152 for SparseMatrix arrays
+// (declared there without definitions; the LoadDistMatrix overloads belong to
+// the reference's unfinished load-balancing scheme and are not provided).
+// A "host array" is numMatrices structs in host memory whose V / COL / ROW are
+// host arrays of NNZ / NNZ / M + 1 entries; a "device array" is numMatrices
+// structs in device memory whose members are device arrays.
+void DeepAllocateSparseHost(SparseMatrix** sparseMatrixArray, uint32_t m, uint32_t n,
+                            const uint32_t nnz[], uint32_t numMatrices);
+void DeepFreeSparseHost(SparseMatrix* sparseMatrixArray, uint32_t numMatrices);
+// Sized after hostSparseMatrixArray (M, N, NNZ of each matrix); values are not copied.
+void DeepAllocateSparseCuda(SparseMatrix** deviceSparseArray,
+                            const SparseMatrix* hostSparseMatrixArray, uint32_t numMatrices,
+                            int deviceId);
+void DeepFreeSparseCuda(SparseMatrix* deviceSparseArray, uint32_t numMatrices, int deviceId);
+void DeepCopyDeviceToDevice(SparseMatrix* deviceDstArray, SparseMatrix* deviceSrcArray,
+                            uint32_t numMatrices, int deviceId);
+void DeepCopyHostToDevice(SparseMatrix* deviceDstArray, const SparseMatrix* hostSrcArray,
+                          uint32_t numMatrices, int deviceId);
+void DeepCopyDeviceToHost(SparseMatrix* hostDstArray, SparseMatrix* deviceSrcArray,
+                          uint32_t numMatrices, int deviceId);
+void DeepCopyHostToHost(SparseMatrix* hostDstArray, SparseMatrix* hostSrcArray,
+                        uint32_t numMatrices);
+}  // namespace Sapphire::Compute
+
 namespace sb200::compat
 {
 // Arithmetic mode used by the shims (process-wide; default SB200_MODE_TF32,

@@ -57,7 +57,14 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->split_explicit_hi = 0;
     ctx->merge_mn_boxes = 1;
     ctx->use_cta_pairs = 1;
+    ctx->split_tail_wave = 1;
     ctx->encode_tiled = nullptr;
+    ctx->tmaps = nullptr;
+    ctx->tmap_clock = 0;
+    ctx->tmap_hits = 0;
+    ctx->tmap_misses = 0;
+    ctx->wait_limit_ns = 2000000000ull;
+    ctx->test_stall_kb = -1;
     ctx->d_sp_pattern = nullptr;
     ctx->sp_pattern_bytes = 0;
     ctx->sp_valid = 0;
@@ -77,6 +84,12 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
         return SB200_ERR_CUDA;
     }
     ctx->encode_tiled = fn;
+    ctx->tmaps = new (std::nothrow) TensorMapSlot[TENSOR_MAP_SLOTS]();
+    if (!ctx->tmaps) {
+        cudaFree(ctx->d_status);
+        delete ctx;
+        return SB200_ERR_ALLOC;
+    }
     *out = ctx;
     return SB200_OK;
 }
@@ -89,6 +102,7 @@ extern "C" int sb200_ctx_destroy(sb200_ctx* ctx)
     if (ctx->d_workspace) cudaFree(ctx->d_workspace);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_sp_pattern) cudaFree(ctx->d_sp_pattern);
+    delete[] ctx->tmaps;
     delete ctx;
     return SB200_OK;
 }
@@ -111,6 +125,18 @@ extern "C" int sb200_last_path(const sb200_ctx* ctx) { return ctx ? ctx->last_pa
 
 extern "C" int64_t sb200_launch_count(const sb200_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+extern "C" int64_t sb200_ctx_counter(const sb200_ctx* ctx, int which)
+{
+    if (!ctx)
+        return -1;
+    switch (which) {
+        case SB200_COUNTER_LAUNCHES: return ctx->launches;
+        case SB200_COUNTER_TENSOR_MAP_HITS: return ctx->tmap_hits;
+        case SB200_COUNTER_TENSOR_MAP_MISSES: return ctx->tmap_misses;
+        default: return -1;
+    }
+}
+
 extern "C" int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value)
 {
     if (!ctx)
@@ -124,6 +150,17 @@ extern "C" int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value)
             return SB200_OK;
         case SB200_OPT_CTA_PAIRS:
             ctx->use_cta_pairs = value != 0;
+            return SB200_OK;
+        case SB200_OPT_SPLIT_TAIL_WAVE:
+            ctx->split_tail_wave = value != 0;
+            return SB200_OK;
+        case SB200_OPT_WAIT_LIMIT_US:
+            if (value < 100)
+                return SB200_ERR_INVALID_ARG;
+            ctx->wait_limit_ns = static_cast<uint64_t>(value) * 1000ull;
+            return SB200_OK;
+        case SB200_OPT_TEST_STALL_KBLOCKS:
+            ctx->test_stall_kb = value < 0 ? -1 : value;
             return SB200_OK;
         default:
             return SB200_ERR_INVALID_ARG;

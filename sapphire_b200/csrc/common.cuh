@@ -57,6 +57,23 @@ struct SpPatternKey {
     const void *rowA, *colA, *rowB, *colB;
     uint32_t M, K, N, nnzA, nnzB;
 };
+
+// One encoded TMA descriptor of the context's cache.  The key is everything
+// cuTensorMapEncodeTiled was given, so a hit is valid whatever happened to the
+// memory behind `base` in between (a descriptor holds an address and a shape,
+// no state).  All key fields are 64-bit: the key is compared with memcmp.
+struct TensorMapKey {
+    uint64_t base;
+    int64_t contig, rows, ld, batches, batch_stride;
+    int64_t box_rows;      // rows (3-D map) or chunks (merged 4-D map) per box
+    int64_t kind;          // 0: K-major 3-D, 1: MN-major 3-D, 2: MN-major merged 4-D
+};
+struct alignas(64) TensorMapSlot {
+    CUtensorMap map;
+    TensorMapKey key;
+    uint64_t stamp;        // last use; 0 = empty
+};
+constexpr int TENSOR_MAP_SLOTS = 64;
 }  // namespace sb200
 
 struct sb200_ctx {
@@ -70,7 +87,13 @@ struct sb200_ctx {
     int split_explicit_hi;     // 3xTF32: rewrite the high part in shared memory too
     int merge_mn_boxes;        // fetch an MN-major tile with one 4-D TMA box when possible
     int use_cta_pairs;         // large TF32 problems run on the two-CTA (cta_group::2) kernel
+    int split_tail_wave;       // a mostly empty last wave of pair tiles goes to the one-CTA kernel
     void* encode_tiled;        // cuTensorMapEncodeTiled, resolved at context creation
+    sb200::TensorMapSlot* tmaps;   // [TENSOR_MAP_SLOTS] encoded descriptors, least recently used replaced
+    uint64_t tmap_clock;
+    int64_t tmap_hits, tmap_misses;
+    uint64_t wait_limit_ns;    // bound of every mbarrier wait inside the GEMM kernels
+    int test_stall_kb;         // test hook: TMA producers stop after this many k-blocks (< 0: off)
     uint32_t* d_sp_pattern;    // sparse GEMM: row bitmaps kept from the symbolic pass
     size_t sp_pattern_bytes;
     sb200::SpPatternKey sp_key;

@@ -207,6 +207,204 @@ void Gemm(SparseMatrix** hostOutput, SparseMatrix** cudaOutput, SparseMatrix* cu
 
 }  // namespace Sapphire::Compute::Sparse::Cuda
 
+// ------------------------------------------- deep allocate / free / copy family
+namespace Sapphire::Compute {
+
+namespace {
+
+void cuda_check(cudaError_t e, const char* what)
+{
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+    }
+}
+
+// The structs of a device array, read back so that their member pointers can be used.
+std::vector<SparseMatrix> fetch_descriptors(const SparseMatrix* deviceArray, uint32_t numMatrices)
+{
+    std::vector<SparseMatrix> h(numMatrices);
+    if (numMatrices)
+        cuda_check(cudaMemcpy(h.data(), deviceArray, numMatrices * sizeof(SparseMatrix),
+                              cudaMemcpyDeviceToHost), "read sparse descriptors");
+    return h;
+}
+
+void copy_members(SparseMatrix& dst, const SparseMatrix& src, cudaMemcpyKind kind)
+{
+    if (dst.M != src.M || dst.NNZ < src.NNZ)
+        throw std::runtime_error("DeepCopy: destination matrix is smaller than the source");
+    cuda_check(cudaMemcpy(dst.ROW, src.ROW, (static_cast<size_t>(src.M) + 1) * 4, kind), "copy ROW");
+    if (src.NNZ) {
+        cuda_check(cudaMemcpy(dst.COL, src.COL, static_cast<size_t>(src.NNZ) * 4, kind), "copy COL");
+        cuda_check(cudaMemcpy(dst.V, src.V, static_cast<size_t>(src.NNZ) * 4, kind), "copy V");
+    }
+}
+
+}  // namespace
+
+void DeepAllocateSparseHost(SparseMatrix** sparseMatrixArray, uint32_t m, uint32_t n,
+                            const uint32_t nnz[], uint32_t numMatrices)
+{
+    SparseMatrix* h = static_cast<SparseMatrix*>(calloc(numMatrices ? numMatrices : 1, sizeof(SparseMatrix)));
+    if (!h)
+        throw std::bad_alloc();
+    for (uint32_t i = 0; i < numMatrices; ++i) {
+        const size_t k = nnz[i] ? nnz[i] : 1;
+        h[i].M = m;
+        h[i].N = n;
+        h[i].NNZ = nnz[i];
+        h[i].V = static_cast<float*>(calloc(k, 4));
+        h[i].COL = static_cast<uint32_t*>(calloc(k, 4));
+        h[i].ROW = static_cast<uint32_t*>(calloc(static_cast<size_t>(m) + 1, 4));
+        if (!h[i].V || !h[i].COL || !h[i].ROW) {
+            DeepFreeSparseHost(h, i + 1);
+            throw std::bad_alloc();
+        }
+    }
+    *sparseMatrixArray = h;
+}
+
+void DeepFreeSparseHost(SparseMatrix* sparseMatrixArray, uint32_t numMatrices)
+{
+    if (!sparseMatrixArray)
+        return;
+    for (uint32_t i = 0; i < numMatrices; ++i) {
+        free(sparseMatrixArray[i].V);
+        free(sparseMatrixArray[i].COL);
+        free(sparseMatrixArray[i].ROW);
+    }
+    free(sparseMatrixArray);
+}
+
+void DeepAllocateSparseCuda(SparseMatrix** deviceSparseArray, const SparseMatrix* hostSparseMatrixArray,
+                            uint32_t numMatrices, int deviceId)
+{
+    cuda_check(cudaSetDevice(deviceId), "cudaSetDevice");
+    std::vector<SparseMatrix> d(numMatrices);
+    try {
+        for (uint32_t i = 0; i < numMatrices; ++i) {
+            d[i] = hostSparseMatrixArray[i];
+            d[i].V = nullptr; d[i].COL = nullptr; d[i].ROW = nullptr;
+            const size_t k = d[i].NNZ ? d[i].NNZ : 1;
+            cuda_check(cudaMalloc(&d[i].V, k * 4), "alloc V");
+            cuda_check(cudaMalloc(&d[i].COL, k * 4), "alloc COL");
+            cuda_check(cudaMalloc(&d[i].ROW, (static_cast<size_t>(d[i].M) + 1) * 4), "alloc ROW");
+        }
+        void* arr = nullptr;
+        cuda_check(cudaMalloc(&arr, (numMatrices ? numMatrices : 1) * sizeof(SparseMatrix)),
+                   "alloc sparse descriptors");
+        if (numMatrices)
+            cuda_check(cudaMemcpy(arr, d.data(), numMatrices * sizeof(SparseMatrix), cudaMemcpyHostToDevice),
+                       "write sparse descriptors");
+        *deviceSparseArray = static_cast<SparseMatrix*>(arr);
+    } catch (...) {
+        for (auto& x : d)
+            sb200_csr_free(&x);
+        throw;
+    }
+}
+
+void DeepFreeSparseCuda(SparseMatrix* deviceSparseArray, uint32_t numMatrices, int deviceId)
+{
+    if (!deviceSparseArray)
+        return;
+    cuda_check(cudaSetDevice(deviceId), "cudaSetDevice");
+    auto d = fetch_descriptors(deviceSparseArray, numMatrices);
+    for (auto& x : d)
+        sb200_csr_free(&x);
+    cudaFree(deviceSparseArray);
+}
+
+void DeepCopyDeviceToDevice(SparseMatrix* deviceDstArray, SparseMatrix* deviceSrcArray,
+                            uint32_t numMatrices, int deviceId)
+{
+    cuda_check(cudaSetDevice(deviceId), "cudaSetDevice");
+    auto dst = fetch_descriptors(deviceDstArray, numMatrices);
+    const auto src = fetch_descriptors(deviceSrcArray, numMatrices);
+    for (uint32_t i = 0; i < numMatrices; ++i) {
+        copy_members(dst[i], src[i], cudaMemcpyDeviceToDevice);
+        dst[i].NNZ = src[i].NNZ;
+        dst[i].N = src[i].N;
+    }
+    if (numMatrices)
+        cuda_check(cudaMemcpy(deviceDstArray, dst.data(), numMatrices * sizeof(SparseMatrix),
+                              cudaMemcpyHostToDevice), "write sparse descriptors");
+}
+
+void DeepCopyHostToDevice(SparseMatrix* deviceDstArray, const SparseMatrix* hostSrcArray,
+                          uint32_t numMatrices, int deviceId)
+{
+    cuda_check(cudaSetDevice(deviceId), "cudaSetDevice");
+    auto dst = fetch_descriptors(deviceDstArray, numMatrices);
+    for (uint32_t i = 0; i < numMatrices; ++i) {
+        copy_members(dst[i], hostSrcArray[i], cudaMemcpyHostToDevice);
+        dst[i].NNZ = hostSrcArray[i].NNZ;
+        dst[i].N = hostSrcArray[i].N;
+    }
+    if (numMatrices)
+        cuda_check(cudaMemcpy(deviceDstArray, dst.data(), numMatrices * sizeof(SparseMatrix),
+                              cudaMemcpyHostToDevice), "write sparse descriptors");
+}
+
+void DeepCopyDeviceToHost(SparseMatrix* hostDstArray, SparseMatrix* deviceSrcArray,
+                          uint32_t numMatrices, int deviceId)
+{
+    cuda_check(cudaSetDevice(deviceId), "cudaSetDevice");
+    const auto src = fetch_descriptors(deviceSrcArray, numMatrices);
+    for (uint32_t i = 0; i < numMatrices; ++i) {
+        copy_members(hostDstArray[i], src[i], cudaMemcpyDeviceToHost);
+        hostDstArray[i].NNZ = src[i].NNZ;
+        hostDstArray[i].N = src[i].N;
+    }
+}
+
+void DeepCopyHostToHost(SparseMatrix* hostDstArray, SparseMatrix* hostSrcArray, uint32_t numMatrices)
+{
+    for (uint32_t i = 0; i < numMatrices; ++i) {
+        SparseMatrix& d = hostDstArray[i];
+        const SparseMatrix& s = hostSrcArray[i];
+        if (d.M != s.M || d.NNZ < s.NNZ)
+            throw std::runtime_error("DeepCopyHostToHost: destination matrix is smaller than the source");
+        std::copy(s.ROW, s.ROW + s.M + 1, d.ROW);
+        std::copy(s.COL, s.COL + s.NNZ, d.COL);
+        std::copy(s.V, s.V + s.NNZ, d.V);
+        d.NNZ = s.NNZ;
+        d.N = s.N;
+    }
+}
+
+}  // namespace Sapphire::Compute
+
+namespace Sapphire::Compute::Sparse::Naive {
+
+void Gemm(SparseMatrix** output, SparseMatrix* a, SparseMatrix* b, uint32_t m, uint32_t n,
+          size_t numMatrices)
+{
+    int deviceId = 0;
+    if (cudaGetDevice(&deviceId) != cudaSuccess)
+        throw std::runtime_error("Sparse::Naive::Gemm: no CUDA device (this build has no CPU path)");
+    const uint32_t count = static_cast<uint32_t>(numMatrices);
+    SparseMatrix *dA = nullptr, *dB = nullptr, *dC = nullptr;
+    try {
+        DeepAllocateSparseCuda(&dA, a, count, deviceId);
+        DeepAllocateSparseCuda(&dB, b, count, deviceId);
+        DeepCopyHostToDevice(dA, a, count, deviceId);
+        DeepCopyHostToDevice(dB, b, count, deviceId);
+        Cuda::Gemm(output, &dC, dA, dB, m, n, numMatrices, deviceId, true);
+    } catch (...) {
+        DeepFreeSparseCuda(dA, count, deviceId);
+        DeepFreeSparseCuda(dB, count, deviceId);
+        DeepFreeSparseCuda(dC, count, deviceId);
+        throw;
+    }
+    DeepFreeSparseCuda(dA, count, deviceId);
+    DeepFreeSparseCuda(dB, count, deviceId);
+    DeepFreeSparseCuda(dC, count, deviceId);
+}
+
+}  // namespace Sapphire::Compute::Sparse::Naive
+
 // ------------------------------------------------------------- C test hooks
 // These forward to the C++ shims and turn exceptions back into status codes so
 // that a ctypes caller can exercise the Sapphire-signature layer.
@@ -305,6 +503,75 @@ int sb200_compat_sparse_gemm(const sb200_csr* A, const sb200_csr* B, sb200_csr* 
     } catch (const std::exception&) {
         return SB200_ERR_CUDA;
     }
+}
+
+// Sapphire::Compute::Sparse::Naive::Gemm: host arrays in, host array out
+// (free the output with sb200_compat_deep_free_sparse_host).
+int sb200_compat_sparse_naive_gemm(sb200_csr** output, sb200_csr* a, sb200_csr* b, unsigned m,
+                                   unsigned n, size_t numMatrices)
+{
+    try {
+        Sapphire::Compute::Sparse::Naive::Gemm(output, a, b, m, n, numMatrices);
+        return SB200_OK;
+    } catch (const std::exception&) {
+        return SB200_ERR_CUDA;
+    }
+}
+
+// The deep allocate / free / copy family, one hook per function.
+#define SB200_COMPAT_GUARD(call)                 \
+    try {                                        \
+        call;                                    \
+        return SB200_OK;                         \
+    } catch (const std::bad_alloc&) {            \
+        return SB200_ERR_ALLOC;                  \
+    } catch (const std::exception&) {            \
+        return SB200_ERR_CUDA;                   \
+    }
+
+int sb200_compat_deep_allocate_sparse_host(sb200_csr** array, unsigned m, unsigned n,
+                                           const unsigned* nnz, unsigned numMatrices)
+{
+    SB200_COMPAT_GUARD(Sapphire::Compute::DeepAllocateSparseHost(array, m, n, nnz, numMatrices))
+}
+
+int sb200_compat_deep_free_sparse_host(sb200_csr* array, unsigned numMatrices)
+{
+    SB200_COMPAT_GUARD(Sapphire::Compute::DeepFreeSparseHost(array, numMatrices))
+}
+
+int sb200_compat_deep_allocate_sparse_cuda(sb200_csr** deviceArray, const sb200_csr* hostArray,
+                                           unsigned numMatrices, int deviceId)
+{
+    SB200_COMPAT_GUARD(Sapphire::Compute::DeepAllocateSparseCuda(deviceArray, hostArray, numMatrices, deviceId))
+}
+
+int sb200_compat_deep_free_sparse_cuda(sb200_csr* deviceArray, unsigned numMatrices, int deviceId)
+{
+    SB200_COMPAT_GUARD(Sapphire::Compute::DeepFreeSparseCuda(deviceArray, numMatrices, deviceId))
+}
+
+int sb200_compat_deep_copy_host_to_device(sb200_csr* deviceDst, const sb200_csr* hostSrc,
+                                          unsigned numMatrices, int deviceId)
+{
+    SB200_COMPAT_GUARD(Sapphire::Compute::DeepCopyHostToDevice(deviceDst, hostSrc, numMatrices, deviceId))
+}
+
+int sb200_compat_deep_copy_device_to_host(sb200_csr* hostDst, sb200_csr* deviceSrc,
+                                          unsigned numMatrices, int deviceId)
+{
+    SB200_COMPAT_GUARD(Sapphire::Compute::DeepCopyDeviceToHost(hostDst, deviceSrc, numMatrices, deviceId))
+}
+
+int sb200_compat_deep_copy_device_to_device(sb200_csr* deviceDst, sb200_csr* deviceSrc,
+                                            unsigned numMatrices, int deviceId)
+{
+    SB200_COMPAT_GUARD(Sapphire::Compute::DeepCopyDeviceToDevice(deviceDst, deviceSrc, numMatrices, deviceId))
+}
+
+int sb200_compat_deep_copy_host_to_host(sb200_csr* hostDst, sb200_csr* hostSrc, unsigned numMatrices)
+{
+    SB200_COMPAT_GUARD(Sapphire::Compute::DeepCopyHostToHost(hostDst, hostSrc, numMatrices))
 }
 
 }  // extern "C"

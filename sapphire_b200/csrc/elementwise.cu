@@ -78,7 +78,7 @@ __global__ void cross_entropy_kernel(float* __restrict__ loss, const float* __re
     if (i >= batch) return;
     float s = 0.0f;
     for (int j = 0; j < unit; ++j) {
-        const int idx = i * unit + j;
+        const int64_t idx = static_cast<int64_t>(i) * unit + j;
         const float v = x[idx] == 0.0f ? CE_FLOOR : x[idx];
         s = __fsub_rn(s, __fmul_rn(label[idx], logf(v)));
     }

@@ -2,6 +2,8 @@
 // tile constants, kernel parameters, the bounded mbarrier wait, the epilogue
 // store and the tensor-map builders.
 #pragma once
+#include <cstring>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -13,7 +15,7 @@ constexpr int BLOCK_K = 32;                     // fp32 elements = 128 bytes
 constexpr int UMMA_K = 8;                       // k per tcgen05.mma, kind::tf32
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 4;
 constexpr int CHUNK_BYTES = 32 * BLOCK_K * 4;   // one MN-major chunk: 32 k-rows x 128 B
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+constexpr uint64_t DEFAULT_WAIT_LIMIT_NS = 2000000000ull;   // a context option shortens it
 constexpr int SPLIT_CHUNK_KB = 8;               // 3xTF32: 256 k per tensor-core accumulation chain
 
 struct KernelParams {
@@ -34,6 +36,9 @@ struct KernelParams {
     const float* mask; long long ldm, strideM;  // ReLU-backward gate matrix or null
     float* owner[MAX_OWNERS];                   // reduce-scatter epilogue: row-block owners' buffers
     int rows_per_owner;                         // 0: plain store to D
+    unsigned long long wait_limit_ns;           // bound of every mbarrier wait
+    int test_stall_kb;                          // >= 0: the TMA producer stops after this many k-blocks
+                                                // (test hook: every other role's wait then runs out)
 };
 
 // What the epilogue does with an accumulator: D = post((C + bias) + acc), where
@@ -81,6 +86,7 @@ __device__ __forceinline__ void tile_coords(int r, int tiles_m, int tiles_n, int
 struct Abort {
     volatile int* flag;
     unsigned* status;
+    unsigned long long limit_ns;
 };
 
 __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, const Abort& ab,
@@ -94,7 +100,7 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, const A
         if ((++spins & 63u) == 0) {
             if (*ab.flag)
                 return false;
-            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (ptx::globaltimer_ns() - t0 > ab.limit_ns) {
                 *ab.flag = 1;
                 atomicCAS(ab.status, 0u, code);
                 return false;
@@ -164,16 +170,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Tensor map over a stack of row-major matrices: dim0 = contiguous extent,
-// dim1 = rows, dim2 = batch; box = 32 contiguous elements x box_rows x 1,
-// out-of-range elements read as zero.  K-major tiles use the plain 128-byte
-// swizzle; MN-major tiles the 128-byte swizzle with a 32-byte atom, the only
-// MN-major layout the tensor core reads for 32-bit operands.
-// The same for one warp's 32 rows x 32 columns, with lane-contiguous global
-// accesses.  After tcgen05.ld lane l holds 32 columns of row l; going through a
-// per-warp shared-memory tile (32 rows x 36 floats) the warp instead moves
-// 4 rows x 128 contiguous bytes per instruction: 8 lanes per row, one float4
-// each: lane l handles rows 4 i + l / 8 (i = 0..7), columns col0 + 4 (l % 8) .. + 3.
+// Coalesced epilogue store of one warp's 32 rows x 32 columns.  After
+// tcgen05.ld lane l holds 32 columns of row l; going through a per-warp
+// shared-memory tile (32 rows x 36 floats) the warp instead moves 4 rows x 128
+// contiguous bytes per instruction: 8 lanes per row, one float4 each: lane l
+// handles rows 4 i + l / 8 (i = 0..7), columns col0 + 4 (l % 8) .. + 3.
 // `row0` is the global row of lane 0's TMEM lane; D / C point at the matrix
 // origin of the batch.  Requires 16-byte aligned rows.
 //
@@ -479,6 +480,42 @@ __device__ __forceinline__ void colsum_finish(float4 acc4, float* scratch, int t
     }
 }
 
+// Looks the descriptor up in the context's cache; on a miss encodes it into the
+// least recently used slot.  `encode` fills a CUtensorMap and returns a CUresult.
+template <typename Encode>
+inline int cached_map(sb200_ctx* ctx, CUtensorMap* out, const TensorMapKey& key, Encode encode)
+{
+    TensorMapSlot* slots = ctx->tmaps;
+    int victim = 0;
+    uint64_t oldest = ~0ull;
+    for (int i = 0; i < TENSOR_MAP_SLOTS; ++i) {
+        if (slots[i].stamp && memcmp(&slots[i].key, &key, sizeof(key)) == 0) {
+            slots[i].stamp = ++ctx->tmap_clock;
+            ctx->tmap_hits += 1;
+            memcpy(out, &slots[i].map, sizeof(CUtensorMap));
+            return SB200_OK;
+        }
+        if (slots[i].stamp < oldest) {
+            oldest = slots[i].stamp;
+            victim = i;
+        }
+    }
+    ctx->tmap_misses += 1;
+    TensorMapSlot& v = slots[victim];
+    v.stamp = 0;
+    if (encode(&v.map) != CUDA_SUCCESS)
+        return SB200_ERR_CUDA;
+    v.key = key;
+    v.stamp = ++ctx->tmap_clock;
+    memcpy(out, &v.map, sizeof(CUtensorMap));
+    return SB200_OK;
+}
+
+// Tensor map over a stack of row-major matrices: dim0 = contiguous extent,
+// dim1 = rows, dim2 = batch; box = 32 contiguous elements x box_rows x 1,
+// out-of-range elements read as zero.  K-major tiles use the plain 128-byte
+// swizzle; MN-major tiles the 128-byte swizzle with a 32-byte atom, the only
+// MN-major layout the tensor core reads for 32-bit operands.
 inline int make_map(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t contig, int64_t rows,
              int64_t ld, int64_t batch, int64_t batch_stride, int box_rows, bool mn_major)
 {
@@ -486,17 +523,20 @@ inline int make_map(sb200_ctx* ctx, CUtensorMap* map, const float* base, int64_t
     if (!enc)
         return SB200_ERR_UNSUPPORTED;
     const int64_t nb = (batch_stride == 0) ? 1 : batch;
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(contig), static_cast<cuuint64_t>(rows),
-                          static_cast<cuuint64_t>(nb)};
     const int64_t bs = (batch_stride == 0 || nb == 1) ? rows * ld : batch_stride;
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4, static_cast<cuuint64_t>(bs) * 4};
-    cuuint32_t box[3] = {32, static_cast<cuuint32_t>(box_rows), 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
+    const TensorMapKey key{reinterpret_cast<uint64_t>(base), contig, rows, ld, nb, bs, box_rows,
+                           mn_major ? 1 : 0};
+    return cached_map(ctx, map, key, [&](CUtensorMap* m) {
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(contig), static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(nb)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4, static_cast<cuuint64_t>(bs) * 4};
+        cuuint32_t box[3] = {32, static_cast<cuuint32_t>(box_rows), 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    });
 }
 
 // MN-major operand whose contiguous extent is a multiple of 32: view it as
@@ -510,18 +550,18 @@ inline int make_map_merged(sb200_ctx* ctx, CUtensorMap* map, const float* base, 
     if (!enc)
         return SB200_ERR_UNSUPPORTED;
     const int64_t nb = (batch_stride == 0) ? 1 : batch;
-    cuuint64_t dims[4] = {32, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(contig / 32),
-                          static_cast<cuuint64_t>(nb)};
     const int64_t bs = (batch_stride == 0 || nb == 1) ? rows * ld : batch_stride;
-    cuuint64_t strides[3] = {static_cast<cuuint64_t>(ld) * 4, 128,
-                             static_cast<cuuint64_t>(bs) * 4};
-    cuuint32_t box[4] = {32, static_cast<cuuint32_t>(BLOCK_K), static_cast<cuuint32_t>(chunks), 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? SB200_OK : SB200_ERR_CUDA;
+    const TensorMapKey key{reinterpret_cast<uint64_t>(base), contig, rows, ld, nb, bs, chunks, 2};
+    return cached_map(ctx, map, key, [&](CUtensorMap* m) {
+        cuuint64_t dims[4] = {32, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(contig / 32),
+                              static_cast<cuuint64_t>(nb)};
+        cuuint64_t strides[3] = {static_cast<cuuint64_t>(ld) * 4, 128, static_cast<cuuint64_t>(bs) * 4};
+        cuuint32_t box[4] = {32, static_cast<cuuint32_t>(BLOCK_K), static_cast<cuuint32_t>(chunks), 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    });
 }
 
 }  // namespace gemm

@@ -97,7 +97,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const Abort ab{abort_flag, p.status};
+    const Abort ab{abort_flag, p.status, p.wait_limit_ns};
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -139,6 +139,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            int issued = 0;
             for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                 const int b = static_cast<int>(t / tiles_per_batch);
                 const int r = static_cast<int>(t % tiles_per_batch);
@@ -149,6 +150,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                 const int ba = p.a_batched ? b : 0;
                 const int bb = p.b_batched ? b : 0;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (p.test_stall_kb >= 0 && issued++ >= p.test_stall_kb) {
+                        ok = false;                        // test hook: the other roles' waits run out
+                        break;
+                    }
                     if (!(ok = wait_bar(&empty_bar[s], ph ^ 1u, ab, FAULT_PRODUCER_WAIT)))
                         break;
                     uint8_t* sa = smem + s * L::STAGE_BYTES;
@@ -558,6 +563,8 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     for (int o = 0; o < MAX_OWNERS; ++o) p.owner[o] = g.owner[o];
     p.rows_per_owner = static_cast<int>(g.rows_per_owner);
     p.status = ctx->d_status;
+    p.wait_limit_ns = ctx->wait_limit_ns;
+    p.test_stall_kb = ctx->test_stall_kb;
     p.explicit_hi = ctx->split_explicit_hi;
     p.colsum_out = COLSUM ? g.colsum_out : nullptr;
     p.colsum_scale = g.colsum_scale;
@@ -606,19 +613,20 @@ bool tcgen05_eligible(const GemmArgs& g)
         return false;
     if (!aligned16(g.A) || !aligned16(g.B))
         return false;
-    if ((g.lda & 3) || (g.ldb & 3) || (g.strideA & 3) || (g.strideB & 3))
+    if ((g.lda & 3) || (g.ldb & 3))
+        return false;
+    // a batch stride is only ever added to the base when there is a second batch
+    if (g.batch > 1 && ((g.strideA & 3) || (g.strideB & 3)))
         return false;
     if (g.strideA < 0 || g.strideB < 0)
         return false;
     return true;
 }
 
-int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
+namespace {
+
+int launch_one_cta(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 {
-    if (!tcgen05_eligible(g))
-        return SB200_ERR_UNSUPPORTED;
-    if (pair_kernel_preferred(ctx, g))
-        return launch_gemm_tcgen05_pair(ctx, g, stream);
     if (g.mode == SB200_MODE_TF32X3) {
         // 128-wide tiles: three raw stages plus a three-deep ring of low-part tiles
         return launch_layout<128, 3, true, false>(ctx, g, stream);
@@ -642,6 +650,67 @@ int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     if (bn == 256) return launch_layout<256, 4, false, false>(ctx, g, stream);
     if (bn == 128) return launch_layout<128, 6, false, false>(ctx, g, stream);
     return launch_layout<64, 8, false, false>(ctx, g, stream);
+}
+
+// Wave quantisation of the pair kernel.  Its tiles all take the same time, so T
+// tiles on P pairs cost ceil(T / P) waves: one 4096^3 product is 256 tiles on 74
+// pairs, 3.46 waves of work in the time of 4.  When the last wave would be
+// mostly empty the bottom rows of the product go to the one-CTA kernel instead
+// (128 x 256 tiles, one per SM, about 0.56 of a pair wave each): rows [0, m1)
+// stay on the pairs with m1 chosen so that they fill whole waves.  Returns m1
+// (== M: do not split).  Costs are in pair waves.
+int64_t pair_rows_before_tail(const sb200_ctx* ctx, const GemmArgs& g)
+{
+    if (g.rows_per_owner)                       // row numbers select the owner: keep one launch
+        return g.M;
+    const long long P = ctx->sm_count / 2, S = ctx->sm_count;
+    const long long tiles_m = (g.M + 255) / 256, tiles_n = (g.N + 255) / 256;
+    const long long T = tiles_m * tiles_n * g.batch;
+    const double whole = static_cast<double>((T + P - 1) / P);
+    if (whole > 8.0 || T % P == 0)
+        return g.M;                             // long runs lose little to the last wave
+    double best = whole * 0.93;                 // a second launch must buy a clear gain
+    int64_t best_m1 = g.M;
+    for (long long r = tiles_m - 1; r >= 1 && r >= tiles_m - 8; --r) {
+        const long long t1 = r * tiles_n * g.batch;
+        if (t1 < P)
+            break;
+        const long long rest_rows = g.M - r * 256;
+        const long long t2 = ((rest_rows + 127) / 128) * tiles_n * g.batch;
+        const double cost = static_cast<double>((t1 + P - 1) / P) +
+                            0.56 * static_cast<double>((t2 + S - 1) / S) + 0.08;
+        if (cost < best) {
+            best = cost;
+            best_m1 = r * 256;
+        }
+    }
+    return best_m1;
+}
+
+}  // namespace
+
+int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
+{
+    if (!tcgen05_eligible(g))
+        return SB200_ERR_UNSUPPORTED;
+    if (pair_kernel_preferred(ctx, g)) {
+        const int64_t m1 = ctx->split_tail_wave ? pair_rows_before_tail(ctx, g) : g.M;
+        if (m1 >= g.M)
+            return launch_gemm_tcgen05_pair(ctx, g, stream);
+        GemmArgs top = g;
+        top.M = m1;
+        const int rc = launch_gemm_tcgen05_pair(ctx, top, stream);
+        if (rc)
+            return rc;
+        GemmArgs rest = g;                      // rows [m1, M): same strides, shifted bases
+        rest.M = g.M - m1;
+        rest.A = g.transA ? g.A + m1 : g.A + m1 * g.lda;
+        if (g.C) rest.C = g.C + m1 * g.ldc;
+        rest.D = g.D + m1 * g.ldd;
+        if (g.mask) rest.mask = g.mask + m1 * g.ldmask;
+        return launch_one_cta(ctx, rest, stream);
+    }
+    return launch_one_cta(ctx, g, stream);
 }
 
 }  // namespace sb200

@@ -51,7 +51,7 @@ __device__ __forceinline__ bool wait_bar_cluster(uint64_t* bar, uint32_t parity,
         if ((++spins & 63u) == 0) {
             if (*ab.flag)
                 return false;
-            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (ptx::globaltimer_ns() - t0 > ab.limit_ns) {
                 *ab.flag = 1;
                 atomicCAS(ab.status, 0u, code);
                 return false;
@@ -82,7 +82,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();                // 0 = leader
-    const Abort ab{abort_flag, p.status};
+    const Abort ab{abort_flag, p.status, p.wait_limit_ns};
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PAIR_STAGES; ++s) {
@@ -118,6 +118,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            int issued = 0;
             for (long long t = pair_id; ok && t < p.total_tiles; t += n_pairs) {
                 const int b = static_cast<int>(t / tiles_per_batch);
                 const int r = static_cast<int>(t % tiles_per_batch);
@@ -128,6 +129,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
                 const int ba = p.a_batched ? b : 0;
                 const int bb = p.b_batched ? b : 0;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (p.test_stall_kb >= 0 && issued++ >= p.test_stall_kb) {
+                        ok = false;                        // test hook: the other roles' waits run out
+                        break;
+                    }
                     if (!(ok = wait_bar_cluster(&empty_bar[s], ph ^ 1u, ab, FAULT_PRODUCER_WAIT)))
                         break;
                     uint8_t* sa = smem + s * PAIR_STAGE_BYTES;
@@ -352,6 +357,8 @@ int launch_pair_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     for (int o = 0; o < MAX_OWNERS; ++o) p.owner[o] = g.owner[o];
     p.rows_per_owner = static_cast<int>(g.rows_per_owner);
     p.status = ctx->d_status;
+    p.wait_limit_ns = ctx->wait_limit_ns;
+    p.test_stall_kb = ctx->test_stall_kb;
     p.explicit_hi = 0;
     p.colsum_out = nullptr;
     p.colsum_scale = 0.0f;

@@ -736,6 +736,10 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
 {
     if (!ctx || !A || !B)
         return SB200_ERR_INVALID_ARG;
+    // the workspace below is allocated, and every later launch made, on the context's
+    // device whatever device the calling thread had current
+    if (cudaSetDevice(ctx->device) != cudaSuccess)
+        return SB200_ERR_CUDA;
     if (A->N != B->M)
         return SB200_ERR_INVALID_ARG;
     if (!A->ROW || !B->ROW || (A->NNZ && (!A->COL || !A->V)) || (B->NNZ && (!B->COL || !B->V)))

@@ -50,6 +50,9 @@ class Context:
     def launch_count(self) -> int:
         return L.lib().sb200_launch_count(self._h)
 
+    def counter(self, which: int) -> int:
+        return L.lib().sb200_ctx_counter(self._h, which)
+
     def set_option(self, option: int, value: int) -> None:
         L.check("sb200_ctx_set_option", L.lib().sb200_ctx_set_option(self._h, option, value))
 

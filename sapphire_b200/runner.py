@@ -249,8 +249,16 @@ class FusedWeightGradient:
             dist.all_reduce(self.tick, group=self.group)
 
     def start(self, x: torch.Tensor, dy: torch.Tensor, dw_full: torch.Tensor, db: torch.Tensor,
-              mode: int = 0) -> None:
+              mode: int = 0, total_rows: int = 0) -> None:
+        """``total_rows``: rows of the global batch when the ranks' shares differ
+        (0: every rank holds ``x.shape[0]`` rows)."""
         from . import ops
+        # the gather below must stay a copy-engine transfer: torch turns copy_ into
+        # cudaMemcpyAsync only between dense tensors of one dtype, anything else would
+        # become an elementwise kernel reading a peer mapping
+        if (dw_full.dtype != torch.float32 or not dw_full.is_contiguous()
+                or tuple(dw_full.shape) != (self.n_in, self.n_out)):
+            raise ValueError("dw_full must be a contiguous fp32 [n_in, n_out] tensor")
         cur, nxt = self.windows[self.turn % 3], self.windows[(self.turn + 1) % 3]
         self.turn += 1
         dev = torch.device("cuda", self.ctx.device)
@@ -258,7 +266,8 @@ class FusedWeightGradient:
         nxt.mine.zero_()
         # dB: 1 / (global batch), so that the SUM over ranks below is the mean over the batch
         ops.gemm_reduce_scatter(self.ctx, x, dy, cur.pointers, self.n_out, trans_a=True, mode=mode,
-                                colsum_out=db, colsum_scale=1.0 / (x.shape[0] * self.world))
+                                colsum_out=db,
+                                colsum_scale=1.0 / (total_rows or x.shape[0] * self.world))
         self._barrier()
         self.done.record(main)
         with torch.cuda.stream(self.side):

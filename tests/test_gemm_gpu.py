@@ -285,6 +285,119 @@ def test_config3_full_size_row_sample_and_linearity(ctx, oracle, n):
         del y, y0, alone
 
 
+@pytest.mark.parametrize("mode", [L.MODE_TF32, L.MODE_TF32X3])
+def test_config4_full_size_linear_backward(ctx, oracle, mode):
+    """dY [8192 x 4096], X [8192 x 4096], W [4096 x 4096] ~ N(0, 0.02): dx = dy.W^T
+    and dW = x^T.dy with the fused bias gradient, at the size the benchmark runs
+    (other kernel instances than the small case: the K = 8192 chain, the column-sum
+    warps over 32 row tiles, the panel tile order).  A sample of rows of dx and of
+    dW against the CPU loop, every element of dB."""
+    rows_total, width = 8192, 4096
+    dy, x, w = W.linear_backward(0, 0, rows_total, width, width)
+    tdy, tx, tw = dev(dy), dev(x), dev(w)
+    dx = ops.gemm(ctx, tdy, tw, trans_b=True, mode=mode)
+    db = torch.empty(width, device=DEV)
+    dw = ops.gemm(ctx, tx, tdy, trans_a=True, mode=mode, colsum_out=db,
+                  colsum_scale=1.0 / rows_total)
+    ctx.check_device_status()
+    assert ctx.last_path() == L.PATH_TCGEN05
+    rows = [0, 127, 128, 4095, 4096, 8191]
+    wt = np.ascontiguousarray(w.T)
+    want_dx = oracle.gemm(np.zeros((1, len(rows), width), np.float32), dy[rows][None], wt[None])[0]
+    assert rel_fro(dx[rows].cpu().numpy(), want_dx) <= TOL[mode]
+    wrows = [0, 1, 255, 256, 2049, 4095]                 # rows of dW = columns of x
+    xt = np.ascontiguousarray(x[:, wrows].T)
+    want_dw = oracle.gemm(np.zeros((1, len(wrows), width), np.float32), xt[None], dy[None])[0]
+    assert rel_fro(dw[wrows].cpu().numpy(), want_dw) <= TOL[mode]
+    assert rel_fro(db.cpu().numpy(), oracle.colsum(dy, 1.0 / rows_total)) <= 1e-5
+    assert rel_fro(db.cpu().numpy(), dy.astype(np.float64).sum(0) / rows_total) <= 1e-5
+
+
+@pytest.mark.parametrize("n", [4096, 4000])
+def test_single_product_tail_wave_split(ctx, oracle, n):
+    """One n^3 product is 256 pair tiles on 74 pairs of SMs: the bottom rows go to
+    a second launch of the one-CTA kernel.  The split result must meet the TF32 bar
+    on rows of both parts and agree with the unsplit launch to accumulation rounding."""
+    a, b, c = W.dense_batched(0, [0], n, n, n, "normal")
+    ta, tb, tc = dev(a[0]), dev(b[0]), dev(c[0])
+    before = ctx.launch_count()
+    y = ops.gemm(ctx, ta, tb, tc)
+    split_launches = ctx.launch_count() - before
+    ctx.set_option(L.OPT_SPLIT_TAIL_WAVE, 0)
+    before = ctx.launch_count()
+    y1 = ops.gemm(ctx, ta, tb, tc)
+    whole_launches = ctx.launch_count() - before
+    ctx.set_option(L.OPT_SPLIT_TAIL_WAVE, 1)
+    ctx.check_device_status()
+    assert (split_launches, whole_launches) == (2, 1)
+    rows = [0, 255, 3327, 3328, 3329, n - 129, n - 1]    # both sides of the cut at row 3328
+    want = oracle.gemm(c[0][rows][None], a[0][rows][None], b[0][None])[0]
+    assert rel_fro(y[rows].cpu().numpy(), want) <= 2e-3
+    assert rel_fro(y.cpu().numpy(), y1.cpu().numpy()) <= 1e-5
+    # in place (C aliases D) and with transposed A: the second launch shifts every base
+    yt = tc.clone()
+    ops.gemm(ctx, ta.t().contiguous(), tb, yt, yt, trans_a=True)
+    assert rel_fro(yt.cpu().numpy(), y1.cpu().numpy()) <= 1e-5
+
+
+def test_tensor_map_cache(ctx):
+    """A GEMM on operands the context has seen encodes no TMA descriptor."""
+    a = torch.randn(512, 256, device=DEV)
+    b = torch.randn(256, 384, device=DEV)
+    out = torch.empty(512, 384, device=DEV)
+    ops.gemm(ctx, a, b, None, out)
+    h0, m0 = ctx.counter(L.COUNTER_TENSOR_MAP_HITS), ctx.counter(L.COUNTER_TENSOR_MAP_MISSES)
+    for _ in range(5):
+        ops.gemm(ctx, a, b, None, out)
+    assert ctx.counter(L.COUNTER_TENSOR_MAP_MISSES) == m0
+    assert ctx.counter(L.COUNTER_TENSOR_MAP_HITS) == h0 + 10
+    # another shape at the same address is another descriptor
+    ops.gemm(ctx, a[:256], b, None, out[:256])
+    assert ctx.counter(L.COUNTER_TENSOR_MAP_MISSES) == m0 + 1       # A's; B's is reused
+    # more live descriptors than slots: the oldest are replaced, results stay right
+    outs = []
+    for i in range(70):
+        ai = torch.randn(128, 64 + 4 * i, device=DEV)
+        bi = torch.randn(64 + 4 * i, 128, device=DEV)
+        outs.append((ai, bi, ops.gemm(ctx, ai, bi, mode=L.MODE_TF32X3)))
+    for ai, bi, y in outs[::23]:
+        assert rel_fro(y.cpu().numpy(), ai.double().cpu().numpy() @ bi.double().cpu().numpy()) <= 1e-5
+    ctx.check_device_status()
+
+
+@pytest.mark.parametrize("shape", ["one_cta", "pair", "split_mode"])
+def test_bounded_wait_runs_out_and_context_survives(ctx, shape):
+    """The TMA producers stop after 3 k-blocks (test hook) with the wait limit at
+    2 ms: the MMA issuer's and the epilogue's waits run out, every role leaves
+    through the common exit, TMEM is released, and the host reads
+    SB200_ERR_DEVICE_TIMEOUT -- the error convention in place of the reference's
+    CHECK_CUBLAS.  The same context then runs a normal GEMM."""
+    if shape == "pair":
+        M, N, K, batch, mode = 1024, 512, 256, 40, L.MODE_TF32
+    elif shape == "one_cta":
+        M, N, K, batch, mode = 256, 256, 256, 4, L.MODE_TF32
+    else:
+        M, N, K, batch, mode = 256, 256, 512, 2, L.MODE_TF32X3
+    a = torch.randn(batch, M, K, device=DEV)
+    b = torch.randn(batch, K, N, device=DEV)
+    good = ops.gemm(ctx, a, b, mode=mode)
+    ctx.check_device_status()
+    ctx.set_option(L.OPT_WAIT_LIMIT_US, 2000)
+    ctx.set_option(L.OPT_TEST_STALL_KBLOCKS, 3)
+    try:
+        ops.gemm(ctx, a, b, mode=mode)
+        with pytest.raises(L.Sb200Error) as e:
+            ctx.check_device_status()
+        assert e.value.status == L.ERR_DEVICE_TIMEOUT
+    finally:
+        ctx.set_option(L.OPT_TEST_STALL_KBLOCKS, -1)
+        ctx.set_option(L.OPT_WAIT_LIMIT_US, 2000000)
+    ctx.check_device_status()                            # the word was cleared
+    again = ops.gemm(ctx, a, b, mode=mode)
+    ctx.check_device_status()
+    assert torch.equal(again, good)
+
+
 # ------------------------------------------------ Sapphire-signature shims
 def test_compat_dense_gemm_signature(ctx, oracle):
     """Sapphire::Compute::Dense::Cuda::Gemm(totalSize, out, A, B, M, N, K, deviceId)."""
@@ -294,6 +407,50 @@ def test_compat_dense_gemm_signature(ctx, oracle):
                                          64, 48, 32, 0)
     assert rc == L.OK
     assert rel_fro(out.cpu().numpy(), oracle.gemm(c, a, b)) <= 2e-3
+
+
+@pytest.mark.parametrize("bcA,bcB", [(True, False), (False, True)])
+def test_compat_gemm_matrixwise_broadcast_signature(ctx, oracle, bcA, bcB):
+    """Sapphire::Compute::Dense::Cuda::GemmMatrixWiseBroadcast(out, A, B, M, N, K,
+    batchSize, broadcastA, broadcastB, deviceId): out += A.B with one operand shared."""
+    M, N, K, batch = 96, 80, 64, 5
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((1 if bcA else batch, M, K)).astype(np.float32)
+    b = rng.standard_normal((1 if bcB else batch, K, N)).astype(np.float32)
+    c = rng.uniform(-1, 1, (batch, M, N)).astype(np.float32)
+    out, ta, tb = dev(c), dev(a), dev(b)
+    L.lib().sb200_compat_set_mode(L.MODE_TF32X3)
+    rc = L.lib().sb200_compat_dense_gemm_broadcast(out.data_ptr(), ta.data_ptr(), tb.data_ptr(),
+                                                   M, N, K, batch, int(bcA), int(bcB), 0)
+    L.lib().sb200_compat_set_mode(L.MODE_TF32)
+    assert rc == L.OK
+    want = oracle.gemm(c, np.broadcast_to(a, (batch, M, K)).copy(), np.broadcast_to(b, (batch, K, N)).copy())
+    assert rel_fro(out.cpu().numpy(), want) <= 1e-5
+
+
+@pytest.mark.parametrize("mode", [L.MODE_TF32, L.MODE_TF32X3])
+def test_matmul_backward_accumulates_with_transposed_operand(ctx, oracle, mode):
+    """MulBackProp (Sources/Sapphire/operations/Backward/MathBackward.cpp:46-50):
+    da <- da + dy.b^T and db <- db + a^T.dy, each ONE call that both accumulates in
+    place (C aliases D) and reads a transposed operand, batched."""
+    batch, M, K, N = 3, 160, 96, 200
+    rng = np.random.default_rng(22)
+    a = rng.standard_normal((batch, M, K)).astype(np.float32)
+    b = rng.standard_normal((batch, K, N)).astype(np.float32)
+    dy = rng.standard_normal((batch, M, N)).astype(np.float32)
+    da0 = rng.standard_normal((batch, M, K)).astype(np.float32)
+    db0 = rng.standard_normal((batch, K, N)).astype(np.float32)
+    bt = np.ascontiguousarray(np.swapaxes(b, 1, 2))
+    at = np.ascontiguousarray(np.swapaxes(a, 1, 2))
+    want_da = oracle.gemm(da0, dy, bt)
+    want_db = oracle.gemm(db0, at, dy)
+    da, db = dev(da0), dev(db0)
+    ops.gemm(ctx, dev(dy), dev(b), da, da, trans_b=True, mode=mode)
+    ops.gemm(ctx, dev(a), dev(dy), db, db, trans_a=True, mode=mode)
+    ctx.check_device_status()
+    assert ctx.last_path() == L.PATH_TCGEN05
+    assert rel_fro(da.cpu().numpy(), want_da) <= TOL[mode]
+    assert rel_fro(db.cpu().numpy(), want_db) <= TOL[mode]
 
 
 @pytest.mark.parametrize("ys,as_,bs", [

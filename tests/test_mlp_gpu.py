@@ -86,6 +86,50 @@ def test_mlp_training_matches_oracle(ctx, oracle, mode, tol):
     assert np.mean(got_loss[-1]) < np.mean(got_loss[0])
 
 
+_CURVE = {}
+
+
+def _oracle_curve(oracle, steps):
+    """The CPU oracle's loss curve and final state over `steps` steps at lr 1e-4
+    (computed once: about a second per step)."""
+    if steps not in _CURVE:
+        Ws, bs = W.mlp_init(0)
+        net = oracle.MlpOracle(Ws, bs, 1e-4)
+        losses = [net.step(*W.mlp_batch(t)) for t in range(steps)]
+        _CURVE[steps] = (net, np.stack(losses))
+    return _CURVE[steps]
+
+
+@pytest.mark.parametrize("mode,tol", [(L.MODE_TF32X3, 1e-5), (L.MODE_TF32, 2e-3)])
+def test_mlp_100_steps_match_oracle(ctx, oracle, mode, tol):
+    """The configured run length, 100 SGD steps, at lr 1e-4 (at the configured 0.01
+    the reference's own arithmetic leaves the finite range at step 3, see the next
+    test): loss curve, weights and biases against the CPU oracle in both modes.
+
+    Biases: a bias is lr times a sum over steps of a MEAN over 64 signed per-sample
+    gradients that largely cancel, so a rounding error of the gradients that is
+    1e-3 of their size is a much larger fraction of what is left after the
+    cancellation.  The bias error is therefore measured against the distance the
+    bias would have travelled without cancellation (lr * sum_t mean_i |dy_i|, from
+    the oracle), where it has to meet the same bar as everything else."""
+    steps = 100
+    net, want_loss = _oracle_curve(oracle, steps)
+    Ws, bs = W.mlp_init(0)
+    trainer = mlp.MlpTrainer(ctx, Ws, bs, 1e-4, mode=mode)
+    got_loss = []
+    for t in range(steps):
+        x, onehot = W.mlp_batch(t)
+        got_loss.append(trainer.step(dev(x), dev(onehot)).cpu().numpy())
+    ctx.check_device_status()
+    assert np.isfinite(want_loss).all()
+    assert rel(np.stack(got_loss), want_loss) <= tol
+    for l in range(3):
+        assert rel(trainer.W[l].cpu().numpy(), net.W[l]) <= tol
+        diff = np.linalg.norm(trainer.b[l].cpu().numpy().astype(np.float64) - net.b[l])
+        assert diff <= tol * np.linalg.norm(net.bias_travel[l]), (l, diff, np.linalg.norm(net.bias_travel[l]))
+    assert np.mean(got_loss[-1]) < np.mean(got_loss[0])
+
+
 def test_mlp_lr_0p01_diverges_like_the_reference(ctx, oracle):
     """At lr 0.01 Sapphire's own arithmetic (dW summed over the batch, not
     averaged; cross-entropy gradient label / x with x floored at 1.17549e-30)

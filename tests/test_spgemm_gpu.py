@@ -146,6 +146,114 @@ def test_config5_full_size_properties(ctx, dist):
     Bs = sp.csr_matrix((vB.astype(np.float64), cB, rB), shape=(N, N))
     want = As @ (Bs @ np.ones(N))
     assert np.abs(rowsum.cpu().numpy() - want).max() <= 1e-4
+    # two row blocks of the real product against the CPU oracle (full B): the first
+    # 2048 rows, and 2048 rows around the row of A with the most scalar products
+    from oracle import oracle as O
+    from sapphire_b200 import runner
+    work = W.csr_products(rA, cA, rB)
+    heavy = int(np.argmax(work))
+    lo = min(max(heavy - 1024, 0), M - 2048)
+    rowC = Cm.row.cpu().numpy().view(np.uint32).astype(np.int64)
+    for block in (range(0, 2048), range(lo, lo + 2048)):
+        rb, cb, vb = runner.csr_row_block(rA, cA, vA, block)
+        orow, ocol, oval, _ = O.spgemm(rb, cb, vb, rB, cB, vB, len(block), N)
+        p0, p1 = rowC[block.start], rowC[block.stop]
+        assert np.array_equal(rowC[block.start:block.stop + 1] - p0, orow.astype(np.int64)), "ROW differs"
+        assert np.array_equal(Cm.col[p0:p1].cpu().numpy().view(np.uint32), ocol), "COL differs"
+        got = Cm.val[p0:p1].cpu().numpy()
+        assert np.abs(got - oval).max() <= 1e-5 * max(np.abs(oval).max(), 1.0)
+
+
+def test_sparse_naive_gemm_signature_and_deep_copy_family(ctx, oracle):
+    """Sapphire::Compute::Sparse::Naive::Gemm(output, a, b, m, n, numMatrices) with host
+    arrays in and out, for two matrix pairs, and a round trip host -> device ->
+    device -> host through the deep allocate / copy / free family
+    (Includes/Sapphire/compute/sparse/Sparse.hpp)."""
+    lib = L.lib()
+    M = K = N = 700
+    mats = [(W.csr_random(10 + i, M, K, 0.01), W.csr_random(20 + i, K, N, 0.01)) for i in range(2)]
+    keep = []
+
+    def host_array(which):
+        arr = (L.Csr * 2)()
+        for i, pair in enumerate(mats):
+            r, c, v = (np.ascontiguousarray(x) for x in pair[which])
+            keep.extend([r, c, v])
+            arr[i].ROW, arr[i].COL, arr[i].V = r.ctypes.data, c.ctypes.data, v.ctypes.data
+            arr[i].NNZ, arr[i].M, arr[i].N = c.size, M, (K if which == 0 else N)
+        return arr
+
+    hA, hB = host_array(0), host_array(1)
+    out = C.POINTER(L.Csr)()
+    assert lib.sb200_compat_sparse_naive_gemm(C.byref(out), hA, hB, M, N, 2) == L.OK
+    for i, ((rA, cA, vA), (rB, cB, vB)) in enumerate(mats):
+        orow, ocol, oval, _ = oracle.spgemm(rA, cA, vA, rB, cB, vB, M, N)
+        m = out[i]
+        assert (m.M, m.N, m.NNZ) == (M, N, ocol.size)
+        as_np = lambda ptr, n, t: np.ctypeslib.as_array(C.cast(ptr, C.POINTER(t)), (n,))
+        assert np.array_equal(as_np(m.ROW, M + 1, C.c_uint32), orow)
+        assert np.array_equal(as_np(m.COL, m.NNZ, C.c_uint32), ocol)
+        assert np.abs(as_np(m.V, m.NNZ, C.c_float) - oval).max() <= 1e-5 * max(np.abs(oval).max(), 1.0)
+    assert lib.sb200_compat_deep_free_sparse_host(out, 2) == L.OK
+
+    # deep copy round trip of hA
+    d1, d2 = C.c_void_p(), C.c_void_p()
+    assert lib.sb200_compat_deep_allocate_sparse_cuda(C.byref(d1), hA, 2, 0) == L.OK
+    assert lib.sb200_compat_deep_allocate_sparse_cuda(C.byref(d2), hA, 2, 0) == L.OK
+    assert lib.sb200_compat_deep_copy_host_to_device(d1, hA, 2, 0) == L.OK
+    assert lib.sb200_compat_deep_copy_device_to_device(d2, d1, 2, 0) == L.OK
+    back = C.POINTER(L.Csr)()
+    nnz = (C.c_uint * 2)(hA[0].NNZ, hA[1].NNZ)
+    assert lib.sb200_compat_deep_allocate_sparse_host(C.byref(back), M, K, nnz, 2) == L.OK
+    assert lib.sb200_compat_deep_copy_device_to_host(back, d2, 2, 0) == L.OK
+    again = C.POINTER(L.Csr)()
+    assert lib.sb200_compat_deep_allocate_sparse_host(C.byref(again), M, K, nnz, 2) == L.OK
+    assert lib.sb200_compat_deep_copy_host_to_host(again, back, 2) == L.OK
+    for i, pair in enumerate(mats):
+        r, c, v = pair[0]
+        as_np = lambda ptr, n, t: np.ctypeslib.as_array(C.cast(ptr, C.POINTER(t)), (n,))
+        assert np.array_equal(as_np(again[i].ROW, M + 1, C.c_uint32), r)
+        assert np.array_equal(as_np(again[i].COL, c.size, C.c_uint32), c)
+        assert np.array_equal(as_np(again[i].V, v.size, C.c_float), v)
+    # a destination too small for the source is refused, not overrun
+    small = (C.c_uint * 2)(1, 1)
+    tiny = C.POINTER(L.Csr)()
+    assert lib.sb200_compat_deep_allocate_sparse_host(C.byref(tiny), M, K, small, 2) == L.OK
+    assert lib.sb200_compat_deep_copy_host_to_host(tiny, back, 2) != L.OK
+    for h in (back, again, tiny):
+        assert lib.sb200_compat_deep_free_sparse_host(h, 2) == L.OK
+    assert lib.sb200_compat_deep_free_sparse_cuda(d1, 2, 0) == L.OK
+    assert lib.sb200_compat_deep_free_sparse_cuda(d2, 2, 0) == L.OK
+
+
+def test_sparse_workspace_lives_on_the_context_device(oracle):
+    """A context of GPU 1 used while GPU 0 is current: the sparse work arrays must be
+    allocated on the context's device (needs two GPUs)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx1 = ops.Context(1)
+    torch.cuda.set_device(0)
+    M = N = 512
+    rA, cA, vA = W.csr_random(0, M, N, 0.02)
+    rB, cB, vB = W.csr_random(1, N, N, 0.02)
+    A = ops.CsrMatrix.from_numpy(rA, cA, vA, M, N, "cuda:1")
+    B = ops.CsrMatrix.from_numpy(rB, cB, vB, N, N, "cuda:1")
+    with torch.cuda.device(1):
+        free_before = torch.cuda.mem_get_info(1)[0]
+    with torch.cuda.device(0):
+        free0_before = torch.cuda.mem_get_info(0)[0]
+        torch.cuda.set_device(0)
+        a, b = A.as_struct(), B.as_struct()
+        row_c = torch.empty(M + 1, dtype=torch.int32, device="cuda:1")
+        nnz = C.c_int64(0)
+        st = torch.cuda.current_stream(torch.device("cuda:1")).cuda_stream
+        assert L.lib().sb200_spgemm_csr_symbolic(ctx1.handle, C.byref(a), C.byref(b), row_c.data_ptr(),
+                                                 C.byref(nnz), st) == L.OK
+        free0_after = torch.cuda.mem_get_info(0)[0]
+    orow, _, _, _ = oracle.spgemm(rA, cA, vA, rB, cB, vB, M, N)
+    assert np.array_equal(row_c.cpu().numpy().view(np.uint32), orow)
+    assert free0_after == free0_before                   # nothing was allocated on GPU 0
+    torch.cuda.set_device(0)
 
 
 def test_dense_csr_round_trip_and_product(ctx, oracle):

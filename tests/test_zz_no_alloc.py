@@ -62,6 +62,31 @@ def test_noalloc_colsum_matches_existing_entry_point_twice(ctx):
     assert rel(got, b.double().sum(1) * 0.5) <= 1e-5
 
 
+def test_noalloc_colsum_allocates_nothing_and_clamps_slices(ctx):
+    """What the entry point is for: after a first call (which looks up the scratch
+    array's address) further calls leave the device's free memory unchanged.  The
+    second shape, few columns and many rows, asks for more row slices than the
+    array has (64): the clamp and the empty trailing slices are exercised."""
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(5)
+    dy = torch.randn(4096, 1024, device=DEV, generator=g)
+    tall = torch.randn(16384, 64, device=DEV, generator=g)
+    out = torch.empty(1024, device=DEV)
+    out2 = torch.empty(64, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    lib = L.lib()
+    assert lib.sb200_colsum_noalloc(dy.data_ptr(), 0, 4096, 1024, 1024, out.data_ptr(), 1.0, st) == L.OK
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(0)[0]
+    assert lib.sb200_colsum_noalloc(dy.data_ptr(), 0, 4096, 1024, 1024, out.data_ptr(), 0.25, st) == L.OK
+    assert lib.sb200_colsum_noalloc(tall.data_ptr(), 0, 16384, 64, 64, out2.data_ptr(), 1.0, st) == L.OK
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(0)[0] == free_before
+    assert rel(out, dy.double().sum(0) * 0.25) <= 1e-5
+    assert rel(out2, tall.double().sum(0)) <= 1e-5
+
+
 def test_noalloc_colsum_limits():
     torch.cuda.set_device(0)
     lib = L.lib()
