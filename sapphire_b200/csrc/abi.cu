@@ -69,6 +69,7 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->sp_pattern_bytes = 0;
     ctx->sp_valid = 0;
     ctx->sp_work_valid = 0;
+    ctx->sp_fast_mid = 1;
     ctx->d_status = nullptr;
     if (cudaMalloc(&ctx->d_status, sizeof(unsigned)) != cudaSuccess ||
         cudaMemset(ctx->d_status, 0, sizeof(unsigned)) != cudaSuccess) {
@@ -158,6 +159,9 @@ extern "C" int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value)
             if (value < 100)
                 return SB200_ERR_INVALID_ARG;
             ctx->wait_limit_ns = static_cast<uint64_t>(value) * 1000ull;
+            return SB200_OK;
+        case SB200_OPT_SPGEMM_FAST_MID:
+            ctx->sp_fast_mid = value != 0;
             return SB200_OK;
         case SB200_OPT_TEST_STALL_KBLOCKS:
             ctx->test_stall_kb = value < 0 ? -1 : value;

@@ -99,6 +99,7 @@ struct sb200_ctx {
     sb200::SpPatternKey sp_key;
     int sp_valid;
     int sp_work_valid;         // ... and its per-row / per-nonzero arrays are still in the workspace
+    int sp_fast_mid;           // sparse GEMM: rows of the mid bin run on the kernels specialised for N <= 65536
 };
 
 namespace sb200 {

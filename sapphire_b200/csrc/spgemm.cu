@@ -92,10 +92,9 @@ __device__ __forceinline__ void queue_heavy(const Work& w, uint32_t M, uint32_t 
 // value buffer also goes to the heavy bin, whose kernel has a large one.
 __global__ void __launch_bounds__(256)
 row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
-                    const uint32_t* __restrict__ rowC, uint32_t n_cols, uint32_t heavy_cap)
+                    const uint32_t* __restrict__ rowC, uint32_t cap, uint32_t heavy_cap)
 {
     const int lane = threadIdx.x & 31;
-    const uint32_t cap = mid_cap(n_cols);
     const uint32_t warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const uint32_t nwarps = (gridDim.x * blockDim.x) >> 5;
     for (uint32_t i = warp_global; i < A.M; i += nwarps) {
@@ -142,9 +141,8 @@ row_products_kernel(Csr A, const uint32_t* __restrict__ rowB, Work w,
 // The bins again, from the product counts a previous row_products_kernel left in
 // the workspace, now that the output row sizes are known (one thread per row).
 __global__ void __launch_bounds__(256)
-rebin_kernel(Csr A, Work w, const uint32_t* __restrict__ rowC, uint32_t n_cols, uint32_t heavy_cap)
+rebin_kernel(Csr A, Work w, const uint32_t* __restrict__ rowC, uint32_t cap, uint32_t heavy_cap)
 {
-    const uint32_t cap = mid_cap(n_cols);
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < A.M; i += gridDim.x * blockDim.x) {
         const uint32_t P = w.prod[i];
         if (P == 0)
@@ -669,14 +667,379 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
     }
 }
 
+// ------------------------------------------- mid rows, N <= 65536 columns
+// The bulk of a sparse product: rows with 33 .. 16383 scalar products whose output
+// fits one shared-memory window.  Same two passes and the same bitmap idea as the
+// general row kernel above, rebuilt around what bounds it -- the LSU data pipe
+// (shared-memory wavefronts: a 32-lane access to random banks takes ~3.5, an
+// atomic ~9) and instruction issue:
+//
+//   * rank table: one 4-byte word per group of 16 columns, {pattern bits 0-15,
+//     rank of the group's first column bits 16-28, "group has a column hit by more
+//     than one product" bit 31}: a lookup is ONE 4-byte access (8-byte words are
+//     served half a warp at a time).  Ranks fit 13 bits because the window does.
+//   * accumulation without atomics wherever possible.  The symbolic pass notices
+//     when a product's column bit was already set and flags the column's group in a
+//     second, small bitmap (128 words per row) that is kept with the row bitmap.
+//     In the numeric pass a product of an unflagged group is the only one of its
+//     column: it stores its value.  Products of flagged groups (3 % of the columns
+//     of a 0.1 % dense product collide) swap themselves into the accumulator with
+//     atomicExch and, if they displaced a partial sum, take the slot's content out,
+//     add, and put the sum back until nothing was displaced.  fp32 atomicAdd in
+//     shared memory is a compare-and-swap loop, the most expensive step per product.
+//   * the product walk: 16 lanes per nonzero of A stream that row of B, five
+//     chunks of 16 entries in flight (immediate offsets from one base pointer), each
+//     chunk skipped as soon as both lane groups of the warp are past their row's
+//     end; rows of B of up to 4 entries are done by single threads, rows of 256 and
+//     more by the whole CTA.  One ballot-compacted list per 256 nonzeros of A; no
+//     scan, no per-piece descriptors.
+//   * the next row's kept bitmaps and per-nonzero arrays are loaded into registers
+//     while the current row is walked, so a row starts without a trip to HBM.
+constexpr int MID_THREADS = 256;
+constexpr uint32_t MID_WORDS = 2048;        // bitmap words of 65536 columns
+constexpr uint32_t DUP_WORDS = MID_WORDS / 16;   // one bit per group of 16 columns
+constexpr uint32_t MID_SHORT = 4;
+constexpr uint32_t MID_LONG = 256;
+constexpr uint32_t MID_BATCH = 8;           // rows fetched per atomic
+constexpr int MID_CHUNKS = 5;               // chunks of 16 entries in flight per lane group
+constexpr uint32_t NO_COL = 0xffffffffu;
+constexpr uint32_t FAST_MID_CAP = 6208;     // output entries per row: 4 CTAs of 56.5 KB per SM
+constexpr uint32_t DUP_FLAG = 0x80000000u;
+
+// physical index of rank-table word `g` (group of 16 columns).  Thread t writes
+// words 16 t .. 16 t + 15 with four 16-byte stores; a plain layout would put the
+// lanes of one store 64 bytes apart, on two of the eight 16-byte bank groups.  Each
+// thread permutes its own four 16-byte slots instead: slot ^= (t >> 1) & 3.
+__device__ __forceinline__ uint32_t rank_word(uint32_t g) { return g ^ ((g >> 3) & 12u); }
+
+struct MidEntry {
+    uint32_t qs, len;
+    float a;
+};
+
+template <bool NUMERIC>
+struct MidSmem {
+    uint32_t* table;       // symbolic: bitmap[MID_WORDS] + group flags[DUP_WORDS]; numeric: rank words [2 * MID_WORDS]
+    uint32_t* l_qs;        // [256] lists of one block of A's nonzeros: mid rows of B from slot 0 up,
+    uint32_t* l_len;       // [256] long rows from slot 255 down
+    float* l_a;            // [256]
+    uint32_t* vals;        // [val_cap + 4] accumulators (fp32 bit patterns)
+    uint16_t* cols;        // [val_cap + 4]
+};
+
+// U scalar products of one thread: columns c[] (NO_COL = none), B's values v[], A's value a.
+template <bool NUMERIC, int U>
+__device__ __forceinline__ void mid_products(const MidSmem<NUMERIC>& sm, const uint32_t (&c)[U],
+                                             const float (&v)[U], float a)
+{
+    if constexpr (!NUMERIC) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (c[u] == NO_COL) continue;
+            const uint32_t bit = 1u << (c[u] & 31u);
+            const uint32_t old = atomicOr(&sm.table[c[u] >> 5], bit);
+            if (old & bit)                                         // second product of this column
+                atomicOr(&sm.table[MID_WORDS + (c[u] >> 9)], 1u << ((c[u] >> 4) & 31u));
+        }
+    } else {
+        uint32_t rw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            rw[u] = c[u] != NO_COL ? sm.table[rank_word(c[u] >> 4)] : 0u;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (c[u] == NO_COL) continue;
+            const uint32_t below = (1u << (c[u] & 15u)) - 1u;
+            const uint32_t slot = ((rw[u] >> 16) & 0x1fffu) + __popc(rw[u] & below);
+            const uint32_t p = __float_as_uint(__fmul_rn(a, v[u]));
+            sm.cols[slot] = static_cast<uint16_t>(c[u]);
+            if (!(rw[u] & DUP_FLAG)) {
+                sm.vals[slot] = p;                                 // the only product of its column
+            } else {
+                uint32_t* acc = sm.vals + slot;
+                uint32_t old = atomicExch(acc, p);
+                while (old != 0u) {
+                    // displaced a partial sum: take what is there now, add, put back
+                    const uint32_t cur = atomicExch(acc, 0u);
+                    const float sum = __fadd_rn(__uint_as_float(old), __uint_as_float(cur));
+                    old = atomicExch(acc, __float_as_uint(sum));
+                }
+            }
+        }
+    }
+}
+
+// One row of B, [qs, qs + len), walked by `width` threads of which this is number
+// `me`: MID_CHUNKS chunks of `width` entries in flight, then one chunk at a time.
+template <bool NUMERIC>
+__device__ __forceinline__ void mid_walk_row(const MidSmem<NUMERIC>& sm, const Csr& B, uint32_t qs,
+                                             uint32_t len, float a, uint32_t me, uint32_t width)
+{
+    const uint32_t* pc = B.col + qs + me;
+    const float* pv = B.val + qs + me;
+    uint32_t c[MID_CHUNKS];
+    float v[MID_CHUNKS];
+#pragma unroll
+    for (int u = 0; u < MID_CHUNKS; ++u) {
+        const bool on = me + u * width < len;
+        c[u] = NO_COL;
+        v[u] = 0.0f;
+        if (on) {
+            c[u] = __ldg(pc + u * width);
+            if (NUMERIC) v[u] = __ldg(pv + u * width);
+        }
+    }
+    mid_products<NUMERIC, MID_CHUNKS>(sm, c, v, a);
+    for (uint32_t q = MID_CHUNKS * width + me; q < len; q += width) {
+        const uint32_t c1[1] = {__ldg(B.col + qs + q)};
+        const float v1[1] = {NUMERIC ? __ldg(B.val + qs + q) : 0.0f};
+        mid_products<NUMERIC, 1>(sm, c1, v1, a);
+    }
+}
+
+template <bool NUMERIC>
+__global__ void __launch_bounds__(MID_THREADS, NUMERIC ? 4 : 5)
+mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
+                const uint32_t* __restrict__ n_rows_ptr, uint32_t* __restrict__ next_row,
+                uint32_t pitch, uint32_t val_cap, int vec_ok, uint32_t* __restrict__ pattern,
+                uint32_t* __restrict__ dupmap, const uint32_t* __restrict__ rowC,
+                uint32_t* __restrict__ colC, float* __restrict__ valC)
+{
+    extern __shared__ uint4 sm4[];
+    MidSmem<NUMERIC> sm;
+    sm.table = reinterpret_cast<uint32_t*>(sm4);
+    sm.l_qs = sm.table + (NUMERIC ? 2 * MID_WORDS : MID_WORDS + DUP_WORDS);
+    sm.l_len = sm.l_qs + 256;
+    sm.l_a = reinterpret_cast<float*>(sm.l_len + 256);
+    sm.vals = reinterpret_cast<uint32_t*>(sm.l_a + 256);
+    sm.cols = reinterpret_cast<uint16_t*>(sm.vals + (NUMERIC ? val_cap + 4 : 0));
+    __shared__ uint32_t s_warp[MID_THREADS / 32];
+    __shared__ uint32_t s_next, s_n_mid, s_n_long;
+    __shared__ uint4 s_desc[MID_BATCH];
+    __shared__ uint32_t s_out0[MID_BATCH];
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t sub = tid & 15u, half = tid >> 4;              // lane group of 16 and its index
+    const uint32_t n_rows = *n_rows_ptr;
+    const bool own_words = tid * 8u < pitch;                      // this thread's 8 bitmap words exist
+
+    // what a row needs from global memory before it can start: its kept bitmaps (numeric)
+    // and the first 256 of its per-nonzero records
+    auto load_inputs = [&](const uint4& d, uint4& p0, uint4& p1, uint32_t& dup, MidEntry& e) {
+        if (NUMERIC) {
+            p0 = p1 = make_uint4(0u, 0u, 0u, 0u);
+            dup = 0;
+            if (own_words) {
+                const uint4* src = reinterpret_cast<const uint4*>(pattern + static_cast<size_t>(d.x) * pitch + tid * 8u);
+                p0 = src[0];
+                p1 = src[1];
+                dup = dupmap[static_cast<size_t>(d.x) * DUP_WORDS + (tid >> 1)];
+            }
+        }
+        e.len = 0; e.qs = 0; e.a = 0.0f;
+        if (d.y + tid < d.z) {
+            e.qs = w.bq[d.y + tid];
+            e.len = w.blen[d.y + tid];
+            if (NUMERIC) e.a = A.val[d.y + tid];
+        }
+    };
+
+    for (;;) {
+        __syncthreads();                                          // previous batch done with s_desc
+        if (tid == 0) s_next = atomicAdd(next_row, MID_BATCH);
+        __syncthreads();
+        const uint32_t first = s_next;
+        if (first >= n_rows)
+            break;
+        const uint32_t end = min(first + MID_BATCH, n_rows);
+        if (tid < end - first) {
+            const uint4 d = rows[first + tid];
+            s_desc[tid] = d;
+            s_out0[tid] = NUMERIC ? rowC[d.x] : 0u;
+        }
+        __syncthreads();
+        uint4 pat0, pat1;
+        uint32_t dupw = 0;
+        MidEntry ent;
+        load_inputs(s_desc[0], pat0, pat1, dupw, ent);
+
+        for (uint32_t idx = first; idx < end; ++idx) {
+            const uint4 d = s_desc[idx - first];
+            const uint32_t i = d.x, pa = d.y, pe = d.z;
+            const uint32_t out0 = s_out0[idx - first];
+            // the next row's inputs travel while this row is worked on
+            uint4 npat0 = make_uint4(0u, 0u, 0u, 0u), npat1 = npat0;
+            uint32_t ndupw = 0;
+            MidEntry nent{0u, 0u, 0.0f};
+            if (idx + 1 < end)
+                load_inputs(s_desc[idx + 1 - first], npat0, npat1, ndupw, nent);
+
+            const uint32_t shift = out0 & 3u;
+            uint32_t total = 0;
+            if (tid == 0) {
+                s_n_mid = 0;
+                s_n_long = 0;
+            }
+            if constexpr (NUMERIC) {
+                // ---- rank table from the kept bitmaps
+                const uint32_t bits[8] = {pat0.x, pat0.y, pat0.z, pat0.w, pat1.x, pat1.y, pat1.z, pat1.w};
+                uint32_t c = 0;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) c += __popc(bits[k]);
+                uint32_t run = shift + block_exclusive_scan<MID_THREADS>(c, s_warp, total);
+                if (own_words) {
+                    // this thread's 16 groups are one half of its flag word
+                    const uint32_t flags = (tid & 1u) ? dupw >> 16 : dupw & 0xffffu;
+                    auto word = [&](uint32_t half_bits, int g) -> uint32_t {
+                        const uint32_t o = half_bits | (run << 16) | (((flags >> g) & 1u) << 31);
+                        run += __popc(half_bits);
+                        return o;
+                    };
+#pragma unroll
+                    for (int k = 0; k < 8; k += 2) {
+                        uint4 o;
+                        o.x = word(bits[k] & 0xffffu, 2 * k);
+                        o.y = word(bits[k] >> 16, 2 * k + 1);
+                        o.z = word(bits[k + 1] & 0xffffu, 2 * k + 2);
+                        o.w = word(bits[k + 1] >> 16, 2 * k + 3);
+                        const uint32_t slot = tid * 4u + (k >> 1);
+                        sm4[slot ^ ((slot >> 3) & 3u)] = o;
+                    }
+                }
+                const uint32_t lim4 = (total + shift + 3u) / 4u;
+                uint4* vz = reinterpret_cast<uint4*>(sm.vals);
+                for (uint32_t x = tid; x < lim4; x += MID_THREADS) vz[x] = make_uint4(0u, 0u, 0u, 0u);
+            } else {
+                for (uint32_t x = tid; x < (MID_WORDS + DUP_WORDS) / 4; x += MID_THREADS)
+                    sm4[x] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncthreads();
+
+            // ---- the products, 256 nonzeros of A at a time
+            for (uint32_t p0 = pa; p0 < pe; p0 += MID_THREADS) {
+                MidEntry e = ent;
+                if (p0 != pa) {
+                    __syncthreads();                              // lists of the previous block consumed
+                    if (tid == 0) {
+                        s_n_mid = 0;
+                        s_n_long = 0;
+                    }
+                    e.len = 0; e.qs = 0; e.a = 0.0f;
+                    if (p0 + tid < pe) {
+                        e.qs = w.bq[p0 + tid];
+                        e.len = w.blen[p0 + tid];
+                        if (NUMERIC) e.a = A.val[p0 + tid];
+                    }
+                    __syncthreads();
+                }
+                const bool is_mid = e.len > MID_SHORT && e.len < MID_LONG;
+                const bool is_long = e.len >= MID_LONG;
+                const uint32_t mm = __ballot_sync(0xffffffffu, is_mid);
+                const uint32_t ml = __ballot_sync(0xffffffffu, is_long);
+                const uint32_t below = (1u << lane) - 1u;
+                if (mm) {
+                    uint32_t base = 0;
+                    if (lane == 0) base = atomicAdd(&s_n_mid, __popc(mm));
+                    base = __shfl_sync(0xffffffffu, base, 0);
+                    if (is_mid) {
+                        const uint32_t at = base + __popc(mm & below);
+                        sm.l_qs[at] = e.qs; sm.l_len[at] = e.len; sm.l_a[at] = e.a;
+                    }
+                }
+                if (ml) {
+                    uint32_t base = 0;
+                    if (lane == 0) base = atomicAdd(&s_n_long, __popc(ml));
+                    base = __shfl_sync(0xffffffffu, base, 0);
+                    if (is_long) {
+                        const uint32_t at = 255u - (base + __popc(ml & below));
+                        sm.l_qs[at] = e.qs; sm.l_len[at] = e.len; sm.l_a[at] = e.a;
+                    }
+                }
+                // short rows of B: this thread alone, straight from its registers
+                if (e.len != 0 && e.len <= MID_SHORT) {
+                    uint32_t c[MID_SHORT];
+                    float v[MID_SHORT];
+#pragma unroll
+                    for (uint32_t u = 0; u < MID_SHORT; ++u) {
+                        const bool on = u < e.len;
+                        c[u] = on ? __ldg(B.col + e.qs + u) : NO_COL;
+                        v[u] = (NUMERIC && on) ? __ldg(B.val + e.qs + u) : 0.0f;
+                    }
+                    mid_products<NUMERIC, MID_SHORT>(sm, c, v, e.a);
+                }
+                __syncthreads();
+                // rows of B of 5 .. 255 entries: 16 lanes each
+                const uint32_t n_mid = s_n_mid;
+                for (uint32_t it = half; it < n_mid; it += MID_THREADS / 16)
+                    mid_walk_row<NUMERIC>(sm, B, sm.l_qs[it], sm.l_len[it], sm.l_a[it], sub, 16u);
+                // rows of B of 256 entries and more: the whole CTA
+                const uint32_t n_long = s_n_long;
+                for (uint32_t l = 0; l < n_long; ++l)
+                    mid_walk_row<NUMERIC>(sm, B, sm.l_qs[255u - l], sm.l_len[255u - l], sm.l_a[255u - l], tid,
+                                          MID_THREADS);
+            }
+            __syncthreads();
+
+            if constexpr (!NUMERIC) {
+                // ---- count, and keep the bitmaps for the numeric pass
+                uint32_t c = 0;
+                if (own_words) {
+                    const uint4 b0 = sm4[tid * 2u], b1 = sm4[tid * 2u + 1u];
+                    c = __popc(b0.x) + __popc(b0.y) + __popc(b0.z) + __popc(b0.w) +
+                        __popc(b1.x) + __popc(b1.y) + __popc(b1.z) + __popc(b1.w);
+                    if (pattern) {
+                        uint4* dst = reinterpret_cast<uint4*>(pattern + static_cast<size_t>(i) * pitch + tid * 8u);
+                        dst[0] = b0;
+                        dst[1] = b1;
+                    }
+                }
+                if (pattern && tid < DUP_WORDS)
+                    dupmap[static_cast<size_t>(i) * DUP_WORDS + tid] = sm.table[MID_WORDS + tid];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+                if (lane == 0) s_warp[warp] = c;
+                __syncthreads();
+                if (tid == 0) {
+                    uint32_t t = 0;
+#pragma unroll
+                    for (int x = 0; x < MID_THREADS / 32; ++x) t += s_warp[x];
+                    w.cnt[i] = t;
+                }
+            } else {
+                // ---- the window goes out with 16-byte stores
+                const uint32_t lim = total + shift;
+                uint32_t* gcol = colC + (out0 - shift);           // slot s <-> gcol[s]; 16-byte aligned
+                uint32_t* gval = reinterpret_cast<uint32_t*>(valC) + (out0 - shift);
+                for (uint32_t q = tid; q < (lim + 3u) / 4u; q += MID_THREADS) {
+                    const uint32_t s0 = q * 4u;
+                    if (vec_ok && s0 >= shift && s0 + 4u <= lim) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(sm.cols + s0);
+                        *reinterpret_cast<uint4*>(gcol + s0) =
+                            make_uint4(raw.x & 0xffffu, raw.x >> 16, raw.y & 0xffffu, raw.y >> 16);
+                        *reinterpret_cast<uint4*>(gval + s0) = *reinterpret_cast<const uint4*>(sm.vals + s0);
+                    } else {
+                        for (uint32_t s = max(s0, shift); s < min(s0 + 4u, lim); ++s) {
+                            gcol[s] = sm.cols[s];
+                            gval[s] = sm.vals[s];
+                        }
+                    }
+                }
+            }
+            __syncthreads();                                      // shared memory free for the next row
+            pat0 = npat0; pat1 = npat1; dupw = ndupw; ent = nent;
+        }
+    }
+}
+
 // --------------------------------------------------------------- row scan
-// rowC[0] = 0, rowC[i+1] = sum cnt[0..i]; one CTA, chunks of 8192 counts (eight
-// consecutive ones per thread, read with two 16-byte loads) with a carry.
+// rowC[0] = 0, rowC[i+1] = sum cnt[0..i]; one CTA, chunks of 32768 counts (32
+// consecutive ones per thread, all eight 16-byte loads of a chunk in flight together)
+// with a carry.
 __global__ void __launch_bounds__(1024)
 row_scan_kernel(const uint32_t* __restrict__ cnt, uint32_t M, uint32_t* __restrict__ rowC,
                 unsigned long long* __restrict__ total_out)
 {
-    constexpr uint32_t PER = 8;
+    constexpr uint32_t PER = 32;
     __shared__ unsigned long long s_warp[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) rowC[0] = 0;
@@ -685,10 +1048,13 @@ row_scan_kernel(const uint32_t* __restrict__ cnt, uint32_t M, uint32_t* __restri
         const uint32_t i0 = base + threadIdx.x * PER;
         uint32_t v[PER];
         if (i0 + PER <= M) {                                      // cnt is 16-byte aligned
-            const uint4 lo = *reinterpret_cast<const uint4*>(cnt + i0);
-            const uint4 hi = *reinterpret_cast<const uint4*>(cnt + i0 + 4);
-            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
-            v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+            uint4 q[PER / 4];
+#pragma unroll
+            for (uint32_t k = 0; k < PER / 4; ++k) q[k] = *reinterpret_cast<const uint4*>(cnt + i0 + 4 * k);
+#pragma unroll
+            for (uint32_t k = 0; k < PER / 4; ++k) {
+                v[4 * k] = q[k].x; v[4 * k + 1] = q[k].y; v[4 * k + 2] = q[k].z; v[4 * k + 3] = q[k].w;
+            }
         } else {
 #pragma unroll
             for (uint32_t k = 0; k < PER; ++k) v[k] = i0 + k < M ? cnt[i0 + k] : 0u;
@@ -713,6 +1079,8 @@ row_scan_kernel(const uint32_t* __restrict__ cnt, uint32_t M, uint32_t* __restri
             chunk_total += t;
         }
         unsigned long long run = off + incl - mine;
+        // rowC[i0 + 1 ..]: shifted by one element, so scalar stores (coalesced across the warp
+        // only every 32nd word; the row array is small)
 #pragma unroll
         for (uint32_t k = 0; k < PER; ++k) {
             run += v[k];
@@ -730,6 +1098,7 @@ struct Plan {
     uint32_t pitch;             // bitmap words per row, a multiple of 8 (rows stay 32-byte aligned)
     unsigned long long* d_total;
     uint32_t* pattern;          // [M][pitch] row bitmaps kept between the passes, or null
+    uint32_t* dupmap;           // [M][DUP_WORDS] groups of 16 columns hit more than once (N <= 65536), or null
 };
 
 int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
@@ -777,6 +1146,7 @@ int make_plan(sb200_ctx* ctx, const sb200_csr* A, const sb200_csr* B, Plan* pl)
     if (pl->pitch == 0)
         pl->pitch = 8;
     pl->pattern = nullptr;
+    pl->dupmap = nullptr;
     return SB200_OK;
 }
 
@@ -807,6 +1177,15 @@ uint32_t heavy_window_cap(const Plan& pl)
                            : window_cap<HEAVY_THREADS, uint32_t>(pl.pitch, HEAVY_VAL_CAP);
 }
 
+// Whether the mid bin of this pass runs on the kernels specialised for N <= 65536
+// columns (the numeric one needs the bitmaps and group flags the symbolic one kept).
+bool fast_mid_rows(const sb200_ctx* ctx, const Plan& pl, bool numeric, bool from_pattern)
+{
+    if (pl.B.N > 65536 || !ctx->sp_fast_mid)
+        return false;
+    return !numeric || (from_pattern && pl.pattern && pl.dupmap);
+}
+
 // `reuse`: the per-nonzero and per-row arrays of an earlier call on the same
 // operands are still in the workspace; only the bins are rebuilt (rowC given).
 int bin_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, bool reuse, cudaStream_t stream)
@@ -817,10 +1196,12 @@ int bin_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, bool reuse, c
         return SB200_OK;
     const unsigned blocks = static_cast<unsigned>(ctx->sm_count) * 8;
     const uint32_t heavy_cap = heavy_window_cap(pl);
+    // widest output row the mid bin of the numeric pass takes
+    const uint32_t cap = fast_mid_rows(ctx, pl, true, pl.pattern != nullptr) ? FAST_MID_CAP : mid_cap(pl.B.N);
     if (reuse && rowC)
-        rebin_kernel<<<(pl.A.M + 255) / 256, 256, 0, stream>>>(pl.A, pl.w, rowC, pl.B.N, heavy_cap);
+        rebin_kernel<<<(pl.A.M + 255) / 256, 256, 0, stream>>>(pl.A, pl.w, rowC, cap, heavy_cap);
     else
-        row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w, rowC, pl.B.N, heavy_cap);
+        row_products_kernel<<<blocks, 256, 0, stream>>>(pl.A, pl.B.row, pl.w, rowC, cap, heavy_cap);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
@@ -841,8 +1222,10 @@ int prepare_pattern(sb200_ctx* ctx, Plan* pl, const sb200_csr* A, const sb200_cs
 {
     ctx->sp_valid = 0;
     ctx->sp_work_valid = 0;
-    const size_t need = static_cast<size_t>(A->M) * pl->pitch * 4;
-    if (need == 0 || need > PATTERN_LIMIT)
+    const size_t bitmaps = static_cast<size_t>(A->M) * pl->pitch * 4;
+    // N <= 65536: the group flags of the specialised mid-row kernels follow the bitmaps
+    const size_t need = bitmaps + (B->N <= 65536 ? static_cast<size_t>(A->M) * DUP_WORDS * 4 : 0);
+    if (bitmaps == 0 || need > PATTERN_LIMIT)
         return SB200_OK;                       // numeric pass rebuilds the bitmaps
     if (need > ctx->sp_pattern_bytes) {
         if (ctx->d_sp_pattern) cudaFree(ctx->d_sp_pattern);
@@ -857,6 +1240,7 @@ int prepare_pattern(sb200_ctx* ctx, Plan* pl, const sb200_csr* A, const sb200_cs
         ctx->sp_pattern_bytes = need;
     }
     pl->pattern = ctx->d_sp_pattern;
+    pl->dupmap = B->N <= 65536 ? pl->pattern + static_cast<size_t>(A->M) * pl->pitch : nullptr;
     ctx->sp_key = SpPatternKey{A->ROW, A->COL, B->ROW, B->COL, A->M, A->N, B->N, A->NNZ, B->NNZ};
     return SB200_OK;
 }
@@ -912,6 +1296,41 @@ int launch_rows(sb200_ctx* ctx, const Plan& pl, const uint4* rows, const uint32_
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
 
+// The mid bin on the kernels specialised for N <= 65536 columns.
+template <bool NUMERIC>
+int launch_mid_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, uint32_t* colC, float* valC,
+                    cudaStream_t stream)
+{
+    const uint32_t val_cap = FAST_MID_CAP;
+    const size_t smem = NUMERIC ? 2 * MID_WORDS * 4 + 3 * 256 * 4 + (static_cast<size_t>(val_cap) + 4) * 6
+                                : (MID_WORDS + DUP_WORDS) * 4 + 3 * 256 * 4;
+    auto kern = mid_rows_kernel<NUMERIC>;
+    static thread_local int cached_dev = -1, cached_per_sm = 1;
+    if (cached_dev != ctx->device) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            return SB200_ERR_CUDA;
+        }
+        int n = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, MID_THREADS, smem) != cudaSuccess || n < 1)
+            n = 1;
+        cached_dev = ctx->device;
+        cached_per_sm = n;
+        if (getenv("SB200_VERBOSE"))
+            fprintf(stderr, "sb200: mid_rows<%d> smem %zu B, %d CTAs/SM\n", int(NUMERIC), smem, n);
+    }
+    uint32_t* next_row = pl.w.counters + 3;
+    if (cudaMemsetAsync(next_row, 0, 4, stream) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    const int vec_ok = ((reinterpret_cast<uintptr_t>(colC) | reinterpret_cast<uintptr_t>(valC)) & 15) == 0;
+    kern<<<static_cast<unsigned>(ctx->sm_count) * cached_per_sm, MID_THREADS, smem, stream>>>(
+        pl.A, pl.B, pl.w, pl.w.rows_mid, pl.w.counters + 1, next_row, pl.pitch, val_cap, vec_ok, pl.pattern,
+        pl.dupmap, rowC, colC, valC);
+    ctx->launches += 1;
+    return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+}
+
 template <bool NUMERIC, bool FROM_PATTERN>
 int run_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, uint32_t* colC, float* valC,
              cudaStream_t stream)
@@ -931,7 +1350,10 @@ int run_rows(sb200_ctx* ctx, const Plan& pl, const uint32_t* rowC, uint32_t* col
             pl.w.counters + 3, HEAVY_VAL_CAP, rowC, colC, valC, stream);
     if (rc)
         return rc;
-    if constexpr (!NUMERIC)
+    // N <= 65536: the specialised mid-row kernels (the numeric one reads the kept bitmaps)
+    if (fast_mid_rows(ctx, pl, NUMERIC, FROM_PATTERN))
+        rc = launch_mid_rows<NUMERIC>(ctx, pl, rowC, colC, valC, stream);
+    else if constexpr (!NUMERIC)
         rc = launch_rows<ROW_THREADS, 6, false, false, uint32_t>(
             ctx, pl, pl.w.rows_mid, pl.w.counters + 1, nullptr, nullptr, 0, pl.w.counters + 3, 0, rowC, colC,
             valC, stream);
@@ -1007,10 +1429,13 @@ extern "C" int sb200_spgemm_csr_numeric(sb200_ctx* ctx, const sb200_csr* A, cons
     if (cudaSetDevice(ctx->device) != cudaSuccess)
         return SB200_ERR_CUDA;
     const bool same = same_operands(ctx, A, B);
+    if (same) {
+        pl.pattern = ctx->d_sp_pattern;
+        pl.dupmap = B->N <= 65536 ? pl.pattern + static_cast<size_t>(A->M) * pl.pitch : nullptr;
+    }
     if ((rc = bin_rows(ctx, pl, rowC, same && ctx->sp_work_valid, stream)))
         return rc;
     if (same) {
-        pl.pattern = ctx->d_sp_pattern;
         return run_rows<true, true>(ctx, pl, rowC, colC, valC, stream);
     }
     return run_rows<true, false>(ctx, pl, rowC, colC, valC, stream);

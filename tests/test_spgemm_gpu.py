@@ -52,6 +52,20 @@ def test_spgemm_matches_oracle(ctx, oracle, M, K, N, dens, dist, cap):
     run_case(ctx, oracle, M, K, N, 0, 1, dens, dist, cap or 4096)
 
 
+@pytest.mark.parametrize("dist,cap", [("poisson", 0), ("zipf", 2048)])
+def test_spgemm_general_row_kernel_below_65536_columns(ctx, oracle, dist, cap):
+    """Products of at most 65536 columns run their mid-sized rows on specialised
+    kernels by default; with that switched off the general row kernel takes them.
+    Both must match the oracle, hence each other."""
+    ctx.set_option(L.OPT_SPGEMM_FAST_MID, 0)
+    try:
+        slow = run_case(ctx, oracle, 3000, 3000, 6000, 4, 5, 0.01, dist, cap or 4096)
+    finally:
+        ctx.set_option(L.OPT_SPGEMM_FAST_MID, 1)
+    fast = run_case(ctx, oracle, 3000, 3000, 6000, 4, 5, 0.01, dist, cap or 4096)
+    assert torch.equal(slow.row, fast.row) and torch.equal(slow.col, fast.col)
+
+
 def test_spgemm_callee_allocated_output(ctx, oracle):
     """The drop-in call: the library allocates C, the caller frees it."""
     run_case(ctx, oracle, 1500, 1500, 1500, 2, 3, 0.01, "poisson", fn=ops.spgemm_callee_alloc)
