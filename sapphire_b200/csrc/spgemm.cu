@@ -637,9 +637,20 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
 #pragma unroll
                 for (int u = 0; u < U; ++u)
                     if (slot[u] < lim) cols[slot[u]] = static_cast<ColT>(col[u]);   // slots below `shift`: never copied out
+                // accumulate by exchange: a product swaps itself in; only if it displaced a
+                // partial sum (rare) does it take the slot's content out, add and put the sum
+                // back, until nothing was displaced.  fp32 atomicAdd in shared memory is a
+                // compare-and-swap loop; the exchange is one native atomic in the common case.
 #pragma unroll
-                for (int u = 0; u < U; ++u)
-                    if (slot[u] < lim) atomicAdd(&vals[slot[u]], prod[u]);
+                for (int u = 0; u < U; ++u) {
+                    if (slot[u] >= lim) continue;
+                    uint32_t* acc = reinterpret_cast<uint32_t*>(vals) + slot[u];
+                    uint32_t old = atomicExch(acc, __float_as_uint(prod[u]));
+                    while (old != 0u) {
+                        const uint32_t cur = atomicExch(acc, 0u);
+                        old = atomicExch(acc, __float_as_uint(__fadd_rn(__uint_as_float(old), __uint_as_float(cur))));
+                    }
+                }
             });
             __syncthreads();
             uint32_t* gcol = colC + (out0 + r0 - shift);          // slot s <-> gcol[s]; 16-byte aligned
@@ -798,7 +809,7 @@ __device__ __forceinline__ void mid_walk_row(const MidSmem<NUMERIC>& sm, const C
 }
 
 template <bool NUMERIC>
-__global__ void __launch_bounds__(MID_THREADS, NUMERIC ? 4 : 5)
+__global__ void __launch_bounds__(MID_THREADS, NUMERIC ? 4 : 6)
 mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
                 const uint32_t* __restrict__ n_rows_ptr, uint32_t* __restrict__ next_row,
                 uint32_t pitch, uint32_t val_cap, int vec_ok, uint32_t* __restrict__ pattern,
@@ -968,10 +979,17 @@ mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
                     mid_products<NUMERIC, MID_SHORT>(sm, c, v, e.a);
                 }
                 __syncthreads();
-                // rows of B of 5 .. 255 entries: 16 lanes each
+                // rows of B of 5 .. 255 entries: 16 lanes each.  A few entries left over after
+                // the last full round of the 16 lane groups are walked by the whole CTA
+                // instead (one step each) rather than by a few groups while the others wait.
                 const uint32_t n_mid = s_n_mid;
-                for (uint32_t it = half; it < n_mid; it += MID_THREADS / 16)
+                constexpr uint32_t GROUPS = MID_THREADS / 16;
+                const uint32_t left = n_mid % GROUPS;
+                const uint32_t n_grouped = (n_mid > GROUPS && left <= GROUPS / 4) ? n_mid - left : n_mid;
+                for (uint32_t it = half; it < n_grouped; it += GROUPS)
                     mid_walk_row<NUMERIC>(sm, B, sm.l_qs[it], sm.l_len[it], sm.l_a[it], sub, 16u);
+                for (uint32_t it = n_grouped; it < n_mid; ++it)
+                    mid_walk_row<NUMERIC>(sm, B, sm.l_qs[it], sm.l_len[it], sm.l_a[it], tid, MID_THREADS);
                 // rows of B of 256 entries and more: the whole CTA
                 const uint32_t n_long = s_n_long;
                 for (uint32_t l = 0; l < n_long; ++l)
@@ -1032,59 +1050,50 @@ mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
 }
 
 // --------------------------------------------------------------- row scan
-// rowC[0] = 0, rowC[i+1] = sum cnt[0..i]; one CTA, chunks of 32768 counts (32
-// consecutive ones per thread, all eight 16-byte loads of a chunk in flight together)
-// with a carry.
+// rowC[0] = 0, rowC[i+1] = sum cnt[0..i]; one CTA of 32 warps.  A warp owns 1024
+// consecutive counts per chunk of 32768 and reads / writes them 32 at a time, lane =
+// consecutive element, so every global access is one coalesced 128-byte line (a
+// thread that owns consecutive elements stores with a 128-byte stride between lanes:
+// 20 us for one SM to push 65536 such stores out).
 __global__ void __launch_bounds__(1024)
 row_scan_kernel(const uint32_t* __restrict__ cnt, uint32_t M, uint32_t* __restrict__ rowC,
                 unsigned long long* __restrict__ total_out)
 {
-    constexpr uint32_t PER = 32;
+    constexpr uint32_t PER = 32;                                  // steps of 32 elements per warp and chunk
     __shared__ unsigned long long s_warp[32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) rowC[0] = 0;
     unsigned long long carry = 0;
     for (uint32_t base = 0; base < M; base += 1024 * PER) {
-        const uint32_t i0 = base + threadIdx.x * PER;
+        const uint32_t w0 = base + warp * (32 * PER) + lane;
         uint32_t v[PER];
-        if (i0 + PER <= M) {                                      // cnt is 16-byte aligned
-            uint4 q[PER / 4];
 #pragma unroll
-            for (uint32_t k = 0; k < PER / 4; ++k) q[k] = *reinterpret_cast<const uint4*>(cnt + i0 + 4 * k);
-#pragma unroll
-            for (uint32_t k = 0; k < PER / 4; ++k) {
-                v[4 * k] = q[k].x; v[4 * k + 1] = q[k].y; v[4 * k + 2] = q[k].z; v[4 * k + 3] = q[k].w;
-            }
-        } else {
-#pragma unroll
-            for (uint32_t k = 0; k < PER; ++k) v[k] = i0 + k < M ? cnt[i0 + k] : 0u;
-        }
+        for (uint32_t k = 0; k < PER; ++k) v[k] = w0 + 32 * k < M ? cnt[w0 + 32 * k] : 0u;
         unsigned long long mine = 0;
 #pragma unroll
         for (uint32_t k = 0; k < PER; ++k) mine += v[k];
-        unsigned long long incl = mine;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += t;
-        }
+        for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
         __syncthreads();                                          // s_warp of the previous chunk read
-        if (lane == 31) s_warp[warp] = incl;
+        if (lane == 0) s_warp[warp] = mine;
         __syncthreads();
-        unsigned long long off = carry, chunk_total = 0;
+        unsigned long long run = carry, chunk_total = 0;
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
+        for (uint32_t x = 0; x < 32; ++x) {
             const unsigned long long t = s_warp[x];
-            if (x < warp) off += t;
+            if (x < warp) run += t;
             chunk_total += t;
         }
-        unsigned long long run = off + incl - mine;
-        // rowC[i0 + 1 ..]: shifted by one element, so scalar stores (coalesced across the warp
-        // only every 32nd word; the row array is small)
 #pragma unroll
         for (uint32_t k = 0; k < PER; ++k) {
-            run += v[k];
-            if (i0 + k < M) rowC[i0 + k + 1] = static_cast<uint32_t>(run);
+            uint32_t incl = v[k];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= static_cast<uint32_t>(o)) incl += t;
+            }
+            if (w0 + 32 * k < M) rowC[w0 + 32 * k + 1] = static_cast<uint32_t>(run + incl);
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
         carry += chunk_total;
     }
