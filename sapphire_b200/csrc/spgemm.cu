@@ -637,20 +637,9 @@ cta_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
 #pragma unroll
                 for (int u = 0; u < U; ++u)
                     if (slot[u] < lim) cols[slot[u]] = static_cast<ColT>(col[u]);   // slots below `shift`: never copied out
-                // accumulate by exchange: a product swaps itself in; only if it displaced a
-                // partial sum (rare) does it take the slot's content out, add and put the sum
-                // back, until nothing was displaced.  fp32 atomicAdd in shared memory is a
-                // compare-and-swap loop; the exchange is one native atomic in the common case.
 #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (slot[u] >= lim) continue;
-                    uint32_t* acc = reinterpret_cast<uint32_t*>(vals) + slot[u];
-                    uint32_t old = atomicExch(acc, __float_as_uint(prod[u]));
-                    while (old != 0u) {
-                        const uint32_t cur = atomicExch(acc, 0u);
-                        old = atomicExch(acc, __float_as_uint(__fadd_rn(__uint_as_float(old), __uint_as_float(cur))));
-                    }
-                }
+                for (int u = 0; u < U; ++u)
+                    if (slot[u] < lim) atomicAdd(&vals[slot[u]], prod[u]);
             });
             __syncthreads();
             uint32_t* gcol = colC + (out0 + r0 - shift);          // slot s <-> gcol[s]; 16-byte aligned
