@@ -322,7 +322,7 @@ PROFILE_CASES = {
     "dense_tn": lambda: _case_dense(0, ta=True),
     "dense_nt": lambda: _case_dense(0, tb=True),
     "dense_epilogue": lambda: _case_dense(0, n=8192, batch=1, k=32),
-    "dense_single_4096": lambda: _case_dense(0, n=4096, batch=1),   # tail-wave split: two launches
+    "dense_single_4096": lambda: _case_dense(0, n=4096, batch=1),   # what one GPU of eight runs
     "spgemm": lambda: _case_spgemm("poisson"),                  # 32768 rows of the 65536^2 case
     "spgemm_zipf": lambda: _case_spgemm("zipf"),
     "im2col": _case_im2col,

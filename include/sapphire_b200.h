@@ -96,10 +96,13 @@ int64_t sb200_ctx_counter(const sb200_ctx* ctx, int which);
  *   SB200_OPT_CTA_PAIRS  1, the default: TF32 problems with at least one
  *       256 x 256 tile per pair of SMs run on the two-CTA kernel (clusters of two,
  *       tcgen05 cta_group::2); 0: always the one-CTA kernel.
- *   SB200_OPT_SPLIT_TAIL_WAVE  1, the default: when the 256 x 256 tiles of a problem
- *       would leave the last wave over the SM pairs mostly empty (one 4096^3
- *       product: 3.46 waves of work in the time of 4), the bottom rows of the
- *       product run as a second launch of the one-CTA kernel; 0: one launch.
+ *   SB200_OPT_SPLIT_TAIL_WAVE  0, the default: one launch per request.  1: when the
+ *       256 x 256 tiles of a problem would leave the last wave over the SM pairs
+ *       mostly empty (one 4096^3 product: 3.46 waves of work in the time of 4), the
+ *       bottom rows of the product run as a second launch of the one-CTA kernel.
+ *       Off by default because it measured slower on a power-capped B200 (one
+ *       4096^3: 212 us split, 199 us whole): the SMs of a partly empty wave clock
+ *       higher, which already buys back most of the quantisation loss.
  *   SB200_OPT_WAIT_LIMIT_US  bound of every wait inside the GEMM kernels in
  *       microseconds (default 2,000,000; at least 100).  A wait that runs out ends
  *       the launch with SB200_ERR_DEVICE_TIMEOUT from sb200_check_device_status --

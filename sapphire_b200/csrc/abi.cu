@@ -57,7 +57,7 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->split_explicit_hi = 0;
     ctx->merge_mn_boxes = 1;
     ctx->use_cta_pairs = 1;
-    ctx->split_tail_wave = 1;
+    ctx->split_tail_wave = 0;
     ctx->encode_tiled = nullptr;
     ctx->tmaps = nullptr;
     ctx->tmap_clock = 0;

@@ -315,19 +315,19 @@ def test_config4_full_size_linear_backward(ctx, oracle, mode):
 
 @pytest.mark.parametrize("n", [4096, 4000])
 def test_single_product_tail_wave_split(ctx, oracle, n):
-    """One n^3 product is 256 pair tiles on 74 pairs of SMs: the bottom rows go to
-    a second launch of the one-CTA kernel.  The split result must meet the TF32 bar
-    on rows of both parts and agree with the unsplit launch to accumulation rounding."""
+    """One n^3 product is 256 pair tiles on 74 pairs of SMs; with the tail-wave
+    option on, the bottom rows go to a second launch of the one-CTA kernel.  The
+    split result must meet the TF32 bar on rows of both parts and agree with the
+    single launch (the default) to accumulation rounding."""
     a, b, c = W.dense_batched(0, [0], n, n, n, "normal")
     ta, tb, tc = dev(a[0]), dev(b[0]), dev(c[0])
-    before = ctx.launch_count()
-    y = ops.gemm(ctx, ta, tb, tc)
-    split_launches = ctx.launch_count() - before
-    ctx.set_option(L.OPT_SPLIT_TAIL_WAVE, 0)
     before = ctx.launch_count()
     y1 = ops.gemm(ctx, ta, tb, tc)
     whole_launches = ctx.launch_count() - before
     ctx.set_option(L.OPT_SPLIT_TAIL_WAVE, 1)
+    before = ctx.launch_count()
+    y = ops.gemm(ctx, ta, tb, tc)
+    split_launches = ctx.launch_count() - before
     ctx.check_device_status()
     assert (split_launches, whole_launches) == (2, 1)
     rows = [0, 255, 3327, 3328, 3329, n - 129, n - 1]    # both sides of the cut at row 3328
@@ -337,6 +337,7 @@ def test_single_product_tail_wave_split(ctx, oracle, n):
     # in place (C aliases D) and with transposed A: the second launch shifts every base
     yt = tc.clone()
     ops.gemm(ctx, ta.t().contiguous(), tb, yt, yt, trans_a=True)
+    ctx.set_option(L.OPT_SPLIT_TAIL_WAVE, 0)
     assert rel_fro(yt.cpu().numpy(), y1.cpu().numpy()) <= 1e-5
 
 
