@@ -366,6 +366,8 @@ def main():
                          "scaling) instead of its share of the global batch of 8")
     ap.add_argument("--linear-bwd-comm", default="fused", choices=["fused", "nccl"],
                     help="how the linear_bwd workload sums dW over ranks (see bench_linear_bwd)")
+    ap.add_argument("--mlp-comm", default="peer", choices=["peer", "nccl"],
+                    help="how the mlp workload sums its gradients over ranks (see bench_mlp)")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--case", default=None, help="run one small profiler case and exit")
@@ -653,21 +655,26 @@ def main():
             out["check"] = check
         return out
 
-    def bench_mlp(steps, warmup):
+    def bench_mlp(steps, warmup, comm="peer"):
         """The 784-512-256-10 MLP training step, global batch 64 split over the
-        ranks (strong scaling), one flat gradient allreduce per step.  lr 1e-4: at
-        0.01 Sapphire's un-normalised gradients leave the finite range by step 3."""
+        ranks (strong scaling).  The gradients are summed over the ranks inside the
+        step: comm "peer" = the library's exchange over peer memory fused with the
+        SGD update (two kernels), "nccl" = one all-reduce of the flat bucket + scale +
+        SGD.  lr 1e-4: at 0.01 Sapphire's un-normalised gradients leave the finite
+        range by step 3."""
         from sapphire_b200 import mlp as M
         Ws, bs = W.mlp_init(0)
-        trainer = M.MlpTrainer(ctx, Ws, bs, 1e-4, mode=L.MODE_TF32, world=world)
+        trainer = M.MlpTrainer(ctx, Ws, bs, 1e-4, mode=L.MODE_TF32, world=world, comm=comm, rank=rank)
+        how = ("gradient exchange over peer memory fused with SGD" if trainer.exchange is not None
+               else "NCCL gradient allreduce inside" if world > 1 else "single rank")
         per = 64 // world
         x, onehot = W.mlp_batch(0)
         xs = torch.from_numpy(x[rank * per:(rank + 1) * per]).to(dev)
         ys = torch.from_numpy(onehot[rank * per:(rank + 1) * per]).to(dev)
         ms, launches = timed(lambda: trainer.step(xs, ys), steps, warmup)
         flops = 3 * 2.0 * 64 * sum(i * o for i, o in zip(W.MLP_WIDTHS[:-1], W.MLP_WIDTHS[1:]))
-        out = {"workload": f"MLP 784-512-256-10 SGD step, global batch 64 over {world} rank(s), "
-                           "gradient allreduce inside", "ms_per_step": ms,
+        out = {"workload": f"MLP 784-512-256-10 SGD step, global batch 64 over {world} rank(s), {how}",
+               "ms_per_step": ms,
                "gflops_total": flops / ms / 1e6, "gpu_launches": launches,
                "kernels_per_step": launches // max(steps, 1)}
         try:
@@ -676,6 +683,8 @@ def main():
             out["ms_per_step_cuda_graph"] = gms
         except Exception as e:                       # capture is an optimisation, not the path
             out["cuda_graph_error"] = repr(e)[:200]
+        ctx.check_device_status()
+        trainer.close()
         return out
 
     def bench_conv(steps, warmup):
@@ -767,7 +776,7 @@ def main():
                              "per": "GPU", "peak_source": peak_note},
                 "gpu_launches": r["gpu_launches"]}
     elif args.workload == "mlp":
-        r = bench_mlp(args.steps, args.warmup)
+        r = bench_mlp(args.steps, args.warmup, args.mlp_comm)
         best = min(r["ms_per_step"], r.get("ms_per_step_cuda_graph", r["ms_per_step"]))
         line = {"metric": "MLP training step time", "value": best, "unit": "ms/step",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -797,6 +806,8 @@ def main():
         extras.append(bench_spgemm("poisson", 5, 3))
         extras.append(bench_spgemm("zipf", 5, 3))
         extras.append(bench_mlp(50, 5))
+        if world > 1:
+            extras.append(bench_mlp(50, 5, "nccl"))
         extras.append(bench_conv(10, 3))
         line["other_workloads"] = extras
 

@@ -257,6 +257,46 @@ int sb200_peer_close(sb200_ctx* ctx, void* ptr);
 int sb200_peer_free(sb200_ctx* ctx, void* ptr);
 
 /*
+ * Gradient exchange of a data-parallel step over peer memory, fused with the SGD
+ * update: the sum over ranks that the reference, being single-GPU, never needs
+ * (its optimizer step is Sources/Sapphire/operations/optimizers/SGD.cpp:22-28; the
+ * reduction rule -- weight gradients SUM, bias gradients MEAN -- follows from
+ * Sources/Sapphire/operations/Backward/LinearBackward.cpp:72-73, 93-97).
+ *
+ * A group describes, for each of `world` ranks (one process per GPU, <= 8), three
+ * buffers as mapped into THIS process (sb200_peer_alloc / sb200_peer_open; index
+ * `rank` = this rank's own): grads[r], rank r's flat gradient bucket of `count`
+ * floats; reduced[r], a buffer of `count` floats in which rank r keeps the slice of
+ * the summed gradient it owns; flags[r], SB200_DP_FLAG_WORDS 32-bit words, zeroed
+ * once before the first step.  All buffers 16-byte aligned.
+ *
+ * Per training step every rank calls, on its stream, after its backward pass:
+ *   sb200_dp_reduce  announces this rank's gradients, waits for every peer's, and
+ *                    sums this rank's slice (1 / world of the bucket) over all
+ *                    ranks' buckets in fixed rank order (peer loads);
+ *   sb200_dp_update  waits for every peer's slice, then
+ *                    params <- params - lr * g over all `count` elements, g read
+ *                    from the owning rank's slice; elements from n_sum on are
+ *                    divided by world first.
+ * Both return at once; the waits happen on the GPU and are bounded by
+ * SB200_OPT_WAIT_LIMIT_US (a wait that runs out makes sb200_check_device_status
+ * return SB200_ERR_DEVICE_TIMEOUT).  The step number lives in the flag words, so the
+ * two calls can be captured in a CUDA graph and replayed.  Every rank ends a step
+ * with bit-identical parameters.
+ */
+#define SB200_DP_FLAG_WORDS 32
+typedef struct sb200_dp_group {
+    int world, rank;
+    const float* grads[8];
+    float* reduced[8];
+    uint32_t* flags[8];
+} sb200_dp_group;
+
+int sb200_dp_reduce(sb200_ctx* ctx, const sb200_dp_group* group, int64_t count, sb200_stream stream);
+int sb200_dp_update(sb200_ctx* ctx, const sb200_dp_group* group, float* params, int64_t count,
+                    int64_t n_sum, float lr, sb200_stream stream);
+
+/*
  * CSR matrix, device arrays.  Same fields and order as the reference's
  * SparseMatrix (Includes/Sapphire/compute/sparse/SparseMatrix.hpp:28-38):
  * V values, COL column indices, ROW offsets of length M + 1, then NNZ, M, N

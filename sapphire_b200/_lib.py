@@ -45,6 +45,15 @@ class ConvGeometry(C.Structure):
                                        "padR", "padC", "dilR", "dilC")]
 
 
+class DpGroup(C.Structure):
+    """Mirror of sb200_dp_group."""
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("grads", C.c_void_p * 8),
+                ("reduced", C.c_void_p * 8), ("flags", C.c_void_p * 8)]
+
+
+DP_FLAG_WORDS = 32
+
+
 class Sb200Error(RuntimeError):
     def __init__(self, where: str, status: int):
         self.status = status
@@ -85,6 +94,9 @@ SIGNATURES = {
         C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64,
         C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
         C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_void_p, C.c_float, C.c_void_p]),
+    "sb200_dp_reduce": (C.c_int, [C.c_void_p, C.POINTER(DpGroup), C.c_int64, C.c_void_p]),
+    "sb200_dp_update": (C.c_int, [C.c_void_p, C.POINTER(DpGroup), C.c_void_p, C.c_int64, C.c_int64,
+                                  C.c_float, C.c_void_p]),
     "sb200_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
     "sb200_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),
     "sb200_peer_close": (C.c_int, [C.c_void_p, C.c_void_p]),

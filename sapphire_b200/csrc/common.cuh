@@ -25,7 +25,8 @@ enum DeviceFault : unsigned {
     FAULT_MMA_WAIT_FULL = 0x102,   // MMA issuer waiting for a filled stage
     FAULT_MMA_WAIT_TMEM = 0x103,   // MMA issuer waiting for a drained accumulator
     FAULT_EPI_WAIT = 0x104,        // epilogue waiting for a finished accumulator
-    FAULT_SPLIT_WAIT = 0x105       // hi/lo split warps waiting for a filled stage
+    FAULT_SPLIT_WAIT = 0x105,      // hi/lo split warps waiting for a filled stage
+    FAULT_PEER_WAIT = 0x201        // gradient exchange waiting for another rank's announcement
 };
 
 struct GemmArgs {

@@ -312,13 +312,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                                p.rows_per_owner != 0};
             const float* mrow = epi.mask ? epi.mask + static_cast<long long>(row) * p.ldm : nullptr;
             if constexpr (!SPLIT) {
-                // one chunk per tile: straight from TMEM to global memory
-                if (!(ok = wait_bar(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
-                    break;
-                ptx::tc_fence_after_sync();
+                // one chunk per tile: straight from TMEM to global memory.  The first
+                // chunk's C is requested before the wait for the accumulator, so that it
+                // travels under the tile's main loop (C may alias D, but this tile's
+                // region of D is written by nobody else)
                 CChunk c_now, c_next;
                 if (vec_ok)                                    // zeros when there is no C
                     load_c_chunk(c_next, cmat, p.ldc, m0 + q * 32, n0, p.M, p.N);
+                if (!(ok = wait_bar(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
+                    break;
+                ptx::tc_fence_after_sync();
 #pragma unroll 1
                 for (int c = 0; c < BLOCK_N / 32; ++c) {
                     const int col0 = n0 + c * 32;

@@ -254,12 +254,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
             float* my_stage = epi_stage + q * (EPI_STAGE_BYTES_PER_WARP / 4);
             const Epilogue epi{p.bias, p.mask ? p.mask + b * p.strideM : nullptr, p.ldm, p.relu,
                                p.rows_per_owner != 0};
-            if (!(ok = wait_bar_cluster(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
-                break;
-            ptx::tc_fence_after_sync();
+            // the first chunk's C is requested before the wait for the accumulator: it
+            // travels under the tile's main loop
             CChunk c_now, c_next;
             if (vec_ok)                                    // zeros when there is no C
                 load_c_chunk(c_next, cmat, p.ldc, m0 + q * 32, n0, p.M, p.N);
+            if (!(ok = wait_bar_cluster(&tmem_full[acc], acc_ph, ab, FAULT_EPI_WAIT)))
+                break;
+            ptx::tc_fence_after_sync();
 #pragma unroll 1
             for (int c = 0; c < PAIR_N / 32; ++c) {
                 const int col0 = n0 + c * 32;

@@ -30,17 +30,21 @@ import torch
 
 from . import _lib as L
 from . import ops
-from .runner import GradBucket
+from .runner import GradBucket, PeerGradExchange
 
 
 class MlpTrainer:
     def __init__(self, ctx: ops.Context, weights: Sequence[np.ndarray], biases: Sequence[np.ndarray],
                  lr: float, mode: int = L.MODE_TF32, world: int = 1, fused: bool = True,
-                 row_pad: int = 4):
+                 row_pad: int = 4, comm: str = "nccl", rank: int = 0):
         """``row_pad``: rows of the parameter / gradient buffers are padded to this
         many floats.  4 (16 bytes) puts the 10-column output layer on the
         tensor-core kernel; 1 keeps its rows dense, which sends that layer to the
-        CUDA-core kernel (sequential fp32 sums, bit-identical to the reference)."""
+        CUDA-core kernel (sequential fp32 sums, bit-identical to the reference).
+        ``comm``: how the gradients are summed over ``world`` ranks: "nccl" (one
+        all-reduce of the flat bucket, then the SGD kernel) or "peer" (the two
+        kernels of ``PeerGradExchange``: sum over peer memory fused with the update;
+        needs ``rank``)."""
         self.ctx, self.lr, self.mode, self.world = ctx, float(lr), mode, world
         self.fused, self.row_pad = fused, row_pad
         dev = torch.device("cuda", ctx.device)
@@ -51,7 +55,17 @@ class MlpTrainer:
             dst.copy_(torch.from_numpy(np.ascontiguousarray(w)))
         for dst, b in zip(self.params.dB, biases):
             dst.copy_(torch.from_numpy(np.ascontiguousarray(b)))
-        self.grads = GradBucket.create(shapes, dev, row_pad)
+        self.exchange = None
+        if comm == "peer" and world > 1:
+            self.exchange = PeerGradExchange(ctx, GradBucket.size(shapes, row_pad), 0, rank, world)
+            if not self.exchange.ok:                       # agreed across ranks: all fall back together
+                self.exchange.close()
+                self.exchange = None
+        if self.exchange is not None:
+            self.grads = GradBucket.create(shapes, dev, row_pad, flat=self.exchange.grads)
+            self.exchange.n_sum = self.grads.n_weight
+        else:
+            self.grads = GradBucket.create(shapes, dev, row_pad)
         self.W, self.b = self.params.dW, self.params.dB
 
     def forward_backward(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
@@ -110,9 +124,18 @@ class MlpTrainer:
 
     def step(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
         loss = self.forward_backward(x, onehot)
+        if self.exchange is not None:
+            self.exchange.step(self.params.flat, self.lr)
+            return loss
         self.grads.allreduce(self.world, lambda t, f: ops.scale(self.ctx, t, f))
         ops.sgd_update(self.ctx, self.params.flat, self.grads.flat, self.lr)
         return loss
+
+    def close(self) -> None:
+        """Collective when the trainer exchanges gradients over peer memory."""
+        if self.exchange is not None:
+            self.exchange.close()
+            self.exchange = None
 
     # ------------------------------------------------------------ CUDA graph
     def capture(self, batch: int) -> None:

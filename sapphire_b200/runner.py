@@ -103,11 +103,23 @@ class GradBucket:
     n_weight: int
 
     @staticmethod
-    def create(shapes: Sequence[Tuple[int, int]], device, pad: int = 4) -> "GradBucket":
+    def size(shapes: Sequence[Tuple[int, int]], pad: int = 4) -> int:
+        """Floats in the flat buffer of these layer shapes."""
+        ld = [(o + pad - 1) // pad * pad for _, o in shapes]
+        return sum(i * l for (i, _), l in zip(shapes, ld)) + sum(ld)
+
+    @staticmethod
+    def create(shapes: Sequence[Tuple[int, int]], device, pad: int = 4,
+               flat: "torch.Tensor | None" = None) -> "GradBucket":
+        """``flat``: use this zeroed 1-D fp32 buffer (e.g. memory other ranks map)
+        instead of allocating one."""
         ld = [(o + pad - 1) // pad * pad for _, o in shapes]
         nW = sum(i * l for (i, _), l in zip(shapes, ld))
         nB = sum(ld)
-        flat = torch.zeros(nW + nB, dtype=torch.float32, device=device)
+        if flat is None:
+            flat = torch.zeros(nW + nB, dtype=torch.float32, device=device)
+        elif flat.numel() != nW + nB or flat.dtype != torch.float32 or not flat.is_contiguous():
+            raise ValueError("flat must be a contiguous fp32 buffer of GradBucket.size(shapes, pad) elements")
         dW, dB, off = [], [], 0
         for (i, o), l in zip(shapes, ld):
             dW.append(flat[off:off + i * l].view(i, l)[:, :o])
@@ -131,6 +143,56 @@ class GradBucket:
             tail.mul_(1.0 / world)
         else:
             scale_fn(tail, 1.0 / world)
+
+
+# ------------------------------------------------- gradient exchange, no NCCL
+
+class PeerGradExchange:
+    """The gradient sum of a data-parallel step over peer memory, fused with the SGD
+    update (``sb200_dp_reduce`` + ``sb200_dp_update``): two kernels per step instead
+    of an NCCL all-reduce, a scale and an SGD kernel.
+
+    ``grads`` is this rank's flat gradient bucket (``count`` floats) in memory the
+    other ranks map; build the ``GradBucket`` over it.  ``step(params, lr)`` enqueues
+    the two kernels on the current stream; every rank must call it once per step.
+    ``n_sum``: the first n_sum elements are summed over the ranks, the rest averaged
+    (dW SUM, dB MEAN).  Construction and ``close`` are collective."""
+
+    def __init__(self, ctx, count: int, n_sum: int, rank: int = 0, world: int = 1, group=None):
+        import ctypes as C
+        from . import _lib as L
+        self.ctx, self.count, self.n_sum, self.rank, self.world = ctx, count, n_sum, rank, world
+        self._L, self._C = L, C
+        self._grads = PeerWindow(ctx, 1, count, rank, world, group)
+        self._reduced = PeerWindow(ctx, 1, count, rank, world, group)
+        self._flags = PeerWindow(ctx, 1, L.DP_FLAG_WORDS, rank, world, group)
+        self.ok = self._grads.ok and self._reduced.ok and self._flags.ok
+        self.grads = self._grads.mine.view(-1)
+        self.grads.zero_()
+        self._flags.mine.zero_()
+        torch.cuda.synchronize(ctx.device)
+        if world > 1:
+            dist.barrier(group=group)                      # every rank's flag words are zero
+        g = L.DpGroup()
+        g.world, g.rank = world, rank
+        for r in range(world):
+            g.grads[r] = self._grads.pointers[r]
+            g.reduced[r] = self._reduced.pointers[r]
+            g.flags[r] = self._flags.pointers[r]
+        self._group = g
+
+    def step(self, params: torch.Tensor, lr: float) -> None:
+        L, C = self._L, self._C
+        st = torch.cuda.current_stream(torch.device("cuda", self.ctx.device)).cuda_stream
+        L.check("sb200_dp_reduce", L.lib().sb200_dp_reduce(self.ctx.handle, C.byref(self._group),
+                                                           self.count, st))
+        L.check("sb200_dp_update", L.lib().sb200_dp_update(self.ctx.handle, C.byref(self._group),
+                                                           params.data_ptr(), self.count, self.n_sum,
+                                                           float(lr), st))
+
+    def close(self, group=None) -> None:
+        for w in (self._grads, self._reduced, self._flags):
+            w.close(group)
 
 
 # ------------------------------------------- GEMM fused with its reduce-scatter
