@@ -86,6 +86,28 @@ def test_mlp_training_matches_oracle(ctx, oracle, mode, tol):
     assert np.mean(got_loss[-1]) < np.mean(got_loss[0])
 
 
+def test_gradient_exchange_kernels_single_rank(ctx):
+    """sb200_dp_reduce + sb200_dp_update with a group of one rank: the "sum over
+    ranks" is the rank's own bucket, the update must equal the plain SGD kernel bit
+    for bit (elements from n_sum on divided by world = 1), over several steps (the
+    step counter lives on the device) and for a count that is not a multiple of 4."""
+    from sapphire_b200 import runner
+    for count, n_sum in ((4096 + 512, 4096), (1003, 999)):
+        ex = runner.PeerGradExchange(ctx, count, n_sum, 0, 1)
+        assert ex.ok
+        z = torch.randn(count + 4, device=DEV)[:count] if count % 4 == 0 else torch.randn(count, device=DEV)
+        want = z.clone()
+        for step in range(3):
+            g = torch.randn(count, device=DEV)
+            ex.grads.copy_(g)
+            ex.step(z, 0.01)
+            ops.sgd_update(ctx, want, g, 0.01)
+        torch.cuda.synchronize()
+        ctx.check_device_status()
+        assert torch.equal(z, want)
+        ex.close()
+
+
 _CURVE = {}
 
 

@@ -1,8 +1,8 @@
 """Two-rank runs of the data-parallel MLP step on two GPUs (skipped with fewer),
 with the gradients summed by an NCCL all-reduce and by the library's own exchange
-over peer memory: the weights after three eager steps and two replays of the
-captured CUDA graph must equal the single-process CPU oracle on the full batch,
-which checks the dW SUM / dB MEAN rule end to end."""
+over peer memory: the weights after five steps (for the peer exchange the last two
+are replays of the captured CUDA graph) must equal the single-process CPU oracle on
+the full batch, which checks the dW SUM / dB MEAN rule end to end."""
 import os
 import socket
 import sys
@@ -40,9 +40,14 @@ def _worker(rank, world, port, out_dir, comm):
         trainer.step(*shard(t))
     torch.cuda.synchronize()
     ctx.check_device_status()
-    trainer.capture(shard(0)[0].shape[0])
-    for t in range(3, 5):
-        trainer.step_graph(*shard(t))
+    if comm == "peer":
+        # the exchange keeps its step number on the device: the captured step replays
+        trainer.capture(shard(0)[0].shape[0])
+        for t in range(3, 5):
+            trainer.step_graph(*shard(t))
+    else:
+        for t in range(3, 5):
+            trainer.step(*shard(t))
     torch.cuda.synchronize()
     ctx.check_device_status()
     np.save(os.path.join(out_dir, f"params{rank}.npy"), trainer.params.compact().cpu().numpy())
