@@ -717,6 +717,46 @@ struct MidEntry {
     float a;
 };
 
+// L2 residency hints.  B (tens of MB) is re-read by every row of A and should stay
+// in the 126 MB L2; C (GBs, written once) and the kept row bitmaps (written once,
+// read once) should not push it out.
+struct L2Hints {
+    uint64_t keep, stream;
+};
+__device__ __forceinline__ L2Hints make_l2_hints()
+{
+    L2Hints h;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(h.keep));
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(h.stream));
+    return h;
+}
+__device__ __forceinline__ uint32_t ld_keep_u32(const uint32_t* p, uint64_t pol)
+{
+    uint32_t v;
+    asm volatile("ld.global.nc.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ float ld_keep_f32(const float* p, uint64_t pol)
+{
+    float v;
+    asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ void st_stream_v4(void* p, uint4 v, uint64_t pol)
+{
+    asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w), "l"(pol)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p, uint64_t pol)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.b32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(pol));
+    return v;
+}
+
 template <bool NUMERIC>
 struct MidSmem {
     uint32_t* table;       // symbolic: bitmap[MID_WORDS] + group flags[DUP_WORDS]; numeric: rank words [2 * MID_WORDS]
@@ -773,7 +813,7 @@ __device__ __forceinline__ void mid_products(const MidSmem<NUMERIC>& sm, const u
 // `me`: MID_CHUNKS chunks of `width` entries in flight, then one chunk at a time.
 template <bool NUMERIC>
 __device__ __forceinline__ void mid_walk_row(const MidSmem<NUMERIC>& sm, const Csr& B, uint32_t qs,
-                                             uint32_t len, float a, uint32_t me, uint32_t width)
+                                             uint32_t len, float a, uint32_t me, uint32_t width, uint64_t keep)
 {
     const uint32_t* pc = B.col + qs + me;
     const float* pv = B.val + qs + me;
@@ -785,14 +825,14 @@ __device__ __forceinline__ void mid_walk_row(const MidSmem<NUMERIC>& sm, const C
         c[u] = NO_COL;
         v[u] = 0.0f;
         if (on) {
-            c[u] = __ldg(pc + u * width);
-            if (NUMERIC) v[u] = __ldg(pv + u * width);
+            c[u] = ld_keep_u32(pc + u * width, keep);
+            if (NUMERIC) v[u] = ld_keep_f32(pv + u * width, keep);
         }
     }
     mid_products<NUMERIC, MID_CHUNKS>(sm, c, v, a);
     for (uint32_t q = MID_CHUNKS * width + me; q < len; q += width) {
-        const uint32_t c1[1] = {__ldg(B.col + qs + q)};
-        const float v1[1] = {NUMERIC ? __ldg(B.val + qs + q) : 0.0f};
+        const uint32_t c1[1] = {ld_keep_u32(B.col + qs + q, keep)};
+        const float v1[1] = {NUMERIC ? ld_keep_f32(B.val + qs + q, keep) : 0.0f};
         mid_products<NUMERIC, 1>(sm, c1, v1, a);
     }
 }
@@ -822,6 +862,7 @@ mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
     const uint32_t sub = tid & 15u, half = tid >> 4;              // lane group of 16 and its index
     const uint32_t n_rows = *n_rows_ptr;
     const bool own_words = tid * 8u < pitch;                      // this thread's 8 bitmap words exist
+    const L2Hints l2 = make_l2_hints();
 
     // what a row needs from global memory before it can start: its kept bitmaps (numeric)
     // and the first 256 of its per-nonzero records
@@ -831,8 +872,8 @@ mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
             dup = 0;
             if (own_words) {
                 const uint4* src = reinterpret_cast<const uint4*>(pattern + static_cast<size_t>(d.x) * pitch + tid * 8u);
-                p0 = src[0];
-                p1 = src[1];
+                p0 = ld_stream_v4(src, l2.stream);
+                p1 = ld_stream_v4(src + 1, l2.stream);
                 dup = dupmap[static_cast<size_t>(d.x) * DUP_WORDS + (tid >> 1)];
             }
         }
@@ -962,8 +1003,8 @@ mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
 #pragma unroll
                     for (uint32_t u = 0; u < MID_SHORT; ++u) {
                         const bool on = u < e.len;
-                        c[u] = on ? __ldg(B.col + e.qs + u) : NO_COL;
-                        v[u] = (NUMERIC && on) ? __ldg(B.val + e.qs + u) : 0.0f;
+                        c[u] = on ? ld_keep_u32(B.col + e.qs + u, l2.keep) : NO_COL;
+                        v[u] = (NUMERIC && on) ? ld_keep_f32(B.val + e.qs + u, l2.keep) : 0.0f;
                     }
                     mid_products<NUMERIC, MID_SHORT>(sm, c, v, e.a);
                 }
@@ -976,14 +1017,14 @@ mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
                 const uint32_t left = n_mid % GROUPS;
                 const uint32_t n_grouped = (n_mid > GROUPS && left <= GROUPS / 4) ? n_mid - left : n_mid;
                 for (uint32_t it = half; it < n_grouped; it += GROUPS)
-                    mid_walk_row<NUMERIC>(sm, B, sm.l_qs[it], sm.l_len[it], sm.l_a[it], sub, 16u);
+                    mid_walk_row<NUMERIC>(sm, B, sm.l_qs[it], sm.l_len[it], sm.l_a[it], sub, 16u, l2.keep);
                 for (uint32_t it = n_grouped; it < n_mid; ++it)
-                    mid_walk_row<NUMERIC>(sm, B, sm.l_qs[it], sm.l_len[it], sm.l_a[it], tid, MID_THREADS);
+                    mid_walk_row<NUMERIC>(sm, B, sm.l_qs[it], sm.l_len[it], sm.l_a[it], tid, MID_THREADS, l2.keep);
                 // rows of B of 256 entries and more: the whole CTA
                 const uint32_t n_long = s_n_long;
                 for (uint32_t l = 0; l < n_long; ++l)
                     mid_walk_row<NUMERIC>(sm, B, sm.l_qs[255u - l], sm.l_len[255u - l], sm.l_a[255u - l], tid,
-                                          MID_THREADS);
+                                          MID_THREADS, l2.keep);
             }
             __syncthreads();
 
@@ -996,8 +1037,8 @@ mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
                         __popc(b1.x) + __popc(b1.y) + __popc(b1.z) + __popc(b1.w);
                     if (pattern) {
                         uint4* dst = reinterpret_cast<uint4*>(pattern + static_cast<size_t>(i) * pitch + tid * 8u);
-                        dst[0] = b0;
-                        dst[1] = b1;
+                        st_stream_v4(dst, b0, l2.stream);
+                        st_stream_v4(dst + 1, b1, l2.stream);
                     }
                 }
                 if (pattern && tid < DUP_WORDS)
@@ -1021,9 +1062,9 @@ mid_rows_kernel(Csr A, Csr B, Work w, const uint4* __restrict__ rows,
                     const uint32_t s0 = q * 4u;
                     if (vec_ok && s0 >= shift && s0 + 4u <= lim) {
                         const uint2 raw = *reinterpret_cast<const uint2*>(sm.cols + s0);
-                        *reinterpret_cast<uint4*>(gcol + s0) =
-                            make_uint4(raw.x & 0xffffu, raw.x >> 16, raw.y & 0xffffu, raw.y >> 16);
-                        *reinterpret_cast<uint4*>(gval + s0) = *reinterpret_cast<const uint4*>(sm.vals + s0);
+                        st_stream_v4(gcol + s0, make_uint4(raw.x & 0xffffu, raw.x >> 16, raw.y & 0xffffu, raw.y >> 16),
+                                     l2.stream);
+                        st_stream_v4(gval + s0, *reinterpret_cast<const uint4*>(sm.vals + s0), l2.stream);
                     } else {
                         for (uint32_t s = max(s0, shift); s < min(s0 + 4u, lim); ++s) {
                             gcol[s] = sm.cols[s];
