@@ -48,7 +48,7 @@ sys.path.insert(0, ROOT)
 # kernels (`--case dense_tf32`, `--case spgemm`, `--case spgemm_zipf`); the bench
 # scales them to its own launch
 DENSE_TRAFFIC_4x2048 = 280.8e6
-SPGEMM_TRAFFIC_PER_NNZC = {"poisson": 1762.4e6 / 136.1e6, "zipf": 707.4e6 / 53.3e6}
+SPGEMM_TRAFFIC_PER_NNZC = {"poisson": 1762.4e6 / 136.1e6, "zipf": 671.3e6 / 53.3e6}
 
 DENSE = {"dense_tf32": (4096, 0), "dense_tf32x3": (4096, 1), "dense4000_tf32": (4000, 0),
          "dense4000_tf32x3": (4000, 1)}
