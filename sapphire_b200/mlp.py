@@ -47,6 +47,7 @@ class MlpTrainer:
         needs ``rank``)."""
         self.ctx, self.lr, self.mode, self.world = ctx, float(lr), mode, world
         self.fused, self.row_pad = fused, row_pad
+        self._plan = None                      # prepared calls of the fused step, per batch size
         dev = torch.device("cuda", ctx.device)
         shapes = [w.shape for w in weights]
         # parameters share the gradient bucket's layout: one SGD kernel updates them all
@@ -122,8 +123,72 @@ class MlpTrainer:
             dy = dx
         return loss
 
+    # ------------------------------------------------------- prepared step
+    def _build_plan(self, x: torch.Tensor, onehot: torch.Tensor):
+        """The fused step as a list of calls whose arguments are marshalled once:
+        every buffer of the step is allocated here and reused, only the addresses
+        of the step's input and label change from call to call.  A step launched
+        eagerly then costs a dozen ctypes calls instead of a dozen trips through
+        the shape-checking front end (which took 2-3 times the GPU time of the
+        step); the kernels, their arguments and therefore the results are those
+        of `_forward_backward_fused`."""
+        import ctypes as C
+        ctx, mode = self.ctx, self.mode
+        nl = len(self.W)
+        B = x.shape[0]
+        dev = x.device
+        calls, patch_x, acts = [], [], [x]
+        for l in range(nl):
+            out = torch.empty(B, self.W[l].shape[1], dtype=torch.float32, device=dev)
+            calls.append(ops.prepare_gemm(ctx, acts[-1], self.W[l], out=out, bias=self.b[l], mode=mode,
+                                          relu=l < nl - 1))
+            if l == 0:
+                patch_x.append(calls[-1])
+            acts.append(out)
+        unit = acts[-1].shape[1]
+        ld = (unit + self.row_pad - 1) // self.row_pad * self.row_pad
+        prob = torch.empty(B, unit, dtype=torch.float32, device=dev)
+        loss = torch.empty(B, dtype=torch.float32, device=dev)
+        dlogits = torch.empty((B, ld), dtype=torch.float32, device=dev)[:, :unit]
+        ce = ops.PreparedCall("sb200_softmax_cross_entropy", L.lib().sb200_softmax_cross_entropy,
+                              [ctx.handle, prob.data_ptr(), loss.data_ptr(), dlogits.data_ptr(),
+                               dlogits.stride(0) if B > 1 else max(unit, dlogits.stride(0)),
+                               acts[-1].data_ptr(), onehot.data_ptr(), B, unit],
+                              ctx.device, [prob, loss, dlogits, acts[-1]], loss)
+        calls.append(ce)
+        dy = dlogits
+        for l in reversed(range(nl)):
+            dx = torch.empty(B, self.W[l].shape[0], dtype=torch.float32, device=dev)
+            calls.append(ops.prepare_gemm(ctx, dy, self.W[l], out=dx, trans_b=True, mode=mode,
+                                          relu_gate=acts[l] if l > 0 else None))
+            calls.append(ops.prepare_gemm(ctx, acts[l], dy, out=self.grads.dW[l], trans_a=True, mode=mode,
+                                          colsum_out=self.grads.dB[l], colsum_scale=1.0 / B))
+            if l == 0:
+                patch_x.append(calls[-1])
+            dy = dx
+        for c in calls:
+            c.args = list(c.args)
+        return {"batch": B, "calls": calls, "patch_x": patch_x, "ce": ce, "loss": loss,
+                "x_shape": tuple(x.shape), "y_shape": tuple(onehot.shape)}
+
+    def _run_plan(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
+        plan = self._plan
+        if (plan is None or plan["x_shape"] != tuple(x.shape) or plan["y_shape"] != tuple(onehot.shape)):
+            plan = self._plan = self._build_plan(x, onehot)
+        if not (x.is_contiguous() and onehot.is_contiguous() and x.dtype == torch.float32
+                and onehot.dtype == torch.float32):
+            raise ValueError("the prepared step takes contiguous fp32 inputs")
+        for c in plan["patch_x"]:
+            c.args[8] = x.data_ptr()                       # operand A of the first layer's two GEMMs
+        plan["ce"].args[6] = onehot.data_ptr()
+        for c in plan["calls"]:
+            c()
+        return plan["loss"]
+
     def step(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
-        loss = self.forward_backward(x, onehot)
+        """One training step; returns the per-sample loss (with the fused path a
+        buffer that the next step overwrites)."""
+        loss = self._run_plan(x, onehot) if self.fused else self.forward_backward(x, onehot)
         if self.exchange is not None:
             self.exchange.step(self.params.flat, self.lr)
             return loss

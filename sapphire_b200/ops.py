@@ -77,20 +77,31 @@ def _mat_geometry(t: torch.Tensor):
     return t.shape[0], t.shape[1], t.shape[2], ld, bs
 
 
-def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None,
-         out: Optional[torch.Tensor] = None, *, mode: int = L.MODE_TF32, trans_a: bool = False,
-         trans_b: bool = False, bias: Optional[torch.Tensor] = None,
-         colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0,
-         path: int = L.PATH_AUTO, relu: bool = False,
-         relu_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out = gate(relu((c + bias) + op(a).op(b))), batched over a leading dimension.
+class PreparedCall:
+    """One ABI call with its arguments marshalled once.  Calling it costs a ctypes
+    call and a stream lookup instead of the shape checks and argument building of
+    the front-end function, which is what bounds a step made of a dozen small
+    kernels when it is launched eagerly.  The tensors whose addresses the
+    arguments hold are kept alive by the object; they must not be reallocated."""
+    __slots__ = ("name", "fn", "args", "device", "keep", "result")
 
-    ``c`` may be ``out`` itself (in-place accumulate, Sapphire's
-    ``y <- y + a.b``).  A tensor with batch extent 1 (or 2-D) is shared by all
-    batches.  ``relu`` applies x > 0 ? x : 0 to the result; ``relu_gate`` (the
-    output's shape) zeroes the result where the gate is not positive, the
-    backward pass of a ReLU.  Returns ``out``.
-    """
+    def __init__(self, name, fn, args, device, keep, result=None):
+        self.name, self.fn, self.args, self.device, self.keep, self.result = name, fn, args, device, keep, result
+
+    def __call__(self):
+        rc = self.fn(*self.args, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc:
+            raise L.Sb200Error(self.name, rc)
+        return self.result
+
+
+def prepare_gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, *, mode: int = L.MODE_TF32, trans_a: bool = False,
+                 trans_b: bool = False, bias: Optional[torch.Tensor] = None,
+                 colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0,
+                 path: int = L.PATH_AUTO, relu: bool = False,
+                 relu_gate: Optional[torch.Tensor] = None) -> PreparedCall:
+    """The call `gemm` would make, as a `PreparedCall` (result: ``out``)."""
     ba, ra, ca, lda, sa = _mat_geometry(a)
     bb, rb, cb, ldb, sb = _mat_geometry(b)
     M, K = (ca, ra) if trans_a else (ra, ca)
@@ -122,6 +133,11 @@ def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tenso
         cptr = c.data_ptr()
     if ba not in (1, batch) or bb not in (1, batch):
         raise ValueError("operand batch must be 1 or the output batch")
+    keep = [a, b, c, out, bias, colsum_out, relu_gate]
+    head = (ctx.handle, mode, path, int(trans_a), int(trans_b), M, N, K,
+            a.data_ptr(), lda, sa if ba == batch and batch > 1 else 0,
+            b.data_ptr(), ldb, sb if bb == batch and batch > 1 else 0,
+            cptr, ldc, sc, out.data_ptr(), ldd, sd)
     if relu or relu_gate is not None:
         e = L.GemmEpilogue()
         e.bias = bias.data_ptr() if bias is not None else None
@@ -135,21 +151,32 @@ def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tenso
                 raise ValueError("relu_gate must have the output's shape")
             e.relu_gate, e.ld_gate = relu_gate.data_ptr(), ldg
             e.stride_gate = relu_gate.stride(0) if batch > 1 else 0
-        L.check("sb200_gemm_batched_ex", L.lib().sb200_gemm_batched_ex(
-            ctx.handle, mode, path, int(trans_a), int(trans_b), M, N, K,
-            a.data_ptr(), lda, sa if ba == batch and batch > 1 else 0,
-            b.data_ptr(), ldb, sb if bb == batch and batch > 1 else 0,
-            cptr, ldc, sc, out.data_ptr(), ldd, sd, C.byref(e), batch, _stream_ptr(ctx.device)))
-        return out
-    L.check("sb200_gemm_batched", L.lib().sb200_gemm_batched(
-        ctx.handle, mode, path, int(trans_a), int(trans_b), M, N, K,
-        a.data_ptr(), lda, sa if ba == batch and batch > 1 else 0,
-        b.data_ptr(), ldb, sb if bb == batch and batch > 1 else 0,
-        cptr, ldc, sc, out.data_ptr(), ldd, sd,
-        bias.data_ptr() if bias is not None else None,
-        colsum_out.data_ptr() if colsum_out is not None else None, float(colsum_scale),
-        batch, _stream_ptr(ctx.device)))
-    return out
+        keep.append(e)
+        return PreparedCall("sb200_gemm_batched_ex", L.lib().sb200_gemm_batched_ex,
+                            head + (C.byref(e), batch), ctx.device, keep, out)
+    return PreparedCall("sb200_gemm_batched", L.lib().sb200_gemm_batched,
+                        head + (bias.data_ptr() if bias is not None else None,
+                                colsum_out.data_ptr() if colsum_out is not None else None,
+                                float(colsum_scale), batch), ctx.device, keep, out)
+
+
+def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None, *, mode: int = L.MODE_TF32, trans_a: bool = False,
+         trans_b: bool = False, bias: Optional[torch.Tensor] = None,
+         colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0,
+         path: int = L.PATH_AUTO, relu: bool = False,
+         relu_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = gate(relu((c + bias) + op(a).op(b))), batched over a leading dimension.
+
+    ``c`` may be ``out`` itself (in-place accumulate, Sapphire's
+    ``y <- y + a.b``).  A tensor with batch extent 1 (or 2-D) is shared by all
+    batches.  ``relu`` applies x > 0 ? x : 0 to the result; ``relu_gate`` (the
+    output's shape) zeroes the result where the gate is not positive, the
+    backward pass of a ReLU.  Returns ``out``.
+    """
+    return prepare_gemm(ctx, a, b, c, out, mode=mode, trans_a=trans_a, trans_b=trans_b, bias=bias,
+                        colsum_out=colsum_out, colsum_scale=colsum_scale, path=path, relu=relu,
+                        relu_gate=relu_gate)()
 
 
 def gemm_reduce_scatter(ctx: Context, a: torch.Tensor, b: torch.Tensor, owners, ld_out: int, *,

@@ -290,6 +290,31 @@ def test_mlp_cuda_graph_step_equals_eager_step(ctx):
     assert torch.equal(eager.params.flat, graph.params.flat)
 
 
+def test_prepared_step_equals_the_front_end_calls(ctx):
+    """`step` runs the fused step from calls whose arguments were marshalled once
+    (the eager path of a launch-bound step); `forward_backward` makes the same calls
+    through the shape-checking front end.  Same kernels, same arguments: identical
+    gradients and loss, also when the batch size changes between steps."""
+    Ws, bs = W.mlp_init(0)
+    planned = mlp.MlpTrainer(ctx, Ws, bs, 1e-4, mode=L.MODE_TF32)
+    direct = mlp.MlpTrainer(ctx, Ws, bs, 1e-4, mode=L.MODE_TF32)
+    for t, rows in enumerate((64, 64, 24, 64)):
+        x, onehot = W.mlp_batch(t)
+        x, onehot = dev(x[:rows]), dev(onehot[:rows])
+        n0 = ctx.launch_count()
+        lp = planned.step(x, onehot).clone()
+        n1 = ctx.launch_count()
+        ld = direct.forward_backward(x, onehot).clone()
+        ops.sgd_update(ctx, direct.params.flat, direct.grads.flat, direct.lr)
+        n2 = ctx.launch_count()
+        assert n1 - n0 == n2 - n1 == 11
+        assert torch.equal(lp, ld)
+        assert torch.equal(planned.grads.flat.view(torch.int32), direct.grads.flat.view(torch.int32))
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    assert torch.equal(planned.params.flat.view(torch.int32), direct.params.flat.view(torch.int32))
+
+
 @pytest.mark.parametrize("batch,unit", [(64, 10), (5, 1), (33, 100), (7, 1024)])
 def test_fused_softmax_cross_entropy_equals_the_four_kernels(ctx, batch, unit):
     """One kernel for SoftMax + CrossEntropy + both backward passes: every output
