@@ -108,6 +108,11 @@ int64_t sb200_ctx_counter(const sb200_ctx* ctx, int which);
  *       the launch with SB200_ERR_DEVICE_TIMEOUT from sb200_check_device_status --
  *       the counterpart of the reference's CHECK_CUBLAS
  *       (Includes/Sapphire/compute/cudaUtil/CudaParams.cuh:51-58).
+ *   SB200_OPT_CLUSTER_SPLIT_K  1, the default: a TF32 product with few 128 x 64
+ *       output tiles and an inner dimension of 1024 or more (a wide Linear layer at
+ *       a small batch) runs with a cluster of 2 or 4 CTAs per tile, each multiplying
+ *       a slice of k; the partial tiles are summed in the cluster leader in fixed
+ *       order (bit-reproducible) before the ordinary epilogue; 0: one CTA per tile.
  *   SB200_OPT_SPGEMM_FAST_MID  1, the default: sparse products with at most 65536
  *       columns run their mid-sized rows (33 .. 16383 scalar products) on the kernels
  *       specialised for that width; 0: on the general row kernel (any width).
@@ -116,7 +121,8 @@ int64_t sb200_ctx_counter(const sb200_ctx* ctx, int which);
  *       every other role's wait runs out and the abort path executes. */
 enum { SB200_OPT_SPLIT_EXPLICIT_HI = 1, SB200_OPT_MERGE_MN_BOXES = 2, SB200_OPT_CTA_PAIRS = 3,
        SB200_OPT_SPLIT_TAIL_WAVE = 4, SB200_OPT_WAIT_LIMIT_US = 5,
-       SB200_OPT_TEST_STALL_KBLOCKS = 6, SB200_OPT_SPGEMM_FAST_MID = 7 };
+       SB200_OPT_TEST_STALL_KBLOCKS = 6, SB200_OPT_SPGEMM_FAST_MID = 7,
+       SB200_OPT_CLUSTER_SPLIT_K = 8 };
 int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value);
 
 /* Reads (and clears) the device status word after synchronising the stream.

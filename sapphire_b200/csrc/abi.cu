@@ -58,6 +58,7 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->merge_mn_boxes = 1;
     ctx->use_cta_pairs = 1;
     ctx->split_tail_wave = 0;
+    ctx->cluster_split_k = 1;
     ctx->encode_tiled = nullptr;
     ctx->tmaps = nullptr;
     ctx->tmap_clock = 0;
@@ -154,6 +155,9 @@ extern "C" int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value)
             return SB200_OK;
         case SB200_OPT_SPLIT_TAIL_WAVE:
             ctx->split_tail_wave = value != 0;
+            return SB200_OK;
+        case SB200_OPT_CLUSTER_SPLIT_K:
+            ctx->cluster_split_k = value != 0;
             return SB200_OK;
         case SB200_OPT_WAIT_LIMIT_US:
             if (value < 100)

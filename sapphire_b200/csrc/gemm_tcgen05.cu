@@ -645,6 +645,12 @@ int launch_one_cta(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
         bn = 64;
     else if (g.N <= 128 || tiles(256) < want)
         bn = 128;
+    if (bn == 64) {
+        // few tiles and a long inner dimension: a cluster of CTAs per tile, each a slice of k
+        const int split = cluster_split_k(ctx, g);
+        if (split > 1)
+            return launch_gemm_tcgen05_splitk(ctx, g, split, stream);
+    }
     if (g.colsum_out) {
         if (bn == 256) return launch_layout<256, 4, false, true>(ctx, g, stream);
         if (bn == 128) return launch_layout<128, 6, false, true>(ctx, g, stream);

@@ -341,6 +341,53 @@ def test_single_product_tail_wave_split(ctx, oracle, n):
     assert rel_fro(yt.cpu().numpy(), y1.cpu().numpy()) <= 1e-5
 
 
+@pytest.mark.parametrize("M,N,K,batch,ta,tb", [
+    (64, 512, 1536, 1, 0, 0),       # a wide Linear layer's forward pass at batch 64: 8 tiles x 4 CTAs
+    (64, 784, 1024, 1, 0, 1),       # a dx GEMM (W stored [in, out], read transposed)
+    (256, 256, 1024, 4, 0, 0),      # 32 tiles x 4 CTAs
+    (256, 256, 1024, 6, 0, 0),      # 48 tiles: 2 CTAs per tile
+    (100, 132, 1100, 2, 1, 0),      # ragged everything, K not a multiple of 32, A stored [K, M]
+    (128, 64, 1024, 3, 1, 1),       # both operands in the transposed orientation
+])
+def test_cluster_split_k(ctx, oracle, M, N, K, batch, ta, tb):
+    """Few output tiles and a long inner dimension: a cluster of 2 or 4 CTAs shares a
+    tile, each multiplying a slice of k; the leader sums the partial tiles in fixed
+    order and runs the ordinary epilogue.  Checked against the CPU loop with every
+    epilogue (in-place C, bias + ReLU, ReLU gate), against the one-CTA-per-tile
+    launch, and for run-to-run bit-reproducibility."""
+    rng = np.random.default_rng(M + N + K)
+    a = rng.standard_normal((batch, K, M) if ta else (batch, M, K)).astype(np.float32)
+    b = rng.standard_normal((batch, N, K) if tb else (batch, K, N)).astype(np.float32)
+    c = rng.uniform(-1, 1, (batch, M, N)).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    gate = rng.standard_normal((batch, M, N)).astype(np.float32)
+    ta_, tb_, tg = dev(a), dev(b), dev(gate)
+    want = np.stack([oracle.gemm_ex(ta, tb, M, N, K, a[i], a.shape[2], 0, b[i], b.shape[2], 0, c[i], N, 0,
+                                    N, 0, None, 1, M * N).reshape(M, N) for i in range(batch)])
+    launches = ctx.launch_count()
+    y = dev(c)
+    ops.gemm(ctx, ta_, tb_, y, y, trans_a=bool(ta), trans_b=bool(tb))                 # y <- y + a.b
+    assert ctx.launch_count() - launches == 1 and ctx.last_path() == L.PATH_TCGEN05
+    ctx.check_device_status()
+    assert rel_fro(y.cpu().numpy(), want) <= 2e-3
+    # the same request with one CTA per tile
+    ctx.set_option(L.OPT_CLUSTER_SPLIT_K, 0)
+    y1 = dev(c)
+    ops.gemm(ctx, ta_, tb_, y1, y1, trans_a=bool(ta), trans_b=bool(tb))
+    ctx.set_option(L.OPT_CLUSTER_SPLIT_K, 1)
+    assert rel_fro(y.cpu().numpy(), y1.cpu().numpy()) <= 1e-5
+    assert not torch.equal(y, y1) or K <= 32          # other summation order: it did run the other kernel
+    # bias + ReLU, then the ReLU gate; reproducible bit for bit
+    r1 = ops.gemm(ctx, ta_, tb_, trans_a=bool(ta), trans_b=bool(tb), bias=dev(bias), relu=True)
+    r2 = ops.gemm(ctx, ta_, tb_, trans_a=bool(ta), trans_b=bool(tb), bias=dev(bias), relu=True)
+    assert torch.equal(r1, r2)
+    lin = want - c + bias[None, None, :]
+    assert rel_fro(r1.cpu().numpy(), np.maximum(lin, 0)) <= 2e-3
+    g1 = ops.gemm(ctx, ta_, tb_, trans_a=bool(ta), trans_b=bool(tb), relu_gate=tg)
+    assert rel_fro(g1.cpu().numpy(), np.where(gate > 0, want - c, 0)) <= 2e-3
+    ctx.check_device_status()
+
+
 def test_tensor_map_cache(ctx):
     """A GEMM on operands the context has seen encodes no TMA descriptor."""
     a = torch.randn(512, 256, device=DEV)
@@ -366,7 +413,7 @@ def test_tensor_map_cache(ctx):
     ctx.check_device_status()
 
 
-@pytest.mark.parametrize("shape", ["one_cta", "pair", "split_mode"])
+@pytest.mark.parametrize("shape", ["one_cta", "pair", "split_mode", "cluster_split_k"])
 def test_bounded_wait_runs_out_and_context_survives(ctx, shape):
     """The TMA producers stop after 3 k-blocks (test hook) with the wait limit at
     2 ms: the MMA issuer's and the epilogue's waits run out, every role leaves
@@ -375,6 +422,8 @@ def test_bounded_wait_runs_out_and_context_survives(ctx, shape):
     CHECK_CUBLAS.  The same context then runs a normal GEMM."""
     if shape == "pair":
         M, N, K, batch, mode = 1024, 512, 256, 40, L.MODE_TF32
+    elif shape == "cluster_split_k":
+        M, N, K, batch, mode = 64, 512, 1536, 1, L.MODE_TF32      # (from K = 2048 on, slices of k run as batches)
     elif shape == "one_cta":
         M, N, K, batch, mode = 256, 256, 256, 4, L.MODE_TF32
     else:
