@@ -240,6 +240,27 @@ def _case_dense(mode, ta=False, tb=False, n=2048, batch=4, k=0):
     return {"check": float(out[0, 0, 0]), "launches": ctx.launch_count()}
 
 
+def _case_dense_small_batch(K=1536):
+    """A wide Linear layer's forward pass at batch 64, y = relu(bias + x.W): few
+    tiles and a long inner dimension, the cluster split-k kernel (the operands are
+    small: this case is latency-bound, not a DRAM measurement)."""
+    import torch
+    from sapphire_b200 import ops
+    dev = torch.device("cuda:0")
+    ctx = ops.Context(0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    x = torch.randn(64, K, device=dev, generator=g)
+    w = torch.randn(K, 512, device=dev, generator=g)
+    bias = torch.randn(512, device=dev, generator=g)
+    out = torch.empty(64, 512, device=dev)
+    for _ in range(3):
+        ops.gemm(ctx, x, w, None, out, bias=bias, relu=True)
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    return {"check": float(out[0, 0]), "launches": ctx.launch_count()}
+
+
 def _case_spgemm(dist_name, M=32768, N=65536):
     import torch
     from sapphire_b200 import ops
@@ -322,6 +343,7 @@ PROFILE_CASES = {
     "dense_tn": lambda: _case_dense(0, ta=True),
     "dense_nt": lambda: _case_dense(0, tb=True),
     "dense_epilogue": lambda: _case_dense(0, n=8192, batch=1, k=32),
+    "dense_small_batch": _case_dense_small_batch,               # 64 x 512 x 1536, bias + ReLU: cluster split-k
     "dense_single_4096": lambda: _case_dense(0, n=4096, batch=1),   # what one GPU of eight runs
     "spgemm": lambda: _case_spgemm("poisson"),                  # 32768 rows of the 65536^2 case
     "spgemm_zipf": lambda: _case_spgemm("zipf"),
