@@ -55,6 +55,7 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->d_workspace = nullptr;
     ctx->workspace_bytes = 0;
     ctx->split_explicit_hi = 0;
+    ctx->split_a_tmem = 1;
     ctx->merge_mn_boxes = 1;
     ctx->use_cta_pairs = 1;
     ctx->split_tail_wave = 0;
@@ -158,6 +159,9 @@ extern "C" int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value)
             return SB200_OK;
         case SB200_OPT_CLUSTER_SPLIT_K:
             ctx->cluster_split_k = value != 0;
+            return SB200_OK;
+        case SB200_OPT_SPLIT_A_TMEM:
+            ctx->split_a_tmem = value != 0;
             return SB200_OK;
         case SB200_OPT_WAIT_LIMIT_US:
             if (value < 100)

@@ -86,6 +86,7 @@ struct sb200_ctx {
     float* d_workspace;        // scratch for partial column sums / sparse row work
     size_t workspace_bytes;
     int split_explicit_hi;     // 3xTF32: rewrite the high part in shared memory too
+    int split_a_tmem;          // 3xTF32: both parts of an [M, K] A tile go to TMEM
     int merge_mn_boxes;        // fetch an MN-major tile with one 4-D TMA box when possible
     int use_cta_pairs;         // large TF32 problems run on the two-CTA (cta_group::2) kernel
     int split_tail_wave;       // a mostly empty last wave of pair tiles goes to the one-CTA kernel

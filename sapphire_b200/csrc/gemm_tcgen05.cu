@@ -31,7 +31,7 @@ namespace {
 
 constexpr int TILE_PANEL = 16;          // row tiles (of 128 rows) per panel of the tile order
 
-template <int BLOCK_N, int STAGES, bool SPLIT>
+template <int BLOCK_N, int STAGES, bool SPLIT, bool A_TM = false>
 struct SmemLayout {
     static constexpr int B_TILE_BYTES = BLOCK_N * BLOCK_K * 4;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;   // one raw k-block (A + B)
@@ -39,10 +39,17 @@ struct SmemLayout {
     // have to cover the ~2 us from TMA issue to landed data; a low-part tile exists
     // just between the split warps and the MMAs that consume it (measured: 4 raw + 2 low
     // stages are slower than 3 + 3, the split warps need the slack).
-    static constexpr int LO_STAGES = SPLIT ? 3 : 0;
-    static constexpr int TILES_BYTES = STAGE_BYTES * (STAGES + LO_STAGES);
-    // accumulator buffers in TMEM (512 columns at most)
-    static constexpr int NUM_ACC = SPLIT ? 4 : 2;
+    // A_TM: both parts of A go to TMEM instead (the tensor core reads them from
+    // there), the ring holds the low part of B only.
+    static constexpr int LO_STAGES = SPLIT ? (A_TM ? 4 : 3) : 0;
+    static constexpr int LO_STAGE_BYTES = A_TM ? B_TILE_BYTES : STAGE_BYTES;
+    static constexpr int TILES_BYTES = STAGE_BYTES * STAGES + LO_STAGE_BYTES * LO_STAGES;
+    // accumulator buffers in TMEM (512 columns at most; A_TM: two accumulators and
+    // LO_STAGES slots of 2 x 32 columns for the parts of A)
+    static constexpr int NUM_ACC = SPLIT ? (A_TM ? 2 : 4) : 2;
+    static constexpr int TMEM_COLS = A_TM ? 512 : NUM_ACC * BLOCK_N;
+    static constexpr int A_TMEM_COL0 = NUM_ACC * BLOCK_N;
+    static_assert(!A_TM || A_TMEM_COL0 + LO_STAGES * 2 * BLOCK_K <= 512, "TMEM columns");
     // barriers: full, empty per raw stage; lo_full, lo_empty per low-part stage; tmem_full,
     // tmem_empty per accumulator
     // (rounded to 16 bytes: the epilogue staging tiles that follow take float4 accesses)
@@ -50,6 +57,7 @@ struct SmemLayout {
     // + epilogue staging tiles (4 warps) + alignment slack
     static constexpr int TOTAL = TILES_BYTES + BAR_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP +
                                  COLSUM_SCRATCH_BYTES + 1024;
+    static_assert(TOTAL <= 227 * 1024, "shared memory per CTA");
 };
 
 // hi/lo split of one fp32 value for the 3xTF32 mode.  hi is exactly
@@ -66,17 +74,20 @@ __device__ __forceinline__ void split_tf32(float x, bool rounded, float& hi, flo
     lo = x - hi;
 }
 
-template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT, bool COLSUM>
+template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT, bool COLSUM, bool A_TM>
 __global__ void __launch_bounds__((SPLIT || COLSUM) ? 320 : 192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                     const __grid_constant__ CUtensorMap mapB, const KernelParams p)
 {
-    using L = SmemLayout<BLOCK_N, STAGES, SPLIT>;
+    // A_TM (3xTF32 with A stored [M, K]): the split warps put both parts of A into TMEM
+    static_assert(!A_TM || (SPLIT && !A_MN), "A in TMEM: 3xTF32 mode, A stored [M, K]");
+    using L = SmemLayout<BLOCK_N, STAGES, SPLIT, A_TM>;
     constexpr int B_TILE_BYTES = L::B_TILE_BYTES;
     constexpr int HALF_STAGE = A_TILE_BYTES + B_TILE_BYTES;       // the hi (raw) tiles
     constexpr int LO_STAGES = L::LO_STAGES;
+    constexpr int LO_STAGE_BYTES = L::LO_STAGE_BYTES;
     constexpr int NUM_ACC = L::NUM_ACC;
-    constexpr uint32_t TMEM_COLS = NUM_ACC * BLOCK_N;              // 256 or 512: power of two
+    constexpr uint32_t TMEM_COLS = L::TMEM_COLS;                   // 256 or 512: power of two
     static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
                   "TMEM allocation must be a power of two");
 
@@ -239,8 +250,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                             const uint64_t b_hi =
                                 ptx::make_smem_desc(sb + k * B_KSTEP, B_LBO, B_SBO, B_LAY);
                             const uint32_t first = (kb > kb0 || k > 0) ? 1u : 0u;
-                            if (SPLIT) {
-                                const uint32_t la = ptx::smem_u32(lo_ring + ls * HALF_STAGE);
+                            if (A_TM) {
+                                const uint32_t a_hi_t =
+                                    tmem_base + static_cast<uint32_t>(L::A_TMEM_COL0 +
+                                                                      ls * 2 * BLOCK_K + k * UMMA_K);
+                                const uint32_t a_lo_t = a_hi_t + BLOCK_K;
+                                const uint64_t b_lo = ptx::make_smem_desc(
+                                    ptx::smem_u32(lo_ring + ls * LO_STAGE_BYTES) + k * B_KSTEP, B_LBO,
+                                    B_SBO, B_LAY);
+                                // small terms first
+                                ptx::mma_tf32_a_tmem(d_tmem, a_lo_t, b_hi, idesc, first);
+                                ptx::mma_tf32_a_tmem(d_tmem, a_hi_t, b_lo, idesc, 1u);
+                                ptx::mma_tf32_a_tmem(d_tmem, a_hi_t, b_hi, idesc, 1u);
+                            } else if (SPLIT) {
+                                const uint32_t la = ptx::smem_u32(lo_ring + ls * LO_STAGE_BYTES);
                                 const uint64_t a_lo = ptx::make_smem_desc(
                                     la + k * A_KSTEP, A_LBO, A_SBO, A_LAY);
                                 const uint64_t b_lo = ptx::make_smem_desc(
@@ -417,8 +440,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                     break;
                 if (!(ok = wait_bar(&lo_empty[ls], lph ^ 1u, ab, FAULT_SPLIT_WAIT)))
                     break;
+                if constexpr (A_TM) {
+                    // A: this thread's row of the landed [128 rows x 32 k] tile (128 bytes,
+                    // its 16-byte pieces permuted by the 128-byte swizzle) goes to TMEM
+                    // lane = row, as the high part in 32 columns and the low part in the
+                    // next 32.  Warp w of the CTA reaches TMEM lanes 32 (w % 4) .. + 31.
+                    const int row = (warp & 3) * 32 + lane;
+                    const float4* arow =
+                        reinterpret_cast<const float4*>(smem + s * L::STAGE_BYTES + row * 128);
+                    uint32_t h[32], l[32];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const float4 x = arow[c ^ (row & 7)];
+                        float fh, fl;
+                        split_tf32(x.x, rounded, fh, fl);
+                        h[4 * c + 0] = __float_as_uint(fh); l[4 * c + 0] = __float_as_uint(fl);
+                        split_tf32(x.y, rounded, fh, fl);
+                        h[4 * c + 1] = __float_as_uint(fh); l[4 * c + 1] = __float_as_uint(fl);
+                        split_tf32(x.z, rounded, fh, fl);
+                        h[4 * c + 2] = __float_as_uint(fh); l[4 * c + 2] = __float_as_uint(fl);
+                        split_tf32(x.w, rounded, fh, fl);
+                        h[4 * c + 3] = __float_as_uint(fh); l[4 * c + 3] = __float_as_uint(fl);
+                    }
+                    const uint32_t slot = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                                          static_cast<uint32_t>(L::A_TMEM_COL0 + ls * 2 * BLOCK_K);
+                    ptx::tmem_st_32x32(slot, h);
+                    ptx::tmem_st_32x32(slot + BLOCK_K, l);
+                    // B: every float4 of the landed tile once, its low part to the twin tile
+                    const float4* bhi =
+                        reinterpret_cast<const float4*>(smem + s * L::STAGE_BYTES + A_TILE_BYTES);
+                    float4* bhi_w = reinterpret_cast<float4*>(smem + s * L::STAGE_BYTES + A_TILE_BYTES);
+                    float4* blo = reinterpret_cast<float4*>(lo_ring + ls * LO_STAGE_BYTES);
+                    constexpr int PER_THREAD = B_TILE_BYTES / 16 / 128;
+                    float4 x[PER_THREAD];
+#pragma unroll
+                    for (int j = 0; j < PER_THREAD; ++j)
+                        x[j] = bhi[tid + j * 128];
+#pragma unroll
+                    for (int j = 0; j < PER_THREAD; ++j) {
+                        float4 hh, ll;
+                        split_tf32(x[j].x, rounded, hh.x, ll.x);
+                        split_tf32(x[j].y, rounded, hh.y, ll.y);
+                        split_tf32(x[j].z, rounded, hh.z, ll.z);
+                        split_tf32(x[j].w, rounded, hh.w, ll.w);
+                        blo[tid + j * 128] = ll;
+                        if (rounded)
+                            bhi_w[tid + j * 128] = hh;
+                    }
+                    ptx::tmem_st_wait();
+                    ptx::tc_fence_before_sync();
+                } else {
                 float4* hi = reinterpret_cast<float4*>(smem + s * L::STAGE_BYTES);
-                float4* lo = reinterpret_cast<float4*>(lo_ring + ls * HALF_STAGE);
+                float4* lo = reinterpret_cast<float4*>(lo_ring + ls * LO_STAGE_BYTES);
                 // all loads of a batch first, then the arithmetic, then the stores: the
                 // split must finish well inside one k-block of tensor-core time
                 constexpr int PER_THREAD = HALF_STAGE / 16 / 128;          // float4 per thread
@@ -441,6 +514,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                         if (rounded)
                             hi[tid + (b0 + j) * 128] = h;
                     }
+                }
                 }
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
@@ -508,11 +582,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
 
 // ------------------------------------------------------------------- host
 
-template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT, bool COLSUM>
+template <int BLOCK_N, int STAGES, bool A_MN, bool B_MN, bool SPLIT, bool COLSUM, bool A_TM = false>
 int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 {
-    using L = SmemLayout<BLOCK_N, STAGES, SPLIT>;
-    auto kern = gemm_tcgen05_kernel<BLOCK_N, STAGES, A_MN, B_MN, SPLIT, COLSUM>;
+    using L = SmemLayout<BLOCK_N, STAGES, SPLIT, A_TM>;
+    auto kern = gemm_tcgen05_kernel<BLOCK_N, STAGES, A_MN, B_MN, SPLIT, COLSUM, A_TM>;
     static bool attr_done[16] = {};
     if (ctx->device < 16 && !attr_done[ctx->device]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
@@ -595,6 +669,13 @@ int launch_layout(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 {
     const bool a_mn = g.transA != 0;     // stored [K, M]
     const bool b_mn = g.transB == 0;     // stored [K, N]
+    if constexpr (SPLIT) {
+        // A stored [M, K]: its two parts live in TMEM, the shared memory that frees
+        // holds a fourth raw stage and a fourth low-part tile of B
+        if (!a_mn && ctx->split_a_tmem)
+            return b_mn ? launch_variant<BLOCK_N, 4, false, true, SPLIT, COLSUM, true>(ctx, g, stream)
+                        : launch_variant<BLOCK_N, 4, false, false, SPLIT, COLSUM, true>(ctx, g, stream);
+    }
     if (a_mn)
         return b_mn ? launch_variant<BLOCK_N, STAGES, true, true, SPLIT, COLSUM>(ctx, g, stream)
                     : launch_variant<BLOCK_N, STAGES, true, false, SPLIT, COLSUM>(ctx, g, stream);

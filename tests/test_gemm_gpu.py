@@ -388,6 +388,33 @@ def test_cluster_split_k(ctx, oracle, M, N, K, batch, ta, tb):
     ctx.check_device_status()
 
 
+@pytest.mark.parametrize("M,N,K,batch,tb", [(256, 256, 256, 4, 0), (200, 136, 100, 3, 0),
+                                            (384, 260, 1056, 2, 1), (128, 128, 32, 1, 0),
+                                            (1024, 1024, 2048, 2, 0)])
+def test_tf32x3_parts_of_a_in_tensor_memory(ctx, M, N, K, batch, tb):
+    """fp32-accurate mode, A stored [M, K]: the high and low parts of A's tiles are
+    written to tensor memory and read from there by the tensor core (the default)
+    or both low parts go to shared memory (option off).  The same products in the
+    same order: bit-identical results, and within 1e-5 of the fp64 product."""
+    g = torch.Generator(device=DEV); g.manual_seed(M + N + K)
+    a = torch.randn(batch, M, K, device=DEV, generator=g)
+    b = torch.randn(batch, N, K, device=DEV, generator=g) if tb else \
+        torch.randn(batch, K, N, device=DEV, generator=g)
+    c = torch.rand(batch, M, N, device=DEV, generator=g)
+    bias = torch.randn(N, device=DEV, generator=g)
+    res = []
+    for opt in (1, 0):
+        ctx.set_option(L.OPT_SPLIT_A_TMEM, opt)
+        res.append(ops.gemm(ctx, a, b, c, trans_b=bool(tb), bias=bias, mode=L.MODE_TF32X3))
+        assert ctx.last_path() == L.PATH_TCGEN05
+    ctx.set_option(L.OPT_SPLIT_A_TMEM, 1)
+    ctx.check_device_status()
+    bm = b.transpose(1, 2) if tb else b
+    want = (c.double() + bias.double() + a.double() @ bm.double()).cpu().numpy()
+    assert rel_fro(res[0].cpu().numpy(), want) <= 1e-5
+    assert torch.equal(res[0], res[1])
+
+
 def test_tensor_map_cache(ctx):
     """A GEMM on operands the context has seen encodes no TMA descriptor."""
     a = torch.randn(512, 256, device=DEV)
@@ -413,7 +440,8 @@ def test_tensor_map_cache(ctx):
     ctx.check_device_status()
 
 
-@pytest.mark.parametrize("shape", ["one_cta", "pair", "split_mode", "cluster_split_k"])
+@pytest.mark.parametrize("shape", ["one_cta", "pair", "split_mode", "split_mode_transposed_a",
+                                   "cluster_split_k"])
 def test_bounded_wait_runs_out_and_context_survives(ctx, shape):
     """The TMA producers stop after 3 k-blocks (test hook) with the wait limit at
     2 ms: the MMA issuer's and the epilogue's waits run out, every role leaves
@@ -428,14 +456,15 @@ def test_bounded_wait_runs_out_and_context_survives(ctx, shape):
         M, N, K, batch, mode = 256, 256, 256, 4, L.MODE_TF32
     else:
         M, N, K, batch, mode = 256, 256, 512, 2, L.MODE_TF32X3
-    a = torch.randn(batch, M, K, device=DEV)
+    ta = shape == "split_mode_transposed_a"     # the low parts of A in shared memory, not TMEM
+    a = torch.randn(batch, K, M, device=DEV) if ta else torch.randn(batch, M, K, device=DEV)
     b = torch.randn(batch, K, N, device=DEV)
-    good = ops.gemm(ctx, a, b, mode=mode)
+    good = ops.gemm(ctx, a, b, mode=mode, trans_a=ta)
     ctx.check_device_status()
     ctx.set_option(L.OPT_WAIT_LIMIT_US, 2000)
     ctx.set_option(L.OPT_TEST_STALL_KBLOCKS, 3)
     try:
-        ops.gemm(ctx, a, b, mode=mode)
+        ops.gemm(ctx, a, b, mode=mode, trans_a=ta)
         with pytest.raises(L.Sb200Error) as e:
             ctx.check_device_status()
         assert e.value.status == L.ERR_DEVICE_TIMEOUT
@@ -443,7 +472,7 @@ def test_bounded_wait_runs_out_and_context_survives(ctx, shape):
         ctx.set_option(L.OPT_TEST_STALL_KBLOCKS, -1)
         ctx.set_option(L.OPT_WAIT_LIMIT_US, 2000000)
     ctx.check_device_status()                            # the word was cleared
-    again = ops.gemm(ctx, a, b, mode=mode)
+    again = ops.gemm(ctx, a, b, mode=mode, trans_a=ta)
     ctx.check_device_status()
     assert torch.equal(again, good)
 
