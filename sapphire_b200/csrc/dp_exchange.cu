@@ -93,12 +93,17 @@ __device__ __forceinline__ void wait_flags(const uint32_t* mine, int world, int 
 {
     if (static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != skip) {
         const uint32_t* f = mine + first + threadIdx.x;
-        const uint64_t t0 = now_ns();
+        uint64_t t0 = 0;                       // the timer is slow to read: started at the 16th try
         uint32_t spins = 0;
         while (static_cast<int32_t>(ld_acquire_sys(f) - step) < 0) {
-            if ((++spins & 15u) == 0 && now_ns() - t0 > limit_ns) {
-                atomicCAS(status, 0u, code);
-                break;
+            if ((++spins & 15u) == 0) {
+                const uint64_t now = now_ns();
+                if (t0 == 0) {
+                    t0 = now;
+                } else if (now - t0 > limit_ns) {
+                    atomicCAS(status, 0u, code);
+                    break;
+                }
             }
         }
     }

@@ -92,15 +92,18 @@ struct Abort {
 __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, const Abort& ab,
                                          unsigned code)
 {
-    if (ptx::mbar_try_wait(bar, parity))
-        return true;
-    const uint64_t t0 = ptx::globaltimer_ns();
+    // The global timer is slow to read: the clock of a wait starts at its 64th failed
+    // try, so the waits of the steady state (a few tries) never read it.
+    uint64_t t0 = 0;
     uint32_t spins = 0;
     while (!ptx::mbar_try_wait(bar, parity)) {
         if ((++spins & 63u) == 0) {
             if (*ab.flag)
                 return false;
-            if (ptx::globaltimer_ns() - t0 > ab.limit_ns) {
+            const uint64_t now = ptx::globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > ab.limit_ns) {
                 *ab.flag = 1;
                 atomicCAS(ab.status, 0u, code);
                 return false;
