@@ -31,6 +31,20 @@ def test_library_exports_every_declared_symbol():
     assert sorted(L.SIGNATURES) == decl
 
 
+def test_python_constants_equal_the_header_enumerators():
+    """Every SB200_* enumerator of the public header has a constant of the same value
+    in the ctypes table (named without the prefix), so an option or status added to
+    one side cannot drift from the other."""
+    from sapphire_b200 import _lib as L
+    text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "sapphire_b200.h")).read(),
+                  flags=re.S)
+    enums = dict(re.findall(r"\bSB200_([A-Z0-9_]+)\s*=\s*(-?\d+)", text))
+    assert len(enums) >= 20
+    for name, value in enums.items():
+        assert hasattr(L, name), f"SB200_{name} has no Python constant"
+        assert getattr(L, name) == int(value), name
+
+
 def test_status_strings():
     from sapphire_b200 import _lib as L
     assert L.status_string(L.OK) == "ok"
