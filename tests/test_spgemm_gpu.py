@@ -52,6 +52,41 @@ def test_spgemm_matches_oracle(ctx, oracle, M, K, N, dens, dist, cap):
     run_case(ctx, oracle, M, K, N, 0, 1, dens, dist, cap or 4096)
 
 
+@pytest.mark.parametrize("M,K,N,a,b", [
+    # A (density | Zipf cap), B likewise: the walk classes of the mid-row kernel
+    (500, 300, 65536, 0.05, 0.005),      # rows of B of ~330 entries: walked by the whole CTA
+    (500, 300, 65536, 0.2, 0.005),       # the same with ~20 k products per row: heavy bin
+    (400, 2000, 65536, 0.05, 0.00003),   # rows of B of <= 4 entries: walked by single threads
+    (300, 1500, 65535, 0.03, 0.001),     # one column short of the rank-table kernels' width
+    (300, 1500, 65537, 0.03, 0.001),     # one column beyond it: general row kernel
+    (1, 4096, 65536, 0.5, 0.001),        # a single row of A with 2048 nonzeros
+    (1500, 1500, 40000, ("zipf", 1024), 0.002),   # power-law A on uniform B
+    (1500, 1500, 40000, 0.01, ("zipf", 1024)),    # uniform A on power-law B
+    (700, 700, 33, 0.05, 0.5),           # 33 columns: every product collides
+])
+def test_spgemm_mixed_operands(ctx, oracle, M, K, N, a, b):
+    """A and B drawn from different distributions, so that each way the kernels walk a
+    row of B (single threads, 16-lane groups, the whole CTA) and each bin meets rows
+    of the other kinds."""
+    def draw(seed, rows, cols, spec):
+        if isinstance(spec, tuple):
+            return W.csr_random(seed, rows, cols, None, spec[0], zipf_cap=spec[1])
+        return W.csr_random(seed, rows, cols, spec, "poisson")
+    rA, cA, vA = draw(10, M, K, a)
+    rB, cB, vB = draw(11, K, N, b)
+    A = ops.CsrMatrix.from_numpy(rA, cA, vA, M, K, DEV)
+    B = ops.CsrMatrix.from_numpy(rB, cB, vB, K, N, DEV)
+    Cm = ops.spgemm(ctx, A, B)
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    rc, cc, vc = Cm.to_numpy()
+    orc, occ, ovc, _ = oracle.spgemm(rA, cA, vA, rB, cB, vB, M, N)
+    assert np.array_equal(rc, orc), "ROW differs"
+    assert np.array_equal(cc, occ), "COL differs"
+    if ovc.size:
+        assert np.abs(vc - ovc).max() <= 1e-5 * max(np.abs(ovc).max(), 1.0)
+
+
 @pytest.mark.parametrize("dist,cap", [("poisson", 0), ("zipf", 2048)])
 def test_spgemm_general_row_kernel_below_65536_columns(ctx, oracle, dist, cap):
     """Products of at most 65536 columns run their mid-sized rows on specialised
