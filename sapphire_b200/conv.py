@@ -14,7 +14,7 @@ backward   drX[N, C*kh*kw, P] = filter^T . dY      (transposed operand by descri
 from __future__ import annotations
 
 import ctypes as C
-from typing import Tuple
+from typing import Optional, Tuple
 
 import torch
 
@@ -34,11 +34,19 @@ def _geometry(x_shape, kh: int, kw: int, stride: Pair, pad: Pair, dil: Pair) -> 
 
 
 def im2col(ctx: ops.Context, x: torch.Tensor, kh: int, kw: int, stride: Pair = (1, 1),
-           pad: Pair = (0, 0), dil: Pair = (1, 1), pad_value: float = 0.0) -> torch.Tensor:
-    """x [N, C, H, W] (contiguous) -> cols [N, C*kh*kw, outR*outC]."""
+           pad: Pair = (0, 0), dil: Pair = (1, 1), pad_value: float = 0.0,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [N, C, H, W] (contiguous) -> cols [N, C*kh*kw, outR*outC] (``out`` if given:
+    contiguous, that shape)."""
     N, Cc, H, W = x.shape
     P = out_size(H, pad[0], dil[0], kh, stride[0]) * out_size(W, pad[1], dil[1], kw, stride[1])
-    cols = torch.empty((N, Cc * kh * kw, P), dtype=torch.float32, device=x.device)
+    shape = (N, Cc * kh * kw, P)
+    if out is None:
+        cols = torch.empty(shape, dtype=torch.float32, device=x.device)
+    else:
+        if tuple(out.shape) != shape or not out.is_contiguous() or out.dtype != torch.float32:
+            raise ValueError(f"out must be a contiguous fp32 tensor of shape {shape}")
+        cols = out
     g = _geometry(x.shape, kh, kw, stride, pad, dil)
     L.check("sb200_im2col", L.lib().sb200_im2col(ctx.handle, cols.data_ptr(), x.contiguous().data_ptr(),
                                                   C.byref(g), float(pad_value), ops._stream_ptr(ctx.device)))
