@@ -37,6 +37,7 @@ import os
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 import numpy as np
@@ -53,6 +54,7 @@ SPGEMM_TRAFFIC_PER_NNZC = {"poisson": 1762.4e6 / 136.1e6, "zipf": 671.3e6 / 53.3
 DENSE = {"dense_tf32": (4096, 0), "dense_tf32x3": (4096, 1), "dense4000_tf32": (4000, 0),
          "dense4000_tf32x3": (4000, 1)}
 BATCH = 8
+EXTRAS_DEADLINE_S = 300          # the extra workloads of the default run, all together
 
 
 def dense_workload_text(n: int, per_gpu: int = 0) -> str:
@@ -811,8 +813,40 @@ def main():
     else:
         raise SystemExit(f"unknown workload {args.workload}")
 
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        if args.workload in ("spgemm", "spgemm_zipf"):
+            dist_name = "poisson" if args.workload == "spgemm" else "zipf"
+            sec, flops = cpu_spgemm_sample(dist_name, 8192)
+            line["cpu_baseline"] = {
+                "value": flops / sec / 1e9, "unit": "GFLOP/s", "cores": 1, "kind": "port",
+                "sample": f"first 8192 rows of A against the full B, {sec:.1f} s; CPU Gustavson "
+                          "oracle (the reference ships no sparse GEMM implementation)"}
+        else:
+            n = DENSE.get(args.workload, (4096, 0))[0]
+            rows = 96
+            sec, kind, flops = cpu_gemm_sample(n, rows)
+            line["cpu_baseline"] = {
+                "value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": kind,
+                "sample": f"{rows} output rows of one {n}^3 batch, {sec:.1f} s; Sapphire's CPU GEMM "
+                          "is a single-threaded scalar loop"}
+
     if not args.no_extras and args.workload == "dense_tf32" and not args.per_gpu_batch:
         extras = []
+        line["other_workloads"] = extras
+
+        # The headline above is measured; should one of the extra workloads below stall
+        # (a rank that died, a collective that never completes) every rank leaves after
+        # the deadline and rank 0 still prints the line with the extras finished so far.
+        def give_up():
+            if rank == 0:
+                line["other_workloads_incomplete"] = (
+                    f"stopped after {EXTRAS_DEADLINE_S} s with {len(extras)} extra workload(s) done")
+                os.write(json_fd, (json.dumps(line) + "\n").encode())
+            os._exit(0)
+
+        watchdog = threading.Timer(EXTRAS_DEADLINE_S, give_up)
+        watchdog.daemon = True
+        watchdog.start()
         for name in ("dense_tf32x3", "dense4000_tf32"):
             n, mode = DENSE[name]
             r = bench_dense(n, mode, 5, 3, False)
@@ -831,24 +865,8 @@ def main():
         if world > 1:
             extras.append(bench_mlp(50, 5, "nccl"))
         extras.append(bench_conv(10, 3))
-        line["other_workloads"] = extras
+        watchdog.cancel()
 
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        if args.workload in ("spgemm", "spgemm_zipf"):
-            dist_name = "poisson" if args.workload == "spgemm" else "zipf"
-            sec, flops = cpu_spgemm_sample(dist_name, 8192)
-            line["cpu_baseline"] = {
-                "value": flops / sec / 1e9, "unit": "GFLOP/s", "cores": 1, "kind": "port",
-                "sample": f"first 8192 rows of A against the full B, {sec:.1f} s; CPU Gustavson "
-                          "oracle (the reference ships no sparse GEMM implementation)"}
-        else:
-            n = DENSE.get(args.workload, (4096, 0))[0]
-            rows = 96
-            sec, kind, flops = cpu_gemm_sample(n, rows)
-            line["cpu_baseline"] = {
-                "value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": kind,
-                "sample": f"{rows} output rows of one {n}^3 batch, {sec:.1f} s; Sapphire's CPU GEMM "
-                          "is a single-threaded scalar loop"}
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:
