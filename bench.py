@@ -533,28 +533,36 @@ def main():
         da, db, dc, dy = (torch.empty(m, n, n, device=dev) for _ in range(4))
 
         # per batch: H2D on one stream, GEMM on the compute stream, D2H on a third,
-        # chained by events, so that the copies of batch i+1 overlap the GEMM of batch i
+        # chained by events, so that the copies of batch i+1 overlap the GEMM of batch i.
+        # Steps follow each other like the passes of a streaming job: the uploads of the
+        # next step start while the last product of this one is still on its way back;
+        # a device buffer is overwritten only after its last reader of the step before
+        # (events per batch: product done, result copied out).
         h2d, d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         ev_in = [torch.cuda.Event() for _ in range(m)]
         ev_out = [torch.cuda.Event() for _ in range(m)]
+        ev_back = [torch.cuda.Event() for _ in range(m)]
+        h2d.wait_stream(torch.cuda.current_stream(dev))      # the buffers above are initialised
+        d2h.wait_stream(torch.cuda.current_stream(dev))
 
         def step():
             main = torch.cuda.current_stream(dev)
-            h2d.wait_stream(main)
-            d2h.wait_stream(main)
             for i in range(nb):
                 with torch.cuda.stream(h2d):
+                    h2d.wait_event(ev_out[i])               # the product that read these buffers
                     da[i].copy_(ha[i], non_blocking=True)
                     db[i].copy_(hb[i], non_blocking=True)
                     dc[i].copy_(hc[i], non_blocking=True)
                     ev_in[i].record(h2d)
                 main.wait_event(ev_in[i])
+                main.wait_event(ev_back[i])                 # dy[i] of the step before is on the host
                 ops.gemm(ctx, da[i], db[i], dc[i], dy[i], mode=mode)
                 ev_out[i].record(main)
                 with torch.cuda.stream(d2h):
                     d2h.wait_event(ev_out[i])
                     hy[i].copy_(dy[i], non_blocking=True)
-            main.wait_stream(d2h)
+                    ev_back[i].record(d2h)
+            main.wait_stream(d2h)                           # the step ends when its results are back
 
         ms, _ = timed(step, steps, 1)
         per_batch = n * n * 4
