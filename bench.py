@@ -244,8 +244,8 @@ def _case_dense(mode, ta=False, tb=False, n=2048, batch=4, k=0):
 
 def _case_dense_small_batch(K=1536):
     """A wide Linear layer's forward pass at batch 64, y = relu(bias + x.W): few
-    tiles and a long inner dimension, the cluster split-k kernel (the operands are
-    small: this case is latency-bound, not a DRAM measurement)."""
+    tiles and a long inner dimension, the k-slices kernel (the operands are small: this
+    case is latency-bound, not a DRAM measurement)."""
     import torch
     from sapphire_b200 import ops
     dev = torch.device("cuda:0")
@@ -345,7 +345,7 @@ PROFILE_CASES = {
     "dense_tn": lambda: _case_dense(0, ta=True),
     "dense_nt": lambda: _case_dense(0, tb=True),
     "dense_epilogue": lambda: _case_dense(0, n=8192, batch=1, k=32),
-    "dense_small_batch": _case_dense_small_batch,               # 64 x 512 x 1536, bias + ReLU: cluster split-k
+    "dense_small_batch": _case_dense_small_batch,               # 64 x 512 x 1536, bias + ReLU: k-slices kernel
     "dense_single_4096": lambda: _case_dense(0, n=4096, batch=1),   # what one GPU of eight runs
     "spgemm": lambda: _case_spgemm("poisson"),                  # 32768 rows of the 65536^2 case
     "spgemm_zipf": lambda: _case_spgemm("zipf"),

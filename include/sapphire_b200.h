@@ -108,15 +108,11 @@ int64_t sb200_ctx_counter(const sb200_ctx* ctx, int which);
  *       the launch with SB200_ERR_DEVICE_TIMEOUT from sb200_check_device_status --
  *       the counterpart of the reference's CHECK_CUBLAS
  *       (Includes/Sapphire/compute/cudaUtil/CudaParams.cuh:51-58).
- *   SB200_OPT_CLUSTER_SPLIT_K  1, the default: a TF32 product with few 128 x 64
- *       output tiles and an inner dimension of 1024 or more (a wide Linear layer at
- *       a small batch) runs with a cluster of 2 or 4 CTAs per tile, each multiplying
- *       a slice of k; the partial tiles are summed in the cluster leader in fixed
- *       order (bit-reproducible) before the ordinary epilogue; 0: one CTA per tile.
- *   SB200_OPT_SPLIT_A_TMEM  (TF32X3 mode) 1, the default: when A is stored
- *       [M, K] the high and low parts of its tiles are written to tensor memory
- *       and the tensor core reads them from there; 0: both low parts go to
- *       shared memory, as they always do for a transposed A.  Same results.
+ *   SB200_OPT_K_SLICES  1, the default: a TF32 product with few 128 x 64 output
+ *       tiles and at least 22 k-blocks of 32 runs as S CTAs per tile, each a slice of
+ *       k; the CTA of a tile that finishes last adds the partial tiles in slice
+ *       order (bit-reproducible) and runs the epilogue.  0: one CTA per tile.
+ *       2 .. 16: that many slices whenever the request is eligible (tests, tuning).
  *   SB200_OPT_SPGEMM_FAST_MID  1, the default: sparse products with at most 65536
  *       columns run their mid-sized rows (33 .. 16383 scalar products) on the kernels
  *       specialised for that width; 0: on the general row kernel (any width).
@@ -126,7 +122,7 @@ int64_t sb200_ctx_counter(const sb200_ctx* ctx, int which);
 enum { SB200_OPT_SPLIT_EXPLICIT_HI = 1, SB200_OPT_MERGE_MN_BOXES = 2, SB200_OPT_CTA_PAIRS = 3,
        SB200_OPT_SPLIT_TAIL_WAVE = 4, SB200_OPT_WAIT_LIMIT_US = 5,
        SB200_OPT_TEST_STALL_KBLOCKS = 6, SB200_OPT_SPGEMM_FAST_MID = 7,
-       SB200_OPT_CLUSTER_SPLIT_K = 8, SB200_OPT_SPLIT_A_TMEM = 9 };
+       SB200_OPT_K_SLICES = 8, SB200_OPT_SPLIT_A_TMEM = 9 };
 int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value);
 
 /* Reads (and clears) the device status word after synchronising the stream.

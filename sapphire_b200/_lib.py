@@ -22,7 +22,7 @@ OPT_SPLIT_TAIL_WAVE = 4
 OPT_WAIT_LIMIT_US = 5
 OPT_TEST_STALL_KBLOCKS = 6
 OPT_SPGEMM_FAST_MID = 7
-OPT_CLUSTER_SPLIT_K = 8
+OPT_K_SLICES = 8
 OPT_SPLIT_A_TMEM = 9
 COUNTER_LAUNCHES, COUNTER_TENSOR_MAP_HITS, COUNTER_TENSOR_MAP_MISSES = 0, 1, 2
 

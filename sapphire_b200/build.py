@@ -17,7 +17,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libsapphire_b200.so")
-SOURCES = ["abi.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu", "gemm_tcgen05_splitk.cu", "gemm_simt.cu", "spgemm.cu", "csr_convert.cu", "elementwise.cu", "colsum_noalloc.cu", "im2col.cu", "dp_exchange.cu", "compat_c.cu"]
+SOURCES = ["abi.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu", "gemm_tcgen05_slices.cu", "gemm_simt.cu", "spgemm.cu", "csr_convert.cu", "elementwise.cu", "colsum_noalloc.cu", "im2col.cu", "dp_exchange.cu", "compat_c.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--use_fast_math=false"]
 

@@ -59,7 +59,7 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->merge_mn_boxes = 1;
     ctx->use_cta_pairs = 1;
     ctx->split_tail_wave = 0;
-    ctx->cluster_split_k = 1;
+    ctx->k_slices = 1;
     ctx->encode_tiled = nullptr;
     ctx->tmaps = nullptr;
     ctx->tmap_clock = 0;
@@ -73,8 +73,8 @@ extern "C" int sb200_ctx_create(int device, sb200_ctx** out)
     ctx->sp_work_valid = 0;
     ctx->sp_fast_mid = 1;
     ctx->d_status = nullptr;
-    if (cudaMalloc(&ctx->d_status, sizeof(unsigned)) != cudaSuccess ||
-        cudaMemset(ctx->d_status, 0, sizeof(unsigned)) != cudaSuccess) {
+    if (cudaMalloc(&ctx->d_status, sb200::STATUS_WORDS * sizeof(unsigned)) != cudaSuccess ||
+        cudaMemset(ctx->d_status, 0, sb200::STATUS_WORDS * sizeof(unsigned)) != cudaSuccess) {
         delete ctx;
         return SB200_ERR_ALLOC;
     }
@@ -157,8 +157,10 @@ extern "C" int sb200_ctx_set_option(sb200_ctx* ctx, int option, int value)
         case SB200_OPT_SPLIT_TAIL_WAVE:
             ctx->split_tail_wave = value != 0;
             return SB200_OK;
-        case SB200_OPT_CLUSTER_SPLIT_K:
-            ctx->cluster_split_k = value != 0;
+        case SB200_OPT_K_SLICES:
+            if (value < 0 || value > 16)
+                return SB200_ERR_INVALID_ARG;
+            ctx->k_slices = value;
             return SB200_OK;
         case SB200_OPT_SPLIT_A_TMEM:
             ctx->split_a_tmem = value != 0;

@@ -75,6 +75,11 @@ struct alignas(64) TensorMapSlot {
     uint64_t stamp;        // last use; 0 = empty
 };
 constexpr int TENSOR_MAP_SLOTS = 64;
+// The status allocation: word 0 is the device status word; from SLICE_TICKET_OFFSET on,
+// one ticket counter per output tile of a k-sliced GEMM (zero between launches).
+constexpr int SLICE_TICKET_OFFSET = 16;
+constexpr int SLICE_TICKETS = 240;
+constexpr int STATUS_WORDS = SLICE_TICKET_OFFSET + SLICE_TICKETS;
 }  // namespace sb200
 
 struct sb200_ctx {
@@ -90,7 +95,7 @@ struct sb200_ctx {
     int merge_mn_boxes;        // fetch an MN-major tile with one 4-D TMA box when possible
     int use_cta_pairs;         // large TF32 problems run on the two-CTA (cta_group::2) kernel
     int split_tail_wave;       // a mostly empty last wave of pair tiles goes to the one-CTA kernel
-    int cluster_split_k;       // small problems with a long inner dimension: a cluster of CTAs per tile
+    int k_slices;              // small problems: slices of k on separate SMs, summed by the last to finish
     void* encode_tiled;        // cuTensorMapEncodeTiled, resolved at context creation
     sb200::TensorMapSlot* tmaps;   // [TENSOR_MAP_SLOTS] encoded descriptors, least recently used replaced
     uint64_t tmap_clock;
@@ -113,9 +118,9 @@ int launch_gemm_tcgen05(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream);
 // gemm_tcgen05_2cta.cu
 bool pair_kernel_preferred(const sb200_ctx* ctx, const GemmArgs& g);
 int launch_gemm_tcgen05_pair(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream);
-// gemm_tcgen05_splitk.cu
-int cluster_split_k(const sb200_ctx* ctx, const GemmArgs& g);
-int launch_gemm_tcgen05_splitk(sb200_ctx* ctx, const GemmArgs& g, int split, cudaStream_t stream);
+// gemm_tcgen05_slices.cu
+int k_slices(const sb200_ctx* ctx, const GemmArgs& g);
+int launch_gemm_tcgen05_slices(sb200_ctx* ctx, const GemmArgs& g, int split, cudaStream_t stream);
 // gemm_simt.cu
 int launch_gemm_simt(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream);
 int launch_colsum(sb200_ctx* ctx, const float* B, int transB, int64_t K, int64_t N, int64_t ldb,

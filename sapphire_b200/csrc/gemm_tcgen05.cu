@@ -728,9 +728,9 @@ int launch_one_cta(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
         bn = 128;
     if (bn == 64) {
         // few tiles and a long inner dimension: a cluster of CTAs per tile, each a slice of k
-        const int split = cluster_split_k(ctx, g);
-        if (split > 1)
-            return launch_gemm_tcgen05_splitk(ctx, g, split, stream);
+        const int slices = k_slices(ctx, g);
+        if (slices > 1)
+            return launch_gemm_tcgen05_slices(ctx, g, slices, stream);
     }
     if (g.colsum_out) {
         if (bn == 256) return launch_layout<256, 4, false, true>(ctx, g, stream);

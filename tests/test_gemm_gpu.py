@@ -341,20 +341,10 @@ def test_single_product_tail_wave_split(ctx, oracle, n):
     assert rel_fro(yt.cpu().numpy(), y1.cpu().numpy()) <= 1e-5
 
 
-@pytest.mark.parametrize("M,N,K,batch,ta,tb", [
-    (64, 512, 1536, 1, 0, 0),       # a wide Linear layer's forward pass at batch 64: 8 tiles x 4 CTAs
-    (64, 784, 1024, 1, 0, 1),       # a dx GEMM (W stored [in, out], read transposed)
-    (256, 256, 1024, 4, 0, 0),      # 32 tiles x 4 CTAs
-    (256, 256, 1024, 6, 0, 0),      # 48 tiles: 2 CTAs per tile
-    (100, 132, 1100, 2, 1, 0),      # ragged everything, K not a multiple of 32, A stored [K, M]
-    (128, 64, 1024, 3, 1, 1),       # both operands in the transposed orientation
-])
-def test_cluster_split_k(ctx, oracle, M, N, K, batch, ta, tb):
-    """Few output tiles and a long inner dimension: a cluster of 2 or 4 CTAs shares a
-    tile, each multiplying a slice of k; the leader sums the partial tiles in fixed
-    order and runs the ordinary epilogue.  Checked against the CPU loop with every
-    epilogue (in-place C, bias + ReLU, ReLU gate), against the one-CTA-per-tile
-    launch, and for run-to-run bit-reproducibility."""
+def _split_k_case(ctx, oracle, M, N, K, batch, ta, tb, on, off):
+    """`on()` selects the kernel under test, `off()` one CTA per tile.  Checked against the
+    CPU loop with every epilogue (in-place C, bias + ReLU, ReLU gate), against the
+    one-CTA-per-tile launch, and for run-to-run bit-reproducibility."""
     rng = np.random.default_rng(M + N + K)
     a = rng.standard_normal((batch, K, M) if ta else (batch, M, K)).astype(np.float32)
     b = rng.standard_normal((batch, N, K) if tb else (batch, K, N)).astype(np.float32)
@@ -364,6 +354,7 @@ def test_cluster_split_k(ctx, oracle, M, N, K, batch, ta, tb):
     ta_, tb_, tg = dev(a), dev(b), dev(gate)
     want = np.stack([oracle.gemm_ex(ta, tb, M, N, K, a[i], a.shape[2], 0, b[i], b.shape[2], 0, c[i], N, 0,
                                     N, 0, None, 1, M * N).reshape(M, N) for i in range(batch)])
+    on()
     launches = ctx.launch_count()
     y = dev(c)
     ops.gemm(ctx, ta_, tb_, y, y, trans_a=bool(ta), trans_b=bool(tb))                 # y <- y + a.b
@@ -371,10 +362,10 @@ def test_cluster_split_k(ctx, oracle, M, N, K, batch, ta, tb):
     ctx.check_device_status()
     assert rel_fro(y.cpu().numpy(), want) <= 2e-3
     # the same request with one CTA per tile
-    ctx.set_option(L.OPT_CLUSTER_SPLIT_K, 0)
+    off()
     y1 = dev(c)
     ops.gemm(ctx, ta_, tb_, y1, y1, trans_a=bool(ta), trans_b=bool(tb))
-    ctx.set_option(L.OPT_CLUSTER_SPLIT_K, 1)
+    on()
     assert rel_fro(y.cpu().numpy(), y1.cpu().numpy()) <= 1e-5
     assert not torch.equal(y, y1) or K <= 32          # other summation order: it did run the other kernel
     # bias + ReLU, then the ReLU gate; reproducible bit for bit
@@ -386,6 +377,37 @@ def test_cluster_split_k(ctx, oracle, M, N, K, batch, ta, tb):
     g1 = ops.gemm(ctx, ta_, tb_, trans_a=bool(ta), trans_b=bool(tb), relu_gate=tg)
     assert rel_fro(g1.cpu().numpy(), np.where(gate > 0, want - c, 0)) <= 2e-3
     ctx.check_device_status()
+
+
+def _options(ctx, slices):
+    def f():
+        ctx.set_option(L.OPT_K_SLICES, slices)
+    return f
+
+
+@pytest.mark.parametrize("M,N,K,batch,ta,tb,slices", [
+    (64, 512, 784, 1, 0, 0, 1),       # the MLP's first layer at batch 64 (the policy's own choice)
+    (64, 256, 512, 1, 0, 0, 2),       # its second layer (the policy leaves K = 512 whole: forced)
+    (64, 784, 512, 1, 0, 1, 4),       # the dx GEMM of the first layer (W read transposed)
+    (64, 512, 1536, 1, 0, 0, 1),      # a wider layer
+    (256, 256, 1024, 4, 0, 0, 1),     # 32 tiles
+    (64, 512, 784, 1, 0, 0, 2),
+    (64, 512, 784, 1, 0, 0, 5),       # 25 k-blocks in 5 slices of 5
+    (64, 512, 784, 1, 0, 0, 7),       # ... in slices of 4, 4, 4, 4, 4, 4, 1
+    (64, 512, 784, 1, 0, 0, 16),      # more slices asked for than k-blocks allow: 13 of 2, 2, ..., 1
+    (100, 132, 1100, 2, 1, 0, 3),     # ragged everything, K not a multiple of 32, A stored [K, M]
+    (128, 64, 1024, 3, 1, 1, 8),      # both operands in the transposed orientation
+    (300, 200, 96, 1, 0, 0, 3),       # one k-block per slice
+])
+def test_k_slices(ctx, oracle, M, N, K, batch, ta, tb, slices):
+    """Few output tiles: S CTAs per tile on separate SMs, each a slice of k; the CTA
+    that finishes last adds the partial tiles in slice order and runs the ordinary
+    epilogue.  The ticket counters return to zero by themselves: the calls of this
+    test (and of every later one) follow each other on one context."""
+    try:
+        _split_k_case(ctx, oracle, M, N, K, batch, ta, tb, _options(ctx, slices), _options(ctx, 0))
+    finally:
+        _options(ctx, 1)()
 
 
 @pytest.mark.parametrize("M,N,K,batch,tb", [(256, 256, 256, 4, 0), (200, 136, 100, 3, 0),
@@ -441,7 +463,7 @@ def test_tensor_map_cache(ctx):
 
 
 @pytest.mark.parametrize("shape", ["one_cta", "pair", "split_mode", "split_mode_transposed_a",
-                                   "cluster_split_k"])
+                                   "k_slices"])
 def test_bounded_wait_runs_out_and_context_survives(ctx, shape):
     """The TMA producers stop after 3 k-blocks (test hook) with the wait limit at
     2 ms: the MMA issuer's and the epilogue's waits run out, every role leaves
@@ -450,7 +472,7 @@ def test_bounded_wait_runs_out_and_context_survives(ctx, shape):
     CHECK_CUBLAS.  The same context then runs a normal GEMM."""
     if shape == "pair":
         M, N, K, batch, mode = 1024, 512, 256, 40, L.MODE_TF32
-    elif shape == "cluster_split_k":
+    elif shape == "k_slices":
         M, N, K, batch, mode = 64, 512, 1536, 1, L.MODE_TF32      # (from K = 2048 on, slices of k run as batches)
     elif shape == "one_cta":
         M, N, K, batch, mode = 256, 256, 256, 4, L.MODE_TF32
@@ -472,6 +494,8 @@ def test_bounded_wait_runs_out_and_context_survives(ctx, shape):
         ctx.set_option(L.OPT_TEST_STALL_KBLOCKS, -1)
         ctx.set_option(L.OPT_WAIT_LIMIT_US, 2000000)
     ctx.check_device_status()                            # the word was cleared
+    # (k-slices: every CTA drew its ticket although its waits ran out, so the counters are
+    # back at zero and the next product is complete)
     again = ops.gemm(ctx, a, b, mode=mode, trans_a=ta)
     ctx.check_device_status()
     assert torch.equal(again, good)
