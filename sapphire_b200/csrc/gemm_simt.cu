@@ -17,8 +17,14 @@
 namespace sb200 {
 namespace {
 
-constexpr int TS = 64;   // output tile edge
-constexpr int TK = 16;   // k per shared-memory step
+constexpr int TS = 64;   // edge of the standard output tile
+// Rows and columns of an output tile (TM, TN: 64, or 16 -- columns for narrow outputs
+// such as a 10-class layer, where a 64-wide tile would spend 5/6 of its arithmetic on
+// masked columns; rows and columns when the launch would otherwise be a few CTAs: the
+// ascending-k order forbids splitting k, so more and smaller tiles are the only way to
+// put more SMs on a small product) and k per shared-memory step (TK: 16, or 64 when the launch is a handful of CTAs
+// walking K, so that four times as many loads are in flight per step) are template
+// parameters.  Neither changes the order of the additions.
 
 struct SimtParams {
     int transA, transB;
@@ -32,45 +38,53 @@ struct SimtParams {
     const float* mask; long long ldm, strideM;   // gate matrix or null: D = mask > 0 ? D : 0
 };
 
+template <int TM, int TN, int TK>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const SimtParams p)
 {
-    __shared__ float As[TK][TS + 1];
-    __shared__ float Bs[TK][TS + 1];
+    constexpr int NI = TM / 16;                  // rows per thread
+    constexpr int NJ = TN / 16;                  // columns per thread
+    __shared__ float As[TK][TM + 1];
+    __shared__ float Bs[TK][TN + 1];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-    const long long m0 = static_cast<long long>(blockIdx.y) * TS;
-    const long long n0 = static_cast<long long>(blockIdx.x) * TS;
+    const long long m0 = static_cast<long long>(blockIdx.y) * TM;
+    const long long n0 = static_cast<long long>(blockIdx.x) * TN;
     const long long b = blockIdx.z;
     const float* A = p.A + b * p.strideA;
     const float* B = p.B + b * p.strideB;
 
-    float acc[4][4];
+    float acc[NI][NJ];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < NI; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < NJ; ++j)
             acc[i][j] = 0.0f;
 
     // Tiles go global -> registers -> shared memory; the loads of the next k-step
     // are issued before the current one is multiplied, so their latency hides
     // behind the arithmetic (small problems are a handful of CTAs walking K one
     // step at a time: latency is all there is).
-    constexpr int PER = TK * TS / 256;
-    float ra[PER], rb[PER];
+    constexpr int PER_A = TK * TM / 256, PER_B = TK * TN / 256;
+    static_assert(PER_A >= 1 && PER_B >= 1, "a tile step is at least one element per thread");
+    float ra[PER_A], rb[PER_B];
     auto fetch = [&](long long k0) {
 #pragma unroll
-        for (int e = 0; e < PER; ++e) {
+        for (int e = 0; e < PER_A; ++e) {
             const int i = threadIdx.x + e * 256;
             int kk, mm;
-            if (p.transA) { mm = i % TS; kk = i / TS; }     // stored [K, M]: m contiguous
+            if (p.transA) { mm = i % TM; kk = i / TM; }     // stored [K, M]: m contiguous
             else          { kk = i % TK; mm = i / TK; }     // stored [M, K]: k contiguous
             const long long m = m0 + mm, k = k0 + kk;
             ra[e] = 0.0f;
             if (m < p.M && k < p.K)
                 ra[e] = p.transA ? A[k * p.lda + m] : A[m * p.lda + k];
+        }
+#pragma unroll
+        for (int e = 0; e < PER_B; ++e) {
+            const int i = threadIdx.x + e * 256;
             int kb, nn;
             if (p.transB) { kb = i % TK; nn = i / TK; }     // stored [N, K]: k contiguous
-            else          { nn = i % TS; kb = i / TS; }     // stored [K, N]: n contiguous
+            else          { nn = i % TN; kb = i / TN; }     // stored [K, N]: n contiguous
             const long long n = n0 + nn, k2 = k0 + kb;
             rb[e] = 0.0f;
             if (n < p.N && k2 < p.K)
@@ -79,10 +93,14 @@ gemm_simt_kernel(const SimtParams p)
     };
     auto stash = [&]() {
 #pragma unroll
-        for (int e = 0; e < PER; ++e) {
+        for (int e = 0; e < PER_A; ++e) {
             const int i = threadIdx.x + e * 256;
-            if (p.transA) As[i / TS][i % TS] = ra[e]; else As[i % TK][i / TK] = ra[e];
-            if (p.transB) Bs[i % TK][i / TK] = rb[e]; else Bs[i / TS][i % TS] = rb[e];
+            if (p.transA) As[i / TM][i % TM] = ra[e]; else As[i % TK][i / TK] = ra[e];
+        }
+#pragma unroll
+        for (int e = 0; e < PER_B; ++e) {
+            const int i = threadIdx.x + e * 256;
+            if (p.transB) Bs[i % TK][i / TK] = rb[e]; else Bs[i / TN][i % TN] = rb[e];
         }
     };
     if (p.K > 0) fetch(0);
@@ -91,17 +109,28 @@ gemm_simt_kernel(const SimtParams p)
         __syncthreads();
         if (k0 + TK < p.K) fetch(k0 + TK);
         const int klim = (p.K - k0) < TK ? static_cast<int>(p.K - k0) : TK;
-        for (int kk = 0; kk < klim; ++kk) {
-            float a[4], bv[4];
+        auto k_step = [&](int kk) {
+            float a[NI], bv[NJ];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty + 16 * i];
+            for (int i = 0; i < NI; ++i) a[i] = As[kk][ty + 16 * i];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx + 16 * j];
+            for (int j = 0; j < NJ; ++j) bv[j] = Bs[kk][tx + 16 * j];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < NI; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < NJ; ++j)
                     acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(a[i], bv[j]));
+        };
+        if (NJ == 1 && klim == TK) {
+            // narrow tiles, a whole step: unrolled, so that the shared-memory loads of
+            // several k run ahead of the (strictly ordered) additions; a thread of a
+            // 64-column tile has 16 independent sums to interleave and gains nothing
+#pragma unroll 16
+            for (int kk = 0; kk < TK; ++kk)
+                k_step(kk);
+        } else {
+            for (int kk = 0; kk < klim; ++kk)
+                k_step(kk);
         }
         __syncthreads();
     }
@@ -110,11 +139,11 @@ gemm_simt_kernel(const SimtParams p)
     float* D = p.D + b * p.strideD;
     const float* G = p.mask ? p.mask + b * p.strideM : nullptr;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < NI; ++i) {
         const long long m = m0 + ty + 16 * i;
         if (m >= p.M) continue;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             const long long n = n0 + tx + 16 * j;
             if (n >= p.N) continue;
             float base = C ? C[m * p.ldc + n] : 0.0f;
@@ -163,9 +192,20 @@ int launch_gemm_simt(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
 {
     if (g.M <= 0 || g.N <= 0 || g.batch <= 0)
         return SB200_OK;
-    const long long gx = (g.N + TS - 1) / TS, gy = (g.M + TS - 1) / TS;
+    // 16-column tiles for narrow outputs, and whenever 64-column tiles would leave
+    // three quarters of the SMs without a CTA (four times as many CTAs share the walk);
+    // 16-row tiles too when that still leaves three quarters idle
+    const long long gy64 = (g.M + TS - 1) / TS;
+    const bool narrow = g.N <= 32 || ((g.N + TS - 1) / TS) * gy64 * g.batch * 4 <= ctx->sm_count;
+    const int tn = narrow ? 16 : TS;
+    const long long gx = (g.N + tn - 1) / tn;
+    const bool small = narrow && gx * gy64 * g.batch * 4 <= ctx->sm_count;
+    const int tm = small ? 16 : TS;
+    const long long gy = (g.M + tm - 1) / tm;
     if (gy > 65535 || g.batch > 65535)
         return SB200_ERR_TOO_LARGE;
+    // a handful of CTAs walking K: longer steps, more loads in flight
+    const bool few = gx * gy * g.batch <= 2ll * ctx->sm_count;
     SimtParams p;
     p.transA = g.transA; p.transB = g.transB;
     p.M = g.M; p.N = g.N; p.K = g.K;
@@ -177,7 +217,14 @@ int launch_gemm_simt(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.relu = g.relu;
     p.mask = g.mask; p.ldm = g.ldmask; p.strideM = g.strideMask;
     dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy), static_cast<unsigned>(g.batch));
-    gemm_simt_kernel<<<grid, 256, 0, stream>>>(p);
+    if (small)
+        gemm_simt_kernel<16, 16, 64><<<grid, 256, 0, stream>>>(p);      // always a few CTAs
+    else if (narrow)
+        few ? gemm_simt_kernel<TS, 16, 64><<<grid, 256, 0, stream>>>(p)
+            : gemm_simt_kernel<TS, 16, 16><<<grid, 256, 0, stream>>>(p);
+    else
+        few ? gemm_simt_kernel<TS, TS, 64><<<grid, 256, 0, stream>>>(p)
+            : gemm_simt_kernel<TS, TS, 16><<<grid, 256, 0, stream>>>(p);
     ctx->launches += 1;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }

@@ -97,6 +97,31 @@ def test_auto_path_falls_to_simt_for_tma_hostile_rows(ctx, oracle):
     assert e.value.status == L.ERR_UNSUPPORTED
 
 
+@pytest.mark.parametrize("M,N,K,batch,ta,tb", [
+    (64, 10, 256, 1, 0, 0),        # 16 x 16 tiles (few CTAs even with 16-column tiles), k steps of 64
+    (3200, 10, 100, 1, 0, 0),      # 64 x 16 tiles, 50 CTAs: k steps of 64
+    (64, 256, 10, 1, 0, 1),        # the dx GEMM of the 10-class layer (B read transposed)
+    (256, 10, 64, 1, 1, 0),        # its dW GEMM (A read transposed)
+    (19200, 10, 40, 1, 0, 0),      # 16-column tiles, 300 CTAs: steps of 16
+    (100, 100, 70, 3, 0, 0),       # 64-column tiles, few CTAs: steps of 64
+    (1500, 1500, 24, 1, 1, 1),     # 64-column tiles, 576 CTAs: steps of 16
+    (33, 32, 130, 2, 0, 0),        # 32 columns = two 16-column tiles
+])
+def test_simt_tile_variants_are_bit_exact(ctx, oracle, M, N, K, batch, ta, tb):
+    """The CUDA-core kernel has five instances (tiles of 64 x 64, 64 x 16 or 16 x 16, k
+    steps of 16 or 64); none changes the order of the additions, so each equals the
+    CPU loop bit for bit."""
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    a = rng.standard_normal((batch, K, M) if ta else (batch, M, K)).astype(np.float32)
+    b = rng.standard_normal((batch, N, K) if tb else (batch, K, N)).astype(np.float32)
+    c = rng.uniform(-1, 1, (batch, M, N)).astype(np.float32)
+    want = np.stack([oracle.gemm_ex(ta, tb, M, N, K, a[i], a.shape[2], 0, b[i], b.shape[2], 0, c[i], N, 0,
+                                    N, 0, None, 1, M * N).reshape(M, N) for i in range(batch)])
+    y = ops.gemm(ctx, dev(a), dev(b), dev(c), trans_a=bool(ta), trans_b=bool(tb), path=L.PATH_SIMT)
+    assert ctx.last_path() == L.PATH_SIMT
+    assert np.array_equal(bits(y.cpu().numpy()), bits(want))
+
+
 def test_k_zero_and_empty(ctx):
     c = torch.randn(2, 5, 8, device=DEV)
     a = torch.empty(2, 5, 0, device=DEV)
