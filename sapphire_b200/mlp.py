@@ -157,19 +157,25 @@ class MlpTrainer:
                               ctx.device, [prob, loss, dlogits, acts[-1]], loss)
         calls.append(ce)
         dy = dlogits
+        side = set()                                     # the weight-gradient GEMMs
         for l in reversed(range(nl)):
             dx = torch.empty(B, self.W[l].shape[0], dtype=torch.float32, device=dev)
-            calls.append(ops.prepare_gemm(ctx, dy, self.W[l], out=dx, trans_b=True, mode=mode,
-                                          relu_gate=acts[l] if l > 0 else None))
+            # dW_l needs only dy_l and the layer's input: nothing of the backward chain
+            # waits for it, so it is listed before dx_l and may run beside it
             calls.append(ops.prepare_gemm(ctx, acts[l], dy, out=self.grads.dW[l], trans_a=True, mode=mode,
                                           colsum_out=self.grads.dB[l], colsum_scale=1.0 / B))
+            side.add(len(calls) - 1)
             if l == 0:
                 patch_x.append(calls[-1])
+            calls.append(ops.prepare_gemm(ctx, dy, self.W[l], out=dx, trans_b=True, mode=mode,
+                                          relu_gate=acts[l] if l > 0 else None))
             dy = dx
         for c in calls:
             c.args = list(c.args)
-        return {"batch": B, "calls": calls, "patch_x": patch_x, "ce": ce, "loss": loss,
-                "x_shape": tuple(x.shape), "y_shape": tuple(onehot.shape)}
+        return {"batch": B, "calls": calls, "side": side, "patch_x": patch_x, "ce": ce, "loss": loss,
+                "x_shape": tuple(x.shape), "y_shape": tuple(onehot.shape),
+                "fork": [torch.cuda.Event() for _ in range(nl)], "join": torch.cuda.Event(),
+                "side_stream": torch.cuda.Stream(dev)}
 
     def _run_plan(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
         plan = self._plan
@@ -181,8 +187,28 @@ class MlpTrainer:
         for c in plan["patch_x"]:
             c.args[8] = x.data_ptr()                       # operand A of the first layer's two GEMMs
         plan["ce"].args[6] = onehot.data_ptr()
-        for c in plan["calls"]:
-            c()
+        if not torch.cuda.is_current_stream_capturing():
+            for c in plan["calls"]:
+                c()
+            return plan["loss"]
+        # Under capture the three weight-gradient GEMMs go to a second stream: the
+        # graph then has them beside the dx chain instead of inside it (8 kernels on
+        # the critical path instead of 11; the gradient of the network's input on a
+        # third stream gained nothing more).  Launched eagerly the step is bound by the
+        # host, where the event calls would cost more than the overlap gives.
+        main = torch.cuda.current_stream(x.device)
+        side, forks, k = plan["side_stream"], plan["fork"], 0
+        for i, c in enumerate(plan["calls"]):
+            if i in plan["side"]:
+                forks[k].record(main)                      # dy of this layer is complete in stream order
+                side.wait_event(forks[k])
+                k += 1
+                with torch.cuda.stream(side):
+                    c()
+            else:
+                c()
+        plan["join"].record(side)
+        main.wait_event(plan["join"])                      # gradients complete before the exchange / SGD
         return plan["loss"]
 
     def step(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
