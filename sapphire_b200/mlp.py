@@ -169,13 +169,16 @@ class MlpTrainer:
                 patch_x.append(calls[-1])
             calls.append(ops.prepare_gemm(ctx, dy, self.W[l], out=dx, trans_b=True, mode=mode,
                                           relu_gate=acts[l] if l > 0 else None))
+            if l == 0:
+                late = len(calls) - 1                    # the input's gradient: nobody reads it
             dy = dx
         for c in calls:
             c.args = list(c.args)
-        return {"batch": B, "calls": calls, "side": side, "patch_x": patch_x, "ce": ce, "loss": loss,
+        return {"batch": B, "calls": calls, "side": side, "late": late, "patch_x": patch_x, "ce": ce, "loss": loss,
                 "x_shape": tuple(x.shape), "y_shape": tuple(onehot.shape),
-                "fork": [torch.cuda.Event() for _ in range(nl)], "join": torch.cuda.Event(),
-                "side_stream": torch.cuda.Stream(dev)}
+                "fork": [torch.cuda.Event() for _ in range(nl + 1)], "join": torch.cuda.Event(),
+                "side_stream": torch.cuda.Stream(dev), "late_stream": torch.cuda.Stream(dev),
+                "late_join": torch.cuda.Event(), "late_pending": False}
 
     def _run_plan(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
         plan = self._plan
@@ -193,22 +196,27 @@ class MlpTrainer:
             return plan["loss"]
         # Under capture the three weight-gradient GEMMs go to a second stream: the
         # graph then has them beside the dx chain instead of inside it (8 kernels on
-        # the critical path instead of 11; the gradient of the network's input on a
-        # third stream gained nothing more).  Launched eagerly the step is bound by the
-        # host, where the event calls would cost more than the overlap gives.
+        # the critical path instead of 11).  The gradient of the network's input, which
+        # nobody reads, goes to a third and is joined only at the end of the step, so
+        # the gradient exchange / SGD does not wait for it.  Launched eagerly the step
+        # is bound by the host, where the event calls would cost more than the overlap
+        # gives.
         main = torch.cuda.current_stream(x.device)
-        side, forks, k = plan["side_stream"], plan["fork"], 0
+        side, late, forks, k = plan["side_stream"], plan["late_stream"], plan["fork"], 0
         for i, c in enumerate(plan["calls"]):
-            if i in plan["side"]:
-                forks[k].record(main)                      # dy of this layer is complete in stream order
-                side.wait_event(forks[k])
+            if i in plan["side"] or i == plan["late"]:
+                branch = late if i == plan["late"] else side
+                forks[k].record(main)                      # what the call reads is complete in stream order
+                branch.wait_event(forks[k])
                 k += 1
-                with torch.cuda.stream(side):
+                with torch.cuda.stream(branch):
                     c()
             else:
                 c()
         plan["join"].record(side)
         main.wait_event(plan["join"])                      # gradients complete before the exchange / SGD
+        plan["late_join"].record(late)
+        plan["late_pending"] = True                        # `step` joins it after the update
         return plan["loss"]
 
     def step(self, x: torch.Tensor, onehot: torch.Tensor) -> torch.Tensor:
@@ -217,9 +225,15 @@ class MlpTrainer:
         loss = self._run_plan(x, onehot) if self.fused else self.forward_backward(x, onehot)
         if self.exchange is not None:
             self.exchange.step(self.params.flat, self.lr)
-            return loss
-        self.grads.allreduce(self.world, lambda t, f: ops.scale(self.ctx, t, f))
-        ops.sgd_update(self.ctx, self.params.flat, self.grads.flat, self.lr)
+        else:
+            self.grads.allreduce(self.world, lambda t, f: ops.scale(self.ctx, t, f))
+            ops.sgd_update(self.ctx, self.params.flat, self.grads.flat, self.lr)
+        plan = self._plan
+        if self.fused and plan is not None and plan["late_pending"]:
+            # the branch of the input's gradient rejoins: the step (a captured graph) ends
+            # when it has, and the next step may overwrite what it read
+            torch.cuda.current_stream(x.device).wait_event(plan["late_join"])
+            plan["late_pending"] = False
         return loss
 
     def close(self) -> None:
