@@ -67,6 +67,11 @@ typedef void* sb200_stream;
  * A context is not thread-safe, and its one workspace is not ordered between
  * streams: calls that share a context must be stream-ordered with respect to
  * each other (one stream per context, or event dependencies between streams).
+ * The workspace grows on demand (cudaFree + cudaMalloc, which synchronise the
+ * device): its users are the separate column sums of the 3xTF32 and CUDA-core
+ * paths, the k-sliced small GEMMs, the sparse product and the dense -> CSR
+ * conversion.  Run each kind of call once before a stream capture begins; the
+ * same call inside the capture then allocates nothing.
  */
 int sb200_ctx_create(int device, sb200_ctx** out);
 int sb200_ctx_destroy(sb200_ctx* ctx);
