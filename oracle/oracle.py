@@ -7,13 +7,15 @@ ctypes front end of the two CPU checkers:
 * ``ref``   -- ``oracle/_ref/libsapphire_ref.so``, the reference's own CPU leaf
   files compiled by ``oracle/Makefile`` from the reference tree.  It exists
   only where that tree was present at build time (or the prebuilt ``.so`` was
-  shipped along); ``have_ref()`` says which.
+  shipped along); ``have_ref()`` says which.  ``ref_conv`` is the same for the
+  reference's host convolution (``oracle/_ref/libsapphire_ref_conv.so``).
 
 Only tests, the smoke check and the CPU-baseline legs of the benchmark import
 this module.  The product package never does.
 
 Dense parity is pinned (port == ref bit-for-bit, plus fixtures made from ref
-under ``tests/golden``).  Sparse parity is UNPINNED: the reference ships no
+under ``tests/golden``), the convolution lowering and its composition included.
+Sparse parity is UNPINNED: the reference ships no
 sparse GEMM implementation, see the header of ``sapphire_oracle.c``.
 """
 from __future__ import annotations
@@ -117,6 +119,34 @@ def ref():
     return _ref
 
 
+_REF_CONV_SO = os.path.join(os.path.dirname(_REF_SO), "libsapphire_ref_conv.so")
+_ref_conv = None
+
+
+def have_ref_conv() -> bool:
+    return os.path.exists(_REF_CONV_SO)
+
+
+def ref_conv():
+    """The reference's own host convolution (Convolution.cpp compiled unmodified against
+    stand-in TensorData / CudaDevice headers: oracle/ref_conv_shim.cpp)."""
+    global _ref_conv
+    if _ref_conv is None:
+        if not have_ref_conv():
+            raise FileNotFoundError(
+                f"{_REF_CONV_SO} is missing: run `make -C oracle` where the reference tree is mounted")
+        lib = C.CDLL(_REF_CONV_SO)
+        ints = [C.c_int] * 14
+        lib.ref_im2col.argtypes = [_f32p, _f32p] + ints + [C.c_float]
+        lib.ref_col2im.argtypes = [_f32p, _f32p] + ints
+        lib.ref_conv2d.argtypes = [_f32p] * 3 + [C.c_int] * 15
+        lib.ref_conv2d_backward.argtypes = [_f32p] * 5 + [C.c_int] * 15
+        for n in ("ref_im2col", "ref_col2im", "ref_conv2d", "ref_conv2d_backward"):
+            getattr(lib, n).restype = None
+        _ref_conv = lib
+    return _ref_conv
+
+
 # ---------------------------------------------------------------- dense helpers
 
 def _c(a):
@@ -184,44 +214,76 @@ def conv_out(size, pad, dil, k, stride):
     return (size + 2 * pad - dil * (k - 1) - 1) // stride + 1
 
 
-def im2col(x, kh, kw, stride=(1, 1), pad=(0, 0), dil=(1, 1), pad_value=0.0):
-    """x [N, C, H, W] -> cols [N, C*kh*kw, outR*outC] (taps stored in reverse)."""
+def im2col(x, kh, kw, stride=(1, 1), pad=(0, 0), dil=(1, 1), pad_value=0.0, impl: str = "port"):
+    """x [N, C, H, W] -> cols [N, C*kh*kw, outR*outC] (taps stored in reverse).
+    impl "ref" runs the reference's own Im2Col
+    (Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-115)."""
     x = _c(x)
     N, Cc, H, W = x.shape
-    P = conv_out(H, pad[0], dil[0], kh, stride[0]) * conv_out(W, pad[1], dil[1], kw, stride[1])
-    cols = np.empty((N, Cc * kh * kw, P), dtype=np.float32)
-    port().orc_im2col(cols.reshape(-1), x.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
-                      pad[0], pad[1], dil[0], dil[1], pad_value)
+    oR, oC = conv_out(H, pad[0], dil[0], kh, stride[0]), conv_out(W, pad[1], dil[1], kw, stride[1])
+    cols = np.empty((N, Cc * kh * kw, oR * oC), dtype=np.float32)
+    if impl == "ref":
+        ref_conv().ref_im2col(cols.reshape(-1), x.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
+                              pad[0], pad[1], dil[0], dil[1], oR, oC, pad_value)
+    else:
+        port().orc_im2col(cols.reshape(-1), x.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
+                          pad[0], pad[1], dil[0], dil[1], pad_value)
     return cols
 
 
-def col2im(dx, cols, kh, kw, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
-    """dx [N, C, H, W] += adjoint of im2col applied to cols; returns dx."""
+def col2im(dx, cols, kh, kw, stride=(1, 1), pad=(0, 0), dil=(1, 1), impl: str = "port"):
+    """dx [N, C, H, W] += adjoint of im2col applied to cols; returns dx.
+    impl "ref": the reference's own Col2Im (Convolution.cpp:117-211)."""
     assert dx.dtype == np.float32 and dx.flags.c_contiguous
     cols = _c(cols)
     N, Cc, H, W = dx.shape
-    port().orc_col2im(dx.reshape(-1), cols.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
-                      pad[0], pad[1], dil[0], dil[1])
+    if impl == "ref":
+        oR, oC = conv_out(H, pad[0], dil[0], kh, stride[0]), conv_out(W, pad[1], dil[1], kw, stride[1])
+        ref_conv().ref_col2im(dx.reshape(-1), cols.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
+                              pad[0], pad[1], dil[0], dil[1], oR, oC)
+    else:
+        port().orc_col2im(dx.reshape(-1), cols.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
+                          pad[0], pad[1], dil[0], dil[1])
     return dx
 
 
-def conv2d(y, x, filt, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
+def _conv_geometry(x, filt, stride, pad, dil):
+    N, Cc, H, W = x.shape
+    Cout, _, kh, kw = filt.shape
+    oR, oC = conv_out(H, pad[0], dil[0], kh, stride[0]), conv_out(W, pad[1], dil[1], kw, stride[1])
+    return (N, Cc, H, W, Cout, kh, kw, stride[0], stride[1], pad[0], pad[1], dil[0], dil[1], oR, oC)
+
+
+def conv2d(y, x, filt, stride=(1, 1), pad=(0, 0), dil=(1, 1), impl: str = "port"):
     """y [N, Cout, outR, outC] += conv(x, filt) the way the reference's host path
     composes it: Im2Col, then Gemm(rY[N,Cout,P], rFilter[1,Cout,C*kh*kw], rX)
-    (Sources/Sapphire/compute/dense/naive/Convolution.cpp:217-253)."""
+    (Sources/Sapphire/compute/dense/naive/Convolution.cpp:217-253).  impl "ref" runs
+    that function itself."""
     N, Cout = y.shape[:2]
     kh, kw = filt.shape[-2:]
+    if impl == "ref":
+        out = np.ascontiguousarray(y, dtype=np.float32).copy()
+        ref_conv().ref_conv2d(out.reshape(-1), _c(x).reshape(-1), _c(filt).reshape(-1),
+                              *_conv_geometry(x, filt, stride, pad, dil))
+        return out
     cols = im2col(x, kh, kw, stride, pad, dil)
     f2 = np.repeat(_c(filt).reshape(1, Cout, -1), N, 0)
     return gemm(_c(y).reshape(N, Cout, -1), f2, cols).reshape(y.shape)
 
 
-def conv2d_backward(dx, dfilt, dy, x, filt, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
+def conv2d_backward(dx, dfilt, dy, x, filt, stride=(1, 1), pad=(0, 0), dil=(1, 1), impl: str = "port"):
     """dx += ..., dfilt += ... as Conv2DBackward composes them
     (Convolution.cpp:255-316): drX = filter^T . dY per batch, dFilter += dY_n . rX_n^T
-    over the batches in ascending order, Col2Im(dx, drX).  Returns (dx, dfilt)."""
+    over the batches in ascending order, Col2Im(dx, drX).  Returns (dx, dfilt).
+    impl "ref" runs that function itself."""
     N, Cout = dy.shape[:2]
     kh, kw = filt.shape[-2:]
+    if impl == "ref":
+        dxo = np.ascontiguousarray(dx, dtype=np.float32).copy()
+        dfo = np.ascontiguousarray(dfilt, dtype=np.float32).copy()
+        ref_conv().ref_conv2d_backward(dxo.reshape(-1), dfo.reshape(-1), _c(dy).reshape(-1), _c(x).reshape(-1),
+                                       _c(filt).reshape(-1), *_conv_geometry(x, filt, stride, pad, dil))
+        return dxo, dfo
     cols = im2col(x, kh, kw, stride, pad, dil)
     f2 = _c(filt).reshape(1, Cout, -1)
     dy3 = _c(dy).reshape(N, Cout, -1)

@@ -1,0 +1,117 @@
+// TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+//
+// C entry points around the reference's own host convolution, so that the parity
+// tests can pin the restated lowering (orc_im2col / orc_col2im and the conv
+// composition in oracle.py) against it.  Compiled from the reference's files where
+// they lie, unmodified (oracle/Makefile, target ref_conv):
+//   Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-316  Im2Col, Col2Im, Conv2D, Conv2DBackward
+//   Sources/Sapphire/compute/dense/naive/NaiveGemm.cpp:12-38     Dense::Naive::Gemm
+//   Sources/Sapphire/compute/dense/naive/NaiveBasic.cpp:63-84    Dense::Naive::Transpose
+//   Sources/Sapphire/util/shape.cpp                              Shape
+//   Includes/Sapphire/compute/Broadcast.hpp:82-133               BroadcastWith2Inputs
+// The reference's TensorData and CudaDevice headers pull in the CUDA runtime, cuDNN and
+// the memory pools; oracle/ref_standins/ holds stand-ins with the members the host
+// convolution uses (found first on the include path).  Compute::Gemm and
+// Compute::Transpose, which Conv2D / Conv2DBackward call, are defined below as the
+// host branches of Sources/Sapphire/compute/BasicOps.cpp:183-248 and :269-290 (that file
+// includes the CUDA kernels' headers and cannot be compiled here): the same shape
+// expansion, the reference's own BroadcastWith2Inputs, the reference's own leaf calls.
+#include <Sapphire/compute/BasicOps.hpp>
+#include <Sapphire/compute/Broadcast.hpp>
+#include <Sapphire/compute/dense/naive/Convolution.hpp>
+#include <Sapphire/compute/dense/naive/NaiveBasic.hpp>
+#include <Sapphire/compute/dense/naive/NaiveGemm.hpp>
+#include <algorithm>
+
+namespace Sapphire::Compute
+{
+void Gemm(TensorData& y, const TensorData& a, const TensorData& b)
+{
+    auto shapeOut = y.GetShape();
+    auto shapeA = a.GetShape();
+    auto shapeB = b.GetShape();
+    shapeOut.Expand(2);
+    shapeA.Expand(2);
+    shapeB.Expand(2);
+    const auto M = shapeOut.Rows();
+    const auto N = shapeOut.Cols();
+    const auto K = shapeA.Cols();
+    const auto maxDim = std::max({ y.GetShape().Dim(), a.GetShape().Dim(), b.GetShape().Dim() });
+    shapeOut.Expand(maxDim);
+    shapeA.Expand(maxDim);
+    shapeB.Expand(maxDim);
+    BroadcastWith2Inputs(shapeOut, shapeA, shapeB, shapeOut.Size(), shapeA.Size(), shapeB.Size(),
+                         y.HostMutableRawPtr(), a.HostRawPtr(), b.HostRawPtr(), 0, 2,
+                         Dense::Naive::Gemm, M, N, K);
+}
+
+void Transpose(TensorData& y, const TensorData& x)
+{
+    const auto inputM = x.Rows();
+    const auto inputN = x.Cols();
+    const auto broadcast = x.GetNumUnits(2) == 1;
+    const auto chunkSize = y.GetShape().Size() / (inputM * inputN);
+    Dense::Naive::Transpose(y.HostMutableRawPtr(), x.HostRawPtr(), inputM, inputN, chunkSize, broadcast);
+}
+}  // namespace Sapphire::Compute
+
+using Sapphire::Shape;
+using Sapphire::TensorUtil::TensorData;
+namespace CN = Sapphire::Compute::Dense::Naive;
+
+namespace
+{
+TensorData wrap(std::initializer_list<int> dims, const float* data)
+{
+    return TensorData(Shape(std::vector<int>(dims)), const_cast<float*>(data));
+}
+}  // namespace
+
+extern "C" {
+
+// cols [N, C*kh*kw, P] <- x [N, C, H, W]
+void ref_im2col(float* cols, const float* x, int N, int C, int H, int W, int kh, int kw, int strideRow,
+                int strideCol, int padRow, int padCol, int dilRow, int dilCol, int outR, int outC, float pad)
+{
+    TensorData tCols = wrap({ N, C * kh * kw, outR * outC }, cols);
+    const TensorData tX = wrap({ N, C, H, W }, x);
+    const TensorData tF = wrap({ 1, C, kh, kw }, x);          // only its shape is read
+    CN::Im2Col(tCols, tF, tX, strideRow, strideCol, padRow, padCol, dilRow, dilCol, pad);
+}
+
+// dx [N, C, H, W] += adjoint of im2col applied to cols, with Col2Im's argument order
+// as Conv2DBackward passes it (Convolution.cpp:313-314: strideCol, strideRow)
+void ref_col2im(float* dx, const float* cols, int N, int C, int H, int W, int kh, int kw, int strideRow,
+                int strideCol, int padRow, int padCol, int dilRow, int dilCol, int outR, int outC)
+{
+    TensorData tDx = wrap({ N, C, H, W }, dx);
+    const TensorData tCols = wrap({ N, C * kh * kw, outR * outC }, cols);
+    const TensorData tF = wrap({ 1, C, kh, kw }, cols);       // only its shape is read
+    CN::Col2Im(tDx, tCols, tF, strideCol, strideRow, padRow, padCol, dilRow, dilCol);
+}
+
+// y [N, Cout, outR, outC] += conv(x, filter [Cout, C, kh, kw])
+void ref_conv2d(float* y, const float* x, const float* filt, int N, int C, int H, int W, int Cout, int kh, int kw,
+                int strideRow, int strideCol, int padRow, int padCol, int dilRow, int dilCol, int outR, int outC)
+{
+    TensorData tY = wrap({ N, Cout, outR, outC }, y);
+    const TensorData tX = wrap({ N, C, H, W }, x);
+    const TensorData tF = wrap({ Cout, C, kh, kw }, filt);
+    CN::Conv2D(tY, tX, tF, strideRow, strideCol, padRow, padCol, dilRow, dilCol, Sapphire::CudaDevice());
+}
+
+// dx += input gradient, dfilt += filter gradient
+void ref_conv2d_backward(float* dx, float* dfilt, const float* dy, const float* x, const float* filt, int N, int C,
+                         int H, int W, int Cout, int kh, int kw, int strideRow, int strideCol, int padRow,
+                         int padCol, int dilRow, int dilCol, int outR, int outC)
+{
+    TensorData tDx = wrap({ N, C, H, W }, dx);
+    TensorData tDf = wrap({ Cout, C, kh, kw }, dfilt);
+    const TensorData tDy = wrap({ N, Cout, outR, outC }, dy);
+    const TensorData tX = wrap({ N, C, H, W }, x);
+    const TensorData tF = wrap({ Cout, C, kh, kw }, filt);
+    CN::Conv2DBackward(tDx, tDf, tDy, tX, tF, strideRow, strideCol, padRow, padCol, dilRow, dilCol,
+                       Sapphire::CudaDevice());
+}
+
+}  // extern "C"

@@ -12,17 +12,19 @@
  *                     (oracle/_ref, built from the reference tree by
  *                     oracle/Makefile) and against fixtures generated from it
  *                     (tests/golden).
- *   orc_im2col/col2im PARITY UNPINNED.  Restated from the reference's host
- *                     lowering (Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-211);
- *                     that file needs the reference's TensorData / resource
- *                     manager stack, which does not build from a few files, and
- *                     the reference holds no fixture for it (its own test
- *                     compares the host path with cuDNN at 0.01 absolute,
- *                     Tests/UnitTests/Sources/FunctionTest/Conv2DTest.cpp).  The tests check the
- *                     restatement against an independent formulation instead:
- *                     the lowering + Gemm equals a true (flipped-kernel)
- *                     convolution, the mode the reference asks of cuDNN
- *                     (Sources/Sapphire/compute/dense/cuda/Convolution.cu:39).
+ *   orc_im2col/col2im PINNED.  Restated from the reference's host lowering
+ *                     (Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-211) and
+ *                     checked bit-for-bit against that file itself, compiled
+ *                     unmodified against stand-ins for the reference's
+ *                     TensorData / CudaDevice headers (oracle/ref_conv_shim.cpp,
+ *                     oracle/ref_standins/; the real headers pull in the CUDA
+ *                     runtime, cuDNN and the memory pools), and against fixtures
+ *                     generated from it (tests/golden/conv_golden.npz).  The
+ *                     composition with the Gemm leaf (Conv2D, Conv2DBackward,
+ *                     Convolution.cpp:217-316) is pinned the same way.  The tests
+ *                     also check that the lowering + Gemm equals a true
+ *                     (flipped-kernel) convolution, the mode the reference asks
+ *                     of cuDNN (Sources/Sapphire/compute/dense/cuda/Convolution.cu:39).
  *   orc_spgemm_*      PARITY UNPINNED.  The reference declares a CSR sparse
  *                     GEMM (Includes/Sapphire/compute/sparse/naive/SparseGemm.hpp:15-16,
  *                     Includes/Sapphire/compute/sparse/cuda/SparseGemm.cuh:38-41) but ships

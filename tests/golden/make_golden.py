@@ -1,6 +1,6 @@
 """Generates the golden fixtures of tests/golden from the REFERENCE's own CPU
-code (oracle/_ref/libsapphire_ref.so, compiled from the reference tree by
-oracle/Makefile).  Run where the reference tree is mounted:
+code (oracle/_ref/libsapphire_ref.so and libsapphire_ref_conv.so, compiled from the
+reference tree by oracle/Makefile).  Run where the reference tree is mounted:
 
     make -C oracle && python tests/golden/make_golden.py
 
@@ -35,6 +35,41 @@ def small_case(idx):
     return a, bm, c
 
 
+# N, C, H, W, Cout, kh, kw, stride, pad, dil: the geometries of the convolution tests
+CONV_CASES = [
+    (2, 3, 8, 9, 4, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (1, 2, 11, 7, 5, 3, 2, (2, 1), (0, 1), (1, 2)),
+    (3, 1, 6, 6, 2, 1, 1, (1, 1), (0, 0), (1, 1)),
+    (2, 4, 10, 10, 3, 5, 5, (2, 2), (2, 2), (1, 1)),
+    (1, 2, 9, 12, 2, 2, 3, (3, 2), (1, 0), (2, 1)),
+]
+
+
+def conv_case(idx):
+    """Seeded inputs of convolution case idx: x, filter, y0 (accumulated into), dy, dx0, dfilter0."""
+    N, Cc, H, Wd, Cout, kh, kw, stride, pad, dil = CONV_CASES[idx]
+    rng = np.random.default_rng(500 + idx)
+    oR, oC = O.conv_out(H, pad[0], dil[0], kh, stride[0]), O.conv_out(Wd, pad[1], dil[1], kw, stride[1])
+    x = rng.standard_normal((N, Cc, H, Wd)).astype(np.float32)
+    f = rng.standard_normal((Cout, Cc, kh, kw)).astype(np.float32)
+    y0 = rng.standard_normal((N, Cout, oR, oC)).astype(np.float32)
+    dy = rng.standard_normal((N, Cout, oR, oC)).astype(np.float32)
+    dx0 = rng.standard_normal(x.shape).astype(np.float32)
+    df0 = rng.standard_normal(f.shape).astype(np.float32)
+    return x, f, y0, dy, dx0, df0
+
+
+def conv_outputs(idx, impl):
+    """im2col(x), col2im(dx0, dy-shaped columns), Conv2D and Conv2DBackward of case idx."""
+    _, _, _, _, _, kh, kw, stride, pad, dil = CONV_CASES[idx]
+    x, f, y0, dy, dx0, df0 = conv_case(idx)
+    cols = O.im2col(x, kh, kw, stride, pad, dil, pad_value=0.5, impl=impl)
+    back = O.col2im(dx0.copy(), np.cos(cols), kh, kw, stride, pad, dil, impl=impl)
+    y = O.conv2d(y0, x, f, stride, pad, dil, impl=impl)
+    dx, df = O.conv2d_backward(dx0, df0, dy, x, f, stride, pad, dil, impl=impl)
+    return {"cols": cols, "col2im": back, "y": y, "dx": dx, "df": df}
+
+
 def mlp_reference(steps, impl):
     Ws, bs = W.mlp_init(0)
     net = O.MlpOracle(Ws, bs, 0.01, impl=impl)
@@ -67,6 +102,14 @@ def main():
     np.savez_compressed(os.path.join(HERE, "dense_golden.npz"), **out)
     print("wrote", os.path.join(HERE, "dense_golden.npz"),
           {k: v.shape for k, v in out.items()})
+    # the reference's own host convolution (Convolution.cpp:15-316)
+    assert O.have_ref_conv(), "build oracle/_ref first (make -C oracle)"
+    conv = {}
+    for i in range(len(CONV_CASES)):
+        for k, v in conv_outputs(i, "ref").items():
+            conv[f"case{i}_{k}"] = v
+    np.savez_compressed(os.path.join(HERE, "conv_golden.npz"), **conv)
+    print("wrote", os.path.join(HERE, "conv_golden.npz"), {k: v.shape for k, v in conv.items()})
 
 
 if __name__ == "__main__":

@@ -186,6 +186,50 @@ def test_conv_lowering_is_a_true_convolution(oracle, case):
     assert np.abs(df - (df0 + ft.grad.numpy())).max() <= 2e-5 * max(1.0, np.abs(df).max())
 
 
+def _golden_module():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "make_golden", os.path.join(os.path.dirname(__file__), "golden", "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.mark.parametrize("idx", range(5))
+def test_conv_port_matches_golden_from_the_reference(oracle, idx):
+    """The restated lowering and composition against fixtures written by the reference's
+    own Im2Col, Col2Im, Conv2D and Conv2DBackward
+    (Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-316, compiled unmodified):
+    every element bit for bit, asymmetric strides, paddings and dilations included."""
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "conv_golden.npz"))
+    got = _golden_module().conv_outputs(idx, "port")
+    for k, v in got.items():
+        assert np.array_equal(_bits(v), _bits(gold[f"case{idx}_{k}"])), k
+
+
+def test_conv_port_equals_reference_build(oracle):
+    """Where the reference build is present: the same comparison live, plus a case of the
+    benchmark's geometry class (3 x 3 taps, padding 1) too large for a fixture."""
+    if not oracle.have_ref_conv():
+        pytest.skip("oracle/_ref/libsapphire_ref_conv.so not built (reference tree absent)")
+    mod = _golden_module()
+    for idx in range(len(mod.CONV_CASES)):
+        ref, port = mod.conv_outputs(idx, "ref"), mod.conv_outputs(idx, "port")
+        for k in ref:
+            assert np.array_equal(_bits(ref[k]), _bits(port[k])), (idx, k)
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((2, 16, 32, 32)).astype(np.float32)
+    f = rng.standard_normal((32, 16, 3, 3)).astype(np.float32)
+    y0 = rng.standard_normal((2, 32, 32, 32)).astype(np.float32)
+    args = ((1, 1), (1, 1), (1, 1))
+    assert np.array_equal(_bits(oracle.conv2d(y0, x, f, *args)), _bits(oracle.conv2d(y0, x, f, *args, impl="ref")))
+    dy = rng.standard_normal(y0.shape).astype(np.float32)
+    dx0, df0 = np.zeros_like(x), np.zeros_like(f)
+    a = oracle.conv2d_backward(dx0, df0, dy, x, f, *args)
+    b = oracle.conv2d_backward(dx0, df0, dy, x, f, *args, impl="ref")
+    assert np.array_equal(_bits(a[0]), _bits(b[0])) and np.array_equal(_bits(a[1]), _bits(b[1]))
+
+
 def test_im2col_tap_order_and_padding(oracle):
     """Row c*kh*kw + (kh*kw - 1 - tap) holds tap (fr, fc); outside pixels read the pad value."""
     x = np.arange(1, 1 + 2 * 3 * 3, dtype=np.float32).reshape(1, 2, 3, 3)
