@@ -141,10 +141,23 @@ def ref_conv():
         lib.ref_col2im.argtypes = [_f32p, _f32p] + ints
         lib.ref_conv2d.argtypes = [_f32p] * 3 + [C.c_int] * 15
         lib.ref_conv2d_backward.argtypes = [_f32p] * 5 + [C.c_int] * 15
-        for n in ("ref_im2col", "ref_col2im", "ref_conv2d", "ref_conv2d_backward"):
+        i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+        lib.ref_compute_gemm.argtypes = [_f32p, i32p, C.c_int, _f32p, i32p, C.c_int, _f32p, i32p, C.c_int]
+        for n in ("ref_im2col", "ref_col2im", "ref_conv2d", "ref_conv2d_backward", "ref_compute_gemm"):
             getattr(lib, n).restype = None
         _ref_conv = lib
     return _ref_conv
+
+
+def ref_compute_gemm(y, a, b):
+    """y + a.b by the reference's Compute::Gemm host path (shape expansion and
+    BroadcastWith2Inputs of the reference, Sources/Sapphire/compute/BasicOps.cpp:183-248,
+    Includes/Sapphire/compute/Broadcast.hpp:82-133, over Dense::Naive::Gemm); returns a copy."""
+    out = np.ascontiguousarray(y, dtype=np.float32).copy()
+    sh = lambda t: np.asarray(t.shape, dtype=np.int32)
+    ref_conv().ref_compute_gemm(out.reshape(-1), sh(out), out.ndim, _c(a).reshape(-1), sh(a), a.ndim,
+                                _c(b).reshape(-1), sh(b), b.ndim)
+    return out
 
 
 # ---------------------------------------------------------------- dense helpers

@@ -2,7 +2,8 @@
 //
 // C entry points around the reference's own host convolution, so that the parity
 // tests can pin the restated lowering (orc_im2col / orc_col2im and the conv
-// composition in oracle.py) against it.  Compiled from the reference's files where
+// composition in oracle.py) against it, and the broadcast planner of the Sapphire-
+// signature shims against the reference's BroadcastWith2Inputs.  Compiled from the reference's files where
 // they lie, unmodified (oracle/Makefile, target ref_conv):
 //   Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-316  Im2Col, Col2Im, Conv2D, Conv2DBackward
 //   Sources/Sapphire/compute/dense/naive/NaiveGemm.cpp:12-38     Dense::Naive::Gemm
@@ -112,6 +113,17 @@ void ref_conv2d_backward(float* dx, float* dfilt, const float* dy, const float* 
     const TensorData tF = wrap({ Cout, C, kh, kw }, filt);
     CN::Conv2DBackward(tDx, tDf, tDy, tX, tF, strideRow, strideCol, padRow, padCol, dilRow, dilCol,
                        Sapphire::CudaDevice());
+}
+
+// y <- y + a.b with the reference's batch / broadcast rules over the leading dimensions
+// (Compute::Gemm as restated above: Expand, BroadcastWith2Inputs, Dense::Naive::Gemm)
+void ref_compute_gemm(float* y, const int* yShape, int yDim, const float* a, const int* aShape, int aDim,
+                      const float* b, const int* bShape, int bDim)
+{
+    TensorData tY(Shape(std::vector<int>(yShape, yShape + yDim)), y);
+    const TensorData tA(Shape(std::vector<int>(aShape, aShape + aDim)), const_cast<float*>(a));
+    const TensorData tB(Shape(std::vector<int>(bShape, bShape + bDim)), const_cast<float*>(b));
+    Sapphire::Compute::Gemm(tY, tA, tB);
 }
 
 }  // extern "C"

@@ -102,11 +102,14 @@ struct LeafCall {
 
 // Host-side planner that reproduces the batch/broadcast rules of
 // Compute::Gemm (Sources/Sapphire/compute/BasicOps.cpp:183-248 with
-// Includes/Sapphire/compute/Broadcast.hpp:82-133): shapes are right-aligned
-// and left-padded with 1s, the last two dimensions are the matrix, and a
-// leading dimension of a or b is indexed modulo its own extent.  Instead of
-// one leaf call per broadcast index it emits one strided call per run of the
-// innermost batch dimension (stride 0 for a shared operand).
+// Includes/Sapphire/compute/Broadcast.hpp:82-133) by walking the reference's
+// recursion with offsets in place of pointers: shapes are right-aligned and
+// left-padded with 1s, the last two dimensions are the matrix, leading
+// dimensions equal in all three tensors are folded, and at the first one that
+// differs block c of the loop addresses block (c % extent) of each tensor --
+// the reference's rule, also where it is not numpy's broadcast.  Instead of one
+// leaf call per index it emits one strided call per run of consecutive y
+// blocks whose operand blocks advance by a constant step (0 for a shared one).
 std::vector<LeafCall> PlanGemm(const std::vector<int>& yShape, const std::vector<int>& aShape,
                                const std::vector<int>& bShape);
 

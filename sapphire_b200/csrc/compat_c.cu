@@ -50,63 +50,96 @@ sb200_ctx* ContextFor(int deviceId)
     return ctx;
 }
 
+namespace {
+
+struct MatrixTriple {
+    long long y, a, b;                                 // element offsets of one M x N product
+};
+
+// The reference's recursion (Includes/Sapphire/compute/Broadcast.hpp:82-133), offsets instead
+// of pointers, unsigned arithmetic and all: runs of leading dimensions that are equal in
+// y, a and b are folded into `chunk`; at the first dimension that differs, index c of
+// max(chunkOut, chunkA, chunkB) addresses block (c % chunkX) of each tensor.  (After a
+// folded run that modulo is not numpy's broadcast -- [3,4,M,N] = [3,1,M,K].[3,4,K,N] pairs
+// y block c with a block c % 3, not c / 4 -- and the plan follows the reference, whose
+// loop stays in Sapphire when only the leaf is replaced.)
+void Walk(const std::vector<unsigned>& y, const std::vector<unsigned>& a, const std::vector<unsigned>& b,
+          unsigned totalOut, unsigned totalA, unsigned totalB, long long oy, long long oa, long long ob,
+          unsigned shapeIdx, unsigned matY, unsigned matA, unsigned matB, std::vector<MatrixTriple>& out)
+{
+    const unsigned dims = static_cast<unsigned>(y.size());
+    auto leaf = [&]() {
+        // Dense::Cuda::Gemm(totalSizeOut, ...): totalSizeOut / (M N) matrices, packed
+        const unsigned n = matY ? totalOut / matY : 0;
+        for (unsigned i = 0; i < n; ++i)
+            out.push_back({oy + static_cast<long long>(i) * matY, oa + static_cast<long long>(i) * matA,
+                           ob + static_cast<long long>(i) * matB});
+    };
+    if (shapeIdx >= dims - 2)
+        return leaf();
+    unsigned chunk = 1;
+    while (shapeIdx < dims - 2 && y[shapeIdx] == a[shapeIdx] && y[shapeIdx] == b[shapeIdx]) {
+        chunk *= y[shapeIdx];
+        shapeIdx += 1;
+    }
+    if (shapeIdx >= dims - 2)
+        return leaf();
+    const unsigned chunkA = chunk * a[shapeIdx], chunkB = chunk * b[shapeIdx], chunkOut = chunk * y[shapeIdx];
+    if (chunkA == 0 || chunkB == 0 || chunkOut == 0)
+        return;
+    const unsigned strideA = totalA / chunkA, strideB = totalB / chunkB, strideOut = totalOut / chunkOut;
+    const unsigned maxChunk = std::max(chunkOut, std::max(chunkA, chunkB));
+    for (unsigned c = 0; c < maxChunk; ++c)
+        Walk(y, a, b, strideOut, strideA, strideB, oy + static_cast<long long>(c % chunkOut) * strideOut,
+             oa + static_cast<long long>(c % chunkA) * strideA, ob + static_cast<long long>(c % chunkB) * strideB,
+             shapeIdx + 1, matY, matA, matB, out);
+}
+
+}  // namespace
+
 std::vector<LeafCall> PlanGemm(const std::vector<int>& yShape, const std::vector<int>& aShape,
                                const std::vector<int>& bShape)
 {
-    auto padded = [](const std::vector<int>& s, size_t dim) {
-        std::vector<long long> out(dim, 1);
+    // Shape::Expand: right-aligned, left-padded with 1s (Sources/Sapphire/util/shape.cpp:138-158)
+    auto expanded = [](const std::vector<int>& s, size_t dim) {
+        std::vector<unsigned> out(dim, 1);
         for (size_t i = 0; i < s.size(); ++i)
-            out[dim - s.size() + i] = s[i];
+            out[dim - s.size() + i] = static_cast<unsigned>(s[i]);
         return out;
     };
-    size_t dim = std::max(std::max(yShape.size(), aShape.size()), std::max(bShape.size(), static_cast<size_t>(2)));
-    const auto y = padded(yShape, dim), a = padded(aShape, dim), b = padded(bShape, dim);
-    const size_t nb = dim - 2;                         // batch dimensions
-    const long long M = y[dim - 2], N = y[dim - 1], K = a[dim - 1];
-    const long long matY = M * N, matA = M * K, matB = K * N;
-
-    // element strides of each batch dimension inside its own tensor
-    auto strides = [&](const std::vector<long long>& s, long long mat) {
-        std::vector<long long> st(nb, 0);
-        long long run = mat;
-        for (size_t i = nb; i-- > 0;) {
-            st[i] = run;
-            run *= s[i];
-        }
-        return st;
+    const size_t dim = std::max(std::max(yShape.size(), aShape.size()), std::max(bShape.size(), static_cast<size_t>(2)));
+    const auto y = expanded(yShape, dim), a = expanded(aShape, dim), b = expanded(bShape, dim);
+    const unsigned M = y[dim - 2], N = y[dim - 1], K = a[dim - 1];
+    auto size = [](const std::vector<unsigned>& s) {
+        unsigned n = 1;
+        for (unsigned v : s) n *= v;
+        return n;
     };
-    const auto sy = strides(y, matY), sa = strides(a, matA), sb = strides(b, matB);
+    std::vector<MatrixTriple> seq;
+    Walk(y, a, b, size(y), size(a), size(b), 0, 0, 0, 0, M * N, M * K, K * N, seq);
 
+    // The reference makes one leaf call per index of the loop above.  Here every maximal
+    // run of products whose y blocks are consecutive and whose a and b blocks advance by
+    // a constant, non-negative step (0 = shared operand) becomes one strided-batched call;
+    // the runs keep the reference's order, so a y block that is addressed twice
+    // accumulates as it does there.
     std::vector<LeafCall> plan;
-    if (nb == 0) {
-        plan.push_back({0, 0, 0, 1, 0, 0});
-        return plan;
-    }
-    // innermost batch dimension becomes the strided batch of one call when each
-    // operand either spans it fully or has extent 1 there
-    const size_t in = nb - 1;
-    const bool foldable = (a[in] == y[in] || a[in] == 1) && (b[in] == y[in] || b[in] == 1);
-    const size_t outer_dims = foldable ? in : nb;
-    long long outer = 1;
-    for (size_t i = 0; i < outer_dims; ++i)
-        outer *= y[i];
-    std::vector<long long> idx(outer_dims, 0);
-    for (long long it = 0; it < outer; ++it) {
-        long long oy = 0, oa = 0, ob = 0;
-        for (size_t i = 0; i < outer_dims; ++i) {
-            oy += idx[i] * sy[i];
-            oa += (idx[i] % a[i]) * sa[i];
-            ob += (idx[i] % b[i]) * sb[i];
+    const long long matY = static_cast<long long>(M) * N;
+    size_t i = 0;
+    while (i < seq.size()) {
+        LeafCall c{seq[i].y, seq[i].a, seq[i].b, 1, 0, 0};
+        if (i + 1 < seq.size() && seq[i + 1].y == seq[i].y + matY && seq[i + 1].a >= seq[i].a &&
+            seq[i + 1].b >= seq[i].b) {
+            c.strideA = seq[i + 1].a - seq[i].a;
+            c.strideB = seq[i + 1].b - seq[i].b;
+            size_t j = i + 1;
+            while (j < seq.size() && seq[j].y == seq[j - 1].y + matY && seq[j].a == seq[j - 1].a + c.strideA &&
+                   seq[j].b == seq[j - 1].b + c.strideB)
+                ++j;
+            c.batch = static_cast<long long>(j - i);
         }
-        if (foldable)
-            plan.push_back({oy, oa, ob, y[in], a[in] == 1 ? 0 : matA, b[in] == 1 ? 0 : matB});
-        else
-            plan.push_back({oy, oa, ob, 1, 0, 0});
-        for (size_t i = outer_dims; i-- > 0;) {
-            if (++idx[i] < y[i])
-                break;
-            idx[i] = 0;
-        }
+        plan.push_back(c);
+        i += static_cast<size_t>(c.batch);
     }
     return plan;
 }

@@ -70,6 +70,30 @@ def conv_outputs(idx, impl):
     return {"cols": cols, "col2im": back, "y": y, "dx": dx, "df": df}
 
 
+# (y, a, b) shapes for Compute::Gemm's batch / broadcast rules: the families of the reference's
+# broadcast tests (Tests/UnitTests/Sources/FunctionTest/BroadcastTest.cpp:20-202) and a few more
+BROADCAST_CASES = [
+    ([4, 6, 5], [4, 6, 3], [4, 3, 5]),                   # equal batch: one call
+    ([3, 4, 4, 5], [3, 1, 4, 2], [3, 4, 2, 5]),          # [b,1,M,K].[b,M,K,N]: not numpy's pairing
+    ([4, 4, 5], [4, 2], [4, 2, 5]),                      # [M,K].[M,K,N]: missing dimension
+    ([5, 4, 4, 5], [4, 2], [5, 4, 2, 5]),                # [M,K].[N,M,K,N]
+    ([6, 5], [6, 3], [3, 5]),                            # plain 2-D
+    ([2, 3, 6, 5], [2, 3, 6, 3], [1, 1, 3, 5]),          # shared B
+    ([2, 3, 6, 5], [1, 3, 6, 3], [2, 1, 3, 5]),          # each operand shared along another dimension
+    ([7, 1, 5], [7, 1, 9], [9, 5]),                      # a row vector per batch
+    ([3, 4, 4, 8], [3, 1, 4, 12], [3, 4, 12, 8]),        # the three shapes of the GPU test
+    ([4, 4, 8], [4, 12], [4, 12, 8]),
+    ([5, 4, 4, 8], [4, 12], [5, 4, 12, 8]),
+]
+
+
+def broadcast_case(idx):
+    ys, as_, bs = BROADCAST_CASES[idx]
+    rng = np.random.default_rng(700 + idx)
+    return (rng.standard_normal(ys).astype(np.float32), rng.standard_normal(as_).astype(np.float32),
+            rng.standard_normal(bs).astype(np.float32))
+
+
 def mlp_reference(steps, impl):
     Ws, bs = W.mlp_init(0)
     net = O.MlpOracle(Ws, bs, 0.01, impl=impl)
@@ -110,6 +134,11 @@ def main():
             conv[f"case{i}_{k}"] = v
     np.savez_compressed(os.path.join(HERE, "conv_golden.npz"), **conv)
     print("wrote", os.path.join(HERE, "conv_golden.npz"), {k: v.shape for k, v in conv.items()})
+    # Compute::Gemm's batch / broadcast rules (BasicOps.cpp:183-248 over the reference's
+    # BroadcastWith2Inputs and CPU GEMM)
+    bc = {f"case{i}": O.ref_compute_gemm(*broadcast_case(i)) for i in range(len(BROADCAST_CASES))}
+    np.savez_compressed(os.path.join(HERE, "broadcast_golden.npz"), **bc)
+    print("wrote", os.path.join(HERE, "broadcast_golden.npz"), {k: v.shape for k, v in bc.items()})
 
 
 if __name__ == "__main__":

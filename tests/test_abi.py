@@ -90,37 +90,50 @@ def plan(y, a, b):
     return [tuple(out[6 * i:6 * i + 6]) for i in range(min(n, cap))]
 
 
-def apply_plan(calls, y, a, b, M, N, K):
-    """Executes a plan with numpy on flat buffers (float64), y += a.b per call."""
-    y = y.copy()
-    for (oy, oa, ob, batch, sa, sb) in calls:
-        for i in range(batch):
-            A = a[oa + i * sa: oa + i * sa + M * K].reshape(M, K)
-            B = b[ob + i * sb: ob + i * sb + K * N].reshape(K, N)
-            y[oy + i * M * N: oy + (i + 1) * M * N] += (A @ B).reshape(-1)
-    return y
+def _golden_module():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "make_golden", os.path.join(ROOT, "tests", "golden", "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
-# shape families of the reference's broadcast tests
-# (Tests/UnitTests/Sources/FunctionTest/BroadcastTest.cpp:20-202) and GemmTest.cpp:20-84
-@pytest.mark.parametrize("ys,as_,bs", [
-    ([4, 6, 5], [4, 6, 3], [4, 3, 5]),                   # equal batch: one call
-    ([3, 4, 4, 5], [3, 1, 4, 2], [3, 4, 2, 5]),          # [b,1,M,K].[b,M,K,N]
-    ([4, 4, 5], [4, 2], [4, 2, 5]),                      # [M,K].[M,K,N]: missing dimension
-    ([5, 4, 4, 5], [4, 2], [5, 4, 2, 5]),                # [M,K].[N,M,K,N]
-    ([6, 5], [6, 3], [3, 5]),                            # plain 2-D
-    ([2, 3, 6, 5], [2, 3, 6, 3], [1, 1, 3, 5]),          # shared B
-])
-def test_plan_matches_numpy_broadcast(ys, as_, bs):
-    rng = np.random.default_rng(0)
-    a = rng.standard_normal(as_)
-    b = rng.standard_normal(bs)
-    y0 = rng.standard_normal(ys)
+def _run_plan_with_cpu_gemm(idx):
+    """The plan's leaf calls executed with the reference's CPU GEMM arithmetic."""
+    from oracle import oracle as O
+    mod = _golden_module()
+    ys, as_, bs = mod.BROADCAST_CASES[idx]
+    y0, a, b = mod.broadcast_case(idx)
     M, N, K = ys[-2], ys[-1], as_[-1]
-    calls = plan(ys, as_, bs)
-    got = apply_plan(calls, y0.reshape(-1), a.reshape(-1), b.reshape(-1), M, N, K).reshape(ys)
-    want = y0 + np.matmul(a, b)
-    assert np.allclose(got, want)
+    got = y0.reshape(-1).copy()
+    af, bf = a.reshape(-1), b.reshape(-1)
+    for (oy, oa, ob, batch, sa, sb) in plan(ys, as_, bs):
+        for i in range(batch):
+            A = af[oa + i * sa: oa + i * sa + M * K].reshape(1, M, K)
+            B = bf[ob + i * sb: ob + i * sb + K * N].reshape(1, K, N)
+            seg = slice(oy + i * M * N, oy + (i + 1) * M * N)
+            got[seg] = O.gemm(got[seg].reshape(1, M, N), A, B).reshape(-1)
+    return got.reshape(ys), (y0, a, b)
+
+
+@pytest.mark.parametrize("idx", range(11))
+def test_plan_equals_the_reference_broadcast(idx):
+    """The planner of the Sapphire-signature shims against the reference's own
+    Compute::Gemm host path (shape expansion, BroadcastWith2Inputs, CPU GEMM: fixtures
+    written by the reference build, and that build itself where it is present): the
+    plan's leaf calls give the reference's result bit for bit -- also for
+    [3,4,M,N] = [3,1,M,K].[3,4,K,N], where the reference pairs y block c with a block
+    c % 3 and numpy's broadcast would pair it with c / 4."""
+    from oracle import oracle as O
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "broadcast_golden.npz"))
+    got, (y0, a, b) = _run_plan_with_cpu_gemm(idx)
+    assert np.array_equal(got.view(np.uint32), gold[f"case{idx}"].view(np.uint32))
+    if O.have_ref_conv():
+        assert np.array_equal(got.view(np.uint32), O.ref_compute_gemm(y0, a, b).view(np.uint32))
+    if idx not in (1, 8):                                # every other family is numpy's broadcast too
+        want = y0.astype(np.float64) + np.matmul(a.astype(np.float64), b.astype(np.float64))
+        assert np.allclose(got, want, rtol=1e-4, atol=1e-4)
 
 
 def test_plan_folds_equal_batches_into_one_call():
