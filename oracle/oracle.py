@@ -8,7 +8,7 @@ ctypes front end of the two CPU checkers:
   files compiled by ``oracle/Makefile`` from the reference tree.  It exists
   only where that tree was present at build time (or the prebuilt ``.so`` was
   shipped along); ``have_ref()`` says which.  ``ref_conv`` is the same for the
-  reference's host convolution (``oracle/_ref/libsapphire_ref_conv.so``).
+  reference's host convolution (``oracle/_ref/libsapphire_ref_ops.so``).
 
 Only tests, the smoke check and the CPU-baseline legs of the benchmark import
 this module.  The product package never does.
@@ -119,23 +119,24 @@ def ref():
     return _ref
 
 
-_REF_CONV_SO = os.path.join(os.path.dirname(_REF_SO), "libsapphire_ref_conv.so")
-_ref_conv = None
+_REF_OPS_SO = os.path.join(os.path.dirname(_REF_SO), "libsapphire_ref_ops.so")
+_ref_ops = None
 
 
-def have_ref_conv() -> bool:
-    return os.path.exists(_REF_CONV_SO)
+def have_ref_ops() -> bool:
+    return os.path.exists(_REF_OPS_SO)
 
 
-def ref_conv():
-    """The reference's own host convolution (Convolution.cpp compiled unmodified against
-    stand-in TensorData / CudaDevice headers: oracle/ref_conv_shim.cpp)."""
-    global _ref_conv
-    if _ref_conv is None:
-        if not have_ref_conv():
+def ref_ops():
+    """The reference's own host convolution and Linear backward unit (Convolution.cpp,
+    LinearBackward.cpp, SGD.cpp compiled unmodified against stand-in TensorData /
+    CudaDevice / Model headers: oracle/ref_ops_shim.cpp)."""
+    global _ref_ops
+    if _ref_ops is None:
+        if not have_ref_ops():
             raise FileNotFoundError(
-                f"{_REF_CONV_SO} is missing: run `make -C oracle` where the reference tree is mounted")
-        lib = C.CDLL(_REF_CONV_SO)
+                f"{_REF_OPS_SO} is missing: run `make -C oracle` where the reference tree is mounted")
+        lib = C.CDLL(_REF_OPS_SO)
         ints = [C.c_int] * 14
         lib.ref_im2col.argtypes = [_f32p, _f32p] + ints + [C.c_float]
         lib.ref_col2im.argtypes = [_f32p, _f32p] + ints
@@ -143,10 +144,27 @@ def ref_conv():
         lib.ref_conv2d_backward.argtypes = [_f32p] * 5 + [C.c_int] * 15
         i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
         lib.ref_compute_gemm.argtypes = [_f32p, i32p, C.c_int, _f32p, i32p, C.c_int, _f32p, i32p, C.c_int]
-        for n in ("ref_im2col", "ref_col2im", "ref_conv2d", "ref_conv2d_backward", "ref_compute_gemm"):
+        lib.ref_linear_backprop.argtypes = [_f32p] * 5 + [C.c_int] * 3 + [C.c_float]
+        for n in ("ref_im2col", "ref_col2im", "ref_conv2d", "ref_conv2d_backward", "ref_compute_gemm",
+                  "ref_linear_backprop"):
             getattr(lib, n).restype = None
-        _ref_conv = lib
-    return _ref_conv
+        _ref_ops = lib
+    return _ref_ops
+
+
+def ref_linear_backprop(dx, dy, weight, bias, x, lr):
+    """The reference's LinearBackProp unit with SGD inside
+    (Sources/Sapphire/operations/Backward/LinearBackward.cpp:27-99,
+    Sources/Sapphire/operations/optimizers/SGD.cpp:22-28), run by the reference build.
+    Returns (dx + dy.W^T, updated weight, updated bias) as copies."""
+    B, n_in = x.shape
+    n_out = dy.shape[1]
+    dxo = np.ascontiguousarray(dx, dtype=np.float32).copy()
+    w = np.ascontiguousarray(weight, dtype=np.float32).copy()
+    b = np.ascontiguousarray(bias, dtype=np.float32).reshape(-1).copy()
+    ref_ops().ref_linear_backprop(dxo.reshape(-1), _c(dy).reshape(-1), w.reshape(-1), b, _c(x).reshape(-1),
+                                  B, n_in, n_out, float(lr))
+    return dxo, w, b
 
 
 def ref_compute_gemm(y, a, b):
@@ -155,7 +173,7 @@ def ref_compute_gemm(y, a, b):
     Includes/Sapphire/compute/Broadcast.hpp:82-133, over Dense::Naive::Gemm); returns a copy."""
     out = np.ascontiguousarray(y, dtype=np.float32).copy()
     sh = lambda t: np.asarray(t.shape, dtype=np.int32)
-    ref_conv().ref_compute_gemm(out.reshape(-1), sh(out), out.ndim, _c(a).reshape(-1), sh(a), a.ndim,
+    ref_ops().ref_compute_gemm(out.reshape(-1), sh(out), out.ndim, _c(a).reshape(-1), sh(a), a.ndim,
                                 _c(b).reshape(-1), sh(b), b.ndim)
     return out
 
@@ -236,7 +254,7 @@ def im2col(x, kh, kw, stride=(1, 1), pad=(0, 0), dil=(1, 1), pad_value=0.0, impl
     oR, oC = conv_out(H, pad[0], dil[0], kh, stride[0]), conv_out(W, pad[1], dil[1], kw, stride[1])
     cols = np.empty((N, Cc * kh * kw, oR * oC), dtype=np.float32)
     if impl == "ref":
-        ref_conv().ref_im2col(cols.reshape(-1), x.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
+        ref_ops().ref_im2col(cols.reshape(-1), x.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
                               pad[0], pad[1], dil[0], dil[1], oR, oC, pad_value)
     else:
         port().orc_im2col(cols.reshape(-1), x.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
@@ -252,7 +270,7 @@ def col2im(dx, cols, kh, kw, stride=(1, 1), pad=(0, 0), dil=(1, 1), impl: str = 
     N, Cc, H, W = dx.shape
     if impl == "ref":
         oR, oC = conv_out(H, pad[0], dil[0], kh, stride[0]), conv_out(W, pad[1], dil[1], kw, stride[1])
-        ref_conv().ref_col2im(dx.reshape(-1), cols.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
+        ref_ops().ref_col2im(dx.reshape(-1), cols.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
                               pad[0], pad[1], dil[0], dil[1], oR, oC)
     else:
         port().orc_col2im(dx.reshape(-1), cols.reshape(-1), N, Cc, H, W, kh, kw, stride[0], stride[1],
@@ -276,7 +294,7 @@ def conv2d(y, x, filt, stride=(1, 1), pad=(0, 0), dil=(1, 1), impl: str = "port"
     kh, kw = filt.shape[-2:]
     if impl == "ref":
         out = np.ascontiguousarray(y, dtype=np.float32).copy()
-        ref_conv().ref_conv2d(out.reshape(-1), _c(x).reshape(-1), _c(filt).reshape(-1),
+        ref_ops().ref_conv2d(out.reshape(-1), _c(x).reshape(-1), _c(filt).reshape(-1),
                               *_conv_geometry(x, filt, stride, pad, dil))
         return out
     cols = im2col(x, kh, kw, stride, pad, dil)
@@ -294,7 +312,7 @@ def conv2d_backward(dx, dfilt, dy, x, filt, stride=(1, 1), pad=(0, 0), dil=(1, 1
     if impl == "ref":
         dxo = np.ascontiguousarray(dx, dtype=np.float32).copy()
         dfo = np.ascontiguousarray(dfilt, dtype=np.float32).copy()
-        ref_conv().ref_conv2d_backward(dxo.reshape(-1), dfo.reshape(-1), _c(dy).reshape(-1), _c(x).reshape(-1),
+        ref_ops().ref_conv2d_backward(dxo.reshape(-1), dfo.reshape(-1), _c(dy).reshape(-1), _c(x).reshape(-1),
                                        _c(filt).reshape(-1), *_conv_geometry(x, filt, stride, pad, dil))
         return dxo, dfo
     cols = im2col(x, kh, kw, stride, pad, dil)
@@ -390,6 +408,27 @@ class MlpOracle:
         f["sub"](out.reshape(-1), z.reshape(-1), tmp.reshape(-1), z.size)
         z[...] = out
 
+    def linear_backward(self, l, xin, dy):
+        """Layer l's backward unit (LinearBackward.cpp:27-99): returns dx = dy.W^T with the
+        pre-update weight, then updates W by SGD with dW = x^T.dy (unscaled) and the bias
+        with dB = (1/B) ones.dy."""
+        f = self._leaves()
+        B = xin.shape[0]
+        dx = np.zeros_like(xin)
+        self._gemm_acc(dx, dy, transpose(self.W[l], self.impl))
+        dw = np.zeros_like(self.W[l])
+        self._gemm_acc(dw, transpose(xin, self.impl), dy)
+        self._sgd(self.W[l], dw)
+        db = np.zeros((1, self.b[l].size), dtype=np.float32)
+        self._gemm_acc(db, np.ones((1, B), np.float32), dy)
+        dbs = np.empty_like(db)
+        f["scale"](dbs.reshape(-1), db.reshape(-1), np.float32(1.0 / B), db.size)
+        bl = self.b[l].reshape(1, -1)
+        self.bias_travel[l] += float(self.lr) * np.abs(dy.astype(np.float64)).sum(0) / B
+        self._sgd(bl, dbs)
+        self.b[l] = bl.reshape(-1)
+        return dx
+
     def step(self, x, onehot):
         f = self._leaves()
         B = x.shape[0]
@@ -418,21 +457,7 @@ class MlpOracle:
         dy = np.zeros_like(logits)
         f["softmax_bwd"](dy.reshape(-1), dprob.reshape(-1), prob.reshape(-1), prob.size, unit)
         for l in reversed(range(nl)):
-            xin = acts[l]
-            # dx with the pre-update weight
-            dx = np.zeros_like(xin)
-            self._gemm_acc(dx, dy, transpose(self.W[l], self.impl))
-            dw = np.zeros_like(self.W[l])
-            self._gemm_acc(dw, transpose(xin, self.impl), dy)
-            self._sgd(self.W[l], dw)
-            db = np.zeros((1, self.b[l].size), dtype=np.float32)
-            self._gemm_acc(db, np.ones((1, B), np.float32), dy)
-            dbs = np.empty_like(db)
-            f["scale"](dbs.reshape(-1), db.reshape(-1), np.float32(1.0 / B), db.size)
-            bl = self.b[l].reshape(1, -1)
-            self.bias_travel[l] += float(self.lr) * np.abs(dy.astype(np.float64)).sum(0) / B
-            self._sgd(bl, dbs)
-            self.b[l] = bl.reshape(-1)
+            dx = self.linear_backward(l, acts[l], dy)
             if l > 0:
                 dpre = np.zeros_like(pre[l - 1])
                 f["relu_bwd"](dpre.reshape(-1), dx.reshape(-1), pre[l - 1].reshape(-1), dx.size)

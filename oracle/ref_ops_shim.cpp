@@ -1,27 +1,38 @@
 // TEST INFRASTRUCTURE, NOT PRODUCT CODE.
 //
-// C entry points around the reference's own host convolution, so that the parity
-// tests can pin the restated lowering (orc_im2col / orc_col2im and the conv
-// composition in oracle.py) against it, and the broadcast planner of the Sapphire-
-// signature shims against the reference's BroadcastWith2Inputs.  Compiled from the reference's files where
-// they lie, unmodified (oracle/Makefile, target ref_conv):
+// C entry points around the reference's own host convolution and its Linear backward
+// unit, so that the parity tests can pin against them: the restated lowering
+// (orc_im2col / orc_col2im and the conv composition in oracle.py), the restated Linear
+// backward + SGD of the MLP oracle, and the broadcast planner of the Sapphire-signature
+// shims (against the reference's BroadcastWith2Inputs).  Compiled from the reference's
+// files where they lie, unmodified (oracle/Makefile, target ref):
 //   Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-316  Im2Col, Col2Im, Conv2D, Conv2DBackward
+//   Sources/Sapphire/operations/Backward/LinearBackward.cpp:13-99 LinearBackProp
+//   Sources/Sapphire/operations/optimizers/SGD.cpp:9-28          Optimizer::SGD
 //   Sources/Sapphire/compute/dense/naive/NaiveGemm.cpp:12-38     Dense::Naive::Gemm
-//   Sources/Sapphire/compute/dense/naive/NaiveBasic.cpp:63-84    Dense::Naive::Transpose
+//   Sources/Sapphire/compute/dense/naive/NaiveBasic.cpp          Dense::Naive::Transpose, Scale, Sub
+//   Sources/Sapphire/compute/dense/naive/NaiveInitialize.cpp:34-40 Dense::Naive::Scalar
 //   Sources/Sapphire/util/shape.cpp                              Shape
 //   Includes/Sapphire/compute/Broadcast.hpp:82-133               BroadcastWith2Inputs
+//   Includes/Sapphire/operations/Backward/BackPropWrapper.hpp    (header only)
 // The reference's TensorData and CudaDevice headers pull in the CUDA runtime, cuDNN and
-// the memory pools; oracle/ref_standins/ holds stand-ins with the members the host
-// convolution uses (found first on the include path).  Compute::Gemm and
-// Compute::Transpose, which Conv2D / Conv2DBackward call, are defined below as the
-// host branches of Sources/Sapphire/compute/BasicOps.cpp:183-248 and :269-290 (that file
-// includes the CUDA kernels' headers and cannot be compiled here): the same shape
-// expansion, the reference's own BroadcastWith2Inputs, the reference's own leaf calls.
+// the memory pools, its Model header the whole graph bookkeeping; oracle/ref_standins/
+// holds stand-ins with the members these units use (found first on the include path).
+// Compute::Gemm, Transpose, Scale, Sub and Initialize::Ones / Zeros, which the units call,
+// are defined below as the host branches of Sources/Sapphire/compute/BasicOps.cpp:63-104,
+// 183-290 and Sources/Sapphire/compute/Initialize.cpp:47-73 (those files include the CUDA
+// kernels' headers and cannot be compiled here): the same shape expansion, the reference's
+// own BroadcastWith2Inputs, the reference's own leaf calls.
 #include <Sapphire/compute/BasicOps.hpp>
 #include <Sapphire/compute/Broadcast.hpp>
 #include <Sapphire/compute/dense/naive/Convolution.hpp>
 #include <Sapphire/compute/dense/naive/NaiveBasic.hpp>
 #include <Sapphire/compute/dense/naive/NaiveGemm.hpp>
+#include <Sapphire/compute/dense/naive/NaiveInitialize.hpp>
+#include <Sapphire/compute/Initialize.hpp>
+#include <Sapphire/Model.hpp>
+#include <Sapphire/operations/Backward/LinearBackward.hpp>
+#include <Sapphire/operations/optimizers/SGD.hpp>
 #include <algorithm>
 
 namespace Sapphire::Compute
@@ -54,6 +65,64 @@ void Transpose(TensorData& y, const TensorData& x)
     const auto chunkSize = y.GetShape().Size() / (inputM * inputN);
     Dense::Naive::Transpose(y.HostMutableRawPtr(), x.HostRawPtr(), inputM, inputN, chunkSize, broadcast);
 }
+void Scale(TensorData& y, const TensorData& x, const float factor)
+{
+    auto shapeY = y.GetShape();
+    Dense::Naive::Scale(y.HostMutableRawPtr(), x.HostRawPtr(), factor, shapeY.Size());
+}
+
+namespace
+{
+// Includes/Sapphire/util/UnitUtils.hpp:38-75 (that header includes the graph bookkeeping):
+// how many trailing dimensions all shapes have in common
+int MatchingDim(const std::vector<Shape>& shapes)
+{
+    int curDimFromLast = -1;
+    bool match = true;
+    while (match) {
+        if (shapes.at(0).Dim() + curDimFromLast < 0)
+            break;
+        const int shapeDim = shapes.at(0).At(curDimFromLast);
+        for (const auto& shape : shapes) {
+            if (shape.Dim() + curDimFromLast < 0 || shapeDim != shape.At(curDimFromLast)) {
+                match = false;
+                break;
+            }
+        }
+        if (match)
+            curDimFromLast -= 1;
+    }
+    return -(curDimFromLast + 1);
+}
+}  // namespace
+
+void Sub(TensorData& y, const TensorData& a, const TensorData& b)
+{
+    auto shapeOut = y.GetShape();
+    auto shapeA = a.GetShape();
+    auto shapeB = b.GetShape();
+    const auto maxDim = std::max({ y.GetShape().Dim(), a.GetShape().Dim(), b.GetShape().Dim() });
+    shapeOut.Expand(maxDim);
+    shapeA.Expand(maxDim);
+    shapeB.Expand(maxDim);
+    const int minRequiredDim = MatchingDim({ shapeOut, shapeA, shapeB });
+    BroadcastWith2Inputs(shapeOut, shapeA, shapeB, shapeOut.Size(), shapeA.Size(), shapeB.Size(),
+                         y.HostMutableRawPtr(), a.HostRawPtr(), b.HostRawPtr(), 0, minRequiredDim,
+                         Dense::Naive::Sub, 0, false, false);
+}
+
+namespace Initialize
+{
+void Ones(TensorUtil::TensorData& data)
+{
+    Dense::Naive::Scalar(data.HostMutableRawPtr(), 1.0f, data.GetShape());
+}
+
+void Zeros(TensorUtil::TensorData& data)
+{
+    Dense::Naive::Scalar(data.HostMutableRawPtr(), 0.0f, data.GetShape());
+}
+}  // namespace Initialize
 }  // namespace Sapphire::Compute
 
 using Sapphire::Shape;
@@ -124,6 +193,24 @@ void ref_compute_gemm(float* y, const int* yShape, int yDim, const float* a, con
     const TensorData tA(Shape(std::vector<int>(aShape, aShape + aDim)), const_cast<float*>(a));
     const TensorData tB(Shape(std::vector<int>(bShape, bShape + bDim)), const_cast<float*>(b));
     Sapphire::Compute::Gemm(tY, tA, tB);
+}
+
+// One Linear layer's backward unit with the optimizer inside, as the reference runs it:
+// dx [batch, in] += dy . W^T with the pre-update W; W [in, out] and bias [1, out] updated
+// in place by SGD with dW = x^T . dy (unscaled) and dB = (1 / batch) ones . dy.
+void ref_linear_backprop(float* dx, const float* dy, float* weight, float* bias, const float* x, int batch,
+                         int inFeatures, int outFeatures, float learningRate)
+{
+    Sapphire::Optimizer::SGD sgd(learningRate);
+    Sapphire::ModelManager::CurModel().SetOptimizer(&sgd);
+    {
+        Sapphire::BackProp::LinearBackProp unit(
+            "linear", wrap({ batch, inFeatures }, dx), wrap({ batch, outFeatures }, dy),
+            wrap({ inFeatures, outFeatures }, weight), wrap({ 1, outFeatures }, bias),
+            wrap({ batch, inFeatures }, x), batch);
+        unit.InvokeBackPropIfReady(0);
+    }
+    Sapphire::ModelManager::CurModel().SetOptimizer(nullptr);
 }
 
 }  // extern "C"

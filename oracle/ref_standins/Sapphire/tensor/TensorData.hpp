@@ -1,8 +1,8 @@
 // TEST INFRASTRUCTURE.  Stand-in for the reference's Sapphire/tensor/TensorData.hpp.
 // The real class drags in the CUDA runtime, cuDNN handles and the memory pools
 // (Sources/Sapphire/tensor/TensorData.cpp:7-10), none of which the host convolution
-// uses: Convolution.cpp touches the shape, the host pointer, the compute mode and the
-// shallow-copy / reshape behaviour of a TensorData.  This class provides exactly those
+// or the Linear backward unit use: they touch the shape, the host pointer, the compute
+// mode and the shallow-copy / reshape behaviour of a TensorData.  This class provides exactly those
 // members with the reference's semantics -- a handle on a shared, zero-filled host
 // buffer of Shape.Size() floats (TensorData.cpp:330: buffers are zeroed on allocation;
 // TensorData.hpp:18-213: copies share the buffer; Reshape keeps the data) -- so that
@@ -47,6 +47,8 @@ public:
     void SetMode(ComputeMode mode) { m_mode = mode; }
     [[nodiscard]] Type GetType() const { return m_type; }
     [[nodiscard]] CudaDevice GetDevice() const { return m_device; }
+    [[nodiscard]] CudaDevice GetCudaDevice() const { return m_device; }
+    [[nodiscard]] int GetDescriptorKey() const { return -1; }
 
     void Reshape(const Shape& shape)
     {

@@ -2,7 +2,7 @@
 // includes <cuda_runtime.h>; the reference's host convolution
 // (Sources/Sapphire/compute/dense/naive/Convolution.cpp) only passes a CudaDevice
 // through and compares ComputeMode values.  Found first on the include path when that
-// file is compiled, unmodified, for the CPU checker (oracle/Makefile, target ref_conv).
+// file is compiled, unmodified, for the CPU checker (oracle/Makefile, target ref).
 #ifndef SB200_STANDIN_CUDADEVICE_HPP
 #define SB200_STANDIN_CUDADEVICE_HPP
 

@@ -16,7 +16,7 @@
  *                     (Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-211) and
  *                     checked bit-for-bit against that file itself, compiled
  *                     unmodified against stand-ins for the reference's
- *                     TensorData / CudaDevice headers (oracle/ref_conv_shim.cpp,
+ *                     TensorData / CudaDevice headers (oracle/ref_ops_shim.cpp,
  *                     oracle/ref_standins/; the real headers pull in the CUDA
  *                     runtime, cuDNN and the memory pools), and against fixtures
  *                     generated from it (tests/golden/conv_golden.npz).  The

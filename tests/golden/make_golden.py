@@ -1,5 +1,5 @@
 """Generates the golden fixtures of tests/golden from the REFERENCE's own CPU
-code (oracle/_ref/libsapphire_ref.so and libsapphire_ref_conv.so, compiled from the
+code (oracle/_ref/libsapphire_ref.so and libsapphire_ref_ops.so, compiled from the
 reference tree by oracle/Makefile).  Run where the reference tree is mounted:
 
     make -C oracle && python tests/golden/make_golden.py
@@ -94,6 +94,20 @@ def broadcast_case(idx):
             rng.standard_normal(bs).astype(np.float32))
 
 
+# (batch, in, out) of the Linear backward unit fixtures
+LINEAR_CASES = [(7, 13, 5), (1, 3, 4), (16, 40, 24), (64, 256, 10)]
+
+
+def linear_case(idx):
+    B, n_in, n_out = LINEAR_CASES[idx]
+    rng = np.random.default_rng(900 + idx)
+    x = rng.uniform(0, 1, (B, n_in)).astype(np.float32)
+    dy = rng.standard_normal((B, n_out)).astype(np.float32)
+    w = rng.standard_normal((n_in, n_out)).astype(np.float32)
+    b = rng.standard_normal(n_out).astype(np.float32)
+    return x, dy, w, b
+
+
 def mlp_reference(steps, impl):
     Ws, bs = W.mlp_init(0)
     net = O.MlpOracle(Ws, bs, 0.01, impl=impl)
@@ -127,7 +141,7 @@ def main():
     print("wrote", os.path.join(HERE, "dense_golden.npz"),
           {k: v.shape for k, v in out.items()})
     # the reference's own host convolution (Convolution.cpp:15-316)
-    assert O.have_ref_conv(), "build oracle/_ref first (make -C oracle)"
+    assert O.have_ref_ops(), "build oracle/_ref first (make -C oracle)"
     conv = {}
     for i in range(len(CONV_CASES)):
         for k, v in conv_outputs(i, "ref").items():
@@ -137,6 +151,11 @@ def main():
     # Compute::Gemm's batch / broadcast rules (BasicOps.cpp:183-248 over the reference's
     # BroadcastWith2Inputs and CPU GEMM)
     bc = {f"case{i}": O.ref_compute_gemm(*broadcast_case(i)) for i in range(len(BROADCAST_CASES))}
+    # LinearBackProp with SGD inside (LinearBackward.cpp:27-99, SGD.cpp:22-28)
+    for i in range(len(LINEAR_CASES)):
+        x, dy, w, b = linear_case(i)
+        dx, w1, b1 = O.ref_linear_backprop(np.zeros_like(x), dy, w, b, x, 0.01)
+        bc[f"linear{i}_dx"], bc[f"linear{i}_w"], bc[f"linear{i}_b"] = dx, w1, b1
     np.savez_compressed(os.path.join(HERE, "broadcast_golden.npz"), **bc)
     print("wrote", os.path.join(HERE, "broadcast_golden.npz"), {k: v.shape for k, v in bc.items()})
 

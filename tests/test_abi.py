@@ -129,7 +129,7 @@ def test_plan_equals_the_reference_broadcast(idx):
     gold = np.load(os.path.join(ROOT, "tests", "golden", "broadcast_golden.npz"))
     got, (y0, a, b) = _run_plan_with_cpu_gemm(idx)
     assert np.array_equal(got.view(np.uint32), gold[f"case{idx}"].view(np.uint32))
-    if O.have_ref_conv():
+    if O.have_ref_ops():
         assert np.array_equal(got.view(np.uint32), O.ref_compute_gemm(y0, a, b).view(np.uint32))
     if idx not in (1, 8):                                # every other family is numpy's broadcast too
         want = y0.astype(np.float64) + np.matmul(a.astype(np.float64), b.astype(np.float64))

@@ -210,8 +210,8 @@ def test_conv_port_matches_golden_from_the_reference(oracle, idx):
 def test_conv_port_equals_reference_build(oracle):
     """Where the reference build is present: the same comparison live, plus a case of the
     benchmark's geometry class (3 x 3 taps, padding 1) too large for a fixture."""
-    if not oracle.have_ref_conv():
-        pytest.skip("oracle/_ref/libsapphire_ref_conv.so not built (reference tree absent)")
+    if not oracle.have_ref_ops():
+        pytest.skip("oracle/_ref/libsapphire_ref_ops.so not built (reference tree absent)")
     mod = _golden_module()
     for idx in range(len(mod.CONV_CASES)):
         ref, port = mod.conv_outputs(idx, "ref"), mod.conv_outputs(idx, "port")
@@ -228,6 +228,27 @@ def test_conv_port_equals_reference_build(oracle):
     a = oracle.conv2d_backward(dx0, df0, dy, x, f, *args)
     b = oracle.conv2d_backward(dx0, df0, dy, x, f, *args, impl="ref")
     assert np.array_equal(_bits(a[0]), _bits(b[0])) and np.array_equal(_bits(a[1]), _bits(b[1]))
+
+
+@pytest.mark.parametrize("idx", range(4))
+def test_linear_backward_unit_matches_the_reference(oracle, idx):
+    """The MLP oracle's layer backward + SGD against the reference's own LinearBackProp
+    unit with its optimizer (Sources/Sapphire/operations/Backward/LinearBackward.cpp:27-99,
+    Sources/Sapphire/operations/optimizers/SGD.cpp:22-28, compiled unmodified): dx with the
+    pre-update weight, dW unscaled, dB scaled by 1/batch, z -= lr dz -- bit for bit
+    against fixtures written by the reference build, and live where it is present."""
+    mod = _golden_module()
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "broadcast_golden.npz"))
+    x, dy, w, b = mod.linear_case(idx)
+    net = oracle.MlpOracle([w], [b], 0.01)
+    dx = net.linear_backward(0, x, dy)
+    assert np.array_equal(_bits(dx), _bits(gold[f"linear{idx}_dx"]))
+    assert np.array_equal(_bits(net.W[0]), _bits(gold[f"linear{idx}_w"]))
+    assert np.array_equal(_bits(net.b[0]), _bits(gold[f"linear{idx}_b"]))
+    if oracle.have_ref_ops():
+        rdx, rw, rb = oracle.ref_linear_backprop(np.zeros_like(x), dy, w, b, x, 0.01)
+        assert np.array_equal(_bits(dx), _bits(rdx)) and np.array_equal(_bits(net.W[0]), _bits(rw))
+        assert np.array_equal(_bits(net.b[0]), _bits(rb))
 
 
 def test_im2col_tap_order_and_padding(oracle):
