@@ -203,8 +203,22 @@ int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA, int trans
  * NaiveBasic.cpp:167-174, ActivationBackwardKernel.cu:11-24).  relu_gate must
  * not overlap D.
  *
+ * sgd_lr (0 = off): the product updates a weight in place instead of being a
+ * gradient that is stored first: D = C - sgd_lr * (op(A) . op(B)), and, where
+ * colsum_out is given, colsum_out[n] = colsum_out[n] - sgd_lr * (colsum_scale *
+ * sum_k op(B)[k, n]).  With A = x (transA), B = dy, C = D = the weight,
+ * colsum_out = the bias and colsum_scale = 1 / batch this is the weight and bias
+ * half of the reference's Linear backward unit with its SGD optimizer inside
+ * (Sources/Sapphire/operations/Backward/LinearBackward.cpp:53-99: dW = x^T . dy
+ * unscaled, dB = (1 / batch) ones . dy;
+ * Sources/Sapphire/operations/optimizers/SGD.cpp:22-28: temp = lr * dz, z = z - temp)
+ * in one launch, with the same two roundings per element (the product times lr,
+ * then the subtraction), so the result equals storing the gradient and running
+ * sb200_sgd_update on it bit for bit.  Requires C; not combined with bias, relu or
+ * relu_gate.
+ *
  * bias, colsum_out and colsum_scale as in sb200_gemm_batched, which is this
- * call with relu = 0 and relu_gate = NULL.
+ * call with relu = 0, relu_gate = NULL and sgd_lr = 0.
  */
 typedef struct sb200_gemm_epilogue {
     const float* bias;
@@ -214,6 +228,7 @@ typedef struct sb200_gemm_epilogue {
     const float* relu_gate;
     int64_t ld_gate;
     int64_t stride_gate;
+    float sgd_lr;
 } sb200_gemm_epilogue;
 
 int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int transA, int transB,

@@ -38,7 +38,7 @@ class GemmEpilogue(C.Structure):
     """Mirror of sb200_gemm_epilogue."""
     _fields_ = [("bias", C.c_void_p), ("colsum_out", C.c_void_p), ("colsum_scale", C.c_float),
                 ("relu", C.c_int), ("relu_gate", C.c_void_p), ("ld_gate", C.c_int64),
-                ("stride_gate", C.c_int64)]
+                ("stride_gate", C.c_int64), ("sgd_lr", C.c_float)]
 
 
 class ConvGeometry(C.Structure):

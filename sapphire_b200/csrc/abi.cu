@@ -208,7 +208,8 @@ namespace {
 // can differ between runs.
 int split_k_slices(const sb200_ctx* ctx, const GemmArgs& g, bool has_colsum)
 {
-    if (g.mode != SB200_MODE_TF32 || g.batch != 1 || g.relu || g.mask || g.bias || has_colsum)
+    if (g.mode != SB200_MODE_TF32 || g.batch != 1 || g.relu || g.mask || g.bias || has_colsum ||
+        g.acc_scale != 1.0f)
         return 1;
     if (g.K % 32)
         return 1;
@@ -258,6 +259,7 @@ extern "C" int sb200_gemm_batched(sb200_ctx* ctx, int mode, int path, int transA
     e.relu_gate = nullptr;
     e.ld_gate = 0;
     e.stride_gate = 0;
+    e.sgd_lr = 0.0f;
     return sb200_gemm_batched_ex(ctx, mode, path, transA, transB, M, N, K, A, lda, strideA, B, ldb, strideB,
                                  C, ldc, strideC, D, ldd, strideD, &e, batch, stream_);
 }
@@ -304,6 +306,9 @@ extern "C" int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int tra
         return SB200_ERR_INVALID_ARG;      // aliasing is exact or not at all
     if (colsum_out && batch != 1)
         return SB200_ERR_INVALID_ARG;
+    const float sgd_lr = epilogue->sgd_lr;
+    if (sgd_lr != 0.0f && (!C || bias || epilogue->relu || gate))
+        return SB200_ERR_INVALID_ARG;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (cudaSetDevice(ctx->device) != cudaSuccess)
@@ -325,6 +330,10 @@ extern "C" int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int tra
     g.strideMask = gate ? epilogue->stride_gate : 0;
     for (int o = 0; o < MAX_OWNERS; ++o) g.owner[o] = nullptr;
     g.rows_per_owner = 0;
+    if (sgd_lr != 0.0f) {
+        g.acc_scale = -sgd_lr;
+        g.colsum_lr = sgd_lr;
+    }
 
     const bool tc_ok = tcgen05_eligible(g);
     int rc;
@@ -359,7 +368,7 @@ extern "C" int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int tra
     if (rc)
         return rc;
     if (colsum_out && !fused_colsum)
-        rc = launch_colsum(ctx, B, g.transB, K, N, ldb, colsum_out, colsum_scale, stream);
+        rc = launch_colsum(ctx, B, g.transB, K, N, ldb, colsum_out, colsum_scale, stream, g.colsum_lr);
     return rc;
 }
 

@@ -47,6 +47,10 @@ struct GemmArgs {
     // instead of being stored to D; rows_per_owner == 0 switches it off
     float* owner[8];
     int64_t rows_per_owner;
+    // in-place SGD: the accumulator is multiplied by acc_scale (= -lr; 1 = off) before C is
+    // added, and the column sums update colsum_out: out -= colsum_lr * (colsum_scale * sum)
+    float acc_scale = 1.0f;
+    float colsum_lr = 0.0f;
 };
 constexpr int MAX_OWNERS = 8;
 
@@ -123,8 +127,9 @@ int k_slices(const sb200_ctx* ctx, const GemmArgs& g);
 int launch_gemm_tcgen05_slices(sb200_ctx* ctx, const GemmArgs& g, int split, cudaStream_t stream);
 // gemm_simt.cu
 int launch_gemm_simt(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream);
+// lr != 0: out[n] -= lr * (scale * sum) instead of out[n] = scale * sum
 int launch_colsum(sb200_ctx* ctx, const float* B, int transB, int64_t K, int64_t N, int64_t ldb,
-                  float* out, float scale, cudaStream_t stream);
+                  float* out, float scale, cudaStream_t stream, float lr = 0.0f);
 // workspace (abi.cu)
 int ensure_workspace(sb200_ctx* ctx, size_t bytes);
 

@@ -39,6 +39,9 @@ struct KernelParams {
     unsigned long long wait_limit_ns;           // bound of every mbarrier wait
     int test_stall_kb;                          // >= 0: the TMA producer stops after this many k-blocks
                                                 // (test hook: every other role's wait then runs out)
+    float acc_scale;                            // accumulator times this before C is added (1 = off;
+                                                // -lr: D = C - lr * product, the in-place SGD update)
+    float colsum_lr;                            // != 0: colsum_out[n] -= colsum_lr * (colsum_scale * sum)
 };
 
 // What the epilogue does with an accumulator: D = post((C + bias) + acc), where
@@ -450,12 +453,21 @@ __device__ __forceinline__ void colsum_accumulate(const uint8_t* sb, int tid, fl
     }
 }
 
+// What a finished column sum does to out[n]: store scale * sum, or, for the in-place SGD
+// update of a bias, subtract lr times that (each product rounded on its own).
+__device__ __forceinline__ void colsum_store(float* out, float sum, float scale, float lr)
+{
+    const float g = __fmul_rn(sum, scale);
+    *out = lr != 0.0f ? __fsub_rn(*out, __fmul_rn(g, lr)) : g;
+}
+
 // Combines the threads' partial sums and writes scale * sum for columns
 // [n0, n0 + NCOLS) below N.  `scratch`: COLSUM_SCRATCH_BYTES of shared memory.
 // Uses named barrier 1 among the 128 column-sum threads.
+
 template <bool B_MN, int NCOLS>
 __device__ __forceinline__ void colsum_finish(float4 acc4, float* scratch, int tid, float* out,
-                                              float scale, int n0, int N)
+                                              float scale, int n0, int N, float lr)
 {
     if (B_MN) {
         constexpr int UNITS = NCOLS / 4;
@@ -473,13 +485,13 @@ __device__ __forceinline__ void colsum_finish(float4 acc4, float* scratch, int t
             const float v[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-                if (col + e < N) out[col + e] = v[e] * scale;
+                if (col + e < N) colsum_store(out + col + e, v[e], scale, lr);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
     } else {
-        if (tid < NCOLS && n0 + tid < N) out[n0 + tid] = acc4.x * scale;
+        if (tid < NCOLS && n0 + tid < N) colsum_store(out + n0 + tid, acc4.x, scale, lr);
         if (NCOLS > COLSUM_THREADS && n0 + tid + COLSUM_THREADS < N)
-            out[n0 + tid + COLSUM_THREADS] = acc4.y * scale;
+            colsum_store(out + n0 + tid + COLSUM_THREADS, acc4.y, scale, lr);
     }
 }
 

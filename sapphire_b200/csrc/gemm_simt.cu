@@ -36,6 +36,7 @@ struct SimtParams {
     const float* bias;
     int relu;                                    // D = D > 0 ? D : 0
     const float* mask; long long ldm, strideM;   // gate matrix or null: D = mask > 0 ? D : 0
+    float acc_scale;                             // product times this before C is added (1 = off)
 };
 
 template <int TM, int TN, int TK>
@@ -148,7 +149,7 @@ gemm_simt_kernel(const SimtParams p)
             if (n >= p.N) continue;
             float base = C ? C[m * p.ldc + n] : 0.0f;
             if (p.bias) base = __fadd_rn(base, p.bias[n]);
-            float o = __fadd_rn(base, acc[i][j]);
+            float o = __fadd_rn(base, p.acc_scale != 1.0f ? __fmul_rn(acc[i][j], p.acc_scale) : acc[i][j]);
             if (p.relu) o = o > 0.0f ? o : 0.0f;
             if (G) o = __fadd_rn(0.0f, G[m * p.ldm + n] > 0.0f ? o : 0.0f);
             D[m * p.ldd + n] = o;
@@ -177,13 +178,14 @@ colsum_partial_kernel(const float* __restrict__ B, int transB, long long K, long
 
 __global__ void __launch_bounds__(128)
 colsum_final_kernel(const float* __restrict__ partial, int slices, long long N, float scale,
-                    float* __restrict__ out)
+                    float* __restrict__ out, float lr)
 {
     const long long n = static_cast<long long>(blockIdx.x) * 128 + threadIdx.x;
     if (n >= N) return;
     float s = 0.0f;
     for (int i = 0; i < slices; ++i) s = __fadd_rn(s, partial[static_cast<long long>(i) * N + n]);
-    out[n] = __fmul_rn(s, scale);
+    const float g = __fmul_rn(s, scale);
+    out[n] = lr != 0.0f ? __fsub_rn(out[n], __fmul_rn(g, lr)) : g;     // lr: in-place SGD update of a bias
 }
 
 }  // namespace
@@ -216,6 +218,7 @@ int launch_gemm_simt(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.bias = g.bias;
     p.relu = g.relu;
     p.mask = g.mask; p.ldm = g.ldmask; p.strideM = g.strideMask;
+    p.acc_scale = g.acc_scale;
     dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy), static_cast<unsigned>(g.batch));
     if (small)
         gemm_simt_kernel<16, 16, 64><<<grid, 256, 0, stream>>>(p);      // always a few CTAs
@@ -242,21 +245,30 @@ int colsum_slices(int sm_count, int64_t K, int64_t N)
     return static_cast<int>(want);
 }
 
-int launch_colsum_with_scratch(sb200_ctx* ctx, const float* B, int transB, int64_t K, int64_t N,
-                               int64_t ldb, float* out, float scale, float* scratch, int slices,
-                               cudaStream_t stream)
+namespace {
+int launch_colsum_kernels(sb200_ctx* ctx, const float* B, int transB, int64_t K, int64_t N,
+                          int64_t ldb, float* out, float scale, float* scratch, int slices,
+                          cudaStream_t stream, float lr)
 {
     const int64_t rows_per_slice = (K + slices - 1) / slices;
     dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(slices));
     colsum_partial_kernel<<<grid, 128, 0, stream>>>(B, transB, K, N, ldb, rows_per_slice, scratch);
     colsum_final_kernel<<<static_cast<unsigned>((N + 127) / 128), 128, 0, stream>>>(
-        scratch, slices, N, scale, out);
+        scratch, slices, N, scale, out, lr);
     if (ctx) ctx->launches += 2;
     return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
+}  // namespace
+
+int launch_colsum_with_scratch(sb200_ctx* ctx, const float* B, int transB, int64_t K, int64_t N,
+                               int64_t ldb, float* out, float scale, float* scratch, int slices,
+                               cudaStream_t stream)
+{
+    return launch_colsum_kernels(ctx, B, transB, K, N, ldb, out, scale, scratch, slices, stream, 0.0f);
+}
 
 int launch_colsum(sb200_ctx* ctx, const float* B, int transB, int64_t K, int64_t N, int64_t ldb,
-                  float* out, float scale, cudaStream_t stream)
+                  float* out, float scale, cudaStream_t stream, float lr)
 {
     if (N <= 0)
         return SB200_OK;
@@ -264,8 +276,7 @@ int launch_colsum(sb200_ctx* ctx, const float* B, int transB, int64_t K, int64_t
     const int rc = ensure_workspace(ctx, static_cast<size_t>(slices) * N * sizeof(float));
     if (rc)
         return rc;
-    return launch_colsum_with_scratch(ctx, B, transB, K, N, ldb, out, scale, ctx->d_workspace,
-                                      slices, stream);
+    return launch_colsum_kernels(ctx, B, transB, K, N, ldb, out, scale, ctx->d_workspace, slices, stream, lr);
 }
 
 }  // namespace sb200

@@ -358,6 +358,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                             load_c_chunk(c_next, cmat, p.ldc, m0 + q * 32, col0 + 32, p.M, p.N);
                     }
                     ptx::tmem_ld_wait();
+                    if (p.acc_scale != 1.0f) {             // in-place SGD: D = C + (-lr) * product
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            v[j] = __float_as_uint(__fmul_rn(__uint_as_float(v[j]), p.acc_scale));
+                    }
                     if (vec_ok)
                         store_chunk_coalesced(v, my_stage, dmat, p.ldd, c_now, epi, m0 + q * 32,
                                               col0, p.M, p.N);
@@ -414,7 +419,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                         uint32_t v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            v[j] = __float_as_uint(sum[c * 32 + j]);
+                            v[j] = __float_as_uint(p.acc_scale != 1.0f ? __fmul_rn(sum[c * 32 + j], p.acc_scale)
+                                                                       : sum[c * 32 + j]);
                         // one store per tile after many chunk drains: the plain row
                         // store keeps this path's register count down
                         if (row < p.M)
@@ -565,7 +571,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
                     break;
                 if (mine)
                     colsum_finish<B_MN, BLOCK_N>(acc4, colsum_scratch, tid, p.colsum_out,
-                                                 p.colsum_scale, n0, p.N);
+                                                 p.colsum_scale, n0, p.N, p.colsum_lr);
             }
         }
     }
@@ -645,6 +651,8 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.explicit_hi = ctx->split_explicit_hi;
     p.colsum_out = COLSUM ? g.colsum_out : nullptr;
     p.colsum_scale = g.colsum_scale;
+    p.acc_scale = g.acc_scale;
+    p.colsum_lr = COLSUM ? g.colsum_lr : 0.0f;
 
     const long long grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
     // programmatic stream serialization: the kernel's prologue may start while the

@@ -366,6 +366,8 @@ int launch_pair_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.test_stall_kb = ctx->test_stall_kb;
     p.explicit_hi = 0;
     p.colsum_out = nullptr;
+    p.acc_scale = 1.0f;
+    p.colsum_lr = 0.0f;
     p.colsum_scale = 0.0f;
 
     // a persistent grid must be fully co-resident: ask how many pairs fit at once
@@ -412,7 +414,7 @@ bool pair_kernel_preferred(const sb200_ctx* ctx, const GemmArgs& g)
     // Fused column sums need a "stage filled" signal inside the CTA that holds the
     // B tile; in a pair that barrier lives in the leader only, so such requests
     // stay on the one-CTA kernel.
-    if (g.colsum_out)
+    if (g.colsum_out || g.acc_scale != 1.0f)           // (the in-place SGD epilogue likewise)
         return false;
     if (g.M < 2 * PAIR_M || g.N < PAIR_N)
         return false;

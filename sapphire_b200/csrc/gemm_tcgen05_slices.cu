@@ -335,6 +335,8 @@ int launch_slices_variant(sb200_ctx* ctx, const GemmArgs& g, int split, cudaStre
     p.explicit_hi = 0;
     p.colsum_out = nullptr;
     p.colsum_scale = 0.0f;
+    p.acc_scale = 1.0f;
+    p.colsum_lr = 0.0f;
     const int kb_per_cta = (p.num_kb + split - 1) / split;
 
     if (p.total_tiles > SLICE_TICKETS)
@@ -373,7 +375,8 @@ constexpr int SL_MAX_SPLIT = 8;
 // (few tiles), without column sums or row-block owners.
 int k_slices(const sb200_ctx* ctx, const GemmArgs& g)
 {
-    if (!ctx->k_slices || g.mode != SB200_MODE_TF32 || g.colsum_out || g.rows_per_owner)
+    if (!ctx->k_slices || g.mode != SB200_MODE_TF32 || g.colsum_out || g.rows_per_owner ||
+        g.acc_scale != 1.0f)
         return 1;
     const long long num_kb = (g.K + BLOCK_K - 1) / BLOCK_K;
     const long long tiles = ((g.M + BLOCK_M - 1) / BLOCK_M) * ((g.N + SL_BLOCK_N - 1) / SL_BLOCK_N) * g.batch;

@@ -100,7 +100,7 @@ def prepare_gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[tor
                  trans_b: bool = False, bias: Optional[torch.Tensor] = None,
                  colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0,
                  path: int = L.PATH_AUTO, relu: bool = False,
-                 relu_gate: Optional[torch.Tensor] = None) -> PreparedCall:
+                 relu_gate: Optional[torch.Tensor] = None, sgd_lr: float = 0.0) -> PreparedCall:
     """The call `gemm` would make, as a `PreparedCall` (result: ``out``)."""
     ba, ra, ca, lda, sa = _mat_geometry(a)
     bb, rb, cb, ldb, sb = _mat_geometry(b)
@@ -138,8 +138,9 @@ def prepare_gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[tor
             a.data_ptr(), lda, sa if ba == batch and batch > 1 else 0,
             b.data_ptr(), ldb, sb if bb == batch and batch > 1 else 0,
             cptr, ldc, sc, out.data_ptr(), ldd, sd)
-    if relu or relu_gate is not None:
+    if relu or relu_gate is not None or sgd_lr:
         e = L.GemmEpilogue()
+        e.sgd_lr = float(sgd_lr)
         e.bias = bias.data_ptr() if bias is not None else None
         e.colsum_out = colsum_out.data_ptr() if colsum_out is not None else None
         e.colsum_scale = float(colsum_scale)
@@ -165,18 +166,21 @@ def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tenso
          trans_b: bool = False, bias: Optional[torch.Tensor] = None,
          colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0,
          path: int = L.PATH_AUTO, relu: bool = False,
-         relu_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+         relu_gate: Optional[torch.Tensor] = None, sgd_lr: float = 0.0) -> torch.Tensor:
     """out = gate(relu((c + bias) + op(a).op(b))), batched over a leading dimension.
 
     ``c`` may be ``out`` itself (in-place accumulate, Sapphire's
     ``y <- y + a.b``).  A tensor with batch extent 1 (or 2-D) is shared by all
     batches.  ``relu`` applies x > 0 ? x : 0 to the result; ``relu_gate`` (the
     output's shape) zeroes the result where the gate is not positive, the
-    backward pass of a ReLU.  Returns ``out``.
+    backward pass of a ReLU.  ``sgd_lr`` (non-zero) turns the call into an in-place
+    SGD update: out = c - sgd_lr * op(a).op(b) and colsum_out -= sgd_lr *
+    (colsum_scale * column sums of op(b)) -- a Linear layer's weight and bias updated
+    by their gradients without storing them.  Returns ``out``.
     """
     return prepare_gemm(ctx, a, b, c, out, mode=mode, trans_a=trans_a, trans_b=trans_b, bias=bias,
                         colsum_out=colsum_out, colsum_scale=colsum_scale, path=path, relu=relu,
-                        relu_gate=relu_gate)()
+                        relu_gate=relu_gate, sgd_lr=sgd_lr)()
 
 
 def gemm_reduce_scatter(ctx: Context, a: torch.Tensor, b: torch.Tensor, owners, ld_out: int, *,

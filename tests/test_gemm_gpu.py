@@ -606,6 +606,49 @@ def test_compat_compute_gemm_broadcast_families(ctx, idx):
     assert rel_fro(ty.cpu().numpy(), want) <= 1e-5
 
 
+@pytest.mark.parametrize("mode", [L.MODE_TF32, L.MODE_TF32X3])
+@pytest.mark.parametrize("B,n_in,n_out,path", [(64, 784, 512, L.PATH_AUTO), (64, 256, 12, L.PATH_AUTO),
+                                               (16, 40, 24, L.PATH_AUTO), (7, 13, 5, L.PATH_SIMT),
+                                               (512, 1024, 768, L.PATH_AUTO)])
+def test_in_place_sgd_update_of_a_linear_layer(ctx, oracle, mode, B, n_in, n_out, path):
+    """sgd_lr: W -= lr * x^T.dy and b -= lr * (1/B) colsum(dy) in one launch -- the weight
+    and bias half of the reference's LinearBackProp with its SGD optimizer inside.
+    Bit-identical to storing the gradients and running the SGD kernel on them (the
+    same two roundings per element), and within the mode's tolerance of the CPU oracle's
+    unit, which is itself pinned against the reference's."""
+    rng = np.random.default_rng(B + n_in + n_out)
+    x = rng.uniform(0, 1, (B, n_in)).astype(np.float32)
+    dy = rng.standard_normal((B, n_out)).astype(np.float32)
+    w = rng.standard_normal((n_in, n_out)).astype(np.float32)
+    b = rng.standard_normal(n_out).astype(np.float32)
+    lr = 0.01
+    tx, tdy = dev(x), dev(dy)
+    # gradients stored, then the SGD kernel
+    dw, db = torch.empty(n_in, n_out, device=DEV), torch.empty(n_out, device=DEV)
+    ops.gemm(ctx, tx, tdy, None, dw, trans_a=True, colsum_out=db, colsum_scale=1.0 / B, mode=mode, path=path)
+    w_two, b_two = dev(w), dev(b)
+    ops.sgd_update(ctx, w_two, dw, lr)
+    ops.sgd_update(ctx, b_two, db, lr)
+    # the same in one launch, in place
+    w_one, b_one = dev(w), dev(b)
+    ops.gemm(ctx, tx, tdy, w_one, w_one, trans_a=True, colsum_out=b_one, colsum_scale=1.0 / B, mode=mode,
+             path=path, sgd_lr=lr)
+    ctx.check_device_status()
+    assert torch.equal(w_one, w_two) and torch.equal(b_one, b_two)
+    net = oracle.MlpOracle([w], [b], lr)
+    net.linear_backward(0, x, dy)
+    # the update is lr * gradient on top of an O(1) weight: compare the steps taken
+    step_w, step_b = w - net.W[0], b - net.b[0]
+    tol = 1e-5 if (mode == L.MODE_TF32X3 or path == L.PATH_SIMT) else 2e-3
+    assert rel_fro(w - w_one.cpu().numpy(), step_w) <= tol + 1e-4     # (+ the rounding of w - lr g itself)
+    assert rel_fro(b - b_one.cpu().numpy(), step_b) <= tol + 1e-4
+    # argument rules: needs C, no bias / relu / gate next to it
+    with pytest.raises(L.Sb200Error):
+        ops.gemm(ctx, tx, tdy, None, w_one, trans_a=True, sgd_lr=lr)
+    with pytest.raises(L.Sb200Error):
+        ops.gemm(ctx, tx, tdy, w_one, w_one, trans_a=True, sgd_lr=lr, relu=True)
+
+
 def test_invalid_arguments(ctx):
     a = torch.zeros(4, 8, device=DEV)
     b = torch.zeros(8, 4, device=DEV)
