@@ -118,6 +118,10 @@ int64_t sb200_ctx_counter(const sb200_ctx* ctx, int which);
  *       k; the CTA of a tile that finishes last adds the partial tiles in slice
  *       order (bit-reproducible) and runs the epilogue.  0: one CTA per tile.
  *       2 .. 16: that many slices whenever the request is eligible (tests, tuning).
+ *   SB200_OPT_SPLIT_A_TMEM  (TF32X3 mode) 1, the default: when A is stored
+ *       [M, K] the high and low parts of its tiles are written to tensor memory
+ *       and the tensor core reads them from there; 0: both low parts go to
+ *       shared memory, as they always do for a transposed A.  Same results.
  *   SB200_OPT_SPGEMM_FAST_MID  1, the default: sparse products with at most 65536
  *       columns run their mid-sized rows (33 .. 16383 scalar products) on the kernels
  *       specialised for that width; 0: on the general row kernel (any width).
