@@ -388,7 +388,7 @@ def main():
     ap.add_argument("--per-gpu-batch", type=int, default=0,
                     help="dense workloads: every rank gets this many batches of its own (weak "
                          "scaling) instead of its share of the global batch of 8")
-    ap.add_argument("--linear-bwd-comm", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--linear-bwd-comm", default="fused", choices=["fused", "fused_store", "nccl"],
                     help="how the linear_bwd workload sums dW over ranks (see bench_linear_bwd)")
     ap.add_argument("--mlp-comm", default="peer", choices=["peer", "nccl"],
                     help="how the mlp workload sums its gradients over ranks (see bench_mlp)")
@@ -617,7 +617,10 @@ def main():
                    NVLink from its epilogue (GEMM + reduce-scatter in one kernel),
                    one tiny all-reduce as barrier, then every rank pulls the reduced
                    row blocks from the owners' windows with copy-engine transfers
-                   while the dx GEMM runs (runner.FusedWeightGradient);
+                   while the dx GEMM runs (runner.FusedWeightGradient, route "add");
+          "fused_store"  the tiles are stored into this rank's slot of the owner's
+                   window instead, the owner adds its slots in fixed order (a
+                   bit-reproducible sum), second barrier, same gather (route "store");
           "nccl"   plain GEMM, then an NCCL all-reduce of dW that overlaps the dx GEMM.
         With several ranks the fused dW is checked against the NCCL route once,
         outside the timed region."""
@@ -633,10 +636,11 @@ def main():
         db = torch.empty(width, device=dev)
         comm = torch.cuda.Stream(dev) if world > 1 else None
         done = torch.cuda.Event() if world > 1 else None
-        fused = world > 1 and comm_mode == "fused" and width % (world * 128) == 0
+        fused = world > 1 and comm_mode in ("fused", "fused_store") and width % (world * 128) == 0
         reducer = None
         if fused:
-            reducer = R.FusedWeightGradient(ctx, width, width, rank, world)
+            reducer = R.FusedWeightGradient(ctx, width, width, rank, world,
+                                            route="add" if comm_mode == "fused" else "store")
             if not reducer.ok:                           # agreed across ranks: all fall back together
                 reducer.close()
                 reducer, fused = None, False
@@ -679,8 +683,11 @@ def main():
         flops = 2 * 2.0 * total_rows * width * width
         label = f"linear backward dY[8192x4096] X[8192x4096] W[4096x4096], rows sharded x{world}"
         if world > 1:
-            label += (", dW reduce-scatter fused into the GEMM epilogue (peer adds) + "
-                      "copy-engine gather" if fused else ", dW/dB NCCL allreduce overlapped with the dx GEMM")
+            label += ((", dW reduce-scatter fused into the GEMM epilogue (peer adds) + copy-engine gather"
+                       if comm_mode == "fused" else
+                       ", dW tiles stored into the owners' slots from the GEMM epilogue, slots summed in "
+                       "fixed order, copy-engine gather")
+                      if fused else ", dW/dB NCCL allreduce overlapped with the dx GEMM")
         out = {"workload": label, "ms_per_step": ms, "tflops_total": flops / ms / 1e9,
                "gpu_launches": launches}
         if check:

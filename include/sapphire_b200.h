@@ -274,6 +274,29 @@ int sb200_gemm_reduce_scatter(sb200_ctx* ctx, int mode, int transA, int transB,
                               float* colsum_out, float colsum_scale, sb200_stream stream);
 
 /*
+ * The same product with its row blocks STORED, not added: block o goes to owners[o]
+ * with plain 16-byte stores (full NVLink write rate; fp32 reductions over the links
+ * run at a fraction of it).  Each rank passes, for owner o, the address of ITS OWN
+ * slot in rank o's buffer (slot index = this rank), so nothing needs zeroing and
+ * nothing collides; after a barrier the owner adds its n slots with sb200_sum_blocks
+ * in slot order -- a fixed order, so the summed gradient is bit-reproducible, which
+ * the adds of sb200_gemm_reduce_scatter (arrival order) are not.
+ */
+int sb200_gemm_scatter(sb200_ctx* ctx, int mode, int transA, int transB,
+                       int64_t M, int64_t N, int64_t K,
+                       const float* A, int64_t lda, const float* B, int64_t ldb,
+                       float* const* owners, int n_owners, int64_t ld_out,
+                       float* colsum_out, float colsum_scale, sb200_stream stream);
+
+/* out[r, c] = blocks[0][r, c] + blocks[1][r, c] + ... + blocks[n_blocks - 1][r, c] (fp32
+ * adds in that order) for an [rows, cols] region; block b starts block_stride floats
+ * after block b - 1; out may be blocks[0].  cols, the leading dimensions and the
+ * stride multiples of 4, 16-byte aligned pointers (SB200_ERR_UNSUPPORTED otherwise). */
+int sb200_sum_blocks(sb200_ctx* ctx, float* out, int64_t ld_out, const float* blocks, int n_blocks,
+                     int64_t block_stride, int64_t rows, int64_t cols, int64_t ld_block,
+                     sb200_stream stream);
+
+/*
  * Device buffers that other processes on the node map into their address space
  * (CUDA IPC): sb200_peer_alloc allocates one and fills a 64-byte handle to send
  * to the other ranks (any byte transport), sb200_peer_open maps a received

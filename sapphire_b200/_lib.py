@@ -96,6 +96,12 @@ SIGNATURES = {
         C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64,
         C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
         C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_void_p, C.c_float, C.c_void_p]),
+    "sb200_gemm_scatter": (C.c_int, [
+        C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64,
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+        C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_void_p, C.c_float, C.c_void_p]),
+    "sb200_sum_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
+                                   C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "sb200_dp_reduce": (C.c_int, [C.c_void_p, C.POINTER(DpGroup), C.c_int64, C.c_void_p]),
     "sb200_dp_update": (C.c_int, [C.c_void_p, C.POINTER(DpGroup), C.c_void_p, C.c_int64, C.c_int64,
                                   C.c_float, C.c_void_p]),

@@ -373,13 +373,13 @@ extern "C" int sb200_gemm_batched_ex(sb200_ctx* ctx, int mode, int path, int tra
 }
 
 // ------------------------------------------------- GEMM -> reduce-scatter
-extern "C" int sb200_gemm_reduce_scatter(sb200_ctx* ctx, int mode, int transA, int transB,
-                                         int64_t M, int64_t N, int64_t K,
-                                         const float* A, int64_t lda, const float* B, int64_t ldb,
-                                         float* const* owners, int n_owners, int64_t ld_out,
-                                         float* colsum_out, float colsum_scale, sb200_stream stream_)
+namespace {
+int gemm_to_owners(sb200_ctx* ctx, int mode, int transA, int transB, int64_t M, int64_t N, int64_t K,
+                   const float* A, int64_t lda, const float* B, int64_t ldb, float* const* owners,
+                   int n_owners, int64_t ld_out, float* colsum_out, float colsum_scale,
+                   sb200_stream stream_, int store)
 {
-    TraceRange trace("sb200_gemm_reduce_scatter");
+    TraceRange trace(store ? "sb200_gemm_scatter" : "sb200_gemm_reduce_scatter");
     if (!ctx || !owners || !A || !B)
         return SB200_ERR_INVALID_ARG;
     if (mode != SB200_MODE_TF32 && mode != SB200_MODE_TF32X3)
@@ -413,6 +413,7 @@ extern "C" int sb200_gemm_reduce_scatter(sb200_ctx* ctx, int mode, int transA, i
     g.mask = nullptr; g.ldmask = 0; g.strideMask = 0;
     for (int o = 0; o < MAX_OWNERS; ++o) g.owner[o] = o < n_owners ? owners[o] : nullptr;
     g.rows_per_owner = M / n_owners;
+    g.owner_store = store;
     if (!tcgen05_eligible(g))
         return SB200_ERR_UNSUPPORTED;                           // the CUDA-core kernel has no such epilogue
     const bool fused_colsum = colsum_out && mode == SB200_MODE_TF32;
@@ -425,6 +426,72 @@ extern "C" int sb200_gemm_reduce_scatter(sb200_ctx* ctx, int mode, int transA, i
     if (colsum_out && !fused_colsum)
         rc = launch_colsum(ctx, B, g.transB, K, N, ldb, colsum_out, colsum_scale, stream);
     return rc;
+}
+
+// out[r, c] = blocks[0][r, c] + blocks[1][r, c] + ... in that order
+__global__ void __launch_bounds__(256)
+sum_blocks_kernel(float* __restrict__ out, long long ld_out, const float* blocks, int n_blocks,
+                  long long block_stride, long long rows, long long cols4, long long ld_block)
+{
+    const long long total = rows * cols4;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / cols4, c = (i % cols4) * 4;
+        const float* src = blocks + r * ld_block + c;
+        float4 s = *reinterpret_cast<const float4*>(src);
+        for (int b = 1; b < n_blocks; ++b) {
+            const float4 x = *reinterpret_cast<const float4*>(src + b * block_stride);
+            s.x = __fadd_rn(s.x, x.x); s.y = __fadd_rn(s.y, x.y);
+            s.z = __fadd_rn(s.z, x.z); s.w = __fadd_rn(s.w, x.w);
+        }
+        *reinterpret_cast<float4*>(out + r * ld_out + c) = s;      // (out may be blocks[0] itself)
+    }
+}
+}  // namespace
+
+extern "C" int sb200_gemm_reduce_scatter(sb200_ctx* ctx, int mode, int transA, int transB,
+                                         int64_t M, int64_t N, int64_t K,
+                                         const float* A, int64_t lda, const float* B, int64_t ldb,
+                                         float* const* owners, int n_owners, int64_t ld_out,
+                                         float* colsum_out, float colsum_scale, sb200_stream stream_)
+{
+    return gemm_to_owners(ctx, mode, transA, transB, M, N, K, A, lda, B, ldb, owners, n_owners, ld_out,
+                          colsum_out, colsum_scale, stream_, 0);
+}
+
+extern "C" int sb200_gemm_scatter(sb200_ctx* ctx, int mode, int transA, int transB,
+                                  int64_t M, int64_t N, int64_t K,
+                                  const float* A, int64_t lda, const float* B, int64_t ldb,
+                                  float* const* owners, int n_owners, int64_t ld_out,
+                                  float* colsum_out, float colsum_scale, sb200_stream stream_)
+{
+    return gemm_to_owners(ctx, mode, transA, transB, M, N, K, A, lda, B, ldb, owners, n_owners, ld_out,
+                          colsum_out, colsum_scale, stream_, 1);
+}
+
+extern "C" int sb200_sum_blocks(sb200_ctx* ctx, float* out, int64_t ld_out, const float* blocks, int n_blocks,
+                                int64_t block_stride, int64_t rows, int64_t cols, int64_t ld_block,
+                                sb200_stream stream_)
+{
+    if (!ctx || !out || !blocks || n_blocks < 1 || rows < 0 || cols < 0)
+        return SB200_ERR_INVALID_ARG;
+    if (ld_out < cols || ld_block < cols || block_stride < 0)
+        return SB200_ERR_INVALID_ARG;
+    if ((cols & 3) || (ld_out & 3) || (ld_block & 3) || (block_stride & 3) ||
+        (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(blocks) & 15))
+        return SB200_ERR_UNSUPPORTED;
+    if (rows == 0 || cols == 0)
+        return SB200_OK;
+    if (cudaSetDevice(ctx->device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    const long long total = rows * (cols / 4);
+    long long grid = (total + 255) / 256;
+    if (grid > 8ll * ctx->sm_count)
+        grid = 8ll * ctx->sm_count;
+    sum_blocks_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+        out, ld_out, blocks, n_blocks, block_stride, rows, cols / 4, ld_block);
+    ctx->launches += 1;
+    return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
 }
 
 // ------------------------------------------------- buffers other ranks map

@@ -47,6 +47,7 @@ struct GemmArgs {
     // instead of being stored to D; rows_per_owner == 0 switches it off
     float* owner[8];
     int64_t rows_per_owner;
+    int owner_store = 0;       // 1: blocks are STORED to owner[o] (a slot per source rank), not added
     // in-place SGD: the accumulator is multiplied by acc_scale (= -lr; 1 = off) before C is
     // added, and the column sums update colsum_out: out -= colsum_lr * (colsum_scale * sum)
     float acc_scale = 1.0f;

@@ -36,6 +36,7 @@ struct KernelParams {
     const float* mask; long long ldm, strideM;  // ReLU-backward gate matrix or null
     float* owner[MAX_OWNERS];                   // reduce-scatter epilogue: row-block owners' buffers
     int rows_per_owner;                         // 0: plain store to D
+    int owner_store;                            // with owners: store the tile instead of adding it
     unsigned long long wait_limit_ns;           // bound of every mbarrier wait
     int test_stall_kb;                          // >= 0: the TMA producer stops after this many k-blocks
                                                 // (test hook: every other role's wait then runs out)

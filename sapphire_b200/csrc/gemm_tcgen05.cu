@@ -332,7 +332,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA,
             const float* crow = cmat ? cmat + static_cast<long long>(row) * p.ldc : nullptr;
             float* my_stage = epi_stage + q * (EPI_STAGE_BYTES_PER_WARP / 4);
             const Epilogue epi{p.bias, p.mask ? p.mask + b * p.strideM : nullptr, p.ldm, p.relu,
-                               p.rows_per_owner != 0};
+                               p.rows_per_owner != 0 && !p.owner_store};
             const float* mrow = epi.mask ? epi.mask + static_cast<long long>(row) * p.ldm : nullptr;
             if constexpr (!SPLIT) {
                 // one chunk per tile: straight from TMEM to global memory.  The first
@@ -645,6 +645,7 @@ int launch_variant(sb200_ctx* ctx, const GemmArgs& g, cudaStream_t stream)
     p.mask = g.mask; p.ldm = g.ldmask; p.strideM = g.strideMask;
     for (int o = 0; o < MAX_OWNERS; ++o) p.owner[o] = g.owner[o];
     p.rows_per_owner = static_cast<int>(g.rows_per_owner);
+    p.owner_store = g.owner_store;
     p.status = ctx->d_status;
     p.wait_limit_ns = ctx->wait_limit_ns;
     p.test_stall_kb = ctx->test_stall_kb;

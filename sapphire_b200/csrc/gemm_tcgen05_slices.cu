@@ -329,6 +329,7 @@ int launch_slices_variant(sb200_ctx* ctx, const GemmArgs& g, int split, cudaStre
     p.mask = g.mask; p.ldm = g.ldmask; p.strideM = g.strideMask;
     for (int o = 0; o < MAX_OWNERS; ++o) p.owner[o] = nullptr;
     p.rows_per_owner = 0;
+    p.owner_store = 0;
     p.status = ctx->d_status;
     p.wait_limit_ns = ctx->wait_limit_ns;
     p.test_stall_kb = ctx->test_stall_kb;

@@ -185,9 +185,11 @@ def gemm(ctx: Context, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tenso
 
 def gemm_reduce_scatter(ctx: Context, a: torch.Tensor, b: torch.Tensor, owners, ld_out: int, *,
                         mode: int = L.MODE_TF32, trans_a: bool = False, trans_b: bool = False,
-                        colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0) -> None:
+                        colsum_out: Optional[torch.Tensor] = None, colsum_scale: float = 1.0,
+                        store: bool = False) -> None:
     """op(a).op(b) with row block o of the product added into the buffer at
-    device address ``owners[o]`` (see ``sb200_gemm_reduce_scatter``)."""
+    device address ``owners[o]`` (see ``sb200_gemm_reduce_scatter``), or, with
+    ``store``, stored there (``sb200_gemm_scatter``)."""
     _, ra, ca, lda, _ = _mat_geometry(a)
     _, rb, cb, ldb, _ = _mat_geometry(b)
     M, K = (ca, ra) if trans_a else (ra, ca)
@@ -195,10 +197,21 @@ def gemm_reduce_scatter(ctx: Context, a: torch.Tensor, b: torch.Tensor, owners, 
     if K != K2:
         raise ValueError(f"inner dimensions differ: {K} vs {K2}")
     arr = (C.c_void_p * len(owners))(*[int(p) for p in owners])
-    L.check("sb200_gemm_reduce_scatter", L.lib().sb200_gemm_reduce_scatter(
+    name = "sb200_gemm_scatter" if store else "sb200_gemm_reduce_scatter"
+    L.check(name, getattr(L.lib(), name)(
         ctx.handle, mode, int(trans_a), int(trans_b), M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
         arr, len(owners), int(ld_out), colsum_out.data_ptr() if colsum_out is not None else None,
         float(colsum_scale), _stream_ptr(ctx.device)))
+
+
+def sum_blocks(ctx: Context, out: torch.Tensor, blocks: torch.Tensor) -> torch.Tensor:
+    """out [rows, cols] = blocks[0] + blocks[1] + ... (``blocks``: [n, rows, cols], fp32 adds
+    in that order; ``out`` may be ``blocks[0]``)."""
+    n, rows, cols = blocks.shape
+    L.check("sb200_sum_blocks", L.lib().sb200_sum_blocks(
+        ctx.handle, out.data_ptr(), out.stride(0), blocks.data_ptr(), n, blocks.stride(0), rows, cols,
+        blocks.stride(1), _stream_ptr(ctx.device)))
+    return out
 
 
 # --------------------------------------------------------------------- sparse

@@ -77,7 +77,7 @@ def test_dp_mlp_two_gpus_matches_single_process_oracle(tmp_path, comm):
     assert np.array_equal(got[0].view(np.uint32), got[1].view(np.uint32))
 
 
-def _rs_worker(rank, world, port, out_dir):
+def _rs_worker(rank, world, port, out_dir, route):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world),
                       RANK=str(rank), LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
@@ -89,7 +89,7 @@ def _rs_worker(rank, world, port, out_dir):
     ctx = ops.Context(rank)
     rows, n_in, n_out = 512, 1024, 768                 # per-rank batch rows; dW is [n_in, n_out]
     g = torch.Generator(device=dev); g.manual_seed(100 + rank)
-    reducer = runner.FusedWeightGradient(ctx, n_in, n_out, rank, world)
+    reducer = runner.FusedWeightGradient(ctx, n_in, n_out, rank, world, route=route)
     assert reducer.ok
     dw = torch.empty(n_in, n_out, device=dev)
     db = torch.empty(n_out, device=dev)
@@ -117,17 +117,18 @@ def _rs_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_gemm_fused_with_reduce_scatter_over_peer_memory(tmp_path):
-    """Each rank's dW tiles are added into the owning rank's window from the GEMM
-    epilogue (CUDA IPC peer mappings, system-scope fp32 reductions); after the
-    copy-engine gather every rank holds the sum over ranks, equal to the
-    all-reduce of the local products and to the fp64 product of the gathered
-    operands."""
+@pytest.mark.parametrize("route", ["store", "add"])
+def test_gemm_fused_with_reduce_scatter_over_peer_memory(tmp_path, route):
+    """Each rank's dW tiles go from the GEMM epilogue to the owning rank's window over
+    CUDA IPC peer mappings -- stored into the rank's own slot and summed by the owner in
+    slot order ("store"), or added with system-scope fp32 reductions ("add"); after the
+    copy-engine gather every rank holds the sum over ranks, equal to the all-reduce of
+    the local products and to the fp64 product of the gathered operands."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
-    mp.spawn(_rs_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_rs_worker, args=(2, port, str(tmp_path), route), nprocs=2, join=True)
     r = np.load(os.path.join(str(tmp_path), "rs.npz"))
     scale = np.linalg.norm(r["exact_dw"])
     assert np.linalg.norm(r["dw"] - r["exact_dw"]) / scale <= 1e-5
