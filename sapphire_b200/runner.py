@@ -311,7 +311,11 @@ class FusedWeightGradient:
         self.windows = [PeerWindow(ctx, slots * self.block_rows, n_out, rank, world, group) for _ in range(3)]
         self.ok = all(w.ok for w in self.windows)
         dev = torch.device("cuda", ctx.device)
-        self.side = torch.cuda.Stream(dev)
+        # one stream per owner: a peer copy costs ~60 us whatever its size, so the
+        # world - 1 pulls of a step run side by side, not one after the other
+        self.sides = [torch.cuda.Stream(dev) for _ in range(max(world, 1))]
+        self.side = self.sides[rank if world > 1 else 0]
+        self.pulled = [torch.cuda.Event() for _ in range(max(world, 1))]
         self.done = torch.cuda.Event()
         self.tick = torch.zeros(1, device=dev)
         self.turn = 0
@@ -357,15 +361,18 @@ class FusedWeightGradient:
                                     colsum_out=db, colsum_scale=scale)
             self._barrier()                              # all adds have landed
         self.done.record(main)
-        with torch.cuda.stream(self.side):
-            self.side.wait_event(self.done)
-            for o in range(self.world):
+        for o in range(self.world):
+            with torch.cuda.stream(self.sides[o]):
+                self.sides[o].wait_event(self.done)
                 dw_full[o * rows:(o + 1) * rows].copy_(cur.views[o][:rows], non_blocking=True)
-            if self.world > 1:
-                dist.all_reduce(db, group=self.group)
+                if o == self.rank and self.world > 1:       # the local copy is short: this stream
+                    dist.all_reduce(db, group=self.group)   # also carries the bias gradient
+                self.pulled[o].record(self.sides[o])
 
     def wait(self) -> None:
-        torch.cuda.current_stream(torch.device("cuda", self.ctx.device)).wait_stream(self.side)
+        main = torch.cuda.current_stream(torch.device("cuda", self.ctx.device))
+        for o in range(self.world):
+            main.wait_event(self.pulled[o])
 
     def close(self) -> None:
         for w in self.windows:
