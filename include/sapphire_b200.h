@@ -346,6 +346,19 @@ typedef struct sb200_dp_group {
 } sb200_dp_group;
 
 int sb200_dp_reduce(sb200_ctx* ctx, const sb200_dp_group* group, int64_t count, sb200_stream stream);
+
+/*
+ * A barrier between the ranks' streams over the same kind of flag words (flags[r]: rank
+ * r's SB200_DP_FLAG_WORDS words, mapped by every rank, zeroed once; the words it uses are
+ * not those of sb200_dp_reduce / sb200_dp_update, one set can serve both): a one-warp
+ * kernel announces "this rank's stream has come this far" in every peer's words and
+ * waits, bounded by SB200_OPT_WAIT_LIMIT_US, until every peer has announced the same.
+ * Work enqueued after it on any rank starts after the work enqueued before it on every
+ * rank.  Replaces the one-element all-reduce between a GEMM that writes into peers'
+ * buffers (sb200_gemm_reduce_scatter, sb200_gemm_scatter) and the reads that follow.
+ * No counterpart in the reference.  Replays from a CUDA graph.
+ */
+int sb200_peer_barrier(sb200_ctx* ctx, uint32_t* const* flags, int world, int rank, sb200_stream stream);
 int sb200_dp_update(sb200_ctx* ctx, const sb200_dp_group* group, float* params, int64_t count,
                     int64_t n_sum, float lr, sb200_stream stream);
 

@@ -102,6 +102,7 @@ SIGNATURES = {
         C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_void_p, C.c_float, C.c_void_p]),
     "sb200_sum_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
                                    C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "sb200_peer_barrier": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p]),
     "sb200_dp_reduce": (C.c_int, [C.c_void_p, C.POINTER(DpGroup), C.c_int64, C.c_void_p]),
     "sb200_dp_update": (C.c_int, [C.c_void_p, C.POINTER(DpGroup), C.c_void_p, C.c_int64, C.c_int64,
                                   C.c_float, C.c_void_p]),

@@ -40,6 +40,8 @@ constexpr int FLAG_REDUCED = 8;                  // [8, 16): ... rank r's slice 
 constexpr int FLAG_STEP = 16;                    // steps completed by this rank
 constexpr int FLAG_DONE_REDUCE = 17;             // CTAs of the running reduce kernel that have finished
 constexpr int FLAG_DONE_UPDATE = 18;
+constexpr int FLAG_BARRIER = 20;                 // [20, 28): barrier number rank r has reached
+constexpr int FLAG_BARRIER_STEP = 28;            // barriers passed by this rank
 
 struct DpGroup {
     int world, rank;
@@ -226,10 +228,46 @@ int check_group(const sb200_dp_group* g, DpGroup* out)
     return SB200_OK;
 }
 
+// One warp: tell every peer that this rank's stream has reached barrier `step`, wait until
+// every peer has said the same.  The count lives in the flag words: replays from a graph.
+__global__ void __launch_bounds__(32)
+peer_barrier_kernel(DpGroup g, unsigned long long limit_ns, unsigned* status)
+{
+    uint32_t* mine = g.flags[g.rank];
+    const uint32_t step = mine[FLAG_BARRIER_STEP] + 1;
+    __threadfence_system();
+    if (static_cast<int>(threadIdx.x) < g.world)
+        st_release_sys(g.flags[threadIdx.x] + FLAG_BARRIER + g.rank, step);
+    wait_flags(mine, g.world, g.rank, FLAG_BARRIER, step, limit_ns, status, FAULT_PEER_WAIT);
+    if (threadIdx.x == 0)
+        mine[FLAG_BARRIER_STEP] = step;
+}
+
 }  // namespace
 }  // namespace sb200
 
 using namespace sb200;
+
+extern "C" int sb200_peer_barrier(sb200_ctx* ctx, uint32_t* const* flags, int world, int rank,
+                                  sb200_stream stream_)
+{
+    TraceRange trace("sb200_peer_barrier");
+    if (!ctx || !flags || world < 1 || world > 8 || rank < 0 || rank >= world)
+        return SB200_ERR_INVALID_ARG;
+    DpGroup g = {};
+    g.world = world;
+    g.rank = rank;
+    for (int r = 0; r < world; ++r) {
+        if (!flags[r] || (reinterpret_cast<uintptr_t>(flags[r]) & 3))
+            return SB200_ERR_INVALID_ARG;
+        g.flags[r] = flags[r];
+    }
+    if (cudaSetDevice(ctx->device) != cudaSuccess)
+        return SB200_ERR_CUDA;
+    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(g, ctx->wait_limit_ns, ctx->d_status);
+    ctx->launches += 1;
+    return cudaGetLastError() == cudaSuccess ? SB200_OK : SB200_ERR_CUDA;
+}
 
 extern "C" int sb200_dp_reduce(sb200_ctx* ctx, const sb200_dp_group* group, int64_t count,
                                sb200_stream stream_)

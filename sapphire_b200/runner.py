@@ -273,6 +273,34 @@ def _tensor_over(ptr: int, rows: int, cols: int, device: int, keepalive) -> torc
     return torch.as_tensor(holder, device=torch.device("cuda", device))
 
 
+class PeerBarrier:
+    """A barrier between the ranks' streams without a collective library: every rank
+    holds SB200_DP_FLAG_WORDS flag words that the others map, and ``sb200_peer_barrier``
+    (a one-warp kernel) announces and waits.  ``ok`` as in ``PeerWindow``."""
+
+    def __init__(self, ctx, rank: int = 0, world: int = 1, group=None):
+        import ctypes as C
+        from . import _lib as L
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self.window = PeerWindow(ctx, 1, L.DP_FLAG_WORDS, rank, world, group)
+        self.window.mine.zero_()
+        torch.cuda.synchronize(ctx.device)
+        self.ok = self.window.ok
+        if world > 1:
+            dist.barrier(group=group)                    # every rank's words are zero before the first use
+        self._arr = (C.c_void_p * world)(*[int(p) for p in self.window.pointers])
+        self._fn = L.lib().sb200_peer_barrier
+        self._L = L
+
+    def __call__(self) -> None:
+        self._L.check("sb200_peer_barrier",
+                      self._fn(self.ctx.handle, self._arr, self.world, self.rank,
+                               torch.cuda.current_stream(self.ctx.device).cuda_stream))
+
+    def close(self, group=None) -> None:
+        self.window.close(group)
+
+
 class FusedWeightGradient:
     """dW = sum over ranks of x_r^T . dy_r for a Linear layer whose batch rows are
     split over the ranks, with the scatter half of the reduce-scatter inside the
@@ -309,7 +337,9 @@ class FusedWeightGradient:
         self.block_rows = n_in // world
         slots = world if route == "store" else 1
         self.windows = [PeerWindow(ctx, slots * self.block_rows, n_out, rank, world, group) for _ in range(3)]
-        self.ok = all(w.ok for w in self.windows)
+        # the barrier between the GEMM that writes into the peers' windows and the reads
+        self.barrier = PeerBarrier(ctx, rank, world, group) if world > 1 else None
+        self.ok = all(w.ok for w in self.windows) and (self.barrier is None or self.barrier.ok)
         dev = torch.device("cuda", ctx.device)
         # one stream per owner: a peer copy costs ~60 us whatever its size, so the
         # world - 1 pulls of a step run side by side, not one after the other
@@ -324,7 +354,9 @@ class FusedWeightGradient:
         self._barrier()
 
     def _barrier(self) -> None:
-        if self.world > 1:
+        if self.barrier is not None and self.ok:
+            self.barrier()
+        elif self.world > 1:
             dist.all_reduce(self.tick, group=self.group)
 
     def start(self, x: torch.Tensor, dy: torch.Tensor, dw_full: torch.Tensor, db: torch.Tensor,
@@ -377,3 +409,5 @@ class FusedWeightGradient:
     def close(self) -> None:
         for w in self.windows:
             w.close(self.group)
+        if self.barrier is not None:
+            self.barrier.close(self.group)

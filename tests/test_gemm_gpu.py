@@ -779,6 +779,36 @@ def test_peer_window_single_rank_linear_backward(ctx):
     reducer.close()
 
 
+def test_peer_barrier_single_rank_and_bounded_wait(ctx):
+    """sb200_peer_barrier with one rank passes at once and counts; with a second "rank"
+    whose flag words nobody ever writes the wait runs out after the context's limit, the
+    status word says so, and the context carries on (no rank is needed to make a wait
+    expire, and nothing hangs)."""
+    import ctypes as C
+    from sapphire_b200 import runner
+    bar = runner.PeerBarrier(ctx, 0, 1)
+    for _ in range(3):
+        bar()
+    ctx.check_device_status()
+    torch.cuda.synchronize()
+    assert int(bar.window.mine.view(torch.int32)[0, 28]) == 3
+    silent = torch.zeros(L.DP_FLAG_WORDS, dtype=torch.int32, device=DEV)     # the rank that never arrives
+    arr = (C.c_void_p * 2)(int(bar.window.pointers[0]), silent.data_ptr())
+    ctx.set_option(L.OPT_WAIT_LIMIT_US, 2000)
+    try:
+        rc = L.lib().sb200_peer_barrier(ctx.handle, arr, 2, 0, torch.cuda.current_stream().cuda_stream)
+        assert rc == L.OK
+        with pytest.raises(L.Sb200Error) as e:
+            ctx.check_device_status()
+        assert e.value.status == L.ERR_DEVICE_TIMEOUT
+    finally:
+        ctx.set_option(L.OPT_WAIT_LIMIT_US, 2000000)
+    assert int(silent[20]) == 4                           # ... which was told that rank 0 had arrived
+    bar()                                                # the context and the words still work
+    ctx.check_device_status()
+    bar.close()
+
+
 def test_epilogue_steps_with_k_zero(ctx):
     """K == 0: D = gate(relu(C + bias)), no product."""
     rng = np.random.default_rng(9)
