@@ -145,8 +145,9 @@ def ref_ops():
         i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
         lib.ref_compute_gemm.argtypes = [_f32p, i32p, C.c_int, _f32p, i32p, C.c_int, _f32p, i32p, C.c_int]
         lib.ref_linear_backprop.argtypes = [_f32p] * 5 + [C.c_int] * 3 + [C.c_float]
+        lib.ref_mul_backprop.argtypes = [_f32p] * 5 + [C.c_int] * 4
         for n in ("ref_im2col", "ref_col2im", "ref_conv2d", "ref_conv2d_backward", "ref_compute_gemm",
-                  "ref_linear_backprop"):
+                  "ref_linear_backprop", "ref_mul_backprop"):
             getattr(lib, n).restype = None
         _ref_ops = lib
     return _ref_ops
@@ -165,6 +166,22 @@ def ref_linear_backprop(dx, dy, weight, bias, x, lr):
     ref_ops().ref_linear_backprop(dxo.reshape(-1), _c(dy).reshape(-1), w.reshape(-1), b, _c(x).reshape(-1),
                                   B, n_in, n_out, float(lr))
     return dxo, w, b
+
+
+def matmul_backward(da, db, dy, a, b, impl: str = "port"):
+    """The MatMul backward unit (Sources/Sapphire/operations/Backward/MathBackward.cpp:39-51):
+    da [batch, M, K] + dy . b^T and db [batch, K, N] + a^T . dy, each a Transpose into a
+    fresh buffer followed by an accumulating Gemm.  impl "ref" runs the reference's own
+    MulBackProp.  Returns copies (da, db)."""
+    batch, M, K = a.shape
+    N = b.shape[2]
+    dao = np.ascontiguousarray(da, dtype=np.float32).copy()
+    dbo = np.ascontiguousarray(db, dtype=np.float32).copy()
+    if impl == "ref":
+        ref_ops().ref_mul_backprop(dao.reshape(-1), dbo.reshape(-1), _c(dy).reshape(-1), _c(a).reshape(-1),
+                                   _c(b).reshape(-1), batch, M, K, N)
+        return dao, dbo
+    return gemm(dao, dy, transpose(b)), gemm(dbo, transpose(a), dy)
 
 
 def ref_compute_gemm(y, a, b):

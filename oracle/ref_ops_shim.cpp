@@ -9,6 +9,8 @@
 //   Sources/Sapphire/compute/dense/naive/Convolution.cpp:15-316  Im2Col, Col2Im, Conv2D, Conv2DBackward
 //   Sources/Sapphire/operations/Backward/LinearBackward.cpp:13-99 LinearBackProp
 //   Sources/Sapphire/operations/optimizers/SGD.cpp:9-28          Optimizer::SGD
+//   Sources/Sapphire/operations/Backward/MathBackward.cpp:13-51  MulBackProp (the file's other
+//                                                                units link against stubs below)
 //   Sources/Sapphire/compute/dense/naive/NaiveGemm.cpp:12-38     Dense::Naive::Gemm
 //   Sources/Sapphire/compute/dense/naive/NaiveBasic.cpp          Dense::Naive::Transpose, Scale, Sub
 //   Sources/Sapphire/compute/dense/naive/NaiveInitialize.cpp:34-40 Dense::Naive::Scalar
@@ -32,6 +34,7 @@
 #include <Sapphire/compute/Initialize.hpp>
 #include <Sapphire/Model.hpp>
 #include <Sapphire/operations/Backward/LinearBackward.hpp>
+#include <Sapphire/operations/Backward/MathBackward.hpp>
 #include <Sapphire/operations/optimizers/SGD.hpp>
 #include <algorithm>
 
@@ -109,6 +112,22 @@ void Sub(TensorData& y, const TensorData& a, const TensorData& b)
     BroadcastWith2Inputs(shapeOut, shapeA, shapeB, shapeOut.Size(), shapeA.Size(), shapeB.Size(),
                          y.HostMutableRawPtr(), a.HostRawPtr(), b.HostRawPtr(), 0, minRequiredDim,
                          Dense::Naive::Sub, 0, false, false);
+}
+
+// MathBackward.cpp also holds the Add / Dot / Mean units; nothing here runs them
+void Add(TensorData&, const TensorData&, const TensorData&)
+{
+    throw std::runtime_error("Compute::Add is not part of the CPU checker");
+}
+
+void Dot(TensorData&, const TensorData&, const TensorData&)
+{
+    throw std::runtime_error("Compute::Dot is not part of the CPU checker");
+}
+
+void MeanBackward(TensorData&, const TensorData&, int)
+{
+    throw std::runtime_error("Compute::MeanBackward is not part of the CPU checker");
 }
 
 namespace Initialize
@@ -211,6 +230,17 @@ void ref_linear_backprop(float* dx, const float* dy, float* weight, float* bias,
         unit.InvokeBackPropIfReady(0);
     }
     Sapphire::ModelManager::CurModel().SetOptimizer(nullptr);
+}
+
+// The MatMul backward unit: da [batch, M, K] += dy . b^T, db [batch, K, N] += a^T . dy
+// (MulBackProp::m_runBackProp: two Transposes, two accumulating Gemms)
+void ref_mul_backprop(float* da, float* db, const float* dy, const float* a, const float* b, int batch, int M,
+                      int K, int N)
+{
+    Sapphire::BackProp::MulBackProp unit("mul", wrap({ batch, M, K }, a), wrap({ batch, M, K }, da),
+                                         wrap({ batch, K, N }, b), wrap({ batch, K, N }, db),
+                                         wrap({ batch, M, N }, dy));
+    unit.InvokeBackPropIfReady(0);
 }
 
 }  // extern "C"

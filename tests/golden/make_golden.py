@@ -108,6 +108,22 @@ def linear_case(idx):
     return x, dy, w, b
 
 
+# (batch, M, K, N) of the MatMul backward unit fixtures
+MATMUL_CASES = [(1, 5, 7, 3), (3, 16, 12, 20), (2, 33, 8, 40)]
+
+
+def matmul_case(idx):
+    """da0, db0, dy, a, b of MatMul backward case idx."""
+    batch, M, K, N = MATMUL_CASES[idx]
+    rng = np.random.default_rng(1100 + idx)
+    a = rng.standard_normal((batch, M, K)).astype(np.float32)
+    b = rng.standard_normal((batch, K, N)).astype(np.float32)
+    dy = rng.standard_normal((batch, M, N)).astype(np.float32)
+    da0 = rng.standard_normal((batch, M, K)).astype(np.float32)
+    db0 = rng.standard_normal((batch, K, N)).astype(np.float32)
+    return da0, db0, dy, a, b
+
+
 def mlp_reference(steps, impl):
     Ws, bs = W.mlp_init(0)
     net = O.MlpOracle(Ws, bs, 0.01, impl=impl)
@@ -156,6 +172,10 @@ def main():
         x, dy, w, b = linear_case(i)
         dx, w1, b1 = O.ref_linear_backprop(np.zeros_like(x), dy, w, b, x, 0.01)
         bc[f"linear{i}_dx"], bc[f"linear{i}_w"], bc[f"linear{i}_b"] = dx, w1, b1
+    # MulBackProp (MathBackward.cpp:13-51)
+    for i in range(len(MATMUL_CASES)):
+        da, db = O.matmul_backward(*matmul_case(i), impl="ref")
+        bc[f"matmul{i}_da"], bc[f"matmul{i}_db"] = da, db
     np.savez_compressed(os.path.join(HERE, "broadcast_golden.npz"), **bc)
     print("wrote", os.path.join(HERE, "broadcast_golden.npz"), {k: v.shape for k, v in bc.items()})
 

@@ -251,6 +251,24 @@ def test_linear_backward_unit_matches_the_reference(oracle, idx):
         assert np.array_equal(_bits(net.b[0]), _bits(rb))
 
 
+@pytest.mark.parametrize("idx", range(3))
+def test_matmul_backward_unit_matches_the_reference(oracle, idx):
+    """da += dy.b^T and db += a^T.dy as the GPU tests state them (transposed operand,
+    accumulate in place) against the reference's own MulBackProp
+    (Sources/Sapphire/operations/Backward/MathBackward.cpp:13-51, compiled unmodified):
+    bit for bit against fixtures written by the reference build, and live where it is
+    present."""
+    mod = _golden_module()
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "broadcast_golden.npz"))
+    args = mod.matmul_case(idx)
+    da, db = oracle.matmul_backward(*args)
+    assert np.array_equal(_bits(da), _bits(gold[f"matmul{idx}_da"]))
+    assert np.array_equal(_bits(db), _bits(gold[f"matmul{idx}_db"]))
+    if oracle.have_ref_ops():
+        rda, rdb = oracle.matmul_backward(*args, impl="ref")
+        assert np.array_equal(_bits(da), _bits(rda)) and np.array_equal(_bits(db), _bits(rdb))
+
+
 def test_im2col_tap_order_and_padding(oracle):
     """Row c*kh*kw + (kh*kw - 1 - tap) holds tap (fr, fc); outside pixels read the pad value."""
     x = np.arange(1, 1 + 2 * 3 * 3, dtype=np.float32).reshape(1, 2, 3, 3)
