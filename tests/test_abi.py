@@ -79,6 +79,11 @@ def test_null_arguments_rejected():
     assert lib.sb200_gemm_batched(None, 0, 0, 0, 0, 1, 1, 1, None, 1, 0, None, 1, 0, None, 1, 0,
                                   None, 1, 0, None, None, 0.0, 1, None) == L.ERR_INVALID_ARG
     assert lib.sb200_csr_free(None) == L.ERR_INVALID_ARG
+    # the multi-GPU entry points check their arguments before they touch a device
+    for fn in (lib.sb200_gemm_reduce_scatter, lib.sb200_gemm_scatter):
+        assert fn(None, 0, 0, 0, 128, 4, 4, None, 4, None, 4, None, 1, 4, None, 0.0, None) == L.ERR_INVALID_ARG
+    assert lib.sb200_sum_blocks(None, None, 4, None, 1, 0, 1, 4, 4, None) == L.ERR_INVALID_ARG
+    assert lib.sb200_peer_barrier(None, None, 1, 0, None) == L.ERR_INVALID_ARG
 
 
 def plan(y, a, b):
