@@ -176,8 +176,8 @@ def main():
     for i in range(len(MATMUL_CASES)):
         da, db = O.matmul_backward(*matmul_case(i), impl="ref")
         bc[f"matmul{i}_da"], bc[f"matmul{i}_db"] = da, db
-    np.savez_compressed(os.path.join(HERE, "broadcast_golden.npz"), **bc)
-    print("wrote", os.path.join(HERE, "broadcast_golden.npz"), {k: v.shape for k, v in bc.items()})
+    np.savez_compressed(os.path.join(HERE, "compute_units_golden.npz"), **bc)
+    print("wrote", os.path.join(HERE, "compute_units_golden.npz"), {k: v.shape for k, v in bc.items()})
 
 
 if __name__ == "__main__":

@@ -131,7 +131,7 @@ def test_plan_equals_the_reference_broadcast(idx):
     [3,4,M,N] = [3,1,M,K].[3,4,K,N], where the reference pairs y block c with a block
     c % 3 and numpy's broadcast would pair it with c / 4."""
     from oracle import oracle as O
-    gold = np.load(os.path.join(ROOT, "tests", "golden", "broadcast_golden.npz"))
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "compute_units_golden.npz"))
     got, (y0, a, b) = _run_plan_with_cpu_gemm(idx)
     assert np.array_equal(got.view(np.uint32), gold[f"case{idx}"].view(np.uint32))
     if O.have_ref_ops():

@@ -583,7 +583,7 @@ def test_matmul_backward_accumulates_with_transposed_operand(ctx, oracle, mode):
 def test_compat_compute_gemm_broadcast_families(ctx, idx):
     """The reference's BroadcastTest families (BroadcastTest.cpp:20-202) through the
     Compute::Gemm shim on the device, against fixtures written by the reference's own
-    host path (tests/golden/broadcast_golden.npz) -- including the family whose pairing
+    host path (tests/golden/compute_units_golden.npz) -- including the family whose pairing
     of y and a blocks is the reference's, not numpy's."""
     import ctypes as C
     import importlib.util
@@ -593,7 +593,7 @@ def test_compat_compute_gemm_broadcast_families(ctx, idx):
     spec.loader.exec_module(mod)
     ys, as_, bs = mod.BROADCAST_CASES[idx]
     y0, a, b = mod.broadcast_case(idx)
-    want = np.load(os.path.join(os.path.dirname(__file__), "golden", "broadcast_golden.npz"))[f"case{idx}"]
+    want = np.load(os.path.join(os.path.dirname(__file__), "golden", "compute_units_golden.npz"))[f"case{idx}"]
     ty, ta, tb = dev(y0), dev(a), dev(b)
     arr = lambda s: (C.c_int * len(s))(*s)
     L.lib().sb200_compat_set_mode(L.MODE_TF32X3)

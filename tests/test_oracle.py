@@ -238,7 +238,7 @@ def test_linear_backward_unit_matches_the_reference(oracle, idx):
     pre-update weight, dW unscaled, dB scaled by 1/batch, z -= lr dz -- bit for bit
     against fixtures written by the reference build, and live where it is present."""
     mod = _golden_module()
-    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "broadcast_golden.npz"))
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "compute_units_golden.npz"))
     x, dy, w, b = mod.linear_case(idx)
     net = oracle.MlpOracle([w], [b], 0.01)
     dx = net.linear_backward(0, x, dy)
@@ -259,7 +259,7 @@ def test_matmul_backward_unit_matches_the_reference(oracle, idx):
     bit for bit against fixtures written by the reference build, and live where it is
     present."""
     mod = _golden_module()
-    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "broadcast_golden.npz"))
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "compute_units_golden.npz"))
     args = mod.matmul_case(idx)
     da, db = oracle.matmul_backward(*args)
     assert np.array_equal(_bits(da), _bits(gold[f"matmul{idx}_da"]))
