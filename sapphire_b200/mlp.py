@@ -203,9 +203,9 @@ class MlpTrainer:
         # gives.
         # (One context on three streams: allowed here because no two of these calls touch
         # the context's workspace at once -- in TF32 mode the dW GEMMs carry their column
-        # sums inside the kernel and only GEMMs on the main stream can be k-sliced; in
-        # 3xTF32 mode only the column sums of the dW calls use it, all on the one side
-        # stream, and nothing is k-sliced.)
+        # sums inside the kernel, and the GEMMs that may be k-sliced (forward, dx) form one
+        # chain, the input's gradient being its last link; in 3xTF32 mode only the column
+        # sums of the dW calls use it, all on the one side stream, and nothing is k-sliced.)
         main = torch.cuda.current_stream(x.device)
         side, late, forks, k = plan["side_stream"], plan["late_stream"], plan["fork"], 0
         for i, c in enumerate(plan["calls"]):
