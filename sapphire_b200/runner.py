@@ -315,12 +315,13 @@ class FusedWeightGradient:
              the owning rank's window (``sb200_gemm_scatter``, plain 16-byte stores);
              after a barrier every owner adds its ``world`` slots in slot order
              (``sb200_sum_blocks``: a fixed order, the sum is bit-reproducible), a
-             second barrier, the same gather.  Measured level with "add" on 2 and 4
-             GPUs (0.464 / 0.380 ms against 0.454 / 0.369 ms for 8192 x 4096 x 4096).
+             second barrier, the same gather.  Measured about level with "add" on 2 and 4
+             GPUs and slower on 8 (8192 x 4096 x 4096: 0.331 against 0.309 ms on 4,
+             0.728 against 0.392 ms on 8).
 
-    start()  runs the route up to the gather, which goes to a second stream together
-             with the all-reduce of the bias gradient;
-    wait()   makes the current stream wait for that second stream.
+    start()  runs the route up to the gather, which goes to one stream per owner (with
+             the all-reduce of the bias gradient on this rank's own);
+    wait()   makes the current stream wait for those streams.
 
     Work that needs no exchange (the dx GEMM) goes between the two calls.  Three
     windows rotate: a window is written again (or zeroed) only after every peer has
