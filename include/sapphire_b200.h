@@ -291,7 +291,8 @@ int sb200_gemm_scatter(sb200_ctx* ctx, int mode, int transA, int transB,
 /* out[r, c] = blocks[0][r, c] + blocks[1][r, c] + ... + blocks[n_blocks - 1][r, c] (fp32
  * adds in that order) for an [rows, cols] region; block b starts block_stride floats
  * after block b - 1; out may be blocks[0].  cols, the leading dimensions and the
- * stride multiples of 4, 16-byte aligned pointers (SB200_ERR_UNSUPPORTED otherwise). */
+ * stride multiples of 4, 16-byte aligned pointers (SB200_ERR_UNSUPPORTED otherwise).
+ * Like the two calls above it has no counterpart in the single-GPU reference. */
 int sb200_sum_blocks(sb200_ctx* ctx, float* out, int64_t ld_out, const float* blocks, int n_blocks,
                      int64_t block_stride, int64_t rows, int64_t cols, int64_t ld_block,
                      sb200_stream stream);
